@@ -1,0 +1,298 @@
+/* onn_b200.h -- C ABI of libonn_b200.so: sm_100a (B200) kernels for OpenNN's transformer
+ * training path (3-D [batch, seq, feature] fp32 tensors; Embedding, MultiHeadAttention,
+ * Dense<3>, Normalization3d, Addition<3>, CrossEntropyError3d, Adam).
+ *
+ * These entry points are what OpenNN's `...Cuda` layer methods would call instead of
+ * cuBLAS / cuDNN / opennn/kernel.cu.  Each declaration names the reference code it
+ * replaces (paths inside the OpenNN checkout).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless named host_*; tensors are fp32, row-major,
+ *     contiguous; token ids and targets are floats holding integers (as in OpenNN);
+ *   - weights are [inputs, outputs] (OpenNN's layout); arena sub-buffers are 32-byte aligned;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - every function returns ONN_OK (0) or a negative ONN_ERR_* code, never throws, and
+ *     never allocates device memory: scratch is passed in by the caller (`workspace`,
+ *     sized by the matching *_workspace_floats query);
+ *   - there is no CPU fallback: without a CUDA device every compute call returns ONN_ERR_CUDA.
+ *
+ * Tensor-core operands.  Contractions run on tcgen05 with kind::tf32: the tensor cores
+ * read fp32 storage and ignore the low 13 mantissa bits.  To keep that an unbiased
+ * rounding instead of a truncation, every kernel that PRODUCES a future GEMM operand can
+ * store it rounded to the nearest tf32 value (flag ONN_ROUND_OUTPUT_TF32), and GEMM-bearing
+ * calls take ONN_INPUTS_TF32_READY when their inputs were produced that way.  Without that
+ * flag they first round copies of their inputs into the workspace.
+ */
+#ifndef ONN_B200_H
+#define ONN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ONN_OK                     0
+#define ONN_ERR_INVALID_ARGUMENT  -1
+#define ONN_ERR_CUDA              -2   /* a CUDA call or launch failed (cudaGetLastError) */
+#define ONN_ERR_UNSUPPORTED       -3
+#define ONN_ERR_WORKSPACE         -4   /* workspace missing or too small */
+#define ONN_ERR_DEVICE_TIMEOUT    -5   /* a bounded device-side wait ran out (see onn_gemm_device_status) */
+#define ONN_ERR_NCCL              -6
+#define ONN_ERR_LIMIT             -7   /* size beyond a stated fixed maximum */
+
+/* flags */
+#define ONN_ROUND_OUTPUT_TF32   1u     /* store the result rounded to nearest tf32 */
+#define ONN_ACCUMULATE          2u     /* add into the destination instead of overwriting */
+#define ONN_INPUTS_TF32_READY   4u     /* inputs already hold tf32-representable values */
+#define ONN_DEFER_SOFTMAX       8u     /* Dense "Softmax": leave logits; the loss kernel fuses the softmax */
+
+/* activations of Dense<3> used by the transformer (opennn/standard_networks.cpp:745,753,890) */
+#define ONN_ACT_LINEAR   0
+#define ONN_ACT_RELU     1
+#define ONN_ACT_SOFTMAX  2
+
+const char* onn_status_string(int status);
+int onn_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * General strided-batched GEMM, the primitive under Dense and MultiHeadAttention.
+ * Replaces cublasSgemm / cublasSgemmStridedBatched at opennn/dense_layer.h:1137-1152,
+ * 1339-1373 and opennn/multihead_attention_layer.cpp:644-715, 740-756, 804-996.
+ *
+ *   C[z] = alpha * opA(A[z]) * opB(B[z])  (+ bias)  (relu)  (+ C[z] if ONN_ACCUMULATE)
+ *
+ * opA(A) is M x K, opB(B) is K x N, C is M x N row-major with leading dimension ldc.
+ *   a_major = 0: A stored row-major [M, K] (lda = row pitch);  1: stored [K, M] (transposed).
+ *   b_major = 0: B stored row-major [N, K] (i.e. B^T, ldb = row pitch);  1: stored [K, N].
+ * Batch z = zo * batch_inner + zi addresses X + zo*stride_outer + zi*stride_inner for each
+ * of A, B, C (strides in floats; 0 = shared operand).  bias is per output column (N) or NULL.
+ * relu_mask (optional, same layout as C): the result is multiplied by (relu_mask > 0),
+ * which fuses the ReLU derivative of the consuming Dense layer into a dX GEMM.
+ * split_k > 1 splits the reduction over CTAs that accumulate with fp32 atomics; C must
+ * then hold the value to accumulate into (zero for a plain product).
+ * ------------------------------------------------------------------------------------- */
+typedef struct onn_gemm_args
+{
+    const float* A; const float* B; float* C;
+    const float* bias;          /* [N] or NULL */
+    const float* relu_mask;     /* [M, N] with ldc / C batch strides, or NULL */
+    int64_t M, N, K;
+    int64_t lda, ldb, ldc;
+    int32_t a_major, b_major;
+    int32_t batch_inner, batch_outer;            /* both >= 1 */
+    int64_t a_stride_inner, a_stride_outer;
+    int64_t b_stride_inner, b_stride_outer;
+    int64_t c_stride_inner, c_stride_outer;
+    float alpha;
+    int32_t relu;               /* apply max(x, 0) after bias */
+    int32_t split_k;            /* 0 or 1 = none */
+    uint32_t flags;             /* ONN_ROUND_OUTPUT_TF32 | ONN_ACCUMULATE */
+} onn_gemm_args;
+
+int onn_gemm(const onn_gemm_args* args, void* stream);
+
+/* Which implementation the next onn_gemm calls use: 0 = automatic (tcgen05 whenever the
+ * operands meet the TMA alignment rules: 16-byte aligned bases and pitches), 1 = force the
+ * CUDA-core fp32 kernel, 2 = require tcgen05 (ONN_ERR_UNSUPPORTED if it cannot run).
+ * The environment variable ONN_B200_GEMM=simt|tc sets the initial value. */
+int onn_gemm_set_mode(int mode);
+/* 0, or ONN_ERR_DEVICE_TIMEOUT if a tcgen05 GEMM gave up on a bounded barrier wait since
+ * the last call (the status word is read back and cleared; synchronises the device). */
+int onn_gemm_device_status(void);
+/* Number of kernels this library launched since load (all entry points). */
+uint64_t onn_launch_count(void);
+
+/* Element-wise fp32 -> nearest tf32 (dst may equal src). */
+int onn_round_tf32(const float* src, float* dst, int64_t n, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Embedding.  Forward replaces embedding_forward_kernel (opennn/kernel.cu:714-761, called
+ * from opennn/embedding_layer.cpp:331-367); CPU semantics opennn/embedding_layer.cpp:147-186:
+ *   out[b,s,:] = W[id,:] * sqrt(E) (if scale) + PE[s,:] (if add_pe and id > 0);
+ *   id = (integer) ids[b,s]; id outside [0, V) gives a zero row.
+ * The multiply and the add are separate roundings (no FMA), matching the CPU path bit for bit.
+ * row_is_zero (optional, [B*S] bytes) receives 1 where every output feature has |x| <= 1e-7:
+ * the key-padding flag MultiHeadAttention derives from its source input
+ * (opennn/multihead_attention_layer.cpp:574-603).
+ * ------------------------------------------------------------------------------------- */
+int onn_embedding_fwd(const float* ids, const float* W, const float* PE, float* out,
+                      uint8_t* row_is_zero,
+                      int64_t B, int64_t S, int64_t E, int64_t V,
+                      int scale, int add_pe, uint32_t flags, void* stream);
+
+/* Backward replaces embedding_backward_kernel (opennn/kernel.cu:764-800) plus the fan-in
+ * sum Layer::add_gradients (opennn/layer.cpp:447-457); CPU semantics
+ * opennn/embedding_layer.cpp:193-226:  dW[id,:] += (dY + dY2)[b,s,:] * sqrt(E) for 0 < id < V.
+ * dW must be zero on entry (the training loop zeroes the gradient arena each step);
+ * dY2 may be NULL. */
+int onn_embedding_bwd(const float* ids, const float* dY, const float* dY2, float* dW,
+                      int64_t B, int64_t S, int64_t E, int64_t V, int scale, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Normalization3d (LayerNorm over the last dimension) with the preceding Addition<3> fused.
+ * Forward replaces addition_kernel + layernorm_forward_kernel (opennn/kernel.cu:691-699,
+ * 1141-1204; opennn/normalization_layer_3d.cpp:198-215); CPU semantics
+ * opennn/normalization_layer_3d.cpp:87-125:
+ *   x = A (+ R);  mean = mean(x);  std = sqrt(mean((x-mean)^2) + eps);  y = gamma*(x-mean)/std + beta.
+ * R (the residual) may be NULL; `sum` (optional) receives x, the Addition layer's output;
+ * mean and inv_std are [rows]; row_is_zero as in onn_embedding_fwd (optional).
+ * ------------------------------------------------------------------------------------- */
+int onn_layernorm_fwd(const float* A, const float* R, const float* gamma, const float* beta,
+                      float* Y, float* sum, float* mean, float* inv_std, uint8_t* row_is_zero,
+                      int64_t rows, int64_t E, float eps, uint32_t flags, void* stream);
+
+/* Backward replaces layernorm_backward_kernel (opennn/kernel.cu:1207-1269) and the fan-in
+ * sum; CPU semantics opennn/normalization_layer_3d.cpp:128-188.  dY2, dY3 (optional) are
+ * further consumer gradients summed on load.  X is the layer input (A + R).  dX is the
+ * gradient for the layer input; with the Addition fused both addends receive this same
+ * tensor (opennn/addition_layer.h:79-90).  workspace: onn_layernorm_bwd_workspace_floats. */
+size_t onn_layernorm_bwd_workspace_floats(int64_t rows, int64_t E);
+int onn_layernorm_bwd(const float* dY, const float* dY2, const float* dY3, const float* X,
+                      const float* mean, const float* inv_std, const float* gamma,
+                      float* dX, float* dgamma, float* dbeta,
+                      int64_t rows, int64_t E, float* workspace, uint32_t flags, void* stream);
+
+/* Addition<3> stand-alone: out = a + b.  Replaces addition_kernel (opennn/kernel.cu:691-699). */
+int onn_add(const float* a, const float* b, float* out, int64_t n, uint32_t flags, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Dense<3>.  Forward replaces cublasSgemm + cudnnAddTensor + cudnnActivationForward /
+ * cudnnSoftmaxForward (opennn/dense_layer.h:1117-1232); CPU semantics dense_layer.h:767-813:
+ *   Y = act(X W + b), X [rows, in], W [in, out], b [out].
+ * ONN_ACT_SOFTMAX normalises each row unless ONN_DEFER_SOFTMAX is set (then Y holds logits
+ * for onn_ce3d_fwd_bwd).  workspace is used only without ONN_INPUTS_TF32_READY.
+ * ------------------------------------------------------------------------------------- */
+size_t onn_dense_workspace_floats(int64_t rows, int64_t in, int64_t out);
+int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y,
+                  int64_t rows, int64_t in, int64_t out, int activation,
+                  float* workspace, uint32_t flags, void* stream);
+
+/* Backward replaces cudnnActivationBackward + 3 GEMMs (opennn/dense_layer.h:1235-1374);
+ * CPU semantics dense_layer.h:816-866:  delta = dY * act'(Y) (ReLU: Y > 0; Linear and
+ * Softmax: delta = dY), dW = X^T delta, db = column sums of delta, dX = delta W^T.
+ * dY is overwritten with delta for ReLU (as the reference does in place).  dX may be NULL.
+ * dW and db are ACCUMULATED into (the gradient arena is zeroed once per step).
+ * dX_relu_mask (optional, [rows, in]): dX is multiplied by (mask > 0), i.e. the ReLU
+ * derivative of the layer that produced X, saving that layer a pass over its gradient. */
+int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
+                  float* dW, float* db, float* dX, const float* dX_relu_mask,
+                  int64_t rows, int64_t in, int64_t out, int activation,
+                  float* workspace, uint32_t flags, void* stream);
+
+/* Row softmax over the last dimension, in place (opennn/layer.cpp:338-371). */
+int onn_softmax_rows(float* Y, int64_t rows, int64_t cols, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * MultiHeadAttention.  Forward replaces the 17 launches of
+ * opennn/multihead_attention_layer.cpp:624-776 (4 projections, transposes, strided-batched
+ * QK^T, mask kernels, cudnnSoftmaxForward, PV, output projection); CPU semantics
+ * multihead_attention_layer.cpp:183-282.
+ *   Xq [B,Sq,E]; Xs [B,Sk,E] (pass Xq again for self-attention); W* [E,E] in x out, head h
+ *   owns columns h*hd..; Y [B,Sq,E].  Key padding: source rows with all |x| <= 1e-7 get
+ *   score -1e9; causal: keys after the query get -inf.
+ * source_row_is_zero (optional, [B*Sk] bytes): flags from the producer of Xs; NULL makes
+ * the call compute them.
+ * The forward workspace doubles as the saved state for onn_mha_bwd (Q, K, V, attention
+ * weights, concatenated head outputs) and must be kept until then.
+ * ------------------------------------------------------------------------------------- */
+typedef struct onn_mha_params
+{
+    const float* Wq; const float* bq; const float* Wk; const float* bk;
+    const float* Wv; const float* bv; const float* Wo; const float* bo;
+} onn_mha_params;
+
+typedef struct onn_mha_grads
+{
+    float* dWq; float* dbq; float* dWk; float* dbk;
+    float* dWv; float* dbv; float* dWo; float* dbo;
+} onn_mha_grads;
+
+size_t onn_mha_fwd_workspace_floats(int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H);
+size_t onn_mha_bwd_workspace_floats(int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H);
+
+int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_params* params,
+                const uint8_t* source_row_is_zero, float* Y,
+                int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H, int causal,
+                float* fwd_workspace, uint32_t flags, void* stream);
+
+/* Backward replaces opennn/multihead_attention_layer.cpp:779-1018; CPU semantics :285-454,
+ * 493-553.  Parameter gradients are ACCUMULATED into (zeroed arena).  Self-attention
+ * (Xs == Xq): dXq receives dXq + dXk + dXv and dXs must be NULL.  Cross-attention: dXs
+ * receives dXk + dXv; with ONN_ACCUMULATE it is added into dXs instead (the encoder output
+ * feeds every decoder layer, so the fan-in sum of opennn/layer.cpp:447-457 happens here). */
+int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_params* params,
+                const float* fwd_workspace, const float* dY,
+                const onn_mha_grads* grads, float* dXq, float* dXs,
+                int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H, int causal,
+                float* bwd_workspace, uint32_t flags, void* stream);
+
+/* Attention-weight view inside the forward workspace ([B,H,Sq,Sk]), for tests and tools. */
+const float* onn_mha_attention_weights(const float* fwd_workspace,
+                                       int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H);
+
+/* ---------------------------------------------------------------------------------------
+ * CrossEntropyError3d.  One fused pass replaces the softmax of the output layer
+ * (opennn/layer.cpp:338-371 / cudnnSoftmaxForward) and
+ * cross_entropy_3d_multiple_{forward,counts,backward}_kernel + cudnnReduceTensor + two
+ * blocking D2H copies (opennn/kernel.cu:273-347, 466-499; opennn/cross_entropy_error_3d.cpp:
+ * 370-454, 498-528).  CPU semantics cross_entropy_error_3d.cpp:78-136, 154-247:
+ *   active = 0 < (integer) target < V;  p = softmax(logits);
+ *   error = sum over active of -log(p[target] + FLT_EPSILON) / #active;
+ *   accuracy = #(argmax p == target) / #active;
+ *   gradient wrt logits = (p - onehot) / #active on active tokens, 0 elsewhere.
+ * onn_ce3d_count_active writes #active of `targets` to counts[0] (float, device).  With
+ * several ranks the counts are summed across ranks before onn_ce3d_fwd_bwd so every rank
+ * scales by the global count.
+ * onn_ce3d_fwd_bwd: logits [rows, V] is overwritten in place with the gradient
+ * (inputs_are_probabilities != 0: the buffer already holds probabilities, as a plain
+ * Softmax Dense layer leaves them).  probabilities_out (optional) receives p.
+ * stats (device, 4 floats) receives {sum of -log terms, #correct, #active(local), 0};
+ * row_scratch is [2*rows] floats.
+ * ------------------------------------------------------------------------------------- */
+int onn_ce3d_count_active(const float* targets, int64_t rows, int64_t V, float* counts, void* stream);
+int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_count,
+                     float* probabilities_out, float* stats, float* row_scratch,
+                     int64_t rows, int64_t V, int inputs_are_probabilities,
+                     uint32_t flags, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * AdaptiveMomentEstimation.  Replaces adam_update_kernel (opennn/kernel.cu:6-68) and adds
+ * the global-norm clip only the CPU path has (opennn/adaptive_moment_estimation.cpp:444-473):
+ *   norm = ||g||;  g' = g * clip/norm if clip > 0 and norm > clip;
+ *   m = b1 m + (1-b1) g';  v = b2 v + (1-b2) g'^2;
+ *   p -= lr * (m / bc1) / (sqrt(v / bc2) + eps).
+ * onn_grad_sqnorm writes sum(g^2) to sqnorm[0] (device) deterministically; workspace is
+ * onn_grad_sqnorm_workspace_floats(n) floats.
+ * onn_adam reads the squared norm from device memory (no host sync), optionally writes a
+ * tf32-rounded copy of the updated parameters (p_tf32, the tensor-core operand copy) and
+ * zeroes g for the next step when zero_grad != 0.  grad_scale multiplies g before
+ * everything else (1/world for averaged all-reduces; 1 otherwise).
+ * ------------------------------------------------------------------------------------- */
+size_t onn_grad_sqnorm_workspace_floats(int64_t n);
+int onn_grad_sqnorm(const float* g, int64_t n, float* sqnorm, float* workspace, void* stream);
+int onn_adam(float* p, float* m, float* v, float* g, float* p_tf32, int64_t n,
+             float lr, float beta1, float beta2, float eps, float bc1, float bc2,
+             float clip_norm, const float* sqnorm, float grad_scale, int zero_grad, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Data-parallel gradient exchange (no counterpart in the reference, which is single-GPU):
+ * NCCL all-reduce (sum) of contiguous fp32 buffers on a dedicated communication stream.
+ * One process per GPU.  The 128-byte unique id is created on rank 0 with onn_dp_unique_id
+ * and handed to the other ranks by the caller (any out-of-band channel).
+ * ------------------------------------------------------------------------------------- */
+typedef struct onn_dp_comm onn_dp_comm;
+int onn_dp_unique_id(void* host_id128);
+int onn_dp_init(onn_dp_comm** comm, const void* host_id128, int world, int rank);
+/* Enqueue all-reduce(sum) of buf[0..n) in place on the comm stream after `after_stream`'s
+ * current work; onn_dp_wait makes `stream` wait for everything enqueued so far. */
+int onn_dp_allreduce(onn_dp_comm* comm, float* buf, int64_t n, void* after_stream);
+int onn_dp_wait(onn_dp_comm* comm, void* stream);
+int onn_dp_finalize(onn_dp_comm* comm);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ONN_B200_H */

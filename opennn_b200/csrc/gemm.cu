@@ -1,0 +1,82 @@
+// Front end of the GEMM primitive: argument checks, choice between the tcgen05 kernel and
+// the CUDA-core kernel, library-wide bookkeeping (launch counter, status strings).
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "gemm_internal.h"
+#include "launch_counter.h"
+
+namespace onn
+{
+
+std::atomic<uint64_t> g_launch_count{0};
+
+static int initial_mode()
+{
+    const char* env = std::getenv("ONN_B200_GEMM");
+    if(env && std::strcmp(env, "simt") == 0) return 1;
+    if(env && std::strcmp(env, "tc") == 0) return 2;
+    return 0;
+}
+
+static std::atomic<int> g_mode{initial_mode()};
+
+int gemm(const onn_gemm_args& g, cudaStream_t stream)
+{
+    ONN_CHECK_ARG(g.A && g.B && g.C);
+    ONN_CHECK_ARG(g.M > 0 && g.N > 0 && g.K > 0);
+    ONN_CHECK_ARG(g.batch_inner >= 1 && g.batch_outer >= 1);
+    ONN_CHECK_ARG((g.a_major == 0 || g.a_major == 1) && (g.b_major == 0 || g.b_major == 1));
+    ONN_CHECK_ARG(g.lda >= (g.a_major == 0 ? g.K : g.M));
+    ONN_CHECK_ARG(g.ldb >= (g.b_major == 0 ? g.K : g.N));
+    ONN_CHECK_ARG(g.ldc >= g.N);
+    // split-K partial sums are added atomically: a nonlinear epilogue or rounding cannot follow
+    ONN_CHECK_ARG(g.split_k <= 1 || (!g.relu && !g.relu_mask && !(g.flags & ONN_ROUND_OUTPUT_TF32)));
+
+    const int mode = g_mode.load(std::memory_order_relaxed);
+    const bool tc_ok = gemm_tc_supported(g);
+    if(mode == 2 && !tc_ok) return ONN_ERR_UNSUPPORTED;
+    if(mode != 1 && tc_ok) return gemm_tc_launch(g, stream);
+    return gemm_simt_launch(g, stream);
+}
+
+}  // namespace onn
+
+using namespace onn;
+
+extern "C" int onn_gemm(const onn_gemm_args* args, void* stream)
+{
+    ONN_CHECK_ARG(args);
+    return gemm(*args, (cudaStream_t)stream);
+}
+
+extern "C" int onn_gemm_set_mode(int mode)
+{
+    ONN_CHECK_ARG(mode >= 0 && mode <= 2);
+    g_mode.store(mode, std::memory_order_relaxed);
+    return ONN_OK;
+}
+
+extern "C" int onn_gemm_device_status(void) { return gemm_tc_read_status(); }
+
+extern "C" uint64_t onn_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+
+extern "C" int onn_version(void) { return 100; }
+
+extern "C" const char* onn_status_string(int status)
+{
+    switch(status)
+    {
+        case ONN_OK: return "ok";
+        case ONN_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case ONN_ERR_CUDA: return "CUDA call or kernel launch failed";
+        case ONN_ERR_UNSUPPORTED: return "unsupported configuration";
+        case ONN_ERR_WORKSPACE: return "workspace missing or too small";
+        case ONN_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+        case ONN_ERR_NCCL: return "NCCL call failed";
+        case ONN_ERR_LIMIT: return "size beyond a fixed maximum";
+        default: return "unknown status";
+    }
+}

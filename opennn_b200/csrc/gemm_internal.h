@@ -1,0 +1,18 @@
+// Internal interface between the GEMM front end (onn_gemm) and its two device paths.
+#pragma once
+#include <cuda_runtime.h>
+#include "../../include/onn_b200.h"
+
+namespace onn
+{
+// CUDA-core fp32 path: any strides and alignments.
+int gemm_simt_launch(const onn_gemm_args& g, cudaStream_t stream);
+
+// tcgen05 (kind::tf32) path.  Needs 16-byte aligned bases, pitches and batch strides.
+bool gemm_tc_supported(const onn_gemm_args& g);
+int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream);
+int gemm_tc_read_status();
+
+// Front end used by the layer code (same as onn_gemm).
+int gemm(const onn_gemm_args& g, cudaStream_t stream);
+}

@@ -1,0 +1,571 @@
+// tcgen05 GEMM for sm_100a: fp32 storage consumed as tf32 (kind::tf32), fp32 accumulation
+// in tensor memory.
+//
+// One persistent CTA per SM walks a static list of 128 x BN output tiles.  Six warps:
+//   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle, zero fill
+//               out of bounds) into a ring of shared-memory stages, one mbarrier each way;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma 128 x BN x 8 from shared-memory
+//               descriptors; owns the TMEM allocation (two accumulator buffers so the
+//               epilogue of tile i overlaps the main loop of tile i+1);
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32
+//               output rows), alpha / bias / ReLU / mask / accumulate / tf32 rounding,
+//               128-bit stores (or vector fp32 reductions for split-K).
+//
+// Operand layouts (BK = 32 floats = 128 bytes = one swizzle row, UMMA K = 8):
+//   K-major  (reduction dimension contiguous in memory): one box [rows][32 floats];
+//            canonical K-major SWIZZLE_128B layout, 8-row groups 1024 bytes apart (SBO);
+//            the K step inside a stage advances the descriptor start address by 32 bytes.
+//   MN-major (M or N contiguous in memory): one box [32 k-rows][32 floats] per 32 columns,
+//            boxes 4096 bytes apart (LBO), 8-row k-groups 1024 bytes apart (SBO); the K
+//            step advances the start address by 1024 bytes.
+//
+// Every wait on an mbarrier is bounded: a wait that runs out records ONN_ERR_DEVICE_TIMEOUT
+// in a device status word, raises a CTA-wide abort flag that ends all role loops, the
+// producer drains the copies it still has in flight, TMEM is freed and the kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "gemm_internal.h"
+#include "launch_counter.h"
+
+namespace onn
+{
+namespace tc
+{
+
+constexpr int BM = 128;
+constexpr int BK = 32;
+constexpr int UMMA_K = 8;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 4;                 // 16 KiB
+constexpr unsigned long long kWaitCycles = 1ull << 31;     // ~1 s at 2 GHz
+
+__device__ unsigned int g_status;                          // 0 = ok; else first failing wait site
+
+struct Params
+{
+    long long M, N, K;
+    long long ldc;
+    long long c_stride_inner, c_stride_outer;
+    float* C;
+    const float* bias;
+    const float* relu_mask;
+    float alpha;
+    int relu, round, accumulate;
+    int batch_inner, batch_outer;
+    int a_batch_inner_on, a_batch_outer_on, b_batch_inner_on, b_batch_outer_on;
+    int splits;
+    long long k_per_split;                                 // multiple of BK
+    int m_blocks, n_blocks;
+    long long total_work;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Returns false (and raises the abort flag) if the barrier never completes.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int site)
+{
+    if(mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = clock64();
+    unsigned int spins = 0;
+    while(true)
+    {
+        if(mbar_try_wait(bar, parity)) return true;
+        if((++spins & 255u) == 0)
+        {
+            if(*abort_flag) return false;
+            if(clock64() - start > kWaitCycles)
+            {
+                atomicCAS(&g_status, 0u, site);
+                *abort_flag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n" :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v)
+{
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for(int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor, SWIZZLE_128B, Blackwell version field = 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, bits [0,14)
+    desc |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;    // leading byte offset, bits [16,30)
+    desc |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;    // stride byte offset, bits [32,46)
+    desc |= (uint64_t)1 << 46;                              // descriptor version
+    desc |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return desc;
+}
+
+// Instruction descriptor: D = fp32, A = B = tf32, M = 128, N = BN, majors as given.
+__host__ __device__ constexpr uint32_t make_idesc(int bn, int a_mn_major, int b_mn_major)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct WorkItem { int zi, zo, split, m_blk, n_blk; long long k_begin; int k_blocks; };
+
+__device__ __forceinline__ WorkItem decode_work(const Params& p, long long w)
+{
+    constexpr int kGroup = 8;                               // M blocks per raster group (L2 reuse of B panels)
+    const long long tiles = (long long)p.m_blocks * p.n_blocks;
+    const long long t = w % tiles;
+    long long rest = w / tiles;
+    WorkItem it;
+    it.split = (int)(rest % p.splits); rest /= p.splits;
+    it.zi = (int)(rest % p.batch_inner);
+    it.zo = (int)(rest / p.batch_inner);
+    const long long per_group = (long long)kGroup * p.n_blocks;
+    const int group = (int)(t / per_group);
+    const int first_m = group * kGroup;
+    const int group_size = min(p.m_blocks - first_m, kGroup);
+    const int in_group = (int)(t % per_group);
+    it.m_blk = first_m + in_group % group_size;
+    it.n_blk = in_group / group_size;
+    it.k_begin = it.split * p.k_per_split;
+    const long long k_end = min(p.K, it.k_begin + p.k_per_split);
+    it.k_blocks = (int)((k_end - it.k_begin + BK - 1) / BK);
+    return it;
+}
+
+template <int BN, int STAGES, int A_MN, int B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
+{
+    constexpr int B_STAGE_BYTES = BN * BK * 4;
+    constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;                  // two accumulator buffers (power of two >= 32)
+    constexpr uint32_t IDESC = make_idesc(BN, A_MN, B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
+    uint64_t* full_bar = bars;                              // [STAGES]  TMA -> MMA
+    uint64_t* empty_bar = bars + STAGES;                    // [STAGES]  MMA -> TMA
+    uint64_t* acc_full_bar = bars + 2 * STAGES;             // [2]       MMA -> epilogue
+    uint64_t* acc_empty_bar = bars + 2 * STAGES + 2;        // [2]       epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if(threadIdx.x == 0)
+    {
+        for(int s = 0; s < STAGES; s++) { mbar_init(smem_u32(full_bar + s), 1); mbar_init(smem_u32(empty_bar + s), 1); }
+        for(int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full_bar + a), 1); mbar_init(smem_u32(acc_empty_bar + a), kEpilogueWarps); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if(warp == 1)
+    {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if(warp == 0)
+    {
+        // ---------------- TMA producer ----------------
+        if(lane == 0)
+        {
+            uint32_t stage = 0, phase = 0;
+            uint32_t armed[STAGES];                          // parity of the last phase armed per stage (+1), 0 = none
+#pragma unroll
+            for(int s = 0; s < STAGES; s++) armed[s] = 0;
+            bool ok = true;
+            for(long long w = blockIdx.x; ok && w < p.total_work; w += gridDim.x)
+            {
+                const WorkItem it = decode_work(p, w);
+                const int m0 = it.m_blk * BM, n0 = it.n_blk * BN;
+                const int a_zi = p.a_batch_inner_on ? it.zi : 0, a_zo = p.a_batch_outer_on ? it.zo : 0;
+                const int b_zi = p.b_batch_inner_on ? it.zi : 0, b_zo = p.b_batch_outer_on ? it.zo : 0;
+                for(int kb = 0; kb < it.k_blocks; kb++)
+                {
+                    if(!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(full_bar + stage);
+                    const uint32_t a_dst = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+                    const int k0 = (int)(it.k_begin + (long long)kb * BK);
+                    mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                    armed[stage] = phase + 1;
+                    if(A_MN)
+                    {
+#pragma unroll
+                        for(int j = 0; j < BM / 32; j++) tma_load_4d(a_dst + j * 4096, &map_a, bar, m0 + 32 * j, k0, a_zi, a_zo);
+                    }
+                    else
+                        tma_load_4d(a_dst, &map_a, bar, k0, m0, a_zi, a_zo);
+                    if(B_MN)
+                    {
+#pragma unroll
+                        for(int j = 0; j < BN / 32; j++) tma_load_4d(b_dst + j * 4096, &map_b, bar, n0 + 32 * j, k0, b_zi, b_zo);
+                    }
+                    else
+                        tma_load_4d(b_dst, &map_b, bar, k0, n0, b_zi, b_zo);
+                    if(++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if(*abort_flag)
+            {
+                // drain: wait (bounded) until every copy this thread started has landed, so that
+                // no bulk copy is still writing this CTA's shared memory when it exits
+#pragma unroll
+                for(int s = 0; s < STAGES; s++)
+                    if(armed[s])
+                    {
+                        const unsigned long long start = clock64();
+                        while(!mbar_try_wait(smem_u32(full_bar + s), armed[s] - 1))
+                            if(clock64() - start > kWaitCycles) break;
+                    }
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        // ---------------- MMA issuer ----------------
+        if(lane == 0)
+        {
+            uint32_t stage = 0, phase = 0;
+            long long local = 0;
+            bool ok = true;
+            for(long long w = blockIdx.x; ok && w < p.total_work; w += gridDim.x, local++)
+            {
+                const WorkItem it = decode_work(p, w);
+                const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
+                if(!mbar_wait(smem_u32(acc_empty_bar + acc), acc_phase ^ 1, abort_flag, 2)) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for(int kb = 0; kb < it.k_blocks; kb++)
+                {
+                    if(!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, 3)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+                    const uint64_t a_desc = A_MN ? make_smem_desc(a_addr, 4096, 1024) : make_smem_desc(a_addr, 16, 1024);
+                    const uint64_t b_desc = B_MN ? make_smem_desc(b_addr, 4096, 1024) : make_smem_desc(b_addr, 16, 1024);
+#pragma unroll
+                    for(int j = 0; j < BK / UMMA_K; j++)
+                    {
+                        // descriptor start-address field is in 16-byte units
+                        const uint64_t a_step = A_MN ? (uint64_t)(j * 1024 >> 4) : (uint64_t)(j * UMMA_K * 4 >> 4);
+                        const uint64_t b_step = B_MN ? (uint64_t)(j * 1024 >> 4) : (uint64_t)(j * UMMA_K * 4 >> 4);
+                        tcgen05_mma_tf32(d_tmem, a_desc + a_step, b_desc + b_step, IDESC, (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(smem_u32(empty_bar + stage));     // frees the stage once these MMAs have read it
+                    if(++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if(!ok) break;
+                tcgen05_commit(smem_u32(acc_full_bar + acc));        // accumulator complete
+            }
+        }
+    }
+    else
+    {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quadrant = warp & 3;                       // TMEM lanes this warp may read: 32*quadrant ..
+        long long local = 0;
+        for(long long w = blockIdx.x; w < p.total_work; w += gridDim.x, local++)
+        {
+            const WorkItem it = decode_work(p, w);
+            const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
+            bool ok = true;
+            if(lane == 0) ok = mbar_wait(smem_u32(acc_full_bar + acc), acc_phase, abort_flag, 4);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if(!ok) break;
+            tcgen05_fence_after();
+
+            const long long row = (long long)it.m_blk * BM + quadrant * 32 + lane;
+            const long long n0 = (long long)it.n_blk * BN;
+            const long long c_offset = it.zi * p.c_stride_inner + it.zo * p.c_stride_outer;
+            float* c_row = p.C + c_offset + row * p.ldc;
+            const float* mask_row = p.relu_mask ? p.relu_mask + c_offset + row * p.ldc : nullptr;
+            const bool row_ok = row < p.M;
+            const bool use_bias = p.bias != nullptr && it.split == 0;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * BN;
+
+#pragma unroll 1
+            for(int c = 0; c < BN / 32; c++)
+            {
+                const long long n_base = n0 + c * 32;
+                if(n_base >= p.N) break;
+                float v[32];
+                __syncwarp();                                   // tcgen05.ld is warp-collective: reconverge first
+                tmem_load_32(taddr + c * 32, v);
+                if(!row_ok) continue;
+#pragma unroll
+                for(int q4 = 0; q4 < 8; q4++)
+                {
+                    const long long n = n_base + q4 * 4;
+                    if(n >= p.N) break;
+                    float x[4] = { v[q4 * 4] * p.alpha, v[q4 * 4 + 1] * p.alpha, v[q4 * 4 + 2] * p.alpha, v[q4 * 4 + 3] * p.alpha };
+                    if(n + 3 < p.N)
+                    {
+                        if(use_bias) { const float4 b = ld4(p.bias + n); x[0] += b.x; x[1] += b.y; x[2] += b.z; x[3] += b.w; }
+                        if(p.relu) { x[0] = fmaxf(x[0], 0.f); x[1] = fmaxf(x[1], 0.f); x[2] = fmaxf(x[2], 0.f); x[3] = fmaxf(x[3], 0.f); }
+                        if(mask_row)
+                        {
+                            const float4 k = ld4(mask_row + n);
+                            x[0] = k.x > 0.f ? x[0] : 0.f; x[1] = k.y > 0.f ? x[1] : 0.f;
+                            x[2] = k.z > 0.f ? x[2] : 0.f; x[3] = k.w > 0.f ? x[3] : 0.f;
+                        }
+                        if(p.splits > 1)
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                         :: "l"(c_row + n), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+                        else
+                        {
+                            if(p.accumulate) { const float4 o = ld4(c_row + n); x[0] += o.x; x[1] += o.y; x[2] += o.z; x[3] += o.w; }
+                            if(p.round) { x[0] = round_tf32(x[0]); x[1] = round_tf32(x[1]); x[2] = round_tf32(x[2]); x[3] = round_tf32(x[3]); }
+                            st4(c_row + n, make_float4(x[0], x[1], x[2], x[3]));
+                        }
+                    }
+                    else
+                    {
+                        for(int e = 0; e < 4 && n + e < p.N; e++)
+                        {
+                            float y = x[e];
+                            if(use_bias) y += p.bias[n + e];
+                            if(p.relu) y = fmaxf(y, 0.f);
+                            if(mask_row && !(mask_row[n + e] > 0.f)) y = 0.f;
+                            if(p.splits > 1) atomicAdd(c_row + n + e, y);
+                            else
+                            {
+                                if(p.accumulate) y += c_row[n + e];
+                                c_row[n + e] = p.round ? round_tf32(y) : y;
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if(lane == 0) mbar_arrive(smem_u32(acc_empty_bar + acc));
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if(warp == 1)
+    {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, []
+    {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+           result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+static cuuint64_t stride_bytes(long long elements, long long fallback_elements)
+{
+    const long long e = elements > 0 ? elements : fallback_elements;
+    return (cuuint64_t)e * 4ull;
+}
+
+// 4-D map (d0 = contiguous dimension, d1 = pitched dimension, batch inner, batch outer).
+static bool make_map(CUtensorMap* map, const float* base, long long d0, long long d1, long long pitch,
+                     int batch_inner, long long stride_inner, int batch_outer, long long stride_outer,
+                     int box0, int box1)
+{
+    EncodeTiledFn fn = encode_tiled();
+    if(!fn) return false;
+    const bool inner_on = batch_inner > 1 && stride_inner != 0, outer_on = batch_outer > 1 && stride_outer != 0;
+    const cuuint64_t dims[4] = { (cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)(inner_on ? batch_inner : 1),
+                                 (cuuint64_t)(outer_on ? batch_outer : 1) };
+    const long long plane = pitch * d1;
+    const cuuint64_t strides[3] = { (cuuint64_t)pitch * 4ull, stride_bytes(inner_on ? stride_inner : 0, plane),
+                                    stride_bytes(outer_on ? stride_outer : 0, plane) };
+    const cuuint32_t box[4] = { (cuuint32_t)box0, (cuuint32_t)box1, 1, 1 };
+    const cuuint32_t elem[4] = { 1, 1, 1, 1 };
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool mult4(long long x) { return (x & 3) == 0; }
+
+template <int BN, int STAGES, int A_MN, int B_MN>
+static int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream)
+{
+    constexpr int smem = STAGES * (A_STAGE_BYTES + BN * BK * 4) + 1024 + 256;
+    static bool configured = false;
+    if(!configured)
+    {
+        if(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return ONN_ERR_CUDA;
+        configured = true;
+    }
+    const long long cap = (long long)kSmCount * (BN == 64 ? 2 : 1);
+    const int grid = (int)(p.total_work < cap ? p.total_work : cap);
+    gemm_tc_kernel<BN, STAGES, A_MN, B_MN><<<grid, kThreads, smem, stream>>>(map_a, map_b, p);
+    count_launch();
+    return launch_status();
+}
+
+template <int A_MN, int B_MN>
+static int launch_majors(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream)
+{
+    if(bn == 256) return launch_variant<256, 4, A_MN, B_MN>(map_a, map_b, p, stream);
+    if(bn == 128) return launch_variant<128, 6, A_MN, B_MN>(map_a, map_b, p, stream);
+    return launch_variant<64, 4, A_MN, B_MN>(map_a, map_b, p, stream);
+}
+
+}  // namespace tc
+
+bool gemm_tc_supported(const onn_gemm_args& g)
+{
+    using tc::mult4;
+    if(g.a_major == 1 && g.b_major == 0) return false;      // combination no layer needs
+    if(!host_aligned16(g.A) || !host_aligned16(g.B) || !host_aligned16(g.C)) return false;
+    if(!mult4(g.lda) || !mult4(g.ldb) || !mult4(g.ldc)) return false;
+    if(!mult4(g.a_stride_inner) || !mult4(g.a_stride_outer) || !mult4(g.b_stride_inner) || !mult4(g.b_stride_outer)) return false;
+    if(!mult4(g.c_stride_inner) || !mult4(g.c_stride_outer)) return false;
+    if(g.bias && !host_aligned16(g.bias)) return false;
+    if(g.relu_mask && !host_aligned16(g.relu_mask)) return false;
+    if(g.M >= (1LL << 31) || g.N >= (1LL << 31) || g.K >= (1LL << 31)) return false;
+    return tc::encode_tiled() != nullptr;
+}
+
+int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
+{
+    using namespace tc;
+    const int bn = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+
+    Params p;
+    p.M = g.M; p.N = g.N; p.K = g.K; p.ldc = g.ldc;
+    p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
+    p.C = g.C; p.bias = g.bias; p.relu_mask = g.relu_mask; p.alpha = g.alpha;
+    p.relu = g.relu; p.round = (g.flags & ONN_ROUND_OUTPUT_TF32) != 0; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
+    p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
+    p.a_batch_inner_on = g.batch_inner > 1 && g.a_stride_inner != 0; p.a_batch_outer_on = g.batch_outer > 1 && g.a_stride_outer != 0;
+    p.b_batch_inner_on = g.batch_inner > 1 && g.b_stride_inner != 0; p.b_batch_outer_on = g.batch_outer > 1 && g.b_stride_outer != 0;
+
+    const long long k_blocks = (g.K + BK - 1) / BK;
+    long long splits = g.split_k > 1 ? g.split_k : 1;
+    if(splits > k_blocks) splits = k_blocks;
+    const long long blocks_per_split = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + blocks_per_split - 1) / blocks_per_split;   // every split owns at least one k-block
+    p.splits = (int)splits;
+    p.k_per_split = blocks_per_split * BK;
+    p.m_blocks = (int)((g.M + BM - 1) / BM);
+    p.n_blocks = (int)((g.N + bn - 1) / bn);
+    p.total_work = (long long)p.m_blocks * p.n_blocks * splits * g.batch_inner * g.batch_outer;
+
+    CUtensorMap map_a, map_b;
+    bool ok;
+    if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, BK, BM);
+    else ok = make_map(&map_a, g.A, g.M, g.K, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, 32, BK);
+    if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, BK, bn);
+    else ok = ok && make_map(&map_b, g.B, g.N, g.K, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, 32, BK);
+    if(!ok) return ONN_ERR_UNSUPPORTED;
+
+    if(g.a_major == 0 && g.b_major == 0) return launch_majors<0, 0>(bn, map_a, map_b, p, stream);
+    if(g.a_major == 0 && g.b_major == 1) return launch_majors<0, 1>(bn, map_a, map_b, p, stream);
+    if(g.a_major == 1 && g.b_major == 1) return launch_majors<1, 1>(bn, map_a, map_b, p, stream);
+    return ONN_ERR_UNSUPPORTED;
+}
+
+int gemm_tc_read_status()
+{
+    unsigned int status = 0, zero = 0;
+    if(cudaDeviceSynchronize() != cudaSuccess) return ONN_ERR_CUDA;
+    if(cudaMemcpyFromSymbol(&status, tc::g_status, sizeof(status)) != cudaSuccess) return ONN_ERR_CUDA;
+    if(status != 0) cudaMemcpyToSymbol(tc::g_status, &zero, sizeof(zero));
+    return status == 0 ? ONN_OK : ONN_ERR_DEVICE_TIMEOUT;
+}
+
+}  // namespace onn

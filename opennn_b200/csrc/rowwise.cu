@@ -1,0 +1,584 @@
+// HBM-bound row kernels: Embedding forward/backward, Normalization3d (+ fused Addition)
+// forward/backward, Addition, tf32 rounding.  One warp owns one [E]-row; the row lives in
+// registers, reductions are warp shuffles, global access is 128-bit where E % 4 == 0.
+#include "common.cuh"
+#include "launch_counter.h"
+
+namespace onn
+{
+
+constexpr int kRowThreads = 256;                  // 8 warps = 8 rows per CTA per sweep
+constexpr int kRowWarps = kRowThreads / 32;
+constexpr int kMaxVec = 8;                        // float4 per lane kept in registers: E <= 1024
+
+// ---------------------------------------------------------------------------------------
+// Embedding
+// ---------------------------------------------------------------------------------------
+
+// out = W[id] * sqrt(E) + PE[s]; the product and the sum are rounded separately
+// (__fmul_rn / __fadd_rn) so no FMA contraction changes the bits.
+__global__ void __launch_bounds__(kRowThreads)
+embedding_fwd_kernel(const float* __restrict__ ids, const float* __restrict__ W, const float* __restrict__ PE,
+                     float* __restrict__ out, uint8_t* __restrict__ row_is_zero,
+                     long long tokens, int S, int E, long long V, float scale_value, int scale, int add_pe, int round)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * kRowWarps;
+    const bool vec = (E & 3) == 0;
+
+    for(long long token = warp; token < tokens; token += stride)
+    {
+        const long long id = token_index(ids[token]);
+        const bool in_range = id >= 0 && id < V;
+        const bool with_pe = add_pe && id > 0;
+        const float* w_row = W + (in_range ? id : 0) * (long long)E;
+        const float* pe_row = PE + (long long)(token % S) * E;
+        float* out_row = out + token * (long long)E;
+        bool all_zero = true;
+
+        if(vec)
+        {
+            for(int e = lane * 4; e < E; e += 128)
+            {
+                float4 w = in_range ? ld4(w_row + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if(scale)
+                {
+                    w.x = __fmul_rn(w.x, scale_value); w.y = __fmul_rn(w.y, scale_value);
+                    w.z = __fmul_rn(w.z, scale_value); w.w = __fmul_rn(w.w, scale_value);
+                }
+                if(with_pe)
+                {
+                    const float4 p = ld4(pe_row + e);
+                    w.x = __fadd_rn(w.x, p.x); w.y = __fadd_rn(w.y, p.y);
+                    w.z = __fadd_rn(w.z, p.z); w.w = __fadd_rn(w.w, p.w);
+                }
+                if(round) { w.x = round_tf32(w.x); w.y = round_tf32(w.y); w.z = round_tf32(w.z); w.w = round_tf32(w.w); }
+                all_zero = all_zero && fabsf(w.x) <= 1e-7f && fabsf(w.y) <= 1e-7f && fabsf(w.z) <= 1e-7f && fabsf(w.w) <= 1e-7f;
+                st4(out_row + e, w);
+            }
+        }
+        else
+        {
+            for(int e = lane; e < E; e += 32)
+            {
+                float w = in_range ? w_row[e] : 0.f;
+                if(scale) w = __fmul_rn(w, scale_value);
+                if(with_pe) w = __fadd_rn(w, pe_row[e]);
+                if(round) w = round_tf32(w);
+                all_zero = all_zero && fabsf(w) <= 1e-7f;
+                out_row[e] = w;
+            }
+        }
+
+        if(row_is_zero)
+        {
+            all_zero = __all_sync(0xffffffffu, all_zero);
+            if(lane == 0) row_is_zero[token] = all_zero ? 1 : 0;
+        }
+    }
+}
+
+// dW[id] += (dY + dY2) * sqrt(E) for 0 < id < V: fp32 reductions into L2 (vectorised
+// where the row is 16-byte aligned).  Row 0 (padding) is never touched, so it stays zero.
+__global__ void __launch_bounds__(kRowThreads)
+embedding_bwd_kernel(const float* __restrict__ ids, const float* __restrict__ dY, const float* __restrict__ dY2,
+                     float* __restrict__ dW, long long tokens, int E, long long V, float scale_value, int scale)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * kRowWarps;
+    const bool vec = (E & 3) == 0;
+
+    for(long long token = warp; token < tokens; token += stride)
+    {
+        const long long id = token_index(ids[token]);
+        if(id <= 0 || id >= V) continue;
+        const float* g_row = dY + token * (long long)E;
+        const float* g2_row = dY2 ? dY2 + token * (long long)E : nullptr;
+        float* w_row = dW + id * (long long)E;
+
+        if(vec)
+        {
+            for(int e = lane * 4; e < E; e += 128)
+            {
+                float4 g = ld4_stream(g_row + e);
+                if(g2_row) { const float4 h = ld4_stream(g2_row + e); g.x += h.x; g.y += h.y; g.z += h.z; g.w += h.w; }
+                if(scale) { g.x *= scale_value; g.y *= scale_value; g.z *= scale_value; g.w *= scale_value; }
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                             :: "l"(w_row + e), "f"(g.x), "f"(g.y), "f"(g.z), "f"(g.w) : "memory");
+            }
+        }
+        else
+        {
+            for(int e = lane; e < E; e += 32)
+            {
+                float g = g_row[e];
+                if(g2_row) g += g2_row[e];
+                if(scale) g *= scale_value;
+                atomicAdd(w_row + e, g);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Normalization3d
+// ---------------------------------------------------------------------------------------
+
+// Register-resident row path (E % 4 == 0, E <= 1024).  Statistics are two passes over the
+// registers: mean first, then the mean of centred squares (the reference's formulation).
+template <int VEC>
+__global__ void __launch_bounds__(kRowThreads)
+layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
+                     const float* __restrict__ gamma, const float* __restrict__ beta,
+                     float* __restrict__ Y, float* __restrict__ sum_out,
+                     float* __restrict__ mean_out, float* __restrict__ inv_std_out, uint8_t* __restrict__ row_is_zero,
+                     long long rows, int E, float eps, int round)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * kRowWarps;
+    const float inv_E = 1.0f / (float)E;
+
+    float4 g[VEC], b[VEC];
+#pragma unroll
+    for(int i = 0; i < VEC; i++)
+    {
+        const int e = (i * 32 + lane) * 4;
+        g[i] = e < E ? ld4(gamma + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        b[i] = e < E ? ld4(beta + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const float* a_row = A + row * (long long)E;
+        const float* r_row = R ? R + row * (long long)E : nullptr;
+        float4 x[VEC];
+        float total = 0.f;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            const int e = (i * 32 + lane) * 4;
+            x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if(e < E)
+            {
+                x[i] = ld4_stream(a_row + e);
+                if(r_row) { const float4 r = ld4_stream(r_row + e); x[i].x += r.x; x[i].y += r.y; x[i].z += r.z; x[i].w += r.w; }
+                if(sum_out) st4(sum_out + row * (long long)E + e, x[i]);
+                total += (x[i].x + x[i].y) + (x[i].z + x[i].w);
+            }
+        }
+        const float mean = warp_sum(total) * inv_E;
+        float squares = 0.f;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            const int e = (i * 32 + lane) * 4;
+            if(e < E)
+            {
+                x[i].x -= mean; x[i].y -= mean; x[i].z -= mean; x[i].w -= mean;
+                squares += (x[i].x * x[i].x + x[i].y * x[i].y) + (x[i].z * x[i].z + x[i].w * x[i].w);
+            }
+        }
+        const float inv_std = 1.0f / sqrtf(warp_sum(squares) * inv_E + eps);
+        bool all_zero = true;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            const int e = (i * 32 + lane) * 4;
+            if(e < E)
+            {
+                float4 y;
+                y.x = maybe_round(x[i].x * inv_std * g[i].x + b[i].x, round);
+                y.y = maybe_round(x[i].y * inv_std * g[i].y + b[i].y, round);
+                y.z = maybe_round(x[i].z * inv_std * g[i].z + b[i].z, round);
+                y.w = maybe_round(x[i].w * inv_std * g[i].w + b[i].w, round);
+                all_zero = all_zero && fabsf(y.x) <= 1e-7f && fabsf(y.y) <= 1e-7f && fabsf(y.z) <= 1e-7f && fabsf(y.w) <= 1e-7f;
+                st4(Y + row * (long long)E + e, y);
+            }
+        }
+        if(lane == 0) { mean_out[row] = mean; inv_std_out[row] = inv_std; }
+        if(row_is_zero)
+        {
+            all_zero = __all_sync(0xffffffffu, all_zero);
+            if(lane == 0) row_is_zero[row] = all_zero ? 1 : 0;
+        }
+    }
+}
+
+// Any E: three sweeps over the row; the second and third hit L1/L2.
+__global__ void __launch_bounds__(kRowThreads)
+layernorm_fwd_generic_kernel(const float* __restrict__ A, const float* __restrict__ R,
+                             const float* __restrict__ gamma, const float* __restrict__ beta,
+                             float* __restrict__ Y, float* __restrict__ sum_out,
+                             float* __restrict__ mean_out, float* __restrict__ inv_std_out, uint8_t* __restrict__ row_is_zero,
+                             long long rows, int E, float eps, int round)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * kRowWarps;
+    const float inv_E = 1.0f / (float)E;
+
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const float* a_row = A + row * (long long)E;
+        const float* r_row = R ? R + row * (long long)E : nullptr;
+        float total = 0.f;
+        for(int e = lane; e < E; e += 32) total += a_row[e] + (r_row ? r_row[e] : 0.f);
+        const float mean = warp_sum(total) * inv_E;
+        float squares = 0.f;
+        for(int e = lane; e < E; e += 32)
+        {
+            const float c = a_row[e] + (r_row ? r_row[e] : 0.f) - mean;
+            squares += c * c;
+        }
+        const float inv_std = 1.0f / sqrtf(warp_sum(squares) * inv_E + eps);
+        bool all_zero = true;
+        for(int e = lane; e < E; e += 32)
+        {
+            const float x = a_row[e] + (r_row ? r_row[e] : 0.f);
+            if(sum_out) sum_out[row * (long long)E + e] = x;
+            const float y = maybe_round((x - mean) * inv_std * gamma[e] + beta[e], round);
+            all_zero = all_zero && fabsf(y) <= 1e-7f;
+            Y[row * (long long)E + e] = y;
+        }
+        if(lane == 0) { mean_out[row] = mean; inv_std_out[row] = inv_std; }
+        if(row_is_zero)
+        {
+            all_zero = __all_sync(0xffffffffu, all_zero);
+            if(lane == 0) row_is_zero[row] = all_zero ? 1 : 0;
+        }
+    }
+}
+
+// Backward: dx = (d - mean(d) - x_hat * mean(d * x_hat)) * inv_std with d = dy * gamma.
+// Each warp keeps running per-column sums of dy * x_hat and dy in registers across all the
+// rows it visits; the CTA folds its 8 warps through shared memory and writes ONE partial
+// row pair per CTA to `partials` ([gridDim.x][2][E]); colsum_partials_kernel finishes.
+template <int VEC>
+__global__ void __launch_bounds__(kRowThreads)
+layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2, const float* __restrict__ dY3,
+                     const float* __restrict__ X, const float* __restrict__ mean_in, const float* __restrict__ inv_std_in,
+                     const float* __restrict__ gamma, float* __restrict__ dX, float* __restrict__ partials,
+                     long long rows, int E, int round)
+{
+    extern __shared__ float smem[];               // [kRowWarps][2][E]
+    const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
+    const long long warp = (long long)blockIdx.x * kRowWarps + warp_in_block;
+    const long long stride = (long long)gridDim.x * kRowWarps;
+    const float inv_E = 1.0f / (float)E;
+
+    float4 g[VEC], acc_gamma[VEC], acc_beta[VEC];
+#pragma unroll
+    for(int i = 0; i < VEC; i++)
+    {
+        const int e = (i * 32 + lane) * 4;
+        g[i] = e < E ? ld4(gamma + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        acc_gamma[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        acc_beta[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const long long base = row * (long long)E;
+        const float mean = mean_in[row], inv_std = inv_std_in[row];
+        float4 d[VEC], xh[VEC];
+        float sum_d = 0.f, sum_dx = 0.f;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            const int e = (i * 32 + lane) * 4;
+            d[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            xh[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if(e < E)
+            {
+                float4 dy = ld4_stream(dY + base + e);
+                if(dY2) { const float4 t = ld4_stream(dY2 + base + e); dy.x += t.x; dy.y += t.y; dy.z += t.z; dy.w += t.w; }
+                if(dY3) { const float4 t = ld4_stream(dY3 + base + e); dy.x += t.x; dy.y += t.y; dy.z += t.z; dy.w += t.w; }
+                const float4 x = ld4_stream(X + base + e);
+                xh[i].x = (x.x - mean) * inv_std; xh[i].y = (x.y - mean) * inv_std;
+                xh[i].z = (x.z - mean) * inv_std; xh[i].w = (x.w - mean) * inv_std;
+                acc_gamma[i].x += dy.x * xh[i].x; acc_gamma[i].y += dy.y * xh[i].y;
+                acc_gamma[i].z += dy.z * xh[i].z; acc_gamma[i].w += dy.w * xh[i].w;
+                acc_beta[i].x += dy.x; acc_beta[i].y += dy.y; acc_beta[i].z += dy.z; acc_beta[i].w += dy.w;
+                d[i].x = dy.x * g[i].x; d[i].y = dy.y * g[i].y; d[i].z = dy.z * g[i].z; d[i].w = dy.w * g[i].w;
+                sum_d += (d[i].x + d[i].y) + (d[i].z + d[i].w);
+                sum_dx += (d[i].x * xh[i].x + d[i].y * xh[i].y) + (d[i].z * xh[i].z + d[i].w * xh[i].w);
+            }
+        }
+        sum_d = warp_sum(sum_d) * inv_E;
+        sum_dx = warp_sum(sum_dx) * inv_E;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            const int e = (i * 32 + lane) * 4;
+            if(e < E)
+            {
+                float4 o;
+                o.x = maybe_round((d[i].x - sum_d - xh[i].x * sum_dx) * inv_std, round);
+                o.y = maybe_round((d[i].y - sum_d - xh[i].y * sum_dx) * inv_std, round);
+                o.z = maybe_round((d[i].z - sum_d - xh[i].z * sum_dx) * inv_std, round);
+                o.w = maybe_round((d[i].w - sum_d - xh[i].w * sum_dx) * inv_std, round);
+                st4(dX + base + e, o);
+            }
+        }
+    }
+
+    float* mine = smem + (size_t)warp_in_block * 2 * E;
+#pragma unroll
+    for(int i = 0; i < VEC; i++)
+    {
+        const int e = (i * 32 + lane) * 4;
+        if(e < E) { st4(mine + e, acc_gamma[i]); st4(mine + E + e, acc_beta[i]); }
+    }
+    __syncthreads();
+    float* out = partials + (size_t)blockIdx.x * 2 * E;
+    for(int c = threadIdx.x; c < 2 * E; c += kRowThreads)
+    {
+        float total = 0.f;
+#pragma unroll
+        for(int w = 0; w < kRowWarps; w++) total += smem[(size_t)w * 2 * E + c];
+        out[c] = total;
+    }
+}
+
+// Any E: column sums via shared-memory atomics per CTA, then one partial row pair per CTA.
+__global__ void __launch_bounds__(kRowThreads)
+layernorm_bwd_generic_kernel(const float* __restrict__ dY, const float* __restrict__ dY2, const float* __restrict__ dY3,
+                             const float* __restrict__ X, const float* __restrict__ mean_in, const float* __restrict__ inv_std_in,
+                             const float* __restrict__ gamma, float* __restrict__ dX, float* __restrict__ partials,
+                             long long rows, int E, int round)
+{
+    extern __shared__ float smem[];               // [2][E]
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * kRowWarps;
+    const float inv_E = 1.0f / (float)E;
+
+    for(int c = threadIdx.x; c < 2 * E; c += kRowThreads) smem[c] = 0.f;
+    __syncthreads();
+
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const long long base = row * (long long)E;
+        const float mean = mean_in[row], inv_std = inv_std_in[row];
+        float sum_d = 0.f, sum_dx = 0.f;
+        for(int e = lane; e < E; e += 32)
+        {
+            const float dy = dY[base + e] + (dY2 ? dY2[base + e] : 0.f) + (dY3 ? dY3[base + e] : 0.f);
+            const float xh = (X[base + e] - mean) * inv_std;
+            const float d = dy * gamma[e];
+            sum_d += d; sum_dx += d * xh;
+            atomicAdd(smem + e, dy * xh);
+            atomicAdd(smem + E + e, dy);
+        }
+        sum_d = warp_sum(sum_d) * inv_E;
+        sum_dx = warp_sum(sum_dx) * inv_E;
+        for(int e = lane; e < E; e += 32)
+        {
+            const float dy = dY[base + e] + (dY2 ? dY2[base + e] : 0.f) + (dY3 ? dY3[base + e] : 0.f);
+            const float xh = (X[base + e] - mean) * inv_std;
+            dX[base + e] = maybe_round((dy * gamma[e] - sum_d - xh * sum_dx) * inv_std, round);
+        }
+    }
+    __syncthreads();
+    float* out = partials + (size_t)blockIdx.x * 2 * E;
+    for(int c = threadIdx.x; c < 2 * E; c += kRowThreads) out[c] = smem[c];
+}
+
+// out[c] (+)= sum over p of partials[p][c]; one thread per column, coalesced across threads.
+__global__ void colsum_partials_kernel(const float* __restrict__ partials, int count, int columns,
+                                       float* __restrict__ out_a, float* __restrict__ out_b, int split, int accumulate)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if(c >= columns) return;
+    float total = 0.f;
+    for(int p = 0; p < count; p++) total += partials[(size_t)p * columns + c];
+    float* dst = c < split ? out_a + c : out_b + (c - split);
+    *dst = accumulate ? *dst + total : total;
+}
+
+// ---------------------------------------------------------------------------------------
+// Element-wise
+// ---------------------------------------------------------------------------------------
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                           long long n, int round)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n4 = (aligned16(a) && aligned16(b) && aligned16(out)) ? n / 4 : 0;
+    for(long long i = tid; i < n4; i += stride)
+    {
+        const float4 x = ld4_stream(a + 4 * i), y = ld4_stream(b + 4 * i);
+        float4 r = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+        if(round) { r.x = round_tf32(r.x); r.y = round_tf32(r.y); r.z = round_tf32(r.z); r.w = round_tf32(r.w); }
+        st4(out + 4 * i, r);
+    }
+    for(long long i = 4 * n4 + tid; i < n; i += stride) out[i] = maybe_round(a[i] + b[i], round);
+}
+
+__global__ void round_tf32_kernel(const float* __restrict__ src, float* __restrict__ dst, long long n)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n4 = (aligned16(src) && aligned16(dst)) ? n / 4 : 0;
+    for(long long i = tid; i < n4; i += stride)
+    {
+        float4 x = ld4(src + 4 * i);
+        x.x = round_tf32(x.x); x.y = round_tf32(x.y); x.z = round_tf32(x.z); x.w = round_tf32(x.w);
+        st4(dst + 4 * i, x);
+    }
+    for(long long i = 4 * n4 + tid; i < n; i += stride) dst[i] = round_tf32(src[i]);
+}
+
+static int vec_count(long long E) { return (int)((E + 127) / 128); }
+
+}  // namespace onn
+
+using namespace onn;
+
+extern "C" int onn_embedding_fwd(const float* ids, const float* W, const float* PE, float* out, uint8_t* row_is_zero,
+                                 int64_t B, int64_t S, int64_t E, int64_t V, int scale, int add_pe, uint32_t flags, void* stream)
+{
+    ONN_CHECK_ARG(ids && W && out && B > 0 && S > 0 && E > 0 && V > 0);
+    ONN_CHECK_ARG(!add_pe || PE);
+    ONN_CHECK_ARG((E & 3) != 0 || (host_aligned16(W) && host_aligned16(out) && (!add_pe || host_aligned16(PE))));
+    const long long tokens = B * S;
+    const int grid = grid_for(tokens, kRowWarps, 8);
+    embedding_fwd_kernel<<<grid, kRowThreads, 0, (cudaStream_t)stream>>>(
+        ids, W, PE, out, row_is_zero, tokens, (int)S, (int)E, V, sqrtf((float)E), scale, add_pe,
+        (flags & ONN_ROUND_OUTPUT_TF32) != 0);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_embedding_bwd(const float* ids, const float* dY, const float* dY2, float* dW,
+                                 int64_t B, int64_t S, int64_t E, int64_t V, int scale, void* stream)
+{
+    ONN_CHECK_ARG(ids && dY && dW && B > 0 && S > 0 && E > 0 && V > 0);
+    ONN_CHECK_ARG((E & 3) != 0 || (host_aligned16(dY) && host_aligned16(dW) && (!dY2 || host_aligned16(dY2))));
+    const long long tokens = B * S;
+    const int grid = grid_for(tokens, kRowWarps, 8);
+    embedding_bwd_kernel<<<grid, kRowThreads, 0, (cudaStream_t)stream>>>(
+        ids, dY, dY2, dW, tokens, (int)E, V, sqrtf((float)E), scale);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_layernorm_fwd(const float* A, const float* R, const float* gamma, const float* beta,
+                                 float* Y, float* sum, float* mean, float* inv_std, uint8_t* row_is_zero,
+                                 int64_t rows, int64_t E, float eps, uint32_t flags, void* stream)
+{
+    ONN_CHECK_ARG(A && gamma && beta && Y && mean && inv_std && rows > 0 && E > 0);
+    const int round = (flags & ONN_ROUND_OUTPUT_TF32) != 0;
+    const int grid = grid_for(rows, kRowWarps, 8);
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool fast = (E & 3) == 0 && E <= 128 * kMaxVec && host_aligned16(A) && host_aligned16(Y) &&
+                      host_aligned16(gamma) && host_aligned16(beta) && (!R || host_aligned16(R)) && (!sum || host_aligned16(sum));
+#define ONN_LN_FWD(V) layernorm_fwd_kernel<V><<<grid, kRowThreads, 0, s>>>(A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, rows, (int)E, eps, round)
+    if(fast)
+    {
+        switch(vec_count(E))
+        {
+            case 1: ONN_LN_FWD(1); break;
+            case 2: ONN_LN_FWD(2); break;
+            case 3: case 4: ONN_LN_FWD(4); break;
+            default: ONN_LN_FWD(8); break;
+        }
+    }
+    else
+        layernorm_fwd_generic_kernel<<<grid, kRowThreads, 0, s>>>(A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, rows, (int)E, eps, round);
+#undef ONN_LN_FWD
+    count_launch();
+    return launch_status();
+}
+
+// Number of CTAs the backward kernel runs with (= partial row pairs in the workspace).
+static int layernorm_bwd_grid(int64_t rows) { return grid_for(rows, kRowWarps, 2); }
+
+extern "C" size_t onn_layernorm_bwd_workspace_floats(int64_t rows, int64_t E)
+{
+    if(rows <= 0 || E <= 0) return 0;
+    return (size_t)layernorm_bwd_grid(rows) * 2 * (size_t)E;
+}
+
+namespace onn
+{
+// Shared by the workspace entry point and any other front end: launches the row kernel
+// into `partials` and the column reduction into dgamma / dbeta.
+int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, const float* X,
+                         const float* mean, const float* inv_std, const float* gamma,
+                         float* dX, float* dgamma, float* dbeta, int64_t rows, int64_t E,
+                         float* partials, uint32_t flags, cudaStream_t s)
+{
+    const int round = (flags & ONN_ROUND_OUTPUT_TF32) != 0;
+    const int grid = layernorm_bwd_grid(rows);
+    const bool fast = (E & 3) == 0 && E <= 128 * kMaxVec && host_aligned16(dY) && host_aligned16(X) && host_aligned16(dX) &&
+                      host_aligned16(gamma) && (!dY2 || host_aligned16(dY2)) && (!dY3 || host_aligned16(dY3));
+#define ONN_LN_BWD(V) layernorm_bwd_kernel<V><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E, round)
+    if(fast)
+    {
+        const size_t smem = (size_t)kRowWarps * 2 * E * sizeof(float);   // <= 64 KiB at E = 1024
+        if(smem > 48 * 1024)
+        {
+            cudaFuncSetAttribute(layernorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        }
+        switch(vec_count(E))
+        {
+            case 1: ONN_LN_BWD(1); break;
+            case 2: ONN_LN_BWD(2); break;
+            case 3: case 4: ONN_LN_BWD(4); break;
+            default: ONN_LN_BWD(8); break;
+        }
+    }
+    else
+    {
+        const size_t smem = (size_t)2 * E * sizeof(float);
+        if(smem > 48 * 1024)
+        {
+            if(smem > 200 * 1024) return ONN_ERR_UNSUPPORTED;
+            cudaFuncSetAttribute(layernorm_bwd_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        }
+        layernorm_bwd_generic_kernel<<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E, round);
+    }
+#undef ONN_LN_BWD
+    count_launch();
+    if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    const int columns = (int)(2 * E);
+    colsum_partials_kernel<<<(columns + 127) / 128, 128, 0, s>>>(partials, grid, columns, dgamma, dbeta, (int)E,
+                                                                  (flags & ONN_ACCUMULATE) != 0);
+    count_launch();
+    return launch_status();
+}
+}  // namespace onn
+
+extern "C" int onn_layernorm_bwd(const float* dY, const float* dY2, const float* dY3, const float* X,
+                                 const float* mean, const float* inv_std, const float* gamma,
+                                 float* dX, float* dgamma, float* dbeta,
+                                 int64_t rows, int64_t E, float* workspace, uint32_t flags, void* stream)
+{
+    ONN_CHECK_ARG(dY && X && mean && inv_std && gamma && dX && dgamma && dbeta && rows > 0 && E > 0);
+    if(!workspace) return ONN_ERR_WORKSPACE;
+    return layernorm_bwd_launch(dY, dY2, dY3, X, mean, inv_std, gamma, dX, dgamma, dbeta, rows, E, workspace, flags,
+                                (cudaStream_t)stream);
+}
+
+extern "C" int onn_add(const float* a, const float* b, float* out, int64_t n, uint32_t flags, void* stream)
+{
+    ONN_CHECK_ARG(a && b && out && n > 0);
+    const int grid = grid_for((n + 3) / 4, 256, 8);
+    add_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, (flags & ONN_ROUND_OUTPUT_TF32) != 0);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_round_tf32(const float* src, float* dst, int64_t n, void* stream)
+{
+    ONN_CHECK_ARG(src && dst && n > 0);
+    const int grid = grid_for((n + 3) / 4, 256, 8);
+    round_tf32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(src, dst, n);
+    count_launch();
+    return launch_status();
+}

@@ -1,0 +1,623 @@
+// HBM-bound kernels around the contractions: masked attention softmax (+ backward), plain
+// row softmax, the fused CrossEntropyError3d pass, column sums for bias gradients, the
+// ReLU-derivative product, the gradient norm and the fused clip + Adam update.
+#include <float.h>
+
+#include "common.cuh"
+#include "launch_counter.h"
+
+namespace onn
+{
+
+// ---------------------------------------------------------------------------------------
+// Attention softmax: scores [B, H, Sq, Sk] in place.  One warp per (b, h, q) row.
+//   key padding: score := -1e9 where the source row is all-zero (overwrite);
+//   causal:      score += -inf for key > query.
+// ---------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256)
+source_row_is_zero_kernel(const float* __restrict__ X, uint8_t* __restrict__ flags, long long rows, int E)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * 8;
+    for(long long row = warp; row < rows; row += stride)
+    {
+        bool zero = true;
+        for(int e = lane; e < E; e += 32) zero = zero && fabsf(X[row * (long long)E + e]) <= 1e-7f;
+        zero = __all_sync(0xffffffffu, zero);
+        if(lane == 0) flags[row] = zero ? 1 : 0;
+    }
+}
+
+template <int PER_LANE>   // Sk <= 32 * PER_LANE, row in registers
+__global__ void __launch_bounds__(256)
+attention_softmax_kernel(float* __restrict__ scores, const uint8_t* __restrict__ key_is_pad,
+                         long long rows, int H, int Sq, int Sk, int causal, int round)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * 8;
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const int q = (int)(row % Sq);
+        const long long b = row / ((long long)Sq * H);
+        const uint8_t* pad = key_is_pad ? key_is_pad + b * Sk : nullptr;
+        float* p = scores + row * (long long)Sk;
+        float v[PER_LANE];
+        float row_max = -INFINITY;
+#pragma unroll
+        for(int i = 0; i < PER_LANE; i++)
+        {
+            const int k = i * 32 + lane;
+            v[i] = -INFINITY;
+            if(k < Sk)
+            {
+                float s = p[k];
+                if(pad && pad[k]) s = -1e9f;
+                if(causal && k > q) s = -INFINITY;
+                v[i] = s;
+            }
+            row_max = fmaxf(row_max, v[i]);
+        }
+        row_max = warp_max(row_max);
+        float total = 0.f;
+#pragma unroll
+        for(int i = 0; i < PER_LANE; i++)
+        {
+            v[i] = (i * 32 + lane < Sk) ? __expf(v[i] - row_max) : 0.f;
+            total += v[i];
+        }
+        total = warp_sum(total);
+        const float inv = total > 0.f ? 1.0f / total : 0.f;
+#pragma unroll
+        for(int i = 0; i < PER_LANE; i++)
+        {
+            const int k = i * 32 + lane;
+            if(k < Sk) p[k] = maybe_round(v[i] * inv, round);
+        }
+    }
+}
+
+// Any Sk: three sweeps through global memory (the row stays in L1/L2).
+__global__ void __launch_bounds__(256)
+attention_softmax_generic_kernel(float* __restrict__ scores, const uint8_t* __restrict__ key_is_pad,
+                                 long long rows, int H, int Sq, int Sk, int causal, int round)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * 8;
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const int q = (int)(row % Sq);
+        const long long b = row / ((long long)Sq * H);
+        const uint8_t* pad = key_is_pad ? key_is_pad + b * Sk : nullptr;
+        float* p = scores + row * (long long)Sk;
+        float row_max = -INFINITY;
+        for(int k = lane; k < Sk; k += 32)
+        {
+            float s = p[k];
+            if(pad && pad[k]) s = -1e9f;
+            if(causal && k > q) s = -INFINITY;
+            p[k] = s;
+            row_max = fmaxf(row_max, s);
+        }
+        row_max = warp_max(row_max);
+        float total = 0.f;
+        for(int k = lane; k < Sk; k += 32) { const float e = __expf(p[k] - row_max); p[k] = e; total += e; }
+        total = warp_sum(total);
+        const float inv = total > 0.f ? 1.0f / total : 0.f;
+        for(int k = lane; k < Sk; k += 32) p[k] = maybe_round(p[k] * inv, round);
+    }
+}
+
+// dS = P * (dP - rowsum(P * dP)), in place over dP.
+template <int PER_LANE>
+__global__ void __launch_bounds__(256)
+attention_softmax_bwd_kernel(const float* __restrict__ P, float* __restrict__ dP, long long rows, int Sk, int round)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * 8;
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const float* p = P + row * (long long)Sk;
+        float* d = dP + row * (long long)Sk;
+        float pv[PER_LANE], dv[PER_LANE];
+        float dot = 0.f;
+#pragma unroll
+        for(int i = 0; i < PER_LANE; i++)
+        {
+            const int k = i * 32 + lane;
+            pv[i] = k < Sk ? p[k] : 0.f;
+            dv[i] = k < Sk ? d[k] : 0.f;
+            dot += pv[i] * dv[i];
+        }
+        dot = warp_sum(dot);
+#pragma unroll
+        for(int i = 0; i < PER_LANE; i++)
+        {
+            const int k = i * 32 + lane;
+            if(k < Sk) d[k] = maybe_round(pv[i] * (dv[i] - dot), round);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+attention_softmax_bwd_generic_kernel(const float* __restrict__ P, float* __restrict__ dP, long long rows, int Sk, int round)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * 8;
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const float* p = P + row * (long long)Sk;
+        float* d = dP + row * (long long)Sk;
+        float dot = 0.f;
+        for(int k = lane; k < Sk; k += 32) dot += p[k] * d[k];
+        dot = warp_sum(dot);
+        for(int k = lane; k < Sk; k += 32) d[k] = maybe_round(p[k] * (d[k] - dot), round);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Row softmax / CrossEntropyError3d: one CTA per token row of V logits.
+// Sweep 1 (DRAM): online max + sum of exp + argmax.  Sweep 2 (L2): write p or the gradient.
+// ---------------------------------------------------------------------------------------
+
+constexpr int kLossThreads = 256;
+
+struct RowStats { float max; float sum; int argmax; };
+
+__device__ __forceinline__ void online_update(float x, int index, float& m, float& s, int& arg)
+{
+    if(x > m) { s = s * __expf(m - x) + 1.0f; m = x; arg = index; }
+    else s += __expf(x - m);
+}
+
+__device__ __forceinline__ RowStats row_statistics(const float* __restrict__ row, int V, float* scratch_f, int* scratch_i)
+{
+    float m = -INFINITY, s = 0.f;
+    int arg = 0x7fffffff;
+    const bool vec = (V & 3) == 0 && aligned16(row);
+    if(vec)
+    {
+        for(int i = threadIdx.x * 4; i < V; i += kLossThreads * 4)
+        {
+            const float4 x = ld4(row + i);
+            online_update(x.x, i, m, s, arg); online_update(x.y, i + 1, m, s, arg);
+            online_update(x.z, i + 2, m, s, arg); online_update(x.w, i + 3, m, s, arg);
+        }
+    }
+    else
+        for(int i = threadIdx.x; i < V; i += kLossThreads) online_update(row[i], i, m, s, arg);
+
+    // combine (max, sum, argmax) across the CTA; ties resolve to the smallest index,
+    // matching the reference's first-maximum scan.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for(int offset = 16; offset > 0; offset >>= 1)
+    {
+        const float om = __shfl_xor_sync(0xffffffffu, m, offset);
+        const float os = __shfl_xor_sync(0xffffffffu, s, offset);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, offset);
+        const float nm = fmaxf(m, om);
+        const float a = (m == -INFINITY) ? 0.f : s * __expf(m - nm);
+        const float b = (om == -INFINITY) ? 0.f : os * __expf(om - nm);
+        if(om > m || (om == m && oa < arg)) arg = oa;
+        m = nm; s = a + b;
+    }
+    __syncthreads();
+    if(lane == 0) { scratch_f[warp] = m; scratch_f[8 + warp] = s; scratch_i[warp] = arg; }
+    __syncthreads();
+    RowStats r;
+    r.max = scratch_f[0]; r.sum = scratch_f[8]; r.argmax = scratch_i[0];
+#pragma unroll
+    for(int w = 1; w < kLossThreads / 32; w++)
+    {
+        const float om = scratch_f[w], os = scratch_f[8 + w];
+        const int oa = scratch_i[w];
+        const float nm = fmaxf(r.max, om);
+        const float a = (r.max == -INFINITY) ? 0.f : r.sum * __expf(r.max - nm);
+        const float b = (om == -INFINITY) ? 0.f : os * __expf(om - nm);
+        if(om > r.max || (om == r.max && oa < r.argmax)) r.argmax = oa;
+        r.max = nm; r.sum = a + b;
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(kLossThreads)
+softmax_rows_kernel(float* __restrict__ Y, int V)
+{
+    __shared__ float scratch_f[16];
+    __shared__ int scratch_i[8];
+    float* row = Y + (long long)blockIdx.x * V;
+    const RowStats st = row_statistics(row, V, scratch_f, scratch_i);
+    const float inv = st.sum > 0.f ? 1.0f / st.sum : 0.f;
+    const bool vec = (V & 3) == 0 && aligned16(row);
+    if(vec)
+        for(int i = threadIdx.x * 4; i < V; i += kLossThreads * 4)
+        {
+            float4 x = ld4(row + i);
+            x.x = __expf(x.x - st.max) * inv; x.y = __expf(x.y - st.max) * inv;
+            x.z = __expf(x.z - st.max) * inv; x.w = __expf(x.w - st.max) * inv;
+            st4(row + i, x);
+        }
+    else
+        for(int i = threadIdx.x; i < V; i += kLossThreads) row[i] = __expf(row[i] - st.max) * inv;
+}
+
+__global__ void count_active_kernel(const float* __restrict__ targets, long long rows, long long V, float* __restrict__ count)
+{
+    __shared__ float scratch[32];
+    float mine = 0.f;
+    for(long long i = threadIdx.x; i < rows; i += blockDim.x)
+    {
+        const long long t = token_index(targets[i]);
+        mine += (t > 0 && t < V) ? 1.f : 0.f;
+    }
+    const float total = block_sum(mine, scratch);
+    if(threadIdx.x == 0) count[0] = total;
+}
+
+// In place: logits -> gradient (p - onehot) / active on active rows, 0 on inactive rows.
+// row_scratch[row] = -log(p[target] + eps) (0 if inactive); row_scratch[rows + row] = correct.
+__global__ void __launch_bounds__(kLossThreads)
+ce3d_fwd_bwd_kernel(float* __restrict__ logits, const float* __restrict__ targets, const float* __restrict__ active_count,
+                    float* __restrict__ probabilities_out, float* __restrict__ row_scratch,
+                    long long rows, int V, int inputs_are_probabilities, int round)
+{
+    __shared__ float scratch_f[16];
+    __shared__ int scratch_i[8];
+    const long long r = blockIdx.x;
+    float* row = logits + r * (long long)V;
+    float* p_out = probabilities_out ? probabilities_out + r * (long long)V : nullptr;
+    const long long target = token_index(targets[r]);
+    const bool active = target > 0 && target < V;
+    const float count = active_count[0];
+    const float scale = count > 0.f ? 1.0f / count : 0.f;
+    const bool vec = (V & 3) == 0 && aligned16(row) && (!p_out || aligned16(p_out));
+
+    if(!active && !p_out)
+    {
+        // nothing of this row is needed: the gradient is zero and it adds nothing to the loss
+        if(vec) for(int i = threadIdx.x * 4; i < V; i += kLossThreads * 4) st4(row + i, make_float4(0.f, 0.f, 0.f, 0.f));
+        else for(int i = threadIdx.x; i < V; i += kLossThreads) row[i] = 0.f;
+        if(threadIdx.x == 0) { row_scratch[r] = 0.f; row_scratch[rows + r] = 0.f; }
+        return;
+    }
+
+    const RowStats st = row_statistics(row, V, scratch_f, scratch_i);
+    // probabilities in: exp(x - max)/sum would distort them; use them as they are
+    const float shift = inputs_are_probabilities ? 0.f : st.max;
+    const float inv = inputs_are_probabilities ? 1.0f : (st.sum > 0.f ? 1.0f / st.sum : 0.f);
+
+    if(threadIdx.x == 0)
+    {
+        float term = 0.f, correct = 0.f;
+        if(active)
+        {
+            const float x = row[target];
+            const float p = inputs_are_probabilities ? x : __expf(x - shift) * inv;
+            term = -logf(p + FLT_EPSILON);
+            correct = (st.argmax == (int)target) ? 1.f : 0.f;
+        }
+        row_scratch[r] = term;
+        row_scratch[rows + r] = correct;
+    }
+    __syncthreads();   // the target logit is read before anyone overwrites it
+
+    const int t = active ? (int)target : -1;
+#define ONN_CE_ELEMENT(x, index)                                                         \
+    {                                                                                    \
+        const float p = inputs_are_probabilities ? (x) : __expf((x) - shift) * inv;      \
+        const float g = active ? (p - ((index) == t ? 1.0f : 0.0f)) * scale : 0.0f;      \
+        pr = p; (x) = maybe_round(g, round);                                             \
+    }
+    if(vec)
+        for(int i = threadIdx.x * 4; i < V; i += kLossThreads * 4)
+        {
+            float4 x = ld4(row + i), pq;
+            float pr;
+            ONN_CE_ELEMENT(x.x, i) pq.x = pr;
+            ONN_CE_ELEMENT(x.y, i + 1) pq.y = pr;
+            ONN_CE_ELEMENT(x.z, i + 2) pq.z = pr;
+            ONN_CE_ELEMENT(x.w, i + 3) pq.w = pr;
+            st4_stream(row + i, x);
+            if(p_out) st4_stream(p_out + i, pq);
+        }
+    else
+        for(int i = threadIdx.x; i < V; i += kLossThreads)
+        {
+            float x = row[i], pr;
+            ONN_CE_ELEMENT(x, i)
+            row[i] = x;
+            if(p_out) p_out[i] = pr;
+        }
+#undef ONN_CE_ELEMENT
+}
+
+// stats = {sum of loss terms, #correct, #active, 0}: one CTA, fixed order -> deterministic.
+__global__ void ce3d_finish_kernel(const float* __restrict__ row_scratch, const float* __restrict__ targets,
+                                   long long rows, long long V, float* __restrict__ stats)
+{
+    __shared__ float scratch[32];
+    float loss = 0.f, correct = 0.f, active = 0.f;
+    for(long long i = threadIdx.x; i < rows; i += blockDim.x)
+    {
+        loss += row_scratch[i];
+        correct += row_scratch[rows + i];
+        const long long t = token_index(targets[i]);
+        active += (t > 0 && t < V) ? 1.f : 0.f;
+    }
+    loss = block_sum(loss, scratch);
+    correct = block_sum(correct, scratch);
+    active = block_sum(active, scratch);
+    if(threadIdx.x == 0) { stats[0] = loss; stats[1] = correct; stats[2] = active; stats[3] = 0.f; }
+}
+
+// ---------------------------------------------------------------------------------------
+// Bias gradient (column sums) and ReLU derivative
+// ---------------------------------------------------------------------------------------
+
+// out[c] += sum over rows of D[r][c].  Each CTA owns a 32-column strip and a slab of rows,
+// sums it in registers / shared memory and issues one atomic per column.
+__global__ void __launch_bounds__(256)
+colsum_accumulate_kernel(const float* __restrict__ D, long long rows, long long cols, long long ld,
+                         long long rows_per_block, float* __restrict__ out)
+{
+    __shared__ float tile[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const long long c = (long long)blockIdx.x * 32 + tx;
+    const long long r0 = (long long)blockIdx.y * rows_per_block;
+    const long long r1 = min(rows, r0 + rows_per_block);
+    float total = 0.f;
+    if(c < cols)
+        for(long long r = r0 + ty; r < r1; r += 8) total += D[r * ld + c];
+    tile[ty][tx] = total;
+    __syncthreads();
+    if(ty == 0 && c < cols)
+    {
+        float sum = 0.f;
+#pragma unroll
+        for(int w = 0; w < 8; w++) sum += tile[w][tx];
+        atomicAdd(out + c, sum);
+    }
+}
+
+// delta = dY * (Y > 0), in place over dY.
+__global__ void relu_delta_kernel(float* __restrict__ dY, const float* __restrict__ Y, long long n, int round)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n4 = (aligned16(dY) && aligned16(Y)) ? n / 4 : 0;
+    for(long long i = tid; i < n4; i += stride)
+    {
+        float4 d = ld4(dY + 4 * i);
+        const float4 y = ld4_stream(Y + 4 * i);
+        d.x = y.x > 0.f ? maybe_round(d.x, round) : 0.f; d.y = y.y > 0.f ? maybe_round(d.y, round) : 0.f;
+        d.z = y.z > 0.f ? maybe_round(d.z, round) : 0.f; d.w = y.w > 0.f ? maybe_round(d.w, round) : 0.f;
+        st4(dY + 4 * i, d);
+    }
+    for(long long i = 4 * n4 + tid; i < n; i += stride) dY[i] = Y[i] > 0.f ? maybe_round(dY[i], round) : 0.f;
+}
+
+// ---------------------------------------------------------------------------------------
+// Gradient norm and Adam
+// ---------------------------------------------------------------------------------------
+
+constexpr int kNormBlocks = kSmCount * 4;
+
+__global__ void __launch_bounds__(256)
+sqnorm_partial_kernel(const float* __restrict__ g, long long n, float* __restrict__ partials)
+{
+    __shared__ float scratch[32];
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n4 = aligned16(g) ? n / 4 : 0;
+    float a = 0.f, b = 0.f;
+    for(long long i = tid; i < n4; i += stride)
+    {
+        const float4 x = ld4(g + 4 * i);
+        a += x.x * x.x + x.y * x.y; b += x.z * x.z + x.w * x.w;
+    }
+    for(long long i = 4 * n4 + tid; i < n; i += stride) a += g[i] * g[i];
+    const float total = block_sum(a + b, scratch);
+    if(threadIdx.x == 0) partials[blockIdx.x] = total;
+}
+
+__global__ void sqnorm_finish_kernel(const float* __restrict__ partials, int count, float* __restrict__ out)
+{
+    double mine = 0.0;   // few hundred terms: double keeps the final sum order-insensitive in fp32
+    for(int i = threadIdx.x; i < count; i += blockDim.x) mine += (double)partials[i];
+    // fold doubles through shuffles
+    for(int offset = 16; offset > 0; offset >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, offset);
+    __shared__ double warp_totals[32];
+    if((threadIdx.x & 31) == 0) warp_totals[threadIdx.x >> 5] = mine;
+    __syncthreads();
+    if(threadIdx.x == 0)
+    {
+        double total = 0.0;
+        for(int w = 0; w < (int)((blockDim.x + 31) >> 5); w++) total += warp_totals[w];
+        out[0] = (float)total;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ g,
+            float* __restrict__ p_tf32, long long n, float lr, float beta1, float beta2, float eps,
+            float bc1, float bc2, float clip_norm, const float* __restrict__ sqnorm, float grad_scale, int zero_grad)
+{
+    float scale = grad_scale;
+    if(sqnorm && clip_norm > 0.f)
+    {
+        const float norm = sqrtf(sqnorm[0]) * fabsf(grad_scale);
+        if(norm > clip_norm) scale *= clip_norm / norm;
+    }
+    const float one_minus_b1 = 1.0f - beta1, one_minus_b2 = 1.0f - beta2;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool vec = aligned16(p) && aligned16(m) && aligned16(v) && aligned16(g) && (!p_tf32 || aligned16(p_tf32));
+    const long long n4 = vec ? n / 4 : 0;
+
+#define ONN_ADAM_ELEMENT(pp, mm, vv, gg)                                   \
+    {                                                                      \
+        const float ge = (gg) * scale;                                     \
+        (mm) = beta1 * (mm) + one_minus_b1 * ge;                           \
+        (vv) = beta2 * (vv) + one_minus_b2 * ge * ge;                      \
+        (pp) -= lr * ((mm) / bc1) / (sqrtf((vv) / bc2) + eps);       \
+    }
+    for(long long i = tid; i < n4; i += stride)
+    {
+        float4 pp = ld4(p + 4 * i), mm = ld4(m + 4 * i), vv = ld4(v + 4 * i);
+        const float4 gg = ld4(g + 4 * i);
+        ONN_ADAM_ELEMENT(pp.x, mm.x, vv.x, gg.x)
+        ONN_ADAM_ELEMENT(pp.y, mm.y, vv.y, gg.y)
+        ONN_ADAM_ELEMENT(pp.z, mm.z, vv.z, gg.z)
+        ONN_ADAM_ELEMENT(pp.w, mm.w, vv.w, gg.w)
+        st4(p + 4 * i, pp); st4(m + 4 * i, mm); st4(v + 4 * i, vv);
+        if(p_tf32) st4(p_tf32 + 4 * i, make_float4(round_tf32(pp.x), round_tf32(pp.y), round_tf32(pp.z), round_tf32(pp.w)));
+        if(zero_grad) st4(g + 4 * i, make_float4(0.f, 0.f, 0.f, 0.f));
+    }
+    for(long long i = 4 * n4 + tid; i < n; i += stride)
+    {
+        float pp = p[i], mm = m[i], vv = v[i];
+        ONN_ADAM_ELEMENT(pp, mm, vv, g[i])
+        p[i] = pp; m[i] = mm; v[i] = vv;
+        if(p_tf32) p_tf32[i] = round_tf32(pp);
+        if(zero_grad) g[i] = 0.f;
+    }
+#undef ONN_ADAM_ELEMENT
+}
+
+// ---------------------------------------------------------------------------------------
+// Internal launchers used by the layer front ends
+// ---------------------------------------------------------------------------------------
+
+int launch_source_row_is_zero(const float* X, uint8_t* flags, long long rows, int E, cudaStream_t s)
+{
+    source_row_is_zero_kernel<<<grid_for(rows, 8, 8), 256, 0, s>>>(X, flags, rows, E);
+    count_launch();
+    return launch_status();
+}
+
+int launch_attention_softmax(float* scores, const uint8_t* key_is_pad, long long B, int H, int Sq, int Sk,
+                             int causal, int round, cudaStream_t s)
+{
+    const long long rows = B * H * Sq;
+    const int grid = grid_for(rows, 8, 8);
+#define ONN_SM(N) attention_softmax_kernel<N><<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal, round)
+    if(Sk <= 32) ONN_SM(1);
+    else if(Sk <= 64) ONN_SM(2);
+    else if(Sk <= 128) ONN_SM(4);
+    else if(Sk <= 256) ONN_SM(8);
+    else if(Sk <= 512) ONN_SM(16);
+    else if(Sk <= 1024) ONN_SM(32);
+    else attention_softmax_generic_kernel<<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal, round);
+#undef ONN_SM
+    count_launch();
+    return launch_status();
+}
+
+int launch_attention_softmax_bwd(const float* P, float* dP, long long rows, int Sk, int round, cudaStream_t s)
+{
+    const int grid = grid_for(rows, 8, 8);
+#define ONN_SB(N) attention_softmax_bwd_kernel<N><<<grid, 256, 0, s>>>(P, dP, rows, Sk, round)
+    if(Sk <= 32) ONN_SB(1);
+    else if(Sk <= 64) ONN_SB(2);
+    else if(Sk <= 128) ONN_SB(4);
+    else if(Sk <= 256) ONN_SB(8);
+    else if(Sk <= 512) ONN_SB(16);
+    else attention_softmax_bwd_generic_kernel<<<grid, 256, 0, s>>>(P, dP, rows, Sk, round);
+#undef ONN_SB
+    count_launch();
+    return launch_status();
+}
+
+int launch_colsum_accumulate(const float* D, long long rows, long long cols, long long ld, float* out, cudaStream_t s)
+{
+    const long long strips = (cols + 31) / 32;
+    long long slabs = (2LL * kSmCount + strips - 1) / strips;          // ~2 CTAs per SM overall
+    if(slabs > (rows + 255) / 256) slabs = (rows + 255) / 256;
+    if(slabs < 1) slabs = 1;
+    const long long rows_per_block = (rows + slabs - 1) / slabs;
+    dim3 grid((unsigned)strips, (unsigned)slabs);
+    colsum_accumulate_kernel<<<grid, 256, 0, s>>>(D, rows, cols, ld, rows_per_block, out);
+    count_launch();
+    return launch_status();
+}
+
+int launch_relu_delta(float* dY, const float* Y, long long n, int round, cudaStream_t s)
+{
+    relu_delta_kernel<<<grid_for((n + 3) / 4, 256, 8), 256, 0, s>>>(dY, Y, n, round);
+    count_launch();
+    return launch_status();
+}
+
+}  // namespace onn
+
+using namespace onn;
+
+extern "C" int onn_softmax_rows(float* Y, int64_t rows, int64_t cols, void* stream)
+{
+    ONN_CHECK_ARG(Y && rows > 0 && cols > 0 && rows < (1LL << 31) && cols < (1LL << 31));
+    softmax_rows_kernel<<<(unsigned)rows, kLossThreads, 0, (cudaStream_t)stream>>>(Y, (int)cols);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_ce3d_count_active(const float* targets, int64_t rows, int64_t V, float* counts, void* stream)
+{
+    ONN_CHECK_ARG(targets && counts && rows > 0 && V > 0);
+    count_active_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(targets, rows, V, counts);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_count,
+                                float* probabilities_out, float* stats, float* row_scratch,
+                                int64_t rows, int64_t V, int inputs_are_probabilities, uint32_t flags, void* stream)
+{
+    ONN_CHECK_ARG(logits && targets && active_count && stats && row_scratch);
+    ONN_CHECK_ARG(rows > 0 && V > 1 && rows < (1LL << 31) && V < (1LL << 31));
+    cudaStream_t s = (cudaStream_t)stream;
+    ce3d_fwd_bwd_kernel<<<(unsigned)rows, kLossThreads, 0, s>>>(logits, targets, active_count, probabilities_out, row_scratch,
+                                                                 rows, (int)V, inputs_are_probabilities,
+                                                                 (flags & ONN_ROUND_OUTPUT_TF32) != 0);
+    count_launch();
+    if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    ce3d_finish_kernel<<<1, 1024, 0, s>>>(row_scratch, targets, rows, V, stats);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" size_t onn_grad_sqnorm_workspace_floats(int64_t n)
+{
+    return n > 0 ? (size_t)kNormBlocks : 0;
+}
+
+extern "C" int onn_grad_sqnorm(const float* g, int64_t n, float* sqnorm, float* workspace, void* stream)
+{
+    ONN_CHECK_ARG(g && sqnorm && n > 0);
+    if(!workspace) return ONN_ERR_WORKSPACE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = grid_for((n + 3) / 4, 256, 4);
+    sqnorm_partial_kernel<<<grid, 256, 0, s>>>(g, n, workspace);
+    count_launch();
+    if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    sqnorm_finish_kernel<<<1, 256, 0, s>>>(workspace, grid, sqnorm);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_adam(float* p, float* m, float* v, float* g, float* p_tf32, int64_t n,
+                        float lr, float beta1, float beta2, float eps, float bc1, float bc2,
+                        float clip_norm, const float* sqnorm, float grad_scale, int zero_grad, void* stream)
+{
+    ONN_CHECK_ARG(p && m && v && g && n > 0 && bc1 != 0.f && bc2 != 0.f);
+    const int grid = grid_for((n + 3) / 4, 256, 8);
+    adam_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p, m, v, g, p_tf32, n, lr, beta1, beta2, eps,
+                                                        bc1, bc2, clip_norm, sqnorm, grad_scale, zero_grad);
+    count_launch();
+    return launch_status();
+}

@@ -1,0 +1,486 @@
+"""CPU restatement (numpy, fp32) of OpenNN's transformer training path.
+
+TEST INFRASTRUCTURE ONLY.  This module is the checker for the CUDA path: only the tests,
+the smoke check and the benchmark's CPU-baseline leg may import it.  No product code does.
+
+Parity is pinned: `oracle/check_against_ref.py` runs the unmodified reference CPU library
+(built by `oracle/Makefile` into `oracle/_ref/`) on the same seeded inputs and compares
+every function below with it; the outputs it produced are committed under `tests/golden/`.
+
+Each function cites the reference file:line (paths inside the OpenNN checkout) it follows.
+All arithmetic is float32 unless the reference itself uses double.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+F32 = np.float32
+EPSILON = np.finfo(np.float32).eps  # opennn/pch.h:123  numeric_limits<float>::epsilon()
+
+
+def padded(count: int) -> int:
+    """Arena slot size: each view is padded to 8 floats (opennn/tensor_utilities.cpp:472-487)."""
+    return (count + 7) & ~7
+
+
+# --------------------------------------------------------------------------------------
+# Embedding
+# --------------------------------------------------------------------------------------
+
+def positional_encoding(sequence_length: int, embedding_dimension: int) -> np.ndarray:
+    """opennn/embedding_layer.cpp:74-85: first half sin, second half cos (not interleaved);
+    the exponent j/half_depth is a float division, pow/sin/cos run in double."""
+    half_depth = F32(embedding_dimension) / F32(2)
+    half = int(half_depth)
+    table = np.zeros((sequence_length, embedding_dimension), dtype=F32)
+    positions = np.arange(sequence_length, dtype=np.float64)[:, None]
+    for j in range(embedding_dimension):
+        if j < half:
+            exponent = np.float64(F32(j) / half_depth)
+            table[:, j] = np.sin(positions[:, 0] / np.power(10000.0, exponent)).astype(F32)
+        else:
+            exponent = np.float64(F32(j - half) / half_depth)
+            table[:, j] = np.cos(positions[:, 0] / np.power(10000.0, exponent)).astype(F32)
+    return table
+
+
+def token_index(ids: np.ndarray) -> np.ndarray:
+    """static_cast<Index>(float): truncation toward zero (opennn/embedding_layer.cpp:166)."""
+    return np.trunc(ids).astype(np.int64)
+
+
+def embedding_forward(ids, weights, pe, scale=True, add_pe=True):
+    """opennn/embedding_layer.cpp:147-186.  ids [B,S] floats; weights [V,E]; pe [S,E]."""
+    B, S = ids.shape
+    V, E = weights.shape
+    idx = token_index(ids)
+    valid = (idx >= 0) & (idx < V)
+    out = np.zeros((B, S, E), dtype=F32)
+    out[valid] = weights[idx[valid]]
+    if scale:
+        out = out * np.sqrt(F32(E))
+    if add_pe:
+        positive = idx > 0
+        out = out + np.where(positive[:, :, None], pe[None, :S, :], F32(0))
+    return out.astype(F32)
+
+
+def embedding_backward(ids, d_out, vocabulary_size, scale=True):
+    """opennn/embedding_layer.cpp:193-226: scatter-add of sqrt(E)*dY, row 0 forced to zero."""
+    B, S, E = d_out.shape
+    idx = token_index(ids).reshape(-1)
+    g = d_out.reshape(B * S, E).astype(F32)
+    if scale:
+        g = g * np.sqrt(F32(E))
+    d_weights = np.zeros((vocabulary_size, E), dtype=F32)
+    valid = (idx >= 0) & (idx < vocabulary_size)
+    np.add.at(d_weights, idx[valid], g[valid])
+    d_weights[0] = 0
+    return d_weights
+
+
+# --------------------------------------------------------------------------------------
+# Normalization3d
+# --------------------------------------------------------------------------------------
+
+def layernorm_forward(x, gammas, betas):
+    """opennn/normalization_layer_3d.cpp:87-125.  Returns y, mean, std, x_hat;
+    std = sqrt(biased variance + EPSILON)."""
+    mean = x.mean(axis=-1, dtype=F32, keepdims=True)
+    centered = x - mean
+    variance = np.mean(centered * centered, axis=-1, dtype=F32, keepdims=True)
+    std = np.sqrt(variance + EPSILON).astype(F32)
+    x_hat = (centered / std).astype(F32)
+    y = (x_hat * gammas + betas).astype(F32)
+    return y, mean[..., 0], std[..., 0], x_hat
+
+
+def layernorm_backward(d_y, x_hat, std, gammas):
+    """opennn/normalization_layer_3d.cpp:128-188."""
+    E = d_y.shape[-1]
+    d_gamma = (d_y * x_hat).reshape(-1, E).sum(axis=0, dtype=F32)
+    d_beta = d_y.reshape(-1, E).sum(axis=0, dtype=F32)
+    D = (d_y * gammas).astype(F32)
+    sum_D = D.sum(axis=-1, dtype=F32, keepdims=True)
+    sum_D_xhat = (D * x_hat).sum(axis=-1, dtype=F32, keepdims=True)
+    inv_E = F32(1.0) / F32(E)
+    d_x = (D - sum_D * inv_E - x_hat * sum_D_xhat * inv_E) / std[..., None]
+    return d_x.astype(F32), d_gamma, d_beta
+
+
+# --------------------------------------------------------------------------------------
+# Dense<3>
+# --------------------------------------------------------------------------------------
+
+def softmax_last(y):
+    """opennn/layer.cpp:338-371 (3-D) and 326-335 (2-D): max-subtracted exp over the last dim."""
+    m = y.max(axis=-1, keepdims=True)
+    e = np.exp((y - m).astype(F32)).astype(F32)
+    s = e.sum(axis=-1, dtype=F32, keepdims=True)
+    return (e * (F32(1.0) / s)).astype(F32)
+
+
+def dense_forward(x, weights, biases, activation):
+    """opennn/dense_layer.h:767-813 -> layer.h:305-340 (X.W + b) -> layer.h:122-152.
+    Returns (outputs, activation_derivatives)."""
+    rows = x.reshape(-1, x.shape[-1])
+    combos = (rows @ weights + biases).astype(F32).reshape(*x.shape[:-1], weights.shape[1])
+    if activation == "Linear":
+        return combos, np.ones_like(combos)
+    if activation == "RectifiedLinear":
+        return np.maximum(combos, F32(0)), (combos > 0).astype(F32)
+    if activation == "Softmax":
+        return softmax_last(combos), None
+    raise ValueError(activation)
+
+
+def dense_backward(x, weights, d_y, activation_derivatives, activation):
+    """opennn/dense_layer.h:816-866: delta = dY*act' (Softmax: delta = dY, the loss already
+    delivers dlogits), dW = X^T delta, db = colsum(delta), dX = delta W^T."""
+    rows = x.reshape(-1, x.shape[-1])
+    delta = d_y.reshape(-1, d_y.shape[-1])
+    if activation != "Softmax":
+        delta = delta * activation_derivatives.reshape(delta.shape)
+    d_w = (rows.T @ delta).astype(F32)
+    d_b = delta.sum(axis=0, dtype=F32)
+    d_x = (delta @ weights.T).astype(F32).reshape(x.shape)
+    return d_x, d_w, d_b
+
+
+# --------------------------------------------------------------------------------------
+# MultiHeadAttention
+# --------------------------------------------------------------------------------------
+
+def _split_heads(t, H):
+    B, S, E = t.shape
+    return t.reshape(B, S, H, E // H).transpose(0, 2, 1, 3)  # [B,H,S,hd]
+
+
+def _merge_heads(t):
+    B, H, S, hd = t.shape
+    return t.transpose(0, 2, 1, 3).reshape(B, S, H * hd)
+
+
+def key_padding_flags(source):
+    """opennn/multihead_attention_layer.cpp:574-603: a source row is padding when every
+    feature has |x| <= 1e-7 (data-dependent, not token ids)."""
+    return np.all(np.abs(source) <= F32(1e-7), axis=-1)  # [B,Sk]
+
+
+def mha_forward(xq, xs, p, H, causal):
+    """opennn/multihead_attention_layer.cpp:183-282.  p: dict Wq,bq,Wk,bk,Wv,bv,Wo,bo
+    (weights [E,E] in x out; head h = columns h*hd..).  Returns y and the saved state."""
+    B, Sq, E = xq.shape
+    Sk = xs.shape[1]
+    hd = E // H
+    scaling = F32(1.0) / np.sqrt(F32(hd))
+    q = _split_heads((xq.reshape(-1, E) @ p["Wq"] + p["bq"]).astype(F32).reshape(B, Sq, E), H)
+    k = _split_heads((xs.reshape(-1, E) @ p["Wk"] + p["bk"]).astype(F32).reshape(B, Sk, E), H)
+    v = _split_heads((xs.reshape(-1, E) @ p["Wv"] + p["bv"]).astype(F32).reshape(B, Sk, E), H)
+    scores = (np.matmul(q, k.transpose(0, 1, 3, 2)) * scaling).astype(F32)  # [B,H,Sq,Sk]
+    pad = key_padding_flags(xs)
+    scores = np.where(pad[:, None, None, :], F32(-1e9), scores)            # :600 overwrite
+    if causal:
+        future = np.arange(Sk)[None, :] > np.arange(Sq)[:, None]          # :157 column > row
+        scores = np.where(future[None, None], F32(-np.inf), scores)        # :570 additive -inf
+    weights = softmax_last(scores)
+    concat = _merge_heads(np.matmul(weights, v).astype(F32))              # [B,Sq,E]
+    y = (concat.reshape(-1, E) @ p["Wo"] + p["bo"]).astype(F32).reshape(B, Sq, E)
+    saved = dict(q=q, k=k, v=v, weights=weights, concat=concat)
+    return y, saved
+
+
+def mha_backward(xq, xs, p, H, saved, d_y, self_attention):
+    """opennn/multihead_attention_layer.cpp:285-454 and 493-553.
+    Returns gradients dict (same keys as p, prefixed d) and dXq, dXs (dXs None for self)."""
+    B, Sq, E = xq.shape
+    Sk = xs.shape[1]
+    hd = E // H
+    scaling = F32(1.0) / np.sqrt(F32(hd))
+    q, k, v, w, concat = saved["q"], saved["k"], saved["v"], saved["weights"], saved["concat"]
+    dy = d_y.reshape(-1, E)
+    g = {}
+    g["dWo"] = (concat.reshape(-1, E).T @ dy).astype(F32)
+    g["dbo"] = dy.sum(axis=0, dtype=F32)
+    d_concat = (dy @ p["Wo"].T).astype(F32).reshape(B, Sq, E)
+    d_o = _split_heads(d_concat, H)                                       # [B,H,Sq,hd]
+    d_v = np.matmul(w.transpose(0, 1, 3, 2), d_o).astype(F32)
+    d_w = np.matmul(d_o, v.transpose(0, 1, 3, 2)).astype(F32)
+    dot = (w * d_w).sum(axis=-1, dtype=F32, keepdims=True)
+    d_s = (w * (d_w - dot)).astype(F32)
+    d_q = (np.matmul(d_s, k) * scaling).astype(F32)
+    d_k = (np.matmul(d_s.transpose(0, 1, 3, 2), q) * scaling).astype(F32)
+
+    def projection_gradient(d_head, x, W):
+        d = _merge_heads(d_head).reshape(-1, E)
+        return (d @ W.T).astype(F32).reshape(x.shape), (x.reshape(-1, E).T @ d).astype(F32), d.sum(axis=0, dtype=F32)
+
+    d_xq, g["dWq"], g["dbq"] = projection_gradient(d_q, xq, p["Wq"])
+    d_xk, g["dWk"], g["dbk"] = projection_gradient(d_k, xs, p["Wk"])
+    d_xv, g["dWv"], g["dbv"] = projection_gradient(d_v, xs, p["Wv"])
+    if self_attention:
+        return g, (d_xq + d_xk + d_xv).astype(F32), None
+    return g, d_xq, (d_xk + d_xv).astype(F32)
+
+
+# --------------------------------------------------------------------------------------
+# CrossEntropyError3d
+# --------------------------------------------------------------------------------------
+
+def ce3d_error(probabilities, targets):
+    """opennn/cross_entropy_error_3d.cpp:78-136.  Returns (error, accuracy, active_count).
+    Active = 0 < int(target) < V; loss term = -log(p[target] + EPSILON)."""
+    B, S, V = probabilities.shape
+    t = token_index(targets)
+    active = (t > 0) & (t < V)
+    count = int(active.sum())
+    if count == 0:
+        return F32(0), F32(0), 0
+    rows = probabilities[active]
+    picked = rows[np.arange(count), t[active]]
+    total = F32(-np.log((picked + EPSILON).astype(F32)).astype(F32).sum(dtype=F32))
+    correct = int((rows.argmax(axis=-1) == t[active]).sum())
+    return F32(total / F32(count)), F32(F32(correct) / F32(count)), count
+
+
+def ce3d_output_gradients(probabilities, targets):
+    """opennn/cross_entropy_error_3d.cpp:154-247: (p - onehot)/active on active tokens, 0 elsewhere."""
+    B, S, V = probabilities.shape
+    t = token_index(targets)
+    active = (t > 0) & (t < V)
+    count = int(active.sum())
+    scale = F32(1.0) / F32(count) if count > 0 else F32(0)
+    grad = np.zeros_like(probabilities, dtype=F32)
+    onehot = np.zeros((count, V), dtype=F32)
+    onehot[np.arange(count), t[active]] = 1
+    grad[active] = (probabilities[active] - onehot) * scale
+    return grad
+
+
+# --------------------------------------------------------------------------------------
+# Adam
+# --------------------------------------------------------------------------------------
+
+def adam_update(parameters, gradient, m, v, iteration, lr=1e-3, beta_1=0.9, beta_2=0.999, clip_norm=1.0):
+    """opennn/adaptive_moment_estimation.cpp:444-473.  `iteration` is the value AFTER the
+    increment (the loop starts at 1, so the first step passes 2).  Updates in place."""
+    lr, beta_1, beta_2, clip_norm = F32(lr), F32(beta_1), F32(beta_2), F32(clip_norm)
+    bc1 = F32(1) - F32(np.power(beta_1, F32(iteration)))
+    bc2 = F32(1) - F32(np.power(beta_2, F32(iteration)))
+    norm = F32(np.sqrt(np.sum(gradient.astype(np.float64) ** 2)))
+    g = gradient
+    if clip_norm > 0 and norm > clip_norm:
+        g = (gradient * (clip_norm / norm)).astype(F32)
+    m[:] = beta_1 * m + (F32(1) - beta_1) * g
+    v[:] = beta_2 * v + (F32(1) - beta_2) * g * g
+    parameters -= (lr * (m / bc1) / (np.sqrt(v / bc2) + EPSILON)).astype(F32)
+    return norm
+
+
+# --------------------------------------------------------------------------------------
+# Network graph (NeuralNetwork + Transformer builder)
+# --------------------------------------------------------------------------------------
+
+PARAMETER_SHAPES = {
+    # view order inside the arena:
+    "Embedding": lambda l: [("weights", (l["V"], l["E"]))],                      # embedding_layer.cpp:60
+    "MultiHeadAttention": lambda l: [("Wq", (l["E"], l["E"])), ("bq", (l["E"],)),  # multihead_attention_layer.cpp:105-108
+                                     ("Wk", (l["E"], l["E"])), ("bk", (l["E"],)),
+                                     ("Wv", (l["E"], l["E"])), ("bv", (l["E"],)),
+                                     ("Wo", (l["E"], l["E"])), ("bo", (l["E"],))],
+    "Addition3d": lambda l: [],
+    "Normalization3d": lambda l: [("gammas", (l["E"],)), ("betas", (l["E"],))],  # normalization_layer_3d.cpp:49
+    "Dense3d": lambda l: [("biases", (l["out"],)), ("weights", (l["in"], l["out"]))],  # dense_layer.h:484
+}
+
+
+class Network:
+    """Layer DAG with one parameter arena and one gradient arena in the same layout
+    (opennn/neural_network.cpp:66-94, 1489-1497).  Negative input index = external input:
+    -1 decoder ids, -2 encoder ids (opennn/standard_networks.cpp:669-704)."""
+
+    def __init__(self):
+        self.layers = []
+
+    def add(self, kind, inputs=None, **cfg):
+        if inputs is None:
+            inputs = [len(self.layers) - 1]
+        self.layers.append(dict(kind=kind, inputs=list(inputs), **cfg))
+        return len(self.layers) - 1
+
+    def compile(self):
+        offset = 0
+        for layer in self.layers:
+            layer["views"] = {}
+            for name, shape in PARAMETER_SHAPES[layer["kind"]](layer):
+                count = int(np.prod(shape))
+                layer["views"][name] = (offset, shape)
+                offset += padded(count)
+            if layer["kind"] == "Embedding":
+                layer["pe"] = positional_encoding(layer["S"], layer["E"])
+        self.parameters_size = offset
+        self.consumers = [[] for _ in self.layers]
+        for i, layer in enumerate(self.layers):
+            for port, src in enumerate(layer["inputs"]):
+                if src >= 0:
+                    self.consumers[src].append((i, port))
+        return self
+
+    def views(self, arena, layer):
+        return {name: arena[o:o + int(np.prod(shape))].reshape(shape) for name, (o, shape) in layer["views"].items()}
+
+    def default_parameters(self, rng):
+        """The reference's own initial distributions (dense_layer.h:581-597, embedding_layer.cpp:114-126,
+        normalization_layer_3d.cpp:72-79, MHA U(-0.1,0.1)); drawn from OUR seeded generator."""
+        arena = np.zeros(self.parameters_size, dtype=F32)
+        for layer in self.layers:
+            v = self.views(arena, layer)
+            kind = layer["kind"]
+            if kind == "Embedding":
+                v["weights"][:] = F32(0.05) * rng.uniform(-1, 1, v["weights"].shape).astype(F32)
+                v["weights"][0] = 0
+            elif kind == "MultiHeadAttention":
+                for name in v:
+                    v[name][:] = rng.uniform(-0.1, 0.1, v[name].shape).astype(F32)
+            elif kind == "Normalization3d":
+                v["gammas"][:] = 1
+            elif kind == "Dense3d":
+                v["weights"][:] = rng.uniform(-0.1, 0.1, v["weights"].shape).astype(F32)
+        return arena
+
+    def forward(self, arena, external):
+        """opennn/neural_network.cpp:645-699.  external: {-1: decoder ids, -2: encoder ids}."""
+        self.outputs = [None] * len(self.layers)
+        self.saved = [None] * len(self.layers)
+        for i, layer in enumerate(self.layers):
+            ins = [external[s] if s < 0 else self.outputs[s] for s in layer["inputs"]]
+            p = self.views(arena, layer)
+            kind = layer["kind"]
+            if kind == "Embedding":
+                self.outputs[i] = embedding_forward(ins[0], p["weights"], layer["pe"])
+            elif kind == "MultiHeadAttention":
+                xs = ins[1] if len(ins) > 1 else ins[0]
+                self.outputs[i], self.saved[i] = mha_forward(ins[0], xs, p, layer["H"], layer["causal"])
+            elif kind == "Addition3d":
+                self.outputs[i] = (ins[0] + ins[1]).astype(F32)       # addition_layer.h:65-76
+            elif kind == "Normalization3d":
+                y, mean, std, x_hat = layernorm_forward(ins[0], p["gammas"], p["betas"])
+                self.outputs[i], self.saved[i] = y, (std, x_hat)
+            elif kind == "Dense3d":
+                self.outputs[i], self.saved[i] = dense_forward(ins[0], p["weights"], p["biases"], layer["activation"])
+            self.layers[i]["_ins"] = ins
+        return self.outputs[-1]
+
+    def backward(self, arena, d_outputs):
+        """opennn/loss.cpp:284-303: reverse layer walk; fan-out gradients are summed in
+        consumer order (layer.cpp:285-291).  Returns the gradient arena."""
+        gradient = np.zeros(self.parameters_size, dtype=F32)
+        input_grads = [dict() for _ in self.layers]
+        for i in range(len(self.layers) - 1, -1, -1):
+            layer = self.layers[i]
+            if i == len(self.layers) - 1:
+                d_y = d_outputs
+            else:
+                parts = [input_grads[c][port] for c, port in self.consumers[i]]
+                d_y = parts[0]
+                for extra in parts[1:]:
+                    d_y = (d_y + extra).astype(F32)
+            ins = layer["_ins"]
+            p = self.views(arena, layer)
+            g = self.views(gradient, layer)
+            kind = layer["kind"]
+            if kind == "Embedding":
+                g["weights"][:] = embedding_backward(ins[0], d_y, layer["V"])
+            elif kind == "MultiHeadAttention":
+                self_attention = len(ins) == 1
+                xs = ins[0] if self_attention else ins[1]
+                grads, d_xq, d_xs = mha_backward(ins[0], xs, p, layer["H"], self.saved[i], d_y, self_attention)
+                for name in ("Wq", "bq", "Wk", "bk", "Wv", "bv", "Wo", "bo"):
+                    g[name][:] = grads["d" + name]
+                input_grads[i][0] = d_xq
+                if not self_attention:
+                    input_grads[i][1] = d_xs
+            elif kind == "Addition3d":
+                input_grads[i][0] = d_y                               # addition_layer.h:79-90
+                input_grads[i][1] = d_y
+            elif kind == "Normalization3d":
+                std, x_hat = self.saved[i]
+                d_x, g["gammas"][:], g["betas"][:] = layernorm_backward(d_y, x_hat, std, p["gammas"])
+                input_grads[i][0] = d_x
+            elif kind == "Dense3d":
+                d_x, g["weights"][:], g["biases"][:] = dense_backward(ins[0], p["weights"], d_y, self.saved[i], layer["activation"])
+                input_grads[i][0] = d_x
+        return gradient
+
+    def train_step(self, arena, m, v, iteration, external, targets, lr=1e-3):
+        """Loop body of opennn/adaptive_moment_estimation.cpp:249-284 (regularisation "None").
+        Returns (error, accuracy, gradient, iteration_after)."""
+        probabilities = self.forward(arena, external)
+        error, accuracy, _ = ce3d_error(probabilities, targets)
+        gradient = self.backward(arena, ce3d_output_gradients(probabilities, targets))
+        iteration += 1
+        adam_update(arena, gradient, m, v, iteration, lr=lr)
+        return error, accuracy, gradient, iteration
+
+
+def _encoder_block(net, S, E, H, F, source):
+    attention = net.add("MultiHeadAttention", [source], Sq=S, Sk=S, E=E, H=H, causal=False)
+    net.add("Addition3d", [source, attention], E=E)
+    norm_1 = net.add("Normalization3d", S=S, E=E)
+    net.add("Dense3d", **{"in": E, "out": F, "activation": "RectifiedLinear"})
+    dense = net.add("Dense3d", **{"in": F, "out": E, "activation": "Linear"})
+    net.add("Addition3d", [norm_1, dense], E=E)
+    return net.add("Normalization3d", S=S, E=E)
+
+
+def build_transformer(S_in, S_dec, V_in, V_out, E, H, F, L):
+    """opennn/standard_networks.cpp:638-907: post-norm encoder-decoder, 2 + 7L + 10L + 1 layers."""
+    net = Network()
+    decoder = net.add("Embedding", [-1], V=V_out, S=S_dec, E=E)
+    encoder = net.add("Embedding", [-2], V=V_in, S=S_in, E=E)
+    for _ in range(L):
+        encoder = _encoder_block(net, S_in, E, H, F, encoder)
+    for _ in range(L):
+        attention = net.add("MultiHeadAttention", [decoder], Sq=S_dec, Sk=S_dec, E=E, H=H, causal=True)
+        net.add("Addition3d", [decoder, attention], E=E)
+        norm_1 = net.add("Normalization3d", S=S_dec, E=E)
+        cross = net.add("MultiHeadAttention", [norm_1, encoder], Sq=S_dec, Sk=S_in, E=E, H=H, causal=False)
+        net.add("Addition3d", [norm_1, cross], E=E)
+        norm_2 = net.add("Normalization3d", S=S_dec, E=E)
+        net.add("Dense3d", **{"in": E, "out": F, "activation": "RectifiedLinear"})
+        dense = net.add("Dense3d", **{"in": F, "out": E, "activation": "Linear"})
+        net.add("Addition3d", [norm_2, dense], E=E)
+        decoder = net.add("Normalization3d", S=S_dec, E=E)
+    net.add("Dense3d", **{"in": E, "out": V_out, "activation": "Softmax"})
+    return net.compile()
+
+
+def build_decoder_only(S, V, E, H, F, L):
+    """Decoder-only stack assembled the way Transformer::set assembles its decoder minus
+    cross-attention (causal self-attention -> add -> norm -> FFN -> add -> norm)."""
+    net = Network()
+    current = net.add("Embedding", [-1], V=V, S=S, E=E)
+    for _ in range(L):
+        attention = net.add("MultiHeadAttention", [current], Sq=S, Sk=S, E=E, H=H, causal=True)
+        net.add("Addition3d", [current, attention], E=E)
+        norm_1 = net.add("Normalization3d", S=S, E=E)
+        net.add("Dense3d", **{"in": E, "out": F, "activation": "RectifiedLinear"})
+        dense = net.add("Dense3d", **{"in": F, "out": E, "activation": "Linear"})
+        net.add("Addition3d", [norm_1, dense], E=E)
+        current = net.add("Normalization3d", S=S, E=E)
+    net.add("Dense3d", **{"in": E, "out": V, "activation": "Softmax"})
+    return net.compile()
+
+
+# --------------------------------------------------------------------------------------
+# Seeded synthetic inputs shared by the oracle, the reference harness and the CUDA path
+# --------------------------------------------------------------------------------------
+
+def synthetic_ids(rng, batch, sequence_length, vocabulary, min_length, max_length):
+    """Token ids uniform in [1, vocabulary), per-row length ~U[min_length, max_length],
+    right-padded with id 0; stored as floats holding integers (dataset.h:525-558)."""
+    ids = rng.integers(1, vocabulary, size=(batch, sequence_length)).astype(F32)
+    lengths = rng.integers(min_length, max_length + 1, size=batch)
+    ids[np.arange(sequence_length)[None, :] >= lengths[:, None]] = 0
+    return ids
