@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark: train tokens/s (forward + back-propagation + Adam) of the large encoder-decoder
+Transformer (6+6 layers, d_model 1024, 16 heads, FFN 4096, vocabulary 32000, sequence 256,
+GLOBAL batch 512) on 1/2/4/8 B200, data-parallel over NCCL.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Launched by torchrun for N > 1 (one rank per GPU).  Rank 0 prints ONE JSON line.
+
+  value     whole-job decoder tokens per second with the batch already resident in HBM;
+            strong scaling: the global batch of 512 is split over the ranks.
+  e2e       the same step through the host-buffer entry point: pinned host ids are copied to
+            the device inside the timed region and the loss statistics are read back each step.
+  roofline  the dominant kernel (tcgen05 tf32 GEMM at the FFN shape of this workload), timed
+            alone with CUDA events, against the measured dense tensor peak.
+  cpu_baseline  the unmodified reference CPU library (oracle/_ref) on the box's host cores,
+            on a bounded sample of the same workload (N = 1 only).
+
+--impl reference times that CPU library alone (the reference has no multi-GPU path and its
+own CUDA path needs cuDNN + its build system, which this benchmark does not run).
+
+Data are synthetic: token ids uniform in [1, 32000), row lengths ~U[64, 256], right-padded
+with id 0, seed 3; parameters are the reference's default random initialisation.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(name="config5_large_encdec", S_in=256, S_dec=256, V_in=32000, V_out=32000, E=1024, H=16, F=4096, L=6,
+                global_batch=512, micro_batch=64, seed=3, min_len=64, max_len=256)
+METRIC = "train tokens/s (fwd+bwd+Adam)"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peaks = json.load(f)
+        return dict(hbm_gbs=peaks["hbm_gbs"], tflops=peaks["bf16_tflops"], tflops_sustained=peaks.get("bf16_tflops_sustained"),
+                    source="measured (MEASURED_PEAKS.json)")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+def synthetic_batch(rng, batch, w):
+    import numpy as np
+
+    def ids(S, V):
+        x = rng.integers(1, V, size=(batch, S)).astype(np.float32)
+        lengths = rng.integers(w["min_len"], w["max_len"] + 1, size=batch)
+        x[np.arange(S)[None, :] >= lengths[:, None]] = 0
+        return x
+    return ids(w["S_in"], w["V_in"]), ids(w["S_dec"], w["V_out"]), ids(w["S_dec"], w["V_out"])
+
+
+# ---------------------------------------------------------------------------------------
+# reference CPU library (oracle/_ref) on a bounded sample
+# ---------------------------------------------------------------------------------------
+
+def time_reference_cpu(w, batch, steps):
+    """Runs the unmodified reference CPU path (Transformer + CrossEntropyError3d + Adam) on
+    `batch` samples of the workload for `steps` steps; returns (tokens/s of the best step, cores)."""
+    import numpy as np
+    from oracle import ref_runner
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(w["seed"])
+    enc, dec, tgt = synthetic_batch(rng, batch, w)
+    spec = dict(mode="transformer", B=batch, S_in=w["S_in"], S_dec=w["S_dec"], V_in=w["V_in"], V_out=w["V_out"], E=w["E"],
+                H=w["H"], F=w["F"], L=w["L"], steps=steps, lr=1e-3, dump=0, random_parameters=1)
+    _, seconds = ref_runner.run(spec, {"enc_ids": enc, "dec_ids": dec, "targets": tgt}, [], threads=cores)
+    best = min(seconds[1:]) if len(seconds) > 1 else seconds[0]
+    return batch * w["S_dec"] / best, cores, seconds
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOAD
+    from oracle import ref_runner
+    if not ref_runner.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/onn_ref_harness is not built (make -C oracle)"}))
+        return
+    sample_batch = 2
+    steps = max(2, min(args.steps + min(args.warmup, 1), 3))
+    start = time.time()
+    value, cores, seconds = time_reference_cpu(w, sample_batch, steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(seconds) - 1,
+        "warmup": 1, "ms_per_step": 1e3 * min(seconds[1:]), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "global_batch": w["global_batch"], "seq_len": w["S_dec"], "parallelism": "cpu"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
+                         "sample": f"batch {sample_batch} of the {w['global_batch']}-sample step (same S, E, H, F, V, L), "
+                                   f"best of {len(seconds) - 1} steps after 1 warm-up, OpenMP/Eigen on {cores} threads, -O2"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.time() - start,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, sm_max, reasons = [], [], set()
+        for row in self.file.read().splitlines():
+            cells = [c.strip() for c in row.split(",")]
+            if len(cells) < 9:
+                continue
+            try:
+                sm.append(float(cells[1]))
+                sm_max.append(float(cells[2]))
+            except ValueError:
+                continue
+            for label, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), cells[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(label)
+        os.unlink(self.file.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def time_dominant_kernel(capi, torch, w, peaks):
+    """The tcgen05 GEMM at the FFN-up shape of one micro-batch (M = 64*256 tokens, K = 1024,
+    N = 4096), launched back to back on fresh buffers larger than L2, timed with CUDA events."""
+    M, K, N = w["micro_batch"] * w["S_dec"], w["E"], w["F"]
+    copies = 4                                  # 4 x (64 + 16 + 256) MiB of operands and outputs: every launch misses L2
+    A = [torch.randn(M, K, device="cuda") for _ in range(copies)]
+    B = [torch.randn(K, N, device="cuda") * 0.05 for _ in range(copies)]
+    Cm = [torch.empty(M, N, device="cuda") for _ in range(copies)]
+    bias = torch.zeros(N, device="cuda")
+    for i in range(copies):                      # warm-up
+        capi.gemm(A[i], B[i], Cm[i], M, N, K, K, N, N, 0, 1, bias=bias, relu=True)
+    torch.cuda.synchronize()
+    launches = 24
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(launches):
+        j = i % copies
+        capi.gemm(A[j], B[j], Cm[j], M, N, K, K, N, N, 0, 1, bias=bias, relu=True)
+    stop.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(stop) * 1e-3 / launches
+    flops = 2.0 * M * N * K
+    achieved = flops / seconds / 1e12
+
+    # the same product by cuBLAS with TF32 operands, for orientation (not part of any product path)
+    torch.backends.cuda.matmul.allow_tf32 = True
+    for i in range(copies):
+        torch.matmul(A[i], B[i], out=Cm[i])
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(launches):
+        j = i % copies
+        torch.matmul(A[j], B[j], out=Cm[j])
+    stop.record()
+    torch.cuda.synchronize()
+    cublas_tf32 = flops / (start.elapsed_time(stop) * 1e-3 / launches) / 1e12
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+    return {"bound": "tensor", "kernel": "gemm_tc_kernel<256,4,0,1> (Dense forward, tf32 operands, fp32 accumulate)",
+            "shape": {"M": M, "N": N, "K": K}, "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["tflops"], "peak_source": "dense bf16 burst, " + peaks["source"] +
+            "; tf32 operands have half the bf16 rate, so 0.5 is this kernel's ceiling on this scale",
+            "us_per_launch": seconds * 1e6, "cublas_tf32_same_shape_tflops": cublas_tf32, "traffic": None}
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    w = WORKLOAD
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torchrun for --gpus > 1")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+
+    from opennn_b200 import build
+    build(verbose=False)
+    from opennn_b200 import capi, trainer
+
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    peaks = measured_peaks()
+    local_batch = w["global_batch"] // world
+    micro = min(w["micro_batch"], local_batch)
+    t = trainer.Trainer(trainer.TRANSFORMER, w["S_in"], w["S_dec"], w["V_in"], w["V_out"], w["E"], w["H"], w["F"], w["L"], micro)
+    if world > 1:
+        comm = trainer.dp_init_from_torch()
+        t.set_dp(comm, world)
+
+    # synthetic batches: the same global stream on every rank, each rank keeps its contiguous slice
+    rng = np.random.default_rng(w["seed"])
+    pool = 3
+    host_batches, device_batches = [], []
+    for _ in range(pool):
+        enc, dec, tgt = synthetic_batch(rng, w["global_batch"], w)
+        lo, hi = rank * local_batch, (rank + 1) * local_batch
+        pinned = [torch.from_numpy(np.ascontiguousarray(x[lo:hi])).pin_memory() for x in (dec, enc, tgt)]
+        host_batches.append(pinned)
+        device_batches.append([x.cuda() for x in pinned])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = t.stream()
+    tokens_per_step = w["global_batch"] * w["S_dec"]
+
+    def timed(step_fn, steps):
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            start.record(stream)
+            for i in range(steps):
+                step_fn(i)
+            stop.record(stream)
+        barrier()
+        elapsed = torch.tensor([start.elapsed_time(stop)], device="cuda")
+        if world > 1:
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        return float(elapsed.item()) * 1e-3
+
+    def device_step(i):
+        d, e, g = device_batches[i % pool]
+        t.step_device(d, e, g, update=True, want_statistics=False)
+
+    last_stats = [None]
+
+    def host_step(i):
+        d, e, g = host_batches[i % pool]
+        last_stats[0] = t.step_host(d, e, g, update=True, want_statistics=True)
+
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
+        device_step(i)
+    barrier()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches_before = capi.lib().onn_launch_count()
+    seconds = timed(device_step, args.steps)
+    launches = capi.lib().onn_launch_count() - launches_before
+    clocks = sampler.stop() if sampler else None
+
+    host_step(0)                                  # warm the host path (staging buffers)
+    e2e_seconds = timed(host_step, args.steps)
+    status = capi.lib().onn_gemm_device_status()
+    if status != 0:
+        raise SystemExit("a tcgen05 GEMM gave up on a bounded wait: the numbers are void")
+
+    if rank == 0:
+        roofline = time_dominant_kernel(capi, torch, w, peaks)
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import ref_runner
+            if ref_runner.available():
+                value, cores, step_seconds = time_reference_cpu(w, 2, 2)
+                cpu = {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
+                       "sample": f"batch 2 of the {w['global_batch']}-sample step (same S, E, H, F, V, L), second of 2 steps, "
+                                 f"unmodified reference CPU library, OpenMP/Eigen on {cores} threads, -O2"}
+        ids_bytes = 4 * w["global_batch"] * (2 * w["S_dec"] + w["S_in"])
+        line = {
+            "metric": METRIC, "value": tokens_per_step * args.steps / seconds, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": 1e3 * seconds / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "tf32 operands, f32 accumulate/storage", "data": "synthetic",
+            "config": {"workload": w["name"], "global_batch": w["global_batch"], "seq_len": w["S_dec"], "parallelism": f"dp{world}",
+                       "micro_batch": micro, "layers": "6+6", "d_model": w["E"], "heads": w["H"], "ffn": w["F"], "vocab": w["V_out"],
+                       "l2": "per-step working set (tens of GB of activations) far exceeds the 126 MB L2; batches rotate"},
+            "e2e": {"value": tokens_per_step * args.steps / e2e_seconds, "unit": UNIT, "ms_per_step": 1e3 * e2e_seconds / args.steps,
+                    "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4 * (4 * (local_batch // micro) + 2) * world,
+                    "last_loss": last_stats[0][0] if last_stats[0] else None},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+
+    t.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -16,12 +16,10 @@
  *     sized by the matching *_workspace_floats query);
  *   - there is no CPU fallback: without a CUDA device every compute call returns ONN_ERR_CUDA.
  *
- * Tensor-core operands.  Contractions run on tcgen05 with kind::tf32: the tensor cores
- * read fp32 storage and ignore the low 13 mantissa bits.  To keep that an unbiased
- * rounding instead of a truncation, every kernel that PRODUCES a future GEMM operand can
- * store it rounded to the nearest tf32 value (flag ONN_ROUND_OUTPUT_TF32), and GEMM-bearing
- * calls take ONN_INPUTS_TF32_READY when their inputs were produced that way.  Without that
- * flag they first round copies of their inputs into the workspace.
+ * Tensor-core operands.  Contractions run on tcgen05 with kind::tf32 and fp32 accumulation.
+ * Operands stay fp32 in HBM; the TMA copy that stages a tile in shared memory rounds each
+ * element to the nearest tf32 value (tensor maps of type TFLOAT32), so no conversion pass
+ * or shadow copy exists and callers pass ordinary fp32 tensors.
  */
 #ifndef ONN_B200_H
 #define ONN_B200_H
@@ -43,10 +41,9 @@ extern "C" {
 #define ONN_ERR_LIMIT             -7   /* size beyond a stated fixed maximum */
 
 /* flags */
-#define ONN_ROUND_OUTPUT_TF32   1u     /* store the result rounded to nearest tf32 */
 #define ONN_ACCUMULATE          2u     /* add into the destination instead of overwriting */
-#define ONN_INPUTS_TF32_READY   4u     /* inputs already hold tf32-representable values */
 #define ONN_DEFER_SOFTMAX       8u     /* Dense "Softmax": leave logits; the loss kernel fuses the softmax */
+#define ONN_DELTA_READY        16u     /* Dense backward: dY already holds dY * act'(Y) */
 
 /* activations of Dense<3> used by the transformer (opennn/standard_networks.cpp:745,753,890) */
 #define ONN_ACT_LINEAR   0
@@ -88,7 +85,7 @@ typedef struct onn_gemm_args
     float alpha;
     int32_t relu;               /* apply max(x, 0) after bias */
     int32_t split_k;            /* 0 or 1 = none */
-    uint32_t flags;             /* ONN_ROUND_OUTPUT_TF32 | ONN_ACCUMULATE */
+    uint32_t flags;             /* ONN_ACCUMULATE */
 } onn_gemm_args;
 
 int onn_gemm(const onn_gemm_args* args, void* stream);
@@ -103,9 +100,6 @@ int onn_gemm_set_mode(int mode);
 int onn_gemm_device_status(void);
 /* Number of kernels this library launched since load (all entry points). */
 uint64_t onn_launch_count(void);
-
-/* Element-wise fp32 -> nearest tf32 (dst may equal src). */
-int onn_round_tf32(const float* src, float* dst, int64_t n, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Embedding.  Forward replaces embedding_forward_kernel (opennn/kernel.cu:714-761, called
@@ -162,24 +156,24 @@ int onn_add(const float* a, const float* b, float* out, int64_t n, uint32_t flag
  * cudnnSoftmaxForward (opennn/dense_layer.h:1117-1232); CPU semantics dense_layer.h:767-813:
  *   Y = act(X W + b), X [rows, in], W [in, out], b [out].
  * ONN_ACT_SOFTMAX normalises each row unless ONN_DEFER_SOFTMAX is set (then Y holds logits
- * for onn_ce3d_fwd_bwd).  workspace is used only without ONN_INPUTS_TF32_READY.
+ * for onn_ce3d_fwd_bwd).
  * ------------------------------------------------------------------------------------- */
-size_t onn_dense_workspace_floats(int64_t rows, int64_t in, int64_t out);
 int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y,
                   int64_t rows, int64_t in, int64_t out, int activation,
-                  float* workspace, uint32_t flags, void* stream);
+                  uint32_t flags, void* stream);
 
 /* Backward replaces cudnnActivationBackward + 3 GEMMs (opennn/dense_layer.h:1235-1374);
  * CPU semantics dense_layer.h:816-866:  delta = dY * act'(Y) (ReLU: Y > 0; Linear and
  * Softmax: delta = dY), dW = X^T delta, db = column sums of delta, dX = delta W^T.
- * dY is overwritten with delta for ReLU (as the reference does in place).  dX may be NULL.
+ * dY is overwritten with delta for ReLU (as the reference does in place) unless
+ * ONN_DELTA_READY says it already holds delta.  dX may be NULL (ONN_ACCUMULATE adds into it).
  * dW and db are ACCUMULATED into (the gradient arena is zeroed once per step).
  * dX_relu_mask (optional, [rows, in]): dX is multiplied by (mask > 0), i.e. the ReLU
  * derivative of the layer that produced X, saving that layer a pass over its gradient. */
 int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
                   float* dW, float* db, float* dX, const float* dX_relu_mask,
                   int64_t rows, int64_t in, int64_t out, int activation,
-                  float* workspace, uint32_t flags, void* stream);
+                  uint32_t flags, void* stream);
 
 /* Row softmax over the last dimension, in place (opennn/layer.cpp:338-371). */
 int onn_softmax_rows(float* Y, int64_t rows, int64_t cols, void* stream);
@@ -265,14 +259,13 @@ int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_co
  *   p -= lr * (m / bc1) / (sqrt(v / bc2) + eps).
  * onn_grad_sqnorm writes sum(g^2) to sqnorm[0] (device) deterministically; workspace is
  * onn_grad_sqnorm_workspace_floats(n) floats.
- * onn_adam reads the squared norm from device memory (no host sync), optionally writes a
- * tf32-rounded copy of the updated parameters (p_tf32, the tensor-core operand copy) and
- * zeroes g for the next step when zero_grad != 0.  grad_scale multiplies g before
+ * onn_adam reads the squared norm from device memory (no host sync) and zeroes g for the
+ * next step when zero_grad != 0.  grad_scale multiplies g before
  * everything else (1/world for averaged all-reduces; 1 otherwise).
  * ------------------------------------------------------------------------------------- */
 size_t onn_grad_sqnorm_workspace_floats(int64_t n);
 int onn_grad_sqnorm(const float* g, int64_t n, float* sqnorm, float* workspace, void* stream);
-int onn_adam(float* p, float* m, float* v, float* g, float* p_tf32, int64_t n,
+int onn_adam(float* p, float* m, float* v, float* g, int64_t n,
              float lr, float beta1, float beta2, float eps, float bc1, float bc2,
              float clip_norm, const float* sqnorm, float grad_scale, int zero_grad, void* stream);
 

@@ -1,0 +1,85 @@
+/* onn_b200_host.h -- C driver ABI of libonn_b200_host.so, the C++ host mirror of OpenNN's
+ * NeuralNetwork / Transformer / CrossEntropyError3d / AdaptiveMomentEstimation interfaces
+ * (opennn_b200/host/opennn_b200.h).  It lets a C, Python (ctypes) or other FFI caller build
+ * a network and run the body of OpenNN's training loop
+ * (opennn/adaptive_moment_estimation.cpp:697-718: zero gradients, forward_propagate,
+ * Loss::back_propagate, update_parameters) on device-resident or host-resident batches.
+ *
+ * All functions return 0 on success and a negative code on failure;
+ * onn_trainer_last_error() then describes it (the C++ layer throws runtime_error exactly
+ * where OpenNN does; this ABI catches it at the boundary).
+ */
+#ifndef ONN_B200_HOST_H
+#define ONN_B200_HOST_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "onn_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct onn_trainer onn_trainer;
+
+#define ONN_NETWORK_TRANSFORMER   0   /* Transformer (opennn/standard_networks.cpp:638-907) */
+#define ONN_NETWORK_DECODER_ONLY  1   /* causal self-attention stack assembled with add_layer */
+
+const char* onn_trainer_last_error(void);
+
+/* Builds the network, its propagation structures for `micro_batch` samples, the loss
+ * (regularisation "None") and Adam (lr 1e-3, betas 0.9 / 0.999, clip norm 1, iteration 1).
+ * A step processes its batch in chunks of micro_batch samples and accumulates gradients,
+ * so device memory is sized by micro_batch, not by the batch. */
+int onn_trainer_create(onn_trainer** out, int network_kind,
+                       int64_t input_sequence_length, int64_t decoder_sequence_length,
+                       int64_t input_vocabulary_size, int64_t output_vocabulary_size,
+                       int64_t embedding_dimension, int64_t heads_number,
+                       int64_t feed_forward_dimension, int64_t layers_number, int64_t micro_batch);
+void onn_trainer_destroy(onn_trainer* trainer);
+
+int64_t onn_trainer_parameters_number(const onn_trainer* trainer);
+int onn_trainer_layers_number(const onn_trainer* trainer);
+/* name = OpenNN layer type ("Embedding", "MultiHeadAttention", "Addition3d", "Normalization3d",
+ * "Dense3d"), label = e.g. "encoder_self_attention_1"; buffers of `capacity` bytes each. */
+int onn_trainer_layer_info(const onn_trainer* trainer, int layer, char* name, char* label, int capacity,
+                           int64_t* parameters, int64_t* output_size);
+
+/* NeuralNetwork::copy_parameters_device / copy_parameters_host; the arena layout is OpenNN's. */
+int onn_trainer_set_parameters(onn_trainer* trainer, const float* host_parameters);
+int onn_trainer_get_parameters(onn_trainer* trainer, float* host_parameters);
+int onn_trainer_get_gradients(onn_trainer* trainer, float* host_gradients);
+int onn_trainer_set_learning_rate(onn_trainer* trainer, float learning_rate);
+int onn_trainer_set_iteration(onn_trainer* trainer, int64_t iteration);
+
+/* Data parallelism: every rank holds a full replica and calls step with its shard of the
+ * batch; gradients and the active-token count are summed across ranks (onn_dp_*). */
+int onn_trainer_set_dp(onn_trainer* trainer, onn_dp_comm* comm, int world);
+
+/* One optimiser step on a batch of `batch` samples (a multiple of micro_batch).
+ * ids and targets are floats holding integers, [batch, sequence]; encoder_ids is NULL for
+ * the decoder-only network.  update = 0 stops after back-propagation (gradients stay in the
+ * arena for onn_trainer_get_gradients; the next step starts by zeroing them).
+ * statistics (host, 4 floats, may be NULL) receives {error, accuracy, active tokens, gradient
+ * norm before clipping}; reading it is the step's one device-to-host synchronisation.
+ * _device: pointers are device memory.  _host: pointers are host memory (pinned for full
+ * copy speed); the host-to-device copies are part of the step. */
+int onn_trainer_step_device(onn_trainer* trainer, const float* decoder_ids, const float* encoder_ids, const float* targets,
+                            int64_t batch, int update, float* statistics);
+int onn_trainer_step_host(onn_trainer* trainer, const float* decoder_ids, const float* encoder_ids, const float* targets,
+                          int64_t batch, int update, float* statistics);
+
+/* NeuralNetwork::forward_propagate on one micro-batch of device-resident ids
+ * (is_training = 0: the output layer holds probabilities). */
+int onn_trainer_forward(onn_trainer* trainer, const float* decoder_ids, const float* encoder_ids, int is_training);
+int onn_trainer_get_layer_output(onn_trainer* trainer, int layer, float* host_output, int64_t count);
+int onn_trainer_synchronize(onn_trainer* trainer);
+/* The cudaStream_t every kernel of this trainer is launched on (for event timing by the caller). */
+void* onn_trainer_stream(onn_trainer* trainer);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ONN_B200_HOST_H */

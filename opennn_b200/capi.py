@@ -16,10 +16,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libonn_b200.so")
 
 OK = 0
-ROUND_OUTPUT_TF32 = 1
 ACCUMULATE = 2
-INPUTS_TF32_READY = 4
 DEFER_SOFTMAX = 8
+DELTA_READY = 16
 ACT_LINEAR, ACT_RELU, ACT_SOFTMAX = 0, 1, 2
 ACTIVATIONS = {"Linear": ACT_LINEAR, "RectifiedLinear": ACT_RELU, "Softmax": ACT_SOFTMAX}
 
@@ -51,9 +50,9 @@ class MhaGrads(C.Structure):
 
 EXPORTS = [
     "onn_status_string", "onn_version", "onn_gemm", "onn_gemm_set_mode", "onn_gemm_device_status",
-    "onn_launch_count", "onn_round_tf32", "onn_embedding_fwd", "onn_embedding_bwd",
+    "onn_launch_count", "onn_embedding_fwd", "onn_embedding_bwd",
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_add",
-    "onn_dense_workspace_floats", "onn_dense_fwd", "onn_dense_bwd", "onn_softmax_rows",
+    "onn_dense_fwd", "onn_dense_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
     "onn_mha_attention_weights", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
     "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam",
@@ -71,7 +70,7 @@ def lib():
         L = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
         L.onn_status_string.restype = C.c_char_p
         L.onn_launch_count.restype = C.c_uint64
-        for name in ("onn_layernorm_bwd_workspace_floats", "onn_dense_workspace_floats",
+        for name in ("onn_layernorm_bwd_workspace_floats",
                      "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats",
                      "onn_grad_sqnorm_workspace_floats"):
             getattr(L, name).restype = C.c_size_t
@@ -129,12 +128,6 @@ def gemm(A, B, Cmat, M, N, K, lda, ldb, ldc, a_major=0, b_major=1, bias=None, re
     check(lib().onn_gemm(C.byref(g), stream_ptr()), "onn_gemm")
 
 
-def round_tf32(x):
-    out = torch.empty_like(x)
-    check(lib().onn_round_tf32(ptr(x), ptr(out), i64(x.numel()), stream_ptr()), "onn_round_tf32")
-    return out
-
-
 def embedding_fwd(ids, W, PE, scale=True, add_pe=True, flags=0, want_flags=False):
     B, S = ids.shape
     V, E = W.shape
@@ -189,9 +182,8 @@ def dense_fwd(X, W, b, activation, flags=0):
     in_f, out_f = W.shape
     rows = X.numel() // in_f
     Y = torch.empty(*X.shape[:-1], out_f, device="cuda")
-    ws = _empty(lib().onn_dense_workspace_floats(i64(rows), i64(in_f), i64(out_f)))
     check(lib().onn_dense_fwd(ptr(X), ptr(W), ptr(b), ptr(Y), i64(rows), i64(in_f), i64(out_f), ACTIVATIONS[activation],
-                              ptr(ws), C.c_uint32(flags), stream_ptr()), "onn_dense_fwd")
+                              C.c_uint32(flags), stream_ptr()), "onn_dense_fwd")
     return Y
 
 
@@ -202,9 +194,8 @@ def dense_bwd(X, W, Y, dY, activation, flags=0, need_dx=True, relu_mask=None):
     dW = torch.zeros_like(W)
     db = torch.zeros(out_f, device="cuda")
     dX = torch.empty_like(X) if need_dx else None
-    ws = _empty(lib().onn_dense_workspace_floats(i64(rows), i64(in_f), i64(out_f)))
     check(lib().onn_dense_bwd(ptr(X), ptr(W), ptr(Y), ptr(dY), ptr(dW), ptr(db), ptr(dX), ptr(relu_mask), i64(rows), i64(in_f),
-                              i64(out_f), ACTIVATIONS[activation], ptr(ws), C.c_uint32(flags), stream_ptr()), "onn_dense_bwd")
+                              i64(out_f), ACTIVATIONS[activation], C.c_uint32(flags), stream_ptr()), "onn_dense_bwd")
     return dX, dW, db
 
 
@@ -283,10 +274,10 @@ def grad_sqnorm(g):
 
 
 def adam(p, m, v, g, iteration, lr=1e-3, beta1=0.9, beta2=0.999, eps=None, clip_norm=1.0, sqnorm=None,
-         p_tf32=None, grad_scale=1.0, zero_grad=False):
+         grad_scale=1.0, zero_grad=False):
     import numpy as np
     eps = float(np.finfo(np.float32).eps) if eps is None else eps
     bc1 = float(np.float32(1) - np.power(np.float32(beta1), np.float32(iteration)))
     bc2 = float(np.float32(1) - np.power(np.float32(beta2), np.float32(iteration)))
-    check(lib().onn_adam(ptr(p), ptr(m), ptr(v), ptr(g), ptr(p_tf32), i64(p.numel()), f32(lr), f32(beta1), f32(beta2), f32(eps),
+    check(lib().onn_adam(ptr(p), ptr(m), ptr(v), ptr(g), i64(p.numel()), f32(lr), f32(beta1), f32(beta2), f32(eps),
                          f32(bc1), f32(bc2), f32(clip_norm), ptr(sqnorm), f32(grad_scale), int(zero_grad), stream_ptr()), "onn_adam")

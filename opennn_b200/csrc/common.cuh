@@ -1,6 +1,5 @@
 // Shared helpers for the sm_100a kernels: status codes, launch checks, warp/block
-// reductions, 128-bit access helpers and the fp32 -> tf32 round-to-nearest used by every
-// kernel that produces a tensor-core operand.
+// reductions and 128-bit access helpers.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -27,22 +26,6 @@ inline int grid_for(long long work_items, int items_per_block, int blocks_per_sm
     if(blocks > cap) blocks = cap;
     if(blocks < 1) blocks = 1;
     return (int)blocks;
-}
-
-// Round an fp32 value to the nearest tf32-representable value (10 explicit mantissa bits),
-// ties away from zero, kept in an fp32 container.  tcgen05 kind::tf32 ignores the low 13
-// mantissa bits of its operands (truncation, a biased error); producers therefore store
-// operands already rounded so the tensor cores see an unbiased 2^-11 relative error.
-__device__ __forceinline__ float round_tf32(float x)
-{
-    uint32_t bits;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x));
-    return __uint_as_float(bits);
-}
-
-__device__ __forceinline__ float maybe_round(float x, bool round)
-{
-    return round ? round_tf32(x) : x;
 }
 
 __device__ __forceinline__ float warp_sum(float v)

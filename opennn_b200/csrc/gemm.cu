@@ -32,8 +32,8 @@ int gemm(const onn_gemm_args& g, cudaStream_t stream)
     ONN_CHECK_ARG(g.lda >= (g.a_major == 0 ? g.K : g.M));
     ONN_CHECK_ARG(g.ldb >= (g.b_major == 0 ? g.K : g.N));
     ONN_CHECK_ARG(g.ldc >= g.N);
-    // split-K partial sums are added atomically: a nonlinear epilogue or rounding cannot follow
-    ONN_CHECK_ARG(g.split_k <= 1 || (!g.relu && !g.relu_mask && !(g.flags & ONN_ROUND_OUTPUT_TF32)));
+    // split-K partial sums are added atomically: a nonlinear epilogue cannot follow
+    ONN_CHECK_ARG(g.split_k <= 1 || (!g.relu && !g.relu_mask));
 
     const int mode = g_mode.load(std::memory_order_relaxed);
     const bool tc_ok = gemm_tc_supported(g);

@@ -68,7 +68,6 @@ gemm_simt_kernel(const onn_gemm_args g, int splits, long long k_per_split)
         __syncthreads();
     }
 
-    const bool round = (g.flags & ONN_ROUND_OUTPUT_TF32) != 0;
     const bool accumulate = (g.flags & ONN_ACCUMULATE) != 0;
 #pragma unroll
     for(int i = 0; i < 4; i++)
@@ -86,7 +85,7 @@ gemm_simt_kernel(const onn_gemm_args g, int splits, long long k_per_split)
             if(mask && !(mask[m * g.ldc + n] > 0.f)) value = 0.f;
             float* dst = C + m * g.ldc + n;
             if(splits > 1) atomicAdd(dst, value);
-            else *dst = maybe_round(accumulate ? *dst + value : value, round);
+            else *dst = accumulate ? *dst + value : value;
         }
     }
 }

@@ -8,7 +8,7 @@
 //               descriptors; owns the TMEM allocation (two accumulator buffers so the
 //               epilogue of tile i overlaps the main loop of tile i+1);
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32
-//               output rows), alpha / bias / ReLU / mask / accumulate / tf32 rounding,
+//               output rows), alpha / bias / ReLU / mask / accumulate,
 //               128-bit stores (or vector fp32 reductions for split-K).
 //
 // Operand layouts (BK = 32 floats = 128 bytes = one swizzle row, UMMA K = 8):
@@ -16,8 +16,15 @@
 //            canonical K-major SWIZZLE_128B layout, 8-row groups 1024 bytes apart (SBO);
 //            the K step inside a stage advances the descriptor start address by 32 bytes.
 //   MN-major (M or N contiguous in memory): one box [32 k-rows][32 floats] per 32 columns,
-//            boxes 4096 bytes apart (LBO), 8-row k-groups 1024 bytes apart (SBO); the K
-//            step advances the start address by 1024 bytes.
+//            written with the 128-byte swizzle whose atom is 32 bytes (the only MN-major
+//            layout tf32 operands have: SWIZZLE_128B_BASE32B, pattern period 4 rows); boxes
+//            4096 bytes apart (LBO), 4-row k-groups 512 bytes apart (SBO); the K step (8
+//            rows) advances the start address by 1024 bytes.
+//
+// The tensor maps carry the TFLOAT32 data type: the TMA unit then rounds every fp32 element
+// to the nearest tf32 value (ties to even) on its way into shared memory, so the tensor
+// cores -- which ignore the low 13 mantissa bits -- see an unbiased rounding, not a
+// truncation, without any conversion pass over HBM or shared memory.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out records ONN_ERR_DEVICE_TIMEOUT
 // in a device status word, raises a CTA-wide abort flag that ends all role loops, the
@@ -54,7 +61,7 @@ struct Params
     const float* bias;
     const float* relu_mask;
     float alpha;
-    int relu, round, accumulate;
+    int relu, accumulate;
     int batch_inner, batch_outer;
     int a_batch_inner_on, a_batch_outer_on, b_batch_inner_on, b_batch_outer_on;
     int splits;
@@ -159,15 +166,16 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v)
     for(int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
 
-// Shared-memory matrix descriptor, SWIZZLE_128B, Blackwell version field = 1.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+// Shared-memory matrix descriptor, Blackwell version field = 1.
+// layout_type: 2 = SWIZZLE_128B (K-major tiles), 1 = SWIZZLE_128B_BASE32B (MN-major tf32 tiles).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
 {
     uint64_t desc = 0;
     desc |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, bits [0,14)
     desc |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;    // leading byte offset, bits [16,30)
     desc |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;    // stride byte offset, bits [32,46)
     desc |= (uint64_t)1 << 46;                              // descriptor version
-    desc |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    desc |= (uint64_t)layout_type << 61;
     return desc;
 }
 
@@ -319,8 +327,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_STAGE_BYTES;
-                    const uint64_t a_desc = A_MN ? make_smem_desc(a_addr, 4096, 1024) : make_smem_desc(a_addr, 16, 1024);
-                    const uint64_t b_desc = B_MN ? make_smem_desc(b_addr, 4096, 1024) : make_smem_desc(b_addr, 16, 1024);
+                    const uint64_t a_desc = A_MN ? make_smem_desc(a_addr, 4096, 512, 1) : make_smem_desc(a_addr, 16, 1024, 2);
+                    const uint64_t b_desc = B_MN ? make_smem_desc(b_addr, 4096, 512, 1) : make_smem_desc(b_addr, 16, 1024, 2);
 #pragma unroll
                     for(int j = 0; j < BK / UMMA_K; j++)
                     {
@@ -392,7 +400,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         else
                         {
                             if(p.accumulate) { const float4 o = ld4(c_row + n); x[0] += o.x; x[1] += o.y; x[2] += o.z; x[3] += o.w; }
-                            if(p.round) { x[0] = round_tf32(x[0]); x[1] = round_tf32(x[1]); x[2] = round_tf32(x[2]); x[3] = round_tf32(x[3]); }
                             st4(c_row + n, make_float4(x[0], x[1], x[2], x[3]));
                         }
                     }
@@ -408,7 +415,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             else
                             {
                                 if(p.accumulate) y += c_row[n + e];
-                                c_row[n + e] = p.round ? round_tf32(y) : y;
+                                c_row[n + e] = y;
                             }
                         }
                     }
@@ -459,7 +466,7 @@ static cuuint64_t stride_bytes(long long elements, long long fallback_elements)
 // 4-D map (d0 = contiguous dimension, d1 = pitched dimension, batch inner, batch outer).
 static bool make_map(CUtensorMap* map, const float* base, long long d0, long long d1, long long pitch,
                      int batch_inner, long long stride_inner, int batch_outer, long long stride_outer,
-                     int box0, int box1)
+                     int box0, int box1, bool mn_major)
 {
     EncodeTiledFn fn = encode_tiled();
     if(!fn) return false;
@@ -471,8 +478,9 @@ static bool make_map(CUtensorMap* map, const float* base, long long d0, long lon
                                     stride_bytes(outer_on ? stride_outer : 0, plane) };
     const cuuint32_t box[4] = { (cuuint32_t)box0, (cuuint32_t)box1, 1, 1 };
     const cuuint32_t elem[4] = { 1, 1, 1, 1 };
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, const_cast<float*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -529,7 +537,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.M = g.M; p.N = g.N; p.K = g.K; p.ldc = g.ldc;
     p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
     p.C = g.C; p.bias = g.bias; p.relu_mask = g.relu_mask; p.alpha = g.alpha;
-    p.relu = g.relu; p.round = (g.flags & ONN_ROUND_OUTPUT_TF32) != 0; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
+    p.relu = g.relu; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
     p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
     p.a_batch_inner_on = g.batch_inner > 1 && g.a_stride_inner != 0; p.a_batch_outer_on = g.batch_outer > 1 && g.a_stride_outer != 0;
     p.b_batch_inner_on = g.batch_inner > 1 && g.b_stride_inner != 0; p.b_batch_outer_on = g.batch_outer > 1 && g.b_stride_outer != 0;
@@ -547,10 +555,10 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
 
     CUtensorMap map_a, map_b;
     bool ok;
-    if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, BK, BM);
-    else ok = make_map(&map_a, g.A, g.M, g.K, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, 32, BK);
-    if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, BK, bn);
-    else ok = ok && make_map(&map_b, g.B, g.N, g.K, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, 32, BK);
+    if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, BK, BM, false);
+    else ok = make_map(&map_a, g.A, g.M, g.K, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, 32, BK, true);
+    if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, BK, bn, false);
+    else ok = ok && make_map(&map_b, g.B, g.N, g.K, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, 32, BK, true);
     if(!ok) return ONN_ERR_UNSUPPORTED;
 
     if(g.a_major == 0 && g.b_major == 0) return launch_majors<0, 0>(bn, map_a, map_b, p, stream);

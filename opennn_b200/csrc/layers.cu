@@ -10,10 +10,10 @@ namespace onn
 {
 
 int launch_source_row_is_zero(const float* X, uint8_t* flags, long long rows, int E, cudaStream_t s);
-int launch_attention_softmax(float* scores, const uint8_t* key_is_pad, long long B, int H, int Sq, int Sk, int causal, int round, cudaStream_t s);
-int launch_attention_softmax_bwd(const float* P, float* dP, long long rows, int Sk, int round, cudaStream_t s);
+int launch_attention_softmax(float* scores, const uint8_t* key_is_pad, long long B, int H, int Sq, int Sk, int causal, cudaStream_t s);
+int launch_attention_softmax_bwd(const float* P, float* dP, long long rows, int Sk, cudaStream_t s);
 int launch_colsum_accumulate(const float* D, long long rows, long long cols, long long ld, float* out, cudaStream_t s);
-int launch_relu_delta(float* dY, const float* Y, long long n, int round, cudaStream_t s);
+int launch_relu_delta(float* dY, const float* Y, long long n, cudaStream_t s);
 
 #define ONN_TRY(expr) do { const int status_ = (expr); if(status_ != ONN_OK) return status_; } while(0)
 
@@ -57,11 +57,6 @@ static int weight_gradients(const float* X, const float* D, float* dW, float* db
     return ONN_OK;
 }
 
-static int round_copy(const float* src, float* dst, long long n, cudaStream_t s)
-{
-    return onn_round_tf32(src, dst, n, s);
-}
-
 }  // namespace onn
 
 using namespace onn;
@@ -70,32 +65,16 @@ using namespace onn;
 // Dense<3>
 // ---------------------------------------------------------------------------------------
 
-extern "C" size_t onn_dense_workspace_floats(int64_t rows, int64_t in, int64_t out)
-{
-    if(rows <= 0 || in <= 0 || out <= 0) return 0;
-    return pad64((size_t)rows * in) + pad64((size_t)in * out) + pad64((size_t)rows * out);
-}
-
 extern "C" int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y,
                              int64_t rows, int64_t in, int64_t out, int activation,
-                             float* workspace, uint32_t flags, void* stream)
+                             uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(X && W && Y && rows > 0 && in > 0 && out > 0);
     ONN_CHECK_ARG(activation == ONN_ACT_LINEAR || activation == ONN_ACT_RELU || activation == ONN_ACT_SOFTMAX);
     cudaStream_t s = (cudaStream_t)stream;
-    if(!(flags & ONN_INPUTS_TF32_READY))
-    {
-        if(!workspace) return ONN_ERR_WORKSPACE;
-        float* x_copy = workspace;
-        float* w_copy = workspace + pad64((size_t)rows * in);
-        ONN_TRY(round_copy(X, x_copy, rows * in, s));
-        ONN_TRY(round_copy(W, w_copy, in * out, s));
-        X = x_copy; W = w_copy;
-    }
     onn_gemm_args g = plain_gemm(X, 0, in, W, 1, out, Y, out, rows, out, in);
     g.bias = b;
     g.relu = activation == ONN_ACT_RELU;
-    if(activation != ONN_ACT_SOFTMAX) g.flags = flags & ONN_ROUND_OUTPUT_TF32;
     ONN_TRY(gemm(g, s));
     if(activation == ONN_ACT_SOFTMAX && !(flags & ONN_DEFER_SOFTMAX)) ONN_TRY(onn_softmax_rows(Y, rows, out, stream));
     return ONN_OK;
@@ -104,29 +83,16 @@ extern "C" int onn_dense_fwd(const float* X, const float* W, const float* b, flo
 extern "C" int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
                              float* dW, float* db, float* dX, const float* dX_relu_mask,
                              int64_t rows, int64_t in, int64_t out, int activation,
-                             float* workspace, uint32_t flags, void* stream)
+                             uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(X && W && dY && dW && rows > 0 && in > 0 && out > 0);
     ONN_CHECK_ARG(activation == ONN_ACT_LINEAR || activation == ONN_ACT_RELU || activation == ONN_ACT_SOFTMAX);
     ONN_CHECK_ARG(activation != ONN_ACT_RELU || Y);
     cudaStream_t s = (cudaStream_t)stream;
-    const bool ready = (flags & ONN_INPUTS_TF32_READY) != 0;
 
-    // delta = dY * act'(Y); ReLU rewrites dY in place (rounded: it is a tensor-core operand next)
-    if(activation == ONN_ACT_RELU) ONN_TRY(launch_relu_delta(dY, Y, rows * out, 1, s));
+    // delta = dY * act'(Y); ReLU rewrites dY in place, as the reference does
+    if(activation == ONN_ACT_RELU && !(flags & ONN_DELTA_READY)) ONN_TRY(launch_relu_delta(dY, Y, rows * out, s));
     const float* delta = dY;
-
-    if(!ready)
-    {
-        if(!workspace) return ONN_ERR_WORKSPACE;
-        float* x_copy = workspace;
-        float* w_copy = x_copy + pad64((size_t)rows * in);
-        float* d_copy = w_copy + pad64((size_t)in * out);
-        ONN_TRY(round_copy(X, x_copy, rows * in, s));
-        ONN_TRY(round_copy(W, w_copy, in * out, s));
-        X = x_copy; W = w_copy;
-        if(activation != ONN_ACT_RELU) { ONN_TRY(round_copy(dY, d_copy, rows * out, s)); delta = d_copy; }
-    }
 
     ONN_TRY(weight_gradients(X, delta, dW, db, rows, in, out, s));
 
@@ -134,7 +100,7 @@ extern "C" int onn_dense_bwd(const float* X, const float* W, const float* Y, flo
     {
         onn_gemm_args g = plain_gemm(delta, 0, out, W, 0, out, dX, in, rows, in, out);
         g.relu_mask = dX_relu_mask;
-        g.flags = flags & (ONN_ROUND_OUTPUT_TF32 | ONN_ACCUMULATE);
+        g.flags = flags & ONN_ACCUMULATE;
         ONN_TRY(gemm(g, s));
     }
     return ONN_OK;
@@ -148,7 +114,7 @@ namespace
 {
 struct MhaForwardLayout
 {
-    size_t q, k, v, p, ctx, pad, xq, xs, wq, wk, wv, wo, total;
+    size_t q, k, v, p, ctx, pad, total;
     MhaForwardLayout(int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H)
     {
         size_t at = 0;
@@ -159,16 +125,13 @@ struct MhaForwardLayout
         p = take((size_t)B * H * Sq * Sk);
         ctx = take((size_t)B * Sq * E);
         pad = take(((size_t)B * Sk + 3) / 4);
-        xq = take((size_t)B * Sq * E);
-        xs = take((size_t)B * Sk * E);
-        wq = take((size_t)E * E); wk = take((size_t)E * E); wv = take((size_t)E * E); wo = take((size_t)E * E);
         total = at;
     }
 };
 
 struct MhaBackwardLayout
 {
-    size_t dctx, dp, dq, dk, dv, dy, total;
+    size_t dctx, dp, dq, dk, dv, total;
     MhaBackwardLayout(int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H)
     {
         size_t at = 0;
@@ -178,7 +141,6 @@ struct MhaBackwardLayout
         dq = take((size_t)B * Sq * E);
         dk = take((size_t)B * Sk * E);
         dv = take((size_t)B * Sk * E);
-        dy = take((size_t)B * Sq * E);
         total = at;
     }
 };
@@ -229,9 +191,6 @@ extern "C" int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_param
     const MhaForwardLayout L(B, Sq, Sk, E, H);
     const long long hd = E / H;
     const float scale = 1.0f / sqrtf((float)hd);
-    const bool self_attention = Xs == Xq;
-
-    // key-padding flags come from the UNROUNDED source (the reference tests |x| <= 1e-7 on it)
     const uint8_t* pad_flags = source_row_is_zero;
     if(!pad_flags)
     {
@@ -241,28 +200,19 @@ extern "C" int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_param
     }
 
     const float *Wq = params->Wq, *Wk = params->Wk, *Wv = params->Wv, *Wo = params->Wo;
-    if(!(flags & ONN_INPUTS_TF32_READY))
-    {
-        ONN_TRY(round_copy(Xq, ws + L.xq, B * Sq * E, s));
-        if(!self_attention) ONN_TRY(round_copy(Xs, ws + L.xs, B * Sk * E, s));
-        ONN_TRY(round_copy(Wq, ws + L.wq, E * E, s)); ONN_TRY(round_copy(Wk, ws + L.wk, E * E, s));
-        ONN_TRY(round_copy(Wv, ws + L.wv, E * E, s)); ONN_TRY(round_copy(Wo, ws + L.wo, E * E, s));
-        Xq = ws + L.xq; Xs = self_attention ? Xq : ws + L.xs;
-        Wq = ws + L.wq; Wk = ws + L.wk; Wv = ws + L.wv; Wo = ws + L.wo;
-    }
 
     float *q = ws + L.q, *k = ws + L.k, *v = ws + L.v, *p = ws + L.p, *ctx = ws + L.ctx;
 
     // projections, kept in [B, S, E] layout: head h is the column slice h*hd .. of each row
     {
         onn_gemm_args g = plain_gemm(Xq, 0, E, Wq, 1, E, q, E, B * Sq, E, E);
-        g.bias = params->bq; g.flags = ONN_ROUND_OUTPUT_TF32;
+        g.bias = params->bq;
         ONN_TRY(gemm(g, s));
         g = plain_gemm(Xs, 0, E, Wk, 1, E, k, E, B * Sk, E, E);
-        g.bias = params->bk; g.flags = ONN_ROUND_OUTPUT_TF32;
+        g.bias = params->bk;
         ONN_TRY(gemm(g, s));
         g = plain_gemm(Xs, 0, E, Wv, 1, E, v, E, B * Sk, E, E);
-        g.bias = params->bv; g.flags = ONN_ROUND_OUTPUT_TF32;
+        g.bias = params->bv;
         ONN_TRY(gemm(g, s));
     }
     // scores = scale * Q K^T per (b, h)
@@ -273,18 +223,18 @@ extern "C" int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_param
         g.alpha = scale;
         ONN_TRY(gemm(g, s));
     }
-    ONN_TRY(launch_attention_softmax(p, pad_flags, B, (int)H, (int)Sq, (int)Sk, causal, 1, s));
+    ONN_TRY(launch_attention_softmax(p, pad_flags, B, (int)H, (int)Sq, (int)Sk, causal, s));
     // context = P V per (b, h), written straight into the concatenated [B, Sq, E] layout
     {
         onn_gemm_args g = plain_gemm(p, 0, Sk, v, 1, E, ctx, E, Sq, hd, Sk);
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sk, E, hd); head_strides(g, 'c', Sq, E, hd);
-        g.flags = ONN_ROUND_OUTPUT_TF32;
+       
         ONN_TRY(gemm(g, s));
     }
     {
         onn_gemm_args g = plain_gemm(ctx, 0, E, Wo, 1, E, Y, E, B * Sq, E, E);
-        g.bias = params->bo; g.flags = flags & ONN_ROUND_OUTPUT_TF32;
+        g.bias = params->bo;
         ONN_TRY(gemm(g, s));
     }
     return ONN_OK;
@@ -309,14 +259,6 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
     const long long rows_q = B * Sq, rows_s = B * Sk;
 
     const float *Wq = params->Wq, *Wk = params->Wk, *Wv = params->Wv, *Wo = params->Wo;
-    if(!(flags & ONN_INPUTS_TF32_READY))
-    {
-        // the forward call left rounded copies of the inputs and weights in its workspace
-        Xq = fwd_ws + F.xq; Xs = self_attention ? Xq : fwd_ws + F.xs;
-        Wq = fwd_ws + F.wq; Wk = fwd_ws + F.wk; Wv = fwd_ws + F.wv; Wo = fwd_ws + F.wo;
-        ONN_TRY(round_copy(dY, ws + L.dy, rows_q * E, s));
-        dY = ws + L.dy;
-    }
     const float *q = fwd_ws + F.q, *k = fwd_ws + F.k, *v = fwd_ws + F.v, *p = fwd_ws + F.p, *ctx = fwd_ws + F.ctx;
     float *dctx = ws + L.dctx, *dp = ws + L.dp, *dq = ws + L.dq, *dk = ws + L.dk, *dv = ws + L.dv;
 
@@ -324,7 +266,7 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
     ONN_TRY(weight_gradients(ctx, dY, grads->dWo, grads->dbo, rows_q, E, E, s));
     {
         onn_gemm_args g = plain_gemm(dY, 0, E, Wo, 0, E, dctx, E, rows_q, E, E);
-        g.flags = ONN_ROUND_OUTPUT_TF32;
+       
         ONN_TRY(gemm(g, s));
     }
     // dV = P^T dO
@@ -332,7 +274,7 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         onn_gemm_args g = plain_gemm(p, 1, Sk, dctx, 1, E, dv, E, Sk, hd, Sq);
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sq, E, hd); head_strides(g, 'c', Sk, E, hd);
-        g.flags = ONN_ROUND_OUTPUT_TF32;
+       
         ONN_TRY(gemm(g, s));
     }
     // dP = dO V^T
@@ -343,13 +285,13 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         ONN_TRY(gemm(g, s));
     }
     // dS = P * (dP - rowsum(P * dP)), in place
-    ONN_TRY(launch_attention_softmax_bwd(p, dp, B * H * Sq, (int)Sk, 1, s));
+    ONN_TRY(launch_attention_softmax_bwd(p, dp, B * H * Sq, (int)Sk, s));
     // dQ = scale * dS K
     {
         onn_gemm_args g = plain_gemm(dp, 0, Sk, k, 1, E, dq, E, Sq, hd, Sk);
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sk, E, hd); head_strides(g, 'c', Sq, E, hd);
-        g.alpha = scale; g.flags = ONN_ROUND_OUTPUT_TF32;
+        g.alpha = scale;
         ONN_TRY(gemm(g, s));
     }
     // dK = scale * dS^T Q
@@ -357,7 +299,7 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         onn_gemm_args g = plain_gemm(dp, 1, Sk, q, 1, E, dk, E, Sk, hd, Sq);
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sq, E, hd); head_strides(g, 'c', Sk, E, hd);
-        g.alpha = scale; g.flags = ONN_ROUND_OUTPUT_TF32;
+        g.alpha = scale;
         ONN_TRY(gemm(g, s));
     }
     // input projections
@@ -365,10 +307,8 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
     ONN_TRY(weight_gradients(Xs, dk, grads->dWk, grads->dbk, rows_s, E, E, s));
     ONN_TRY(weight_gradients(Xs, dv, grads->dWv, grads->dbv, rows_s, E, E, s));
 
-    const uint32_t round_out = flags & ONN_ROUND_OUTPUT_TF32;
     {
         onn_gemm_args g = plain_gemm(dq, 0, E, Wq, 0, E, dXq, E, rows_q, E, E);
-        if(!self_attention) g.flags = round_out;
         ONN_TRY(gemm(g, s));
     }
     float* source_grad = self_attention ? dXq : dXs;
@@ -377,7 +317,7 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         if(self_attention || (flags & ONN_ACCUMULATE)) g.flags = ONN_ACCUMULATE;
         ONN_TRY(gemm(g, s));
         g = plain_gemm(dv, 0, E, Wv, 0, E, source_grad, E, rows_s, E, E);
-        g.flags = ONN_ACCUMULATE | round_out;
+        g.flags = ONN_ACCUMULATE;
         ONN_TRY(gemm(g, s));
     }
     return ONN_OK;

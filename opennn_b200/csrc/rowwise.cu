@@ -1,5 +1,5 @@
 // HBM-bound row kernels: Embedding forward/backward, Normalization3d (+ fused Addition)
-// forward/backward, Addition, tf32 rounding.  One warp owns one [E]-row; the row lives in
+// forward/backward, Addition.  One warp owns one [E]-row; the row lives in
 // registers, reductions are warp shuffles, global access is 128-bit where E % 4 == 0.
 #include "common.cuh"
 #include "launch_counter.h"
@@ -20,7 +20,7 @@ constexpr int kMaxVec = 8;                        // float4 per lane kept in reg
 __global__ void __launch_bounds__(kRowThreads)
 embedding_fwd_kernel(const float* __restrict__ ids, const float* __restrict__ W, const float* __restrict__ PE,
                      float* __restrict__ out, uint8_t* __restrict__ row_is_zero,
-                     long long tokens, int S, int E, long long V, float scale_value, int scale, int add_pe, int round)
+                     long long tokens, int S, int E, long long V, float scale_value, int scale, int add_pe)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
@@ -53,7 +53,6 @@ embedding_fwd_kernel(const float* __restrict__ ids, const float* __restrict__ W,
                     w.x = __fadd_rn(w.x, p.x); w.y = __fadd_rn(w.y, p.y);
                     w.z = __fadd_rn(w.z, p.z); w.w = __fadd_rn(w.w, p.w);
                 }
-                if(round) { w.x = round_tf32(w.x); w.y = round_tf32(w.y); w.z = round_tf32(w.z); w.w = round_tf32(w.w); }
                 all_zero = all_zero && fabsf(w.x) <= 1e-7f && fabsf(w.y) <= 1e-7f && fabsf(w.z) <= 1e-7f && fabsf(w.w) <= 1e-7f;
                 st4(out_row + e, w);
             }
@@ -65,7 +64,6 @@ embedding_fwd_kernel(const float* __restrict__ ids, const float* __restrict__ W,
                 float w = in_range ? w_row[e] : 0.f;
                 if(scale) w = __fmul_rn(w, scale_value);
                 if(with_pe) w = __fadd_rn(w, pe_row[e]);
-                if(round) w = round_tf32(w);
                 all_zero = all_zero && fabsf(w) <= 1e-7f;
                 out_row[e] = w;
             }
@@ -134,7 +132,7 @@ layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
                      const float* __restrict__ gamma, const float* __restrict__ beta,
                      float* __restrict__ Y, float* __restrict__ sum_out,
                      float* __restrict__ mean_out, float* __restrict__ inv_std_out, uint8_t* __restrict__ row_is_zero,
-                     long long rows, int E, float eps, int round)
+                     long long rows, int E, float eps)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
@@ -190,10 +188,10 @@ layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
             if(e < E)
             {
                 float4 y;
-                y.x = maybe_round(x[i].x * inv_std * g[i].x + b[i].x, round);
-                y.y = maybe_round(x[i].y * inv_std * g[i].y + b[i].y, round);
-                y.z = maybe_round(x[i].z * inv_std * g[i].z + b[i].z, round);
-                y.w = maybe_round(x[i].w * inv_std * g[i].w + b[i].w, round);
+                y.x = (x[i].x * inv_std * g[i].x + b[i].x);
+                y.y = (x[i].y * inv_std * g[i].y + b[i].y);
+                y.z = (x[i].z * inv_std * g[i].z + b[i].z);
+                y.w = (x[i].w * inv_std * g[i].w + b[i].w);
                 all_zero = all_zero && fabsf(y.x) <= 1e-7f && fabsf(y.y) <= 1e-7f && fabsf(y.z) <= 1e-7f && fabsf(y.w) <= 1e-7f;
                 st4(Y + row * (long long)E + e, y);
             }
@@ -213,7 +211,7 @@ layernorm_fwd_generic_kernel(const float* __restrict__ A, const float* __restric
                              const float* __restrict__ gamma, const float* __restrict__ beta,
                              float* __restrict__ Y, float* __restrict__ sum_out,
                              float* __restrict__ mean_out, float* __restrict__ inv_std_out, uint8_t* __restrict__ row_is_zero,
-                             long long rows, int E, float eps, int round)
+                             long long rows, int E, float eps)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
@@ -239,7 +237,7 @@ layernorm_fwd_generic_kernel(const float* __restrict__ A, const float* __restric
         {
             const float x = a_row[e] + (r_row ? r_row[e] : 0.f);
             if(sum_out) sum_out[row * (long long)E + e] = x;
-            const float y = maybe_round((x - mean) * inv_std * gamma[e] + beta[e], round);
+            const float y = ((x - mean) * inv_std * gamma[e] + beta[e]);
             all_zero = all_zero && fabsf(y) <= 1e-7f;
             Y[row * (long long)E + e] = y;
         }
@@ -261,7 +259,7 @@ __global__ void __launch_bounds__(kRowThreads)
 layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2, const float* __restrict__ dY3,
                      const float* __restrict__ X, const float* __restrict__ mean_in, const float* __restrict__ inv_std_in,
                      const float* __restrict__ gamma, float* __restrict__ dX, float* __restrict__ partials,
-                     long long rows, int E, int round)
+                     long long rows, int E)
 {
     extern __shared__ float smem[];               // [kRowWarps][2][E]
     const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
@@ -316,10 +314,10 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
             if(e < E)
             {
                 float4 o;
-                o.x = maybe_round((d[i].x - sum_d - xh[i].x * sum_dx) * inv_std, round);
-                o.y = maybe_round((d[i].y - sum_d - xh[i].y * sum_dx) * inv_std, round);
-                o.z = maybe_round((d[i].z - sum_d - xh[i].z * sum_dx) * inv_std, round);
-                o.w = maybe_round((d[i].w - sum_d - xh[i].w * sum_dx) * inv_std, round);
+                o.x = ((d[i].x - sum_d - xh[i].x * sum_dx) * inv_std);
+                o.y = ((d[i].y - sum_d - xh[i].y * sum_dx) * inv_std);
+                o.z = ((d[i].z - sum_d - xh[i].z * sum_dx) * inv_std);
+                o.w = ((d[i].w - sum_d - xh[i].w * sum_dx) * inv_std);
                 st4(dX + base + e, o);
             }
         }
@@ -348,7 +346,7 @@ __global__ void __launch_bounds__(kRowThreads)
 layernorm_bwd_generic_kernel(const float* __restrict__ dY, const float* __restrict__ dY2, const float* __restrict__ dY3,
                              const float* __restrict__ X, const float* __restrict__ mean_in, const float* __restrict__ inv_std_in,
                              const float* __restrict__ gamma, float* __restrict__ dX, float* __restrict__ partials,
-                             long long rows, int E, int round)
+                             long long rows, int E)
 {
     extern __shared__ float smem[];               // [2][E]
     const int lane = threadIdx.x & 31;
@@ -379,7 +377,7 @@ layernorm_bwd_generic_kernel(const float* __restrict__ dY, const float* __restri
         {
             const float dy = dY[base + e] + (dY2 ? dY2[base + e] : 0.f) + (dY3 ? dY3[base + e] : 0.f);
             const float xh = (X[base + e] - mean) * inv_std;
-            dX[base + e] = maybe_round((dy * gamma[e] - sum_d - xh * sum_dx) * inv_std, round);
+            dX[base + e] = ((dy * gamma[e] - sum_d - xh * sum_dx) * inv_std);
         }
     }
     __syncthreads();
@@ -404,7 +402,7 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partials, int c
 // ---------------------------------------------------------------------------------------
 
 __global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
-                           long long n, int round)
+                           long long n)
 {
     const long long stride = (long long)gridDim.x * blockDim.x;
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -413,24 +411,9 @@ __global__ void add_kernel(const float* __restrict__ a, const float* __restrict_
     {
         const float4 x = ld4_stream(a + 4 * i), y = ld4_stream(b + 4 * i);
         float4 r = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
-        if(round) { r.x = round_tf32(r.x); r.y = round_tf32(r.y); r.z = round_tf32(r.z); r.w = round_tf32(r.w); }
         st4(out + 4 * i, r);
     }
-    for(long long i = 4 * n4 + tid; i < n; i += stride) out[i] = maybe_round(a[i] + b[i], round);
-}
-
-__global__ void round_tf32_kernel(const float* __restrict__ src, float* __restrict__ dst, long long n)
-{
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long n4 = (aligned16(src) && aligned16(dst)) ? n / 4 : 0;
-    for(long long i = tid; i < n4; i += stride)
-    {
-        float4 x = ld4(src + 4 * i);
-        x.x = round_tf32(x.x); x.y = round_tf32(x.y); x.z = round_tf32(x.z); x.w = round_tf32(x.w);
-        st4(dst + 4 * i, x);
-    }
-    for(long long i = 4 * n4 + tid; i < n; i += stride) dst[i] = round_tf32(src[i]);
+    for(long long i = 4 * n4 + tid; i < n; i += stride) out[i] = (a[i] + b[i]);
 }
 
 static int vec_count(long long E) { return (int)((E + 127) / 128); }
@@ -448,8 +431,7 @@ extern "C" int onn_embedding_fwd(const float* ids, const float* W, const float* 
     const long long tokens = B * S;
     const int grid = grid_for(tokens, kRowWarps, 8);
     embedding_fwd_kernel<<<grid, kRowThreads, 0, (cudaStream_t)stream>>>(
-        ids, W, PE, out, row_is_zero, tokens, (int)S, (int)E, V, sqrtf((float)E), scale, add_pe,
-        (flags & ONN_ROUND_OUTPUT_TF32) != 0);
+        ids, W, PE, out, row_is_zero, tokens, (int)S, (int)E, V, sqrtf((float)E), scale, add_pe);
     count_launch();
     return launch_status();
 }
@@ -472,12 +454,11 @@ extern "C" int onn_layernorm_fwd(const float* A, const float* R, const float* ga
                                  int64_t rows, int64_t E, float eps, uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(A && gamma && beta && Y && mean && inv_std && rows > 0 && E > 0);
-    const int round = (flags & ONN_ROUND_OUTPUT_TF32) != 0;
     const int grid = grid_for(rows, kRowWarps, 8);
     cudaStream_t s = (cudaStream_t)stream;
     const bool fast = (E & 3) == 0 && E <= 128 * kMaxVec && host_aligned16(A) && host_aligned16(Y) &&
                       host_aligned16(gamma) && host_aligned16(beta) && (!R || host_aligned16(R)) && (!sum || host_aligned16(sum));
-#define ONN_LN_FWD(V) layernorm_fwd_kernel<V><<<grid, kRowThreads, 0, s>>>(A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, rows, (int)E, eps, round)
+#define ONN_LN_FWD(V) layernorm_fwd_kernel<V><<<grid, kRowThreads, 0, s>>>(A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, rows, (int)E, eps)
     if(fast)
     {
         switch(vec_count(E))
@@ -489,7 +470,7 @@ extern "C" int onn_layernorm_fwd(const float* A, const float* R, const float* ga
         }
     }
     else
-        layernorm_fwd_generic_kernel<<<grid, kRowThreads, 0, s>>>(A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, rows, (int)E, eps, round);
+        layernorm_fwd_generic_kernel<<<grid, kRowThreads, 0, s>>>(A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, rows, (int)E, eps);
 #undef ONN_LN_FWD
     count_launch();
     return launch_status();
@@ -513,11 +494,10 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
                          float* dX, float* dgamma, float* dbeta, int64_t rows, int64_t E,
                          float* partials, uint32_t flags, cudaStream_t s)
 {
-    const int round = (flags & ONN_ROUND_OUTPUT_TF32) != 0;
     const int grid = layernorm_bwd_grid(rows);
     const bool fast = (E & 3) == 0 && E <= 128 * kMaxVec && host_aligned16(dY) && host_aligned16(X) && host_aligned16(dX) &&
                       host_aligned16(gamma) && (!dY2 || host_aligned16(dY2)) && (!dY3 || host_aligned16(dY3));
-#define ONN_LN_BWD(V) layernorm_bwd_kernel<V><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E, round)
+#define ONN_LN_BWD(V) layernorm_bwd_kernel<V><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E)
     if(fast)
     {
         const size_t smem = (size_t)kRowWarps * 2 * E * sizeof(float);   // <= 64 KiB at E = 1024
@@ -541,7 +521,7 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
             if(smem > 200 * 1024) return ONN_ERR_UNSUPPORTED;
             cudaFuncSetAttribute(layernorm_bwd_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         }
-        layernorm_bwd_generic_kernel<<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E, round);
+        layernorm_bwd_generic_kernel<<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E);
     }
 #undef ONN_LN_BWD
     count_launch();
@@ -569,16 +549,8 @@ extern "C" int onn_add(const float* a, const float* b, float* out, int64_t n, ui
 {
     ONN_CHECK_ARG(a && b && out && n > 0);
     const int grid = grid_for((n + 3) / 4, 256, 8);
-    add_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, (flags & ONN_ROUND_OUTPUT_TF32) != 0);
+    add_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a, b, out, n);
     count_launch();
     return launch_status();
 }
 
-extern "C" int onn_round_tf32(const float* src, float* dst, int64_t n, void* stream)
-{
-    ONN_CHECK_ARG(src && dst && n > 0);
-    const int grid = grid_for((n + 3) / 4, 256, 8);
-    round_tf32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(src, dst, n);
-    count_launch();
-    return launch_status();
-}

@@ -33,7 +33,7 @@ source_row_is_zero_kernel(const float* __restrict__ X, uint8_t* __restrict__ fla
 template <int PER_LANE>   // Sk <= 32 * PER_LANE, row in registers
 __global__ void __launch_bounds__(256)
 attention_softmax_kernel(float* __restrict__ scores, const uint8_t* __restrict__ key_is_pad,
-                         long long rows, int H, int Sq, int Sk, int causal, int round)
+                         long long rows, int H, int Sq, int Sk, int causal)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -74,7 +74,7 @@ attention_softmax_kernel(float* __restrict__ scores, const uint8_t* __restrict__
         for(int i = 0; i < PER_LANE; i++)
         {
             const int k = i * 32 + lane;
-            if(k < Sk) p[k] = maybe_round(v[i] * inv, round);
+            if(k < Sk) p[k] = (v[i] * inv);
         }
     }
 }
@@ -82,7 +82,7 @@ attention_softmax_kernel(float* __restrict__ scores, const uint8_t* __restrict__
 // Any Sk: three sweeps through global memory (the row stays in L1/L2).
 __global__ void __launch_bounds__(256)
 attention_softmax_generic_kernel(float* __restrict__ scores, const uint8_t* __restrict__ key_is_pad,
-                                 long long rows, int H, int Sq, int Sk, int causal, int round)
+                                 long long rows, int H, int Sq, int Sk, int causal)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -107,14 +107,14 @@ attention_softmax_generic_kernel(float* __restrict__ scores, const uint8_t* __re
         for(int k = lane; k < Sk; k += 32) { const float e = __expf(p[k] - row_max); p[k] = e; total += e; }
         total = warp_sum(total);
         const float inv = total > 0.f ? 1.0f / total : 0.f;
-        for(int k = lane; k < Sk; k += 32) p[k] = maybe_round(p[k] * inv, round);
+        for(int k = lane; k < Sk; k += 32) p[k] = (p[k] * inv);
     }
 }
 
 // dS = P * (dP - rowsum(P * dP)), in place over dP.
 template <int PER_LANE>
 __global__ void __launch_bounds__(256)
-attention_softmax_bwd_kernel(const float* __restrict__ P, float* __restrict__ dP, long long rows, int Sk, int round)
+attention_softmax_bwd_kernel(const float* __restrict__ P, float* __restrict__ dP, long long rows, int Sk)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -138,13 +138,13 @@ attention_softmax_bwd_kernel(const float* __restrict__ P, float* __restrict__ dP
         for(int i = 0; i < PER_LANE; i++)
         {
             const int k = i * 32 + lane;
-            if(k < Sk) d[k] = maybe_round(pv[i] * (dv[i] - dot), round);
+            if(k < Sk) d[k] = (pv[i] * (dv[i] - dot));
         }
     }
 }
 
 __global__ void __launch_bounds__(256)
-attention_softmax_bwd_generic_kernel(const float* __restrict__ P, float* __restrict__ dP, long long rows, int Sk, int round)
+attention_softmax_bwd_generic_kernel(const float* __restrict__ P, float* __restrict__ dP, long long rows, int Sk)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -156,7 +156,7 @@ attention_softmax_bwd_generic_kernel(const float* __restrict__ P, float* __restr
         float dot = 0.f;
         for(int k = lane; k < Sk; k += 32) dot += p[k] * d[k];
         dot = warp_sum(dot);
-        for(int k = lane; k < Sk; k += 32) d[k] = maybe_round(p[k] * (d[k] - dot), round);
+        for(int k = lane; k < Sk; k += 32) d[k] = (p[k] * (d[k] - dot));
     }
 }
 
@@ -265,7 +265,7 @@ __global__ void count_active_kernel(const float* __restrict__ targets, long long
 __global__ void __launch_bounds__(kLossThreads)
 ce3d_fwd_bwd_kernel(float* __restrict__ logits, const float* __restrict__ targets, const float* __restrict__ active_count,
                     float* __restrict__ probabilities_out, float* __restrict__ row_scratch,
-                    long long rows, int V, int inputs_are_probabilities, int round)
+                    long long rows, int V, int inputs_are_probabilities)
 {
     __shared__ float scratch_f[16];
     __shared__ int scratch_i[8];
@@ -312,7 +312,7 @@ ce3d_fwd_bwd_kernel(float* __restrict__ logits, const float* __restrict__ target
     {                                                                                    \
         const float p = inputs_are_probabilities ? (x) : __expf((x) - shift) * inv;      \
         const float g = active ? (p - ((index) == t ? 1.0f : 0.0f)) * scale : 0.0f;      \
-        pr = p; (x) = maybe_round(g, round);                                             \
+        pr = p; (x) = (g);                                             \
     }
     if(vec)
         for(int i = threadIdx.x * 4; i < V; i += kLossThreads * 4)
@@ -386,7 +386,7 @@ colsum_accumulate_kernel(const float* __restrict__ D, long long rows, long long 
 }
 
 // delta = dY * (Y > 0), in place over dY.
-__global__ void relu_delta_kernel(float* __restrict__ dY, const float* __restrict__ Y, long long n, int round)
+__global__ void relu_delta_kernel(float* __restrict__ dY, const float* __restrict__ Y, long long n)
 {
     const long long stride = (long long)gridDim.x * blockDim.x;
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -395,11 +395,11 @@ __global__ void relu_delta_kernel(float* __restrict__ dY, const float* __restric
     {
         float4 d = ld4(dY + 4 * i);
         const float4 y = ld4_stream(Y + 4 * i);
-        d.x = y.x > 0.f ? maybe_round(d.x, round) : 0.f; d.y = y.y > 0.f ? maybe_round(d.y, round) : 0.f;
-        d.z = y.z > 0.f ? maybe_round(d.z, round) : 0.f; d.w = y.w > 0.f ? maybe_round(d.w, round) : 0.f;
+        d.x = y.x > 0.f ? (d.x) : 0.f; d.y = y.y > 0.f ? (d.y) : 0.f;
+        d.z = y.z > 0.f ? (d.z) : 0.f; d.w = y.w > 0.f ? (d.w) : 0.f;
         st4(dY + 4 * i, d);
     }
-    for(long long i = 4 * n4 + tid; i < n; i += stride) dY[i] = Y[i] > 0.f ? maybe_round(dY[i], round) : 0.f;
+    for(long long i = 4 * n4 + tid; i < n; i += stride) dY[i] = Y[i] > 0.f ? (dY[i]) : 0.f;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -445,7 +445,7 @@ __global__ void sqnorm_finish_kernel(const float* __restrict__ partials, int cou
 
 __global__ void __launch_bounds__(256)
 adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ g,
-            float* __restrict__ p_tf32, long long n, float lr, float beta1, float beta2, float eps,
+            long long n, float lr, float beta1, float beta2, float eps,
             float bc1, float bc2, float clip_norm, const float* __restrict__ sqnorm, float grad_scale, int zero_grad)
 {
     float scale = grad_scale;
@@ -457,7 +457,7 @@ adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
     const float one_minus_b1 = 1.0f - beta1, one_minus_b2 = 1.0f - beta2;
     const long long stride = (long long)gridDim.x * blockDim.x;
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool vec = aligned16(p) && aligned16(m) && aligned16(v) && aligned16(g) && (!p_tf32 || aligned16(p_tf32));
+    const bool vec = aligned16(p) && aligned16(m) && aligned16(v) && aligned16(g);
     const long long n4 = vec ? n / 4 : 0;
 
 #define ONN_ADAM_ELEMENT(pp, mm, vv, gg)                                   \
@@ -476,7 +476,6 @@ adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
         ONN_ADAM_ELEMENT(pp.z, mm.z, vv.z, gg.z)
         ONN_ADAM_ELEMENT(pp.w, mm.w, vv.w, gg.w)
         st4(p + 4 * i, pp); st4(m + 4 * i, mm); st4(v + 4 * i, vv);
-        if(p_tf32) st4(p_tf32 + 4 * i, make_float4(round_tf32(pp.x), round_tf32(pp.y), round_tf32(pp.z), round_tf32(pp.w)));
         if(zero_grad) st4(g + 4 * i, make_float4(0.f, 0.f, 0.f, 0.f));
     }
     for(long long i = 4 * n4 + tid; i < n; i += stride)
@@ -484,7 +483,6 @@ adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
         float pp = p[i], mm = m[i], vv = v[i];
         ONN_ADAM_ELEMENT(pp, mm, vv, g[i])
         p[i] = pp; m[i] = mm; v[i] = vv;
-        if(p_tf32) p_tf32[i] = round_tf32(pp);
         if(zero_grad) g[i] = 0.f;
     }
 #undef ONN_ADAM_ELEMENT
@@ -502,33 +500,33 @@ int launch_source_row_is_zero(const float* X, uint8_t* flags, long long rows, in
 }
 
 int launch_attention_softmax(float* scores, const uint8_t* key_is_pad, long long B, int H, int Sq, int Sk,
-                             int causal, int round, cudaStream_t s)
+                             int causal, cudaStream_t s)
 {
     const long long rows = B * H * Sq;
     const int grid = grid_for(rows, 8, 8);
-#define ONN_SM(N) attention_softmax_kernel<N><<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal, round)
+#define ONN_SM(N) attention_softmax_kernel<N><<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal)
     if(Sk <= 32) ONN_SM(1);
     else if(Sk <= 64) ONN_SM(2);
     else if(Sk <= 128) ONN_SM(4);
     else if(Sk <= 256) ONN_SM(8);
     else if(Sk <= 512) ONN_SM(16);
     else if(Sk <= 1024) ONN_SM(32);
-    else attention_softmax_generic_kernel<<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal, round);
+    else attention_softmax_generic_kernel<<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal);
 #undef ONN_SM
     count_launch();
     return launch_status();
 }
 
-int launch_attention_softmax_bwd(const float* P, float* dP, long long rows, int Sk, int round, cudaStream_t s)
+int launch_attention_softmax_bwd(const float* P, float* dP, long long rows, int Sk, cudaStream_t s)
 {
     const int grid = grid_for(rows, 8, 8);
-#define ONN_SB(N) attention_softmax_bwd_kernel<N><<<grid, 256, 0, s>>>(P, dP, rows, Sk, round)
+#define ONN_SB(N) attention_softmax_bwd_kernel<N><<<grid, 256, 0, s>>>(P, dP, rows, Sk)
     if(Sk <= 32) ONN_SB(1);
     else if(Sk <= 64) ONN_SB(2);
     else if(Sk <= 128) ONN_SB(4);
     else if(Sk <= 256) ONN_SB(8);
     else if(Sk <= 512) ONN_SB(16);
-    else attention_softmax_bwd_generic_kernel<<<grid, 256, 0, s>>>(P, dP, rows, Sk, round);
+    else attention_softmax_bwd_generic_kernel<<<grid, 256, 0, s>>>(P, dP, rows, Sk);
 #undef ONN_SB
     count_launch();
     return launch_status();
@@ -547,9 +545,9 @@ int launch_colsum_accumulate(const float* D, long long rows, long long cols, lon
     return launch_status();
 }
 
-int launch_relu_delta(float* dY, const float* Y, long long n, int round, cudaStream_t s)
+int launch_relu_delta(float* dY, const float* Y, long long n, cudaStream_t s)
 {
-    relu_delta_kernel<<<grid_for((n + 3) / 4, 256, 8), 256, 0, s>>>(dY, Y, n, round);
+    relu_delta_kernel<<<grid_for((n + 3) / 4, 256, 8), 256, 0, s>>>(dY, Y, n);
     count_launch();
     return launch_status();
 }
@@ -582,8 +580,7 @@ extern "C" int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float
     ONN_CHECK_ARG(rows > 0 && V > 1 && rows < (1LL << 31) && V < (1LL << 31));
     cudaStream_t s = (cudaStream_t)stream;
     ce3d_fwd_bwd_kernel<<<(unsigned)rows, kLossThreads, 0, s>>>(logits, targets, active_count, probabilities_out, row_scratch,
-                                                                 rows, (int)V, inputs_are_probabilities,
-                                                                 (flags & ONN_ROUND_OUTPUT_TF32) != 0);
+                                                                 rows, (int)V, inputs_are_probabilities);
     count_launch();
     if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
     ce3d_finish_kernel<<<1, 1024, 0, s>>>(row_scratch, targets, rows, V, stats);
@@ -610,13 +607,13 @@ extern "C" int onn_grad_sqnorm(const float* g, int64_t n, float* sqnorm, float* 
     return launch_status();
 }
 
-extern "C" int onn_adam(float* p, float* m, float* v, float* g, float* p_tf32, int64_t n,
+extern "C" int onn_adam(float* p, float* m, float* v, float* g, int64_t n,
                         float lr, float beta1, float beta2, float eps, float bc1, float bc2,
                         float clip_norm, const float* sqnorm, float grad_scale, int zero_grad, void* stream)
 {
     ONN_CHECK_ARG(p && m && v && g && n > 0 && bc1 != 0.f && bc2 != 0.f);
     const int grid = grid_for((n + 3) / 4, 256, 8);
-    adam_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p, m, v, g, p_tf32, n, lr, beta1, beta2, eps,
+    adam_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p, m, v, g, n, lr, beta1, beta2, eps,
                                                         bc1, bc2, clip_norm, sqnorm, grad_scale, zero_grad);
     count_launch();
     return launch_status();

@@ -1,0 +1,330 @@
+// C driver ABI over the host mirror (include/onn_b200_host.h): builds a network with its
+// loss and optimiser and runs the body of OpenNN's training loop
+// (opennn/adaptive_moment_estimation.cpp:697-718) one optimiser step at a time, in
+// micro-batches, optionally data-parallel with bucketed gradient all-reduces that overlap
+// the rest of back-propagation.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "../../include/onn_b200_host.h"
+#include "opennn_b200.h"
+
+using namespace opennn_b200;
+
+static thread_local string g_last_error;
+
+struct onn_trainer
+{
+    unique_ptr<NeuralNetwork> network;
+    unique_ptr<CrossEntropyError3d> loss;
+    unique_ptr<AdaptiveMomentEstimation> adam;
+    unique_ptr<ForwardPropagationCuda> forward;
+    unique_ptr<BackPropagationCuda> back;
+    unique_ptr<ADAMOptimizationDataCuda> optimization;
+
+    bool decoder_only = false;
+    Index micro_batch = 0, input_sequence_length = 0, decoder_sequence_length = 0, vocabulary_size = 0;
+    cudaStream_t stream = nullptr;
+    bool gradients_dirty = false;
+
+    onn_dp_comm* comm = nullptr;
+    int world = 1;
+    vector<Index> layer_offsets;          // start of each layer's slice in the gradient arena
+    Index pending_high = 0;               // end of the slice not yet handed to the all-reduce
+    Index bucket_floats = 16 << 20;       // 64 MiB buckets: large enough for NVLink bandwidth, small enough to overlap
+
+    TensorCuda staged_decoder, staged_encoder, staged_targets;
+    type* pinned_scalars = nullptr;       // {square norm, global active tokens}
+
+    ~onn_trainer()
+    {
+        if(pinned_scalars) cudaFreeHost(pinned_scalars);
+        if(stream) cudaStreamDestroy(stream);
+    }
+};
+
+template <typename F>
+static int guarded(F&& body)
+{
+    try { body(); return ONN_OK; }
+    catch(const std::exception& e) { g_last_error = e.what(); return ONN_ERR_CUDA; }
+    catch(...) { g_last_error = "unknown exception"; return ONN_ERR_CUDA; }
+}
+
+extern "C" const char* onn_trainer_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
+                                  int64_t input_sequence_length, int64_t decoder_sequence_length,
+                                  int64_t input_vocabulary_size, int64_t output_vocabulary_size,
+                                  int64_t embedding_dimension, int64_t heads_number,
+                                  int64_t feed_forward_dimension, int64_t layers_number, int64_t micro_batch)
+{
+    if(!out || micro_batch <= 0) { g_last_error = "onn_trainer_create: bad arguments"; return ONN_ERR_INVALID_ARGUMENT; }
+    *out = nullptr;
+    return guarded([&]
+    {
+        int devices = 0;
+        if(cudaGetDeviceCount(&devices) != cudaSuccess || devices == 0)
+            throw std::runtime_error("no CUDA device: this library has no CPU path");
+        auto t = std::make_unique<onn_trainer>();
+        check_cuda(cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking), "stream");
+        Device::instance().set_compute_stream(t->stream);
+        t->decoder_only = network_kind == ONN_NETWORK_DECODER_ONLY;
+        t->micro_batch = micro_batch;
+        t->input_sequence_length = input_sequence_length;
+        t->decoder_sequence_length = decoder_sequence_length;
+        t->vocabulary_size = output_vocabulary_size;
+        if(t->decoder_only)
+            t->network = make_decoder_only_network(decoder_sequence_length, output_vocabulary_size, embedding_dimension, heads_number,
+                                                   feed_forward_dimension, layers_number);
+        else
+            t->network = std::make_unique<Transformer>(input_sequence_length, decoder_sequence_length, input_vocabulary_size,
+                                                       output_vocabulary_size, embedding_dimension, heads_number,
+                                                       feed_forward_dimension, layers_number);
+        t->loss = std::make_unique<CrossEntropyError3d>(t->network.get());
+        t->loss->set_regularization_method("None");
+        t->adam = std::make_unique<AdaptiveMomentEstimation>(t->loss.get());
+        t->forward = std::make_unique<ForwardPropagationCuda>(micro_batch, t->network.get());
+        t->back = std::make_unique<BackPropagationCuda>(micro_batch, t->loss.get(), t->forward.get());
+        t->optimization = std::make_unique<ADAMOptimizationDataCuda>(t->adam.get());
+        check_cuda(cudaMallocHost(reinterpret_cast<void**>(&t->pinned_scalars), 8 * sizeof(type)), "pinned scalars");
+
+        Index offset = 0;
+        for(const unique_ptr<Layer>& layer : t->network->get_layers())
+        {
+            t->layer_offsets.push_back(offset);
+            offset += layer->get_parameters_number();
+        }
+        *out = t.release();
+    });
+}
+
+extern "C" void onn_trainer_destroy(onn_trainer* trainer) { delete trainer; }
+
+extern "C" int64_t onn_trainer_parameters_number(const onn_trainer* t) { return t ? t->network->get_parameters_number() : 0; }
+extern "C" int onn_trainer_layers_number(const onn_trainer* t) { return t ? int(t->network->get_layers_number()) : 0; }
+
+extern "C" int onn_trainer_layer_info(const onn_trainer* t, int layer, char* name, char* label, int capacity,
+                                      int64_t* parameters, int64_t* output_size)
+{
+    if(!t || layer < 0 || layer >= int(t->network->get_layers_number())) return ONN_ERR_INVALID_ARGUMENT;
+    Layer* l = t->network->get_layers()[size_t(layer)].get();
+    if(name && capacity > 0) { std::strncpy(name, l->get_name().c_str(), size_t(capacity) - 1); name[capacity - 1] = 0; }
+    if(label && capacity > 0) { std::strncpy(label, l->get_label().c_str(), size_t(capacity) - 1); label[capacity - 1] = 0; }
+    if(parameters) *parameters = l->get_parameters_number();
+    if(output_size) *output_size = t->forward->layers[size_t(layer)]->outputs.size();
+    return ONN_OK;
+}
+
+extern "C" int onn_trainer_set_parameters(onn_trainer* t, const float* host_parameters)
+{
+    if(!t || !host_parameters) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        vector<type>& parameters = t->network->get_parameters();
+        std::memcpy(parameters.data(), host_parameters, parameters.size() * sizeof(type));
+        t->network->copy_parameters_device();
+    });
+}
+
+extern "C" int onn_trainer_get_parameters(onn_trainer* t, float* host_parameters)
+{
+    if(!t || !host_parameters) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        check_cuda(cudaStreamSynchronize(t->stream), "synchronize");
+        t->network->copy_parameters_host();
+        const vector<type>& parameters = t->network->get_parameters();
+        std::memcpy(host_parameters, parameters.data(), parameters.size() * sizeof(type));
+    });
+}
+
+extern "C" int onn_trainer_get_gradients(onn_trainer* t, float* host_gradients)
+{
+    if(!t || !host_gradients) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        check_cuda(cudaStreamSynchronize(t->stream), "synchronize");
+        TensorCuda& gradients = t->back->neural_network.gradients;
+        check_cuda(cudaMemcpy(host_gradients, gradients.data, size_t(gradients.size()) * sizeof(type), cudaMemcpyDeviceToHost), "get_gradients");
+    });
+}
+
+extern "C" int onn_trainer_set_learning_rate(onn_trainer* t, float learning_rate)
+{
+    if(!t) return ONN_ERR_INVALID_ARGUMENT;
+    t->adam->set_learning_rate(learning_rate);
+    return ONN_OK;
+}
+
+extern "C" int onn_trainer_set_iteration(onn_trainer* t, int64_t iteration)
+{
+    if(!t) return ONN_ERR_INVALID_ARGUMENT;
+    t->optimization->iteration = iteration;
+    return ONN_OK;
+}
+
+extern "C" int onn_trainer_set_dp(onn_trainer* t, onn_dp_comm* comm, int world)
+{
+    if(!t || world < 1) return ONN_ERR_INVALID_ARGUMENT;
+    t->comm = world > 1 ? comm : nullptr;
+    t->world = world;
+    return ONN_OK;
+}
+
+// Called after layer `layer` has back-propagated: every gradient slice from this layer's
+// offset up is final on the compute stream.  Hands full buckets to the all-reduce.
+static void gradient_ready(void* context, Index layer)
+{
+    onn_trainer* t = static_cast<onn_trainer*>(context);
+    const Index low = t->layer_offsets[size_t(layer)];
+    if(t->pending_high - low >= t->bucket_floats || (layer == 0 && t->pending_high > low))
+    {
+        check_onn(onn_dp_allreduce(t->comm, t->back->neural_network.gradients.data + low, t->pending_high - low, t->stream),
+                  "gradient all-reduce");
+        t->pending_high = low;
+    }
+}
+
+static void run_step(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,
+                     Index batch, bool update, float* statistics)
+{
+    if(batch <= 0 || batch % t->micro_batch != 0) throw std::runtime_error("step: batch must be a positive multiple of micro_batch");
+    if(!decoder_ids || !targets || (!t->decoder_only && !encoder_ids)) throw std::runtime_error("step: missing ids or targets");
+    Device::instance().set_compute_stream(t->stream);
+    const Index S_dec = t->decoder_sequence_length, S_in = t->input_sequence_length;
+    TensorCuda& gradients = t->back->neural_network.gradients;
+
+    if(t->gradients_dirty) gradients.fill(0);                // adaptive_moment_estimation.cpp:699 (Adam leaves them zero otherwise)
+    t->gradients_dirty = true;
+
+    // #active over the whole batch (and over all ranks): the loss gradient of every micro-batch is scaled by it
+    BatchCuda whole;
+    whole.samples_number = batch;
+    whole.target = TensorViewCuda(const_cast<float*>(targets), {batch, S_dec});
+    t->loss->calculate_active_tokens(whole, *t->back);
+    if(t->comm)
+    {
+        check_onn(onn_dp_allreduce(t->comm, t->back->active_count.data, 1, t->stream), "active-token all-reduce");
+        check_onn(onn_dp_wait(t->comm, t->stream), "active-token wait");
+    }
+
+    const Index chunks = batch / t->micro_batch;
+    for(Index chunk = 0; chunk < chunks; chunk++)
+    {
+        const Index first = chunk * t->micro_batch;
+        BatchCuda micro;
+        micro.samples_number = t->micro_batch;
+        micro.decoder = TensorViewCuda(const_cast<float*>(decoder_ids) + first * S_dec, {t->micro_batch, S_dec});
+        if(!t->decoder_only) micro.input = TensorViewCuda(const_cast<float*>(encoder_ids) + first * S_in, {t->micro_batch, S_in});
+        micro.target = TensorViewCuda(const_cast<float*>(targets) + first * S_dec, {t->micro_batch, S_dec});
+
+        t->network->forward_propagate(micro.get_inputs_device(), *t->forward, true);
+
+        const bool last = chunk == chunks - 1;
+        if(t->comm && last)
+        {
+            t->pending_high = gradients.size();
+            t->loss->gradient_ready_hook = gradient_ready;
+            t->loss->gradient_ready_context = t;
+        }
+        t->loss->back_propagate(micro, *t->forward, *t->back, chunk > 0);
+        t->loss->gradient_ready_hook = nullptr;
+    }
+
+    if(t->comm)
+    {
+        check_onn(onn_dp_allreduce(t->comm, t->back->statistics.data, 4 * t->back->statistics_slot, t->stream), "statistics all-reduce");
+        check_onn(onn_dp_wait(t->comm, t->stream), "gradient wait");
+    }
+
+    if(update)
+    {
+        t->adam->update_parameters(*t->back, *t->optimization);
+        t->gradients_dirty = false;                              // the update kernel zeroes the arena for the next step
+    }
+    else if(statistics)
+        check_onn(onn_grad_sqnorm(gradients.data, gradients.size(), t->optimization->square_norm.data, t->optimization->norm_workspace.data,
+                                  t->stream), "gradient norm");
+
+    if(statistics)
+    {
+        check_cuda(cudaMemcpyAsync(t->pinned_scalars, t->optimization->square_norm.data, sizeof(type), cudaMemcpyDeviceToHost, t->stream), "norm readback");
+        check_cuda(cudaMemcpyAsync(t->pinned_scalars + 1, t->back->active_count.data, sizeof(type), cudaMemcpyDeviceToHost, t->stream), "count readback");
+        t->loss->read_error(*t->back, 0);                        // synchronises the stream
+        // statistics slots were summed over ranks; so is the active count in pinned_scalars[1]
+        double loss_sum = 0, correct = 0;
+        for(Index k = 0; k < t->back->statistics_slot; k++)
+        {
+            loss_sum += t->back->pinned_statistics[4 * k];
+            correct += t->back->pinned_statistics[4 * k + 1];
+        }
+        const double active = t->pinned_scalars[1];
+        statistics[0] = active > 0 ? float(loss_sum / active) : 0.f;
+        statistics[1] = active > 0 ? float(correct / active) : 0.f;
+        statistics[2] = float(active);
+        statistics[3] = std::sqrt(t->pinned_scalars[0]);
+    }
+}
+
+extern "C" int onn_trainer_step_device(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,
+                                       int64_t batch, int update, float* statistics)
+{
+    if(!t) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&] { run_step(t, decoder_ids, encoder_ids, targets, batch, update != 0, statistics); });
+}
+
+extern "C" int onn_trainer_step_host(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,
+                                     int64_t batch, int update, float* statistics)
+{
+    if(!t || !decoder_ids || !targets) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        const Index decoder_count = batch * t->decoder_sequence_length, encoder_count = batch * t->input_sequence_length;
+        if(t->staged_decoder.size() < decoder_count) { t->staged_decoder.resize(decoder_count); t->staged_targets.resize(decoder_count); }
+        if(!t->decoder_only && t->staged_encoder.size() < encoder_count) t->staged_encoder.resize(encoder_count);
+        check_cuda(cudaMemcpyAsync(t->staged_decoder.data, decoder_ids, size_t(decoder_count) * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
+        check_cuda(cudaMemcpyAsync(t->staged_targets.data, targets, size_t(decoder_count) * sizeof(type), cudaMemcpyHostToDevice, t->stream), "targets H2D");
+        if(!t->decoder_only)
+        {
+            if(!encoder_ids) throw std::runtime_error("step: missing encoder ids");
+            check_cuda(cudaMemcpyAsync(t->staged_encoder.data, encoder_ids, size_t(encoder_count) * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
+        }
+        run_step(t, t->staged_decoder.data, t->decoder_only ? nullptr : t->staged_encoder.data, t->staged_targets.data, batch, update != 0, statistics);
+    });
+}
+
+extern "C" int onn_trainer_forward(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, int is_training)
+{
+    if(!t || !decoder_ids) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        Device::instance().set_compute_stream(t->stream);
+        BatchCuda micro;
+        micro.samples_number = t->micro_batch;
+        micro.decoder = TensorViewCuda(const_cast<float*>(decoder_ids), {t->micro_batch, t->decoder_sequence_length});
+        if(!t->decoder_only) micro.input = TensorViewCuda(const_cast<float*>(encoder_ids), {t->micro_batch, t->input_sequence_length});
+        t->network->forward_propagate(micro.get_inputs_device(), *t->forward, is_training != 0);
+    });
+}
+
+extern "C" int onn_trainer_get_layer_output(onn_trainer* t, int layer, float* host_output, int64_t count)
+{
+    if(!t || !host_output || layer < 0 || layer >= int(t->network->get_layers_number())) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        const TensorViewCuda outputs = t->forward->layers[size_t(layer)]->outputs;
+        if(count > outputs.size()) throw std::runtime_error("get_layer_output: count exceeds the layer's output size");
+        check_cuda(cudaStreamSynchronize(t->stream), "synchronize");
+        check_cuda(cudaMemcpy(host_output, outputs.data, size_t(count) * sizeof(type), cudaMemcpyDeviceToHost), "get_layer_output");
+    });
+}
+
+extern "C" int onn_trainer_synchronize(onn_trainer* t)
+{
+    if(!t) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&] { check_cuda(cudaStreamSynchronize(t->stream), "synchronize"); });
+}
+
+extern "C" void* onn_trainer_stream(onn_trainer* t) { return t ? t->stream : nullptr; }

@@ -1,0 +1,162 @@
+"""ctypes binding of libonn_b200_host.so (include/onn_b200_host.h): the C++ host mirror of
+OpenNN's NeuralNetwork / Transformer / CrossEntropyError3d / AdaptiveMomentEstimation.
+
+Python holds no compute: it hands raw pointers (torch tensors' device memory, or pinned host
+memory) and sizes across the C ABI.  There is no fallback path.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import capi
+
+HOST_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libonn_b200_host.so")
+
+TRANSFORMER, DECODER_ONLY = 0, 1
+
+HOST_EXPORTS = [
+    "onn_trainer_last_error", "onn_trainer_create", "onn_trainer_destroy", "onn_trainer_parameters_number",
+    "onn_trainer_layers_number", "onn_trainer_layer_info", "onn_trainer_set_parameters", "onn_trainer_get_parameters",
+    "onn_trainer_get_gradients", "onn_trainer_set_learning_rate", "onn_trainer_set_iteration", "onn_trainer_set_dp",
+    "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_forward", "onn_trainer_get_layer_output",
+    "onn_trainer_synchronize", "onn_trainer_stream",
+]
+
+_host = None
+
+
+def host_lib():
+    global _host
+    if _host is None:
+        capi.lib()      # the kernel library first (RTLD_GLOBAL), the host mirror links against it
+        if not os.path.exists(HOST_LIB_PATH):
+            raise capi.OnnError(f"{HOST_LIB_PATH} is missing: run `python -m opennn_b200._build`")
+        L = C.CDLL(HOST_LIB_PATH)
+        L.onn_trainer_last_error.restype = C.c_char_p
+        L.onn_trainer_parameters_number.restype = C.c_int64
+        L.onn_trainer_destroy.restype = None
+        L.onn_trainer_stream.restype = C.c_void_p
+        _host = L
+    return _host
+
+
+def _check(status, what):
+    if status != 0:
+        raise capi.OnnError(f"{what}: {host_lib().onn_trainer_last_error().decode()} ({status})")
+
+
+def _f32_ptr(array):
+    return array.ctypes.data_as(C.c_void_p)
+
+
+class Trainer:
+    """One network + CrossEntropyError3d + Adam on the current CUDA device."""
+
+    def __init__(self, kind, S_in, S_dec, V_in, V_out, E, H, F, L, micro_batch):
+        self.kind, self.S_in, self.S_dec, self.V_out, self.micro_batch = kind, S_in, S_dec, V_out, micro_batch
+        self._handle = C.c_void_p()
+        i64 = C.c_int64
+        _check(host_lib().onn_trainer_create(C.byref(self._handle), int(kind), i64(S_in), i64(S_dec), i64(V_in), i64(V_out),
+                                             i64(E), i64(H), i64(F), i64(L), i64(micro_batch)), "onn_trainer_create")
+        self.parameters_number = int(host_lib().onn_trainer_parameters_number(self._handle))
+        self.layers_number = int(host_lib().onn_trainer_layers_number(self._handle))
+
+    def close(self):
+        if self._handle:
+            host_lib().onn_trainer_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def layer_info(self, i):
+        name, label = C.create_string_buffer(128), C.create_string_buffer(128)
+        params, out_size = C.c_int64(), C.c_int64()
+        _check(host_lib().onn_trainer_layer_info(self._handle, int(i), name, label, 128, C.byref(params), C.byref(out_size)), "layer_info")
+        return name.value.decode(), label.value.decode(), params.value, out_size.value
+
+    def set_parameters(self, host_array):
+        a = np.ascontiguousarray(host_array, dtype=np.float32)
+        assert a.size == self.parameters_number
+        _check(host_lib().onn_trainer_set_parameters(self._handle, _f32_ptr(a)), "set_parameters")
+
+    def get_parameters(self):
+        a = np.empty(self.parameters_number, dtype=np.float32)
+        _check(host_lib().onn_trainer_get_parameters(self._handle, _f32_ptr(a)), "get_parameters")
+        return a
+
+    def get_gradients(self):
+        a = np.empty(self.parameters_number, dtype=np.float32)
+        _check(host_lib().onn_trainer_get_gradients(self._handle, _f32_ptr(a)), "get_gradients")
+        return a
+
+    def set_learning_rate(self, lr):
+        _check(host_lib().onn_trainer_set_learning_rate(self._handle, C.c_float(lr)), "set_learning_rate")
+
+    def set_dp(self, comm_handle, world):
+        _check(host_lib().onn_trainer_set_dp(self._handle, comm_handle, int(world)), "set_dp")
+
+    def step_device(self, dec_ids, enc_ids, targets, update=True, want_statistics=True):
+        """dec_ids / enc_ids / targets: torch CUDA float tensors [batch, S].  Returns
+        (error, accuracy, active tokens, gradient norm) or None."""
+        stats = (C.c_float * 4)()
+        batch = dec_ids.shape[0]
+        _check(host_lib().onn_trainer_step_device(self._handle, capi.ptr(dec_ids), capi.ptr(enc_ids), capi.ptr(targets),
+                                                  C.c_int64(batch), int(update), stats if want_statistics else None), "step_device")
+        return tuple(stats) if want_statistics else None
+
+    def step_host(self, dec_ids, enc_ids, targets, update=True, want_statistics=True):
+        """Same with host memory: torch CPU tensors (pinned for full copy speed) or numpy arrays."""
+        stats = (C.c_float * 4)()
+
+        def host_ptr(x):
+            if x is None:
+                return C.c_void_p(0)
+            return C.c_void_p(x.data_ptr()) if hasattr(x, "data_ptr") else _f32_ptr(x)
+
+        batch = dec_ids.shape[0]
+        _check(host_lib().onn_trainer_step_host(self._handle, host_ptr(dec_ids), host_ptr(enc_ids), host_ptr(targets),
+                                                C.c_int64(batch), int(update), stats if want_statistics else None), "step_host")
+        return tuple(stats) if want_statistics else None
+
+    def forward(self, dec_ids, enc_ids, is_training=False):
+        _check(host_lib().onn_trainer_forward(self._handle, capi.ptr(dec_ids), capi.ptr(enc_ids), int(is_training)), "forward")
+
+    def layer_output(self, i, count=None):
+        _, _, _, size = self.layer_info(i)
+        count = size if count is None else count
+        a = np.empty(count, dtype=np.float32)
+        _check(host_lib().onn_trainer_get_layer_output(self._handle, int(i), _f32_ptr(a), C.c_int64(count)), "get_layer_output")
+        return a
+
+    def stream(self):
+        """torch view of the CUDA stream the trainer launches on (for torch.cuda.Event timing)."""
+        import torch
+        return torch.cuda.ExternalStream(host_lib().onn_trainer_stream(self._handle))
+
+    def synchronize(self):
+        _check(host_lib().onn_trainer_synchronize(self._handle), "synchronize")
+
+
+def dp_init_from_torch():
+    """Creates the NCCL communicator of libonn_b200 for the ranks of an initialised
+    torch.distributed process group (the 128-byte unique id travels through it)."""
+    import torch
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(), dist.get_rank()
+    uid = (C.c_char * 128)()
+    if rank == 0:
+        capi.check(capi.lib().onn_dp_unique_id(uid), "onn_dp_unique_id")
+    payload = [bytes(uid.raw)]
+    dist.broadcast_object_list(payload, src=0)
+    uid_buffer = (C.c_char * 128).from_buffer_copy(payload[0])
+    comm = C.c_void_p()
+    capi.check(capi.lib().onn_dp_init(C.byref(comm), uid_buffer, int(world), int(rank)), "onn_dp_init")
+    return comm

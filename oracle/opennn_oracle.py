@@ -19,6 +19,12 @@ F32 = np.float32
 EPSILON = np.finfo(np.float32).eps  # opennn/pch.h:123  numeric_limits<float>::epsilon()
 
 
+def _mm(a, b):
+    """Every contraction of the path goes through here (fp32, like the reference's Eigen
+    GEMMs); experiments that model reduced-precision operands replace this one function."""
+    return np.matmul(a, b)
+
+
 def padded(count: int) -> int:
     """Arena slot size: each view is padded to 8 floats (opennn/tensor_utilities.cpp:472-487)."""
     return (count + 7) & ~7
@@ -125,7 +131,7 @@ def dense_forward(x, weights, biases, activation):
     """opennn/dense_layer.h:767-813 -> layer.h:305-340 (X.W + b) -> layer.h:122-152.
     Returns (outputs, activation_derivatives)."""
     rows = x.reshape(-1, x.shape[-1])
-    combos = (rows @ weights + biases).astype(F32).reshape(*x.shape[:-1], weights.shape[1])
+    combos = (_mm(rows, weights) + biases).astype(F32).reshape(*x.shape[:-1], weights.shape[1])
     if activation == "Linear":
         return combos, np.ones_like(combos)
     if activation == "RectifiedLinear":
@@ -142,9 +148,9 @@ def dense_backward(x, weights, d_y, activation_derivatives, activation):
     delta = d_y.reshape(-1, d_y.shape[-1])
     if activation != "Softmax":
         delta = delta * activation_derivatives.reshape(delta.shape)
-    d_w = (rows.T @ delta).astype(F32)
+    d_w = _mm(rows.T, delta).astype(F32)
     d_b = delta.sum(axis=0, dtype=F32)
-    d_x = (delta @ weights.T).astype(F32).reshape(x.shape)
+    d_x = _mm(delta, weights.T).astype(F32).reshape(x.shape)
     return d_x, d_w, d_b
 
 
@@ -175,18 +181,18 @@ def mha_forward(xq, xs, p, H, causal):
     Sk = xs.shape[1]
     hd = E // H
     scaling = F32(1.0) / np.sqrt(F32(hd))
-    q = _split_heads((xq.reshape(-1, E) @ p["Wq"] + p["bq"]).astype(F32).reshape(B, Sq, E), H)
-    k = _split_heads((xs.reshape(-1, E) @ p["Wk"] + p["bk"]).astype(F32).reshape(B, Sk, E), H)
-    v = _split_heads((xs.reshape(-1, E) @ p["Wv"] + p["bv"]).astype(F32).reshape(B, Sk, E), H)
-    scores = (np.matmul(q, k.transpose(0, 1, 3, 2)) * scaling).astype(F32)  # [B,H,Sq,Sk]
+    q = _split_heads((_mm(xq.reshape(-1, E), p["Wq"]) + p["bq"]).astype(F32).reshape(B, Sq, E), H)
+    k = _split_heads((_mm(xs.reshape(-1, E), p["Wk"]) + p["bk"]).astype(F32).reshape(B, Sk, E), H)
+    v = _split_heads((_mm(xs.reshape(-1, E), p["Wv"]) + p["bv"]).astype(F32).reshape(B, Sk, E), H)
+    scores = (_mm(q, k.transpose(0, 1, 3, 2)) * scaling).astype(F32)  # [B,H,Sq,Sk]
     pad = key_padding_flags(xs)
     scores = np.where(pad[:, None, None, :], F32(-1e9), scores)            # :600 overwrite
     if causal:
         future = np.arange(Sk)[None, :] > np.arange(Sq)[:, None]          # :157 column > row
         scores = np.where(future[None, None], F32(-np.inf), scores)        # :570 additive -inf
     weights = softmax_last(scores)
-    concat = _merge_heads(np.matmul(weights, v).astype(F32))              # [B,Sq,E]
-    y = (concat.reshape(-1, E) @ p["Wo"] + p["bo"]).astype(F32).reshape(B, Sq, E)
+    concat = _merge_heads(_mm(weights, v).astype(F32))              # [B,Sq,E]
+    y = (_mm(concat.reshape(-1, E), p["Wo"]) + p["bo"]).astype(F32).reshape(B, Sq, E)
     saved = dict(q=q, k=k, v=v, weights=weights, concat=concat)
     return y, saved
 
@@ -201,20 +207,20 @@ def mha_backward(xq, xs, p, H, saved, d_y, self_attention):
     q, k, v, w, concat = saved["q"], saved["k"], saved["v"], saved["weights"], saved["concat"]
     dy = d_y.reshape(-1, E)
     g = {}
-    g["dWo"] = (concat.reshape(-1, E).T @ dy).astype(F32)
+    g["dWo"] = _mm(concat.reshape(-1, E).T, dy).astype(F32)
     g["dbo"] = dy.sum(axis=0, dtype=F32)
-    d_concat = (dy @ p["Wo"].T).astype(F32).reshape(B, Sq, E)
+    d_concat = _mm(dy, p["Wo"].T).astype(F32).reshape(B, Sq, E)
     d_o = _split_heads(d_concat, H)                                       # [B,H,Sq,hd]
-    d_v = np.matmul(w.transpose(0, 1, 3, 2), d_o).astype(F32)
-    d_w = np.matmul(d_o, v.transpose(0, 1, 3, 2)).astype(F32)
+    d_v = _mm(w.transpose(0, 1, 3, 2), d_o).astype(F32)
+    d_w = _mm(d_o, v.transpose(0, 1, 3, 2)).astype(F32)
     dot = (w * d_w).sum(axis=-1, dtype=F32, keepdims=True)
     d_s = (w * (d_w - dot)).astype(F32)
-    d_q = (np.matmul(d_s, k) * scaling).astype(F32)
-    d_k = (np.matmul(d_s.transpose(0, 1, 3, 2), q) * scaling).astype(F32)
+    d_q = (_mm(d_s, k) * scaling).astype(F32)
+    d_k = (_mm(d_s.transpose(0, 1, 3, 2), q) * scaling).astype(F32)
 
     def projection_gradient(d_head, x, W):
         d = _merge_heads(d_head).reshape(-1, E)
-        return (d @ W.T).astype(F32).reshape(x.shape), (x.reshape(-1, E).T @ d).astype(F32), d.sum(axis=0, dtype=F32)
+        return _mm(d, W.T).astype(F32).reshape(x.shape), _mm(x.reshape(-1, E).T, d).astype(F32), d.sum(axis=0, dtype=F32)
 
     d_xq, g["dWq"], g["dbq"] = projection_gradient(d_q, xq, p["Wq"])
     d_xk, g["dWk"], g["dbk"] = projection_gradient(d_k, xs, p["Wk"])

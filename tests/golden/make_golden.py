@@ -102,8 +102,8 @@ def make_mha(seed=0):
         p = {}
         for w, b in (("Wq", "bq"), ("Wk", "bk"), ("Wv", "bv"), ("Wo", "bo")):
             # MHA's inputs_number and outputs_number are both S*E (layer.cpp:214-225); applied to biases too
-            p[w] = glorot(rng, (E, E), Sq * E, Sq * E) * F32(8)
-            p[b] = glorot(rng, (E,), Sq * E, Sq * E) * F32(8)
+            p[w] = glorot(rng, (E, E), Sq * E, Sq * E) * F32(2.5)
+            p[b] = glorot(rng, (E,), Sq * E, Sq * E) * F32(2.5)
         xq = rng.standard_normal((B, Sq, E)).astype(F32)
         xs = rng.standard_normal((B, Sk, E)).astype(F32) if cross else xq
         if pad_rows:

@@ -34,3 +34,27 @@ def test_status_strings_and_argument_checks(built):
     assert L.onn_add(None, None, None, ctypes.c_int64(4), ctypes.c_uint32(0), None) == -1
     assert L.onn_layernorm_bwd_workspace_floats(ctypes.c_int64(1000), ctypes.c_int64(512)) > 0
     assert L.onn_gemm_set_mode(7) == -1
+
+
+def test_host_library_exports_header(built):
+    from opennn_b200 import capi, trainer
+    symbols = declared_symbols("onn_b200_host.h")
+    ctypes.CDLL(built["kernels"], mode=ctypes.RTLD_GLOBAL)
+    handle = ctypes.CDLL(built["host"])
+    missing = [s for s in symbols if not hasattr(handle, s)]
+    assert not missing, f"declared in onn_b200_host.h but not exported: {missing}"
+    assert sorted(trainer.HOST_EXPORTS) == symbols
+
+
+def test_trainer_refuses_without_gpu(built):
+    """No CPU fallback: without a CUDA device the host mirror fails loudly."""
+    import torch
+    if torch.cuda.is_available():
+        return
+    from opennn_b200 import capi, trainer
+    try:
+        trainer.Trainer(trainer.TRANSFORMER, 8, 8, 16, 16, 8, 2, 16, 1, 2)
+    except capi.OnnError as error:
+        assert "no CUDA device" in str(error)
+    else:
+        raise AssertionError("creating a trainer without a GPU must fail")

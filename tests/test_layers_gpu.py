@@ -1,0 +1,246 @@
+"""GPU parity: every layer entry point of the C ABI against the golden fixtures produced by
+the unmodified reference CPU library (same seeded inputs).  Shapes are the reference's own
+layer-test shapes plus config 1; ragged, padded and out-of-range cases included.
+
+Tolerance: 1e-3 (max-abs and L2, relative) for anything that passes through the tf32
+tensor cores; embedding values are compared bit for bit.
+"""
+
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.util import GOLDEN, TOL, assert_close, golden
+from tests.golden.make_golden import mha_unpack
+
+pytestmark = pytest.mark.gpu
+
+
+def names(prefix):
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, prefix + "*.npz")))
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.fixture(scope="module")
+def capi(built):
+    from opennn_b200 import capi as module
+    module.lib()
+    yield module
+    module.check(module.lib().onn_gemm_set_mode(0))
+
+
+@pytest.fixture(params=["auto", "simt"])
+def gemm_mode(request, capi):
+    """auto = tcgen05 wherever the TMA alignment rules allow it; simt = CUDA-core cross-check."""
+    capi.check(capi.lib().onn_gemm_set_mode(1 if request.param == "simt" else 0))
+    yield request.param
+    assert capi.lib().onn_gemm_device_status() == 0, "a tcgen05 GEMM gave up on a bounded wait"
+    capi.check(capi.lib().onn_gemm_set_mode(0))
+
+
+# ---------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", names("embedding_"))
+def test_embedding(capi, name):
+    g = golden(name)
+    B, S, V, E, scale, add_pe = (int(v) for v in g["spec"])
+    ids, W, pe = dev(g["ids"]), dev(g["weights"]), dev(g["pe"])
+    y, flags = capi.embedding_fwd(ids, W, pe, bool(scale), bool(add_pe), want_flags=True)
+    assert np.array_equal(host(y).view(np.uint32), g["y"].view(np.uint32)), "embedding forward must be bit-exact"
+    expected_flags = np.all(np.abs(g["y"]) <= 1e-7, axis=-1).reshape(-1)
+    assert np.array_equal(host(flags).astype(bool), expected_flags)
+    dW = capi.embedding_bwd(ids, dev(g["delta"]), V, bool(scale))
+    assert_close(host(dW), g["dW"], 1e-5, "dW")
+    assert not host(dW)[0].any(), "padding row gradient must be exactly zero"
+    # fan-in sum of two consumer gradients
+    half = dev(g["delta"] * 0.5)
+    dW2 = capi.embedding_bwd(ids, half, V, bool(scale), dY2=half)
+    assert_close(host(dW2), g["dW"], 1e-5, "dW with two consumers")
+
+
+@pytest.mark.parametrize("name", names("layernorm_"))
+def test_layernorm(capi, name):
+    g = golden(name)
+    x, gamma, beta, delta = dev(g["x"]), dev(g["gammas"]), dev(g["betas"]), dev(g["delta"])
+    y, mean, inv_std, _ = capi.layernorm_fwd(x, gamma, beta)
+    assert_close(host(y), g["y"], 1e-5, "y")
+    dx, dgamma, dbeta = capi.layernorm_bwd(delta, x, mean, inv_std, gamma)
+    assert_close(host(dx), g["dx"], 5e-5, "dx")
+    assert_close(host(dgamma), g["dgamma"], 5e-5, "dgamma")
+    assert_close(host(dbeta), g["dbeta"], 5e-5, "dbeta")
+    # fused residual add: A + R = x, and the sum comes back as the Addition layer's output
+    a = dev(g["x"] * 0.25)
+    r = dev(g["x"] - g["x"] * 0.25)
+    y2, mean2, inv_std2, total = capi.layernorm_fwd(a, gamma, beta, R=r, want_sum=True)
+    assert_close(host(total), host(a) + host(r), 1e-7, "sum")
+    assert_close(host(y2), g["y"], 2e-5, "y (fused add)")
+    # fan-in sum of three consumer gradients
+    third = dev(g["delta"] / 4)
+    dx3, dgamma3, _ = capi.layernorm_bwd(third, x, mean, inv_std, gamma, dY2=third, dY3=dev(g["delta"] / 2))
+    assert_close(host(dx3), g["dx"], 5e-5, "dx (three consumers)")
+    assert_close(host(dgamma3), g["dgamma"], 5e-5, "dgamma (three consumers)")
+
+
+@pytest.mark.parametrize("name", names("dense_"))
+def test_dense(capi, gemm_mode, name):
+    g = golden(name)
+    activation = str(g["activation"])
+    x, W, b, delta = dev(g["x"]), dev(g["weights"]), dev(g["biases"]), dev(g["delta"])
+    y = capi.dense_fwd(x, W, b, activation)
+    assert_close(host(y), g["y"], TOL, "y")
+    dx, dW, db = capi.dense_bwd(x, W, y, delta, activation)
+    assert_close(host(dx), g["dx"], TOL, "dx")
+    assert_close(host(dW), g["dW"], TOL, "dW")
+    assert_close(host(db), g["db"], TOL, "db")
+
+
+@pytest.mark.parametrize("name", names("mha_"))
+def test_mha(capi, gemm_mode, name):
+    g = golden(name)
+    B, Sq, Sk, E, H, causal, cross = (int(v) for v in g["spec"])
+    p = {k: dev(v) for k, v in mha_unpack(g["params"], E).items()}
+    xq = dev(g["xq"])
+    xs = dev(g["xs"]) if cross else xq
+    y, ws = capi.mha_fwd(xq, xs, p, H, bool(causal))
+    assert_close(host(y), g["y"], TOL, "y")
+    weights = capi.mha_attention_weights(ws, B, Sq, Sk, E, H)
+    assert_close(host(weights), g["attention_weights"], TOL, "attention weights")
+    grads, dxq, dxs = capi.mha_bwd(xq, xs, p, H, bool(causal), ws, dev(g["delta"]))
+    assert_close(host(dxq), g["dxq"], TOL, "dxq")
+    if cross:
+        assert_close(host(dxs), g["dxs"], TOL, "dxs")
+    ref = mha_unpack(g["grads"], E)
+    floor = float(np.abs(g["grads"]).max())
+    for key, value in ref.items():
+        assert_close(host(grads["d" + key]), value, TOL, "d" + key, floor=floor)
+
+
+@pytest.mark.parametrize("name", names("ce3d_"))
+def test_ce3d(capi, name):
+    g = golden(name)
+    targets = dev(g["targets"])
+    # from logits (fused softmax), the training path
+    error, accuracy, grad, p = capi.ce3d(dev(g["logits"]), targets, want_probabilities=True)
+    assert abs(error - g["loss"][0]) <= 1e-5 * max(1.0, abs(g["loss"][0]))
+    assert abs(accuracy - g["loss"][1]) <= 1e-6
+    assert_close(host(grad), g["dlogits"], 1e-5, "dlogits")
+    assert_close(host(p), g["p"], 1e-5, "probabilities")
+    # from probabilities, as a plain Softmax Dense layer leaves them
+    error2, accuracy2, grad2, _ = capi.ce3d(dev(g["p"]), targets, inputs_are_probabilities=True)
+    assert abs(error2 - g["loss"][0]) <= 1e-6 * max(1.0, abs(g["loss"][0]))
+    assert accuracy2 == accuracy
+    assert_close(host(grad2), g["dlogits"], 1e-6, "dlogits from probabilities")
+
+
+def test_ce3d_all_masked(capi):
+    logits = torch.randn(2, 3, 16, device="cuda")
+    targets = torch.zeros(2, 3, device="cuda")
+    error, accuracy, grad, _ = capi.ce3d(logits, targets)
+    assert error == 0.0 and accuracy == 0.0 and not host(grad).any()
+
+
+def test_adam_and_norm(capi):
+    from oracle import opennn_oracle as O
+    rng = np.random.default_rng(7)
+    n = 100003                                   # odd size: exercises the scalar tail
+    p0 = rng.standard_normal(n).astype(np.float32)
+    m0 = (0.01 * rng.standard_normal(n)).astype(np.float32)
+    v0 = (0.001 * rng.random(n)).astype(np.float32)
+    for g_scale in (0.1, 1e-4):                  # clip active / inactive
+        g0 = (g_scale * rng.standard_normal(n)).astype(np.float32)
+        p, m, v, g = dev(p0), dev(m0), dev(v0), dev(g0)
+        sqnorm = capi.grad_sqnorm(g)
+        assert abs(float(sqnorm.item()) - float(np.sum(g0.astype(np.float64) ** 2))) <= 1e-5 * float(np.sum(g0.astype(np.float64) ** 2))
+        capi.adam(p, m, v, g, 3, sqnorm=sqnorm, zero_grad=True)
+        pe, me, ve = p0.copy(), m0.copy(), v0.copy()
+        O.adam_update(pe, g0, me, ve, 3)
+        assert_close(host(m), me, 1e-5, "m")
+        assert_close(host(v), ve, 1e-5, "v")
+        assert_close(host(p) - p0, pe - p0, 1e-4, "parameter update")
+        assert not host(g).any(), "zero_grad must clear the gradient"
+
+
+@pytest.mark.parametrize("a_major,b_major", [(0, 1), (0, 0), (1, 1)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (300, 520, 136), (64, 48, 1056), (1000, 72, 40)])
+def test_gemm_layouts(capi, gemm_mode, a_major, b_major, shape):
+    """The GEMM primitive in every operand layout the layers use, with ragged M, N and K
+    (zero-filled TMA boxes, masked epilogue) and each epilogue option."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    mask = rng.standard_normal((M, N)).astype(np.float32)
+    A_store = dev(A if a_major == 0 else A.T)
+    B_store = dev(B.T if b_major == 0 else B)
+    lda = K if a_major == 0 else M
+    ldb = K if b_major == 0 else N
+    reference = A.astype(np.float64) @ B.astype(np.float64)
+
+    out = torch.zeros(M, N, device="cuda")
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major)
+    assert_close(host(out), reference, TOL, "plain")
+
+    out = torch.zeros(M, N, device="cuda")
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, bias=dev(bias), relu=True, alpha=0.5)
+    assert_close(host(out), np.maximum(0.5 * reference + bias, 0), TOL, "alpha + bias + relu")
+
+    start = rng.standard_normal((M, N)).astype(np.float32)
+    out = dev(start)
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, relu_mask=dev(mask), flags=capi.ACCUMULATE)
+    assert_close(host(out), start + reference * (mask > 0), TOL, "mask + accumulate")
+
+    out = dev(start)
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, split_k=5)
+    assert_close(host(out), start + reference, TOL, "split-K")
+
+
+def test_gemm_batched_heads(capi, gemm_mode):
+    """Per-(batch, head) products addressed by strides inside [B, S, E] tensors, as attention uses them."""
+    Bn, H, Sq, Sk, hd = 3, 4, 40, 72, 16
+    E = H * hd
+    rng = np.random.default_rng(11)
+    q = rng.standard_normal((Bn, Sq, E)).astype(np.float32)
+    k = rng.standard_normal((Bn, Sk, E)).astype(np.float32)
+    scores = torch.zeros(Bn, H, Sq, Sk, device="cuda")
+    capi.gemm(dev(q), dev(k), scores, Sq, Sk, hd, E, E, Sk, 0, 0, alpha=0.25, batch_inner=H, batch_outer=Bn,
+              a_strides=(hd, Sq * E), b_strides=(hd, Sk * E), c_strides=(Sq * Sk, H * Sq * Sk))
+    qh = q.reshape(Bn, Sq, H, hd).transpose(0, 2, 1, 3).astype(np.float64)
+    kh = k.reshape(Bn, Sk, H, hd).transpose(0, 2, 1, 3).astype(np.float64)
+    assert_close(host(scores), 0.25 * qh @ kh.transpose(0, 1, 3, 2), TOL, "QK^T")
+    p = rng.random((Bn, H, Sq, Sk)).astype(np.float32)
+    ctx = torch.zeros(Bn, Sq, E, device="cuda")
+    capi.gemm(dev(p), dev(k), ctx, Sq, hd, Sk, Sk, E, E, 0, 1, batch_inner=H, batch_outer=Bn,
+              a_strides=(Sq * Sk, H * Sq * Sk), b_strides=(hd, Sk * E), c_strides=(hd, Sq * E))
+    expected = (p.astype(np.float64) @ kh).transpose(0, 2, 1, 3).reshape(Bn, Sq, E)
+    assert_close(host(ctx), expected, TOL, "PV")
+
+
+def test_gemm_large_linearity(capi):
+    """Full-size property check (config-5 FFN tile counts): C(A1 + A2) = C(A1) + C(A2) and a
+    checksum against fp64 on sampled rows, on the tcgen05 path."""
+    M, N, K = 8192, 4096, 1024
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    A1 = torch.randn(M, K, device="cuda", generator=gen)
+    A2 = torch.randn(M, K, device="cuda", generator=gen)
+    W = torch.randn(K, N, device="cuda", generator=gen) * 0.05
+    outs = []
+    for A in (A1, A2, A1 + A2):
+        out = torch.empty(M, N, device="cuda")
+        capi.gemm(A, W, out, M, N, K, K, N, N, 0, 1)
+        outs.append(out)
+    assert capi.lib().onn_gemm_device_status() == 0
+    assert_close(host(outs[2][::97]), host((outs[0] + outs[1])[::97]), TOL, "linearity")
+    rows = torch.arange(0, M, 511, device="cuda")
+    expected = A1[rows].double() @ W.double()
+    assert_close(host(outs[0][rows]), host(expected), TOL, "sampled rows vs fp64")
