@@ -224,6 +224,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     peaks = measured_peaks()
+    if args.profile_batch:
+        w = dict(w, global_batch=args.profile_batch, name=w["name"] + f" (profiling batch {args.profile_batch})")
     local_batch = w["global_batch"] // world
     micro = min(w["micro_batch"], local_batch)
     t = trainer.Trainer(trainer.TRANSFORMER, w["S_in"], w["S_dec"], w["V_in"], w["V_out"], w["E"], w["H"], w["F"], w["L"], micro)
@@ -274,7 +276,7 @@ def run_ours(args):
         d, e, g = host_batches[i % pool]
         last_stats[0] = t.step_host(d, e, g, update=True, want_statistics=True)
 
-    warmup = max(args.warmup, 3)
+    warmup = args.warmup if args.profile_batch else max(args.warmup, 3)
     for i in range(warmup):
         device_step(i)
     barrier()
@@ -285,6 +287,12 @@ def run_ours(args):
     launches = capi.lib().onn_launch_count() - launches_before
     clocks = sampler.stop() if sampler else None
 
+    if args.profile_batch:
+        if rank == 0:
+            print(json.dumps({"profiling_only": True, "workload": w["name"], "ms_per_step": 1e3 * seconds / args.steps,
+                              "gpu_launches": int(launches)}))
+        t.close()
+        return
     host_step(0)                                  # warm the host path (staging buffers)
     e2e_seconds = timed(host_step, args.steps)
     status = capi.lib().onn_gemm_device_status()
@@ -328,6 +336,9 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--profile-batch", type=int, default=0,
+                        help="profiling aid: run the device-resident loop only, on a global batch of this many samples "
+                             "(the line it prints is not a benchmark result)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -8,8 +8,11 @@
 //               descriptors; owns the TMEM allocation (two accumulator buffers so the
 //               epilogue of tile i overlaps the main loop of tile i+1);
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32
-//               output rows), alpha / bias / ReLU / mask / accumulate,
-//               128-bit stores (or vector fp32 reductions for split-K).
+//               output rows), alpha / bias / ReLU, stage the 32 x 32 block in shared memory
+//               (128-byte swizzle) and hand it to a TMA store -- or a TMA reduce-add for
+//               accumulation and split-K -- so global writes are whole lines and clipped at the
+//               matrix edge by the copy engine.  (With a ReLU mask operand the epilogue falls
+//               back to direct 128-bit loads and stores.)
 //
 // Operand layouts (BK = 32 floats = 128 bytes = one swizzle row, UMMA K = 8):
 //   K-major  (reduction dimension contiguous in memory): one box [rows][32 floats];
@@ -48,6 +51,8 @@ constexpr int UMMA_K = 8;
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 4;                 // 16 KiB
+constexpr int EPI_BLOCK_BYTES = 32 * 32 * 4;               // one warp's 32 rows x 32 columns
+constexpr int EPI_BYTES = kEpilogueWarps * 2 * EPI_BLOCK_BYTES;   // double-buffered per warp: 32 KiB
 constexpr unsigned long long kWaitCycles = 1ull << 31;     // ~1 s at 2 GHz
 
 __device__ unsigned int g_status;                          // 0 = ok; else first failing wait site
@@ -63,7 +68,8 @@ struct Params
     float alpha;
     int relu, accumulate;
     int batch_inner, batch_outer;
-    int a_batch_inner_on, a_batch_outer_on, b_batch_inner_on, b_batch_outer_on;
+    int a_batch_inner_on, a_batch_outer_on, b_batch_inner_on, b_batch_outer_on, c_batch_inner_on, c_batch_outer_on;
+    int a_wide, b_wide;                                    // MN-major operand loaded with one 5-D box per stage
     int splits;
     long long k_per_split;                                 // multiple of BK
     int m_blocks, n_blocks;
@@ -130,6 +136,30 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 :: "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 :: "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -213,7 +243,8 @@ __device__ __forceinline__ WorkItem decode_work(const Params& p, long long w)
 
 template <int BN, int STAGES, int A_MN, int B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, const Params p)
 {
     constexpr int B_STAGE_BYTES = BN * BK * 4;
     constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -222,7 +253,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
+    uint8_t* epi_smem = smem + (size_t)STAGES * STAGE_BYTES;            // 1024-byte aligned: stage sizes are multiples of 1024
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + EPI_BYTES);
     uint64_t* full_bar = bars;                              // [STAGES]  TMA -> MMA
     uint64_t* empty_bar = bars + STAGES;                    // [STAGES]  MMA -> TMA
     uint64_t* acc_full_bar = bars + 2 * STAGES;             // [2]       MMA -> epilogue
@@ -276,15 +308,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     armed[stage] = phase + 1;
                     if(A_MN)
                     {
+                        if(p.a_wide) tma_load_5d(a_dst, &map_a, bar, 0, k0, m0 / 32, a_zi, a_zo);
+                        else
+                        {
 #pragma unroll
-                        for(int j = 0; j < BM / 32; j++) tma_load_4d(a_dst + j * 4096, &map_a, bar, m0 + 32 * j, k0, a_zi, a_zo);
+                            for(int j = 0; j < BM / 32; j++) tma_load_4d(a_dst + j * 4096, &map_a, bar, m0 + 32 * j, k0, a_zi, a_zo);
+                        }
                     }
                     else
                         tma_load_4d(a_dst, &map_a, bar, k0, m0, a_zi, a_zo);
                     if(B_MN)
                     {
+                        if(p.b_wide) tma_load_5d(b_dst, &map_b, bar, 0, k0, n0 / 32, b_zi, b_zo);
+                        else
+                        {
 #pragma unroll
-                        for(int j = 0; j < BN / 32; j++) tma_load_4d(b_dst + j * 4096, &map_b, bar, n0 + 32 * j, k0, b_zi, b_zo);
+                            for(int j = 0; j < BN / 32; j++) tma_load_4d(b_dst + j * 4096, &map_b, bar, n0 + 32 * j, k0, b_zi, b_zo);
+                        }
                     }
                     else
                         tma_load_4d(b_dst, &map_b, bar, k0, n0, b_zi, b_zo);
@@ -350,6 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- epilogue (warps 2..5) ----------------
         const int quadrant = warp & 3;                       // TMEM lanes this warp may read: 32*quadrant ..
         long long local = 0;
+        unsigned int staged_chunks = 0;                      // blocks this warp has handed to the copy engine
         for(long long w = blockIdx.x; w < p.total_work; w += gridDim.x, local++)
         {
             const WorkItem it = decode_work(p, w);
@@ -368,15 +409,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool row_ok = row < p.M;
             const bool use_bias = p.bias != nullptr && it.split == 0;
             const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * BN;
+            const long long warp_row0 = (long long)it.m_blk * BM + quadrant * 32;
+            const bool staged = p.relu_mask == nullptr;
+            const bool reduce = p.accumulate || p.splits > 1;
+            const int c_zi = p.c_batch_inner_on ? it.zi : 0, c_zo = p.c_batch_outer_on ? it.zo : 0;
 
 #pragma unroll 1
             for(int c = 0; c < BN / 32; c++)
             {
                 const long long n_base = n0 + c * 32;
-                if(n_base >= p.N) break;
+                if(n_base >= p.N || warp_row0 >= p.M) break;    // nothing of this block lies inside C
                 float v[32];
                 __syncwarp();                                   // tcgen05.ld is warp-collective: reconverge first
                 tmem_load_32(taddr + c * 32, v);
+                if(staged)
+                {
+                    // this warp's two staging blocks alternate; a block is free again once the copy
+                    // issued from it two chunks ago has finished READING shared memory
+                    const uint32_t block = smem_u32(epi_smem + ((warp - 2) * 2 + (int)(staged_chunks & 1)) * EPI_BLOCK_BYTES);
+                    if(staged_chunks >= 2) { if(lane == 0) bulk_wait_read_1(); __syncwarp(); }
+#pragma unroll
+                    for(int q4 = 0; q4 < 8; q4++)
+                    {
+                        const long long n = n_base + q4 * 4;
+                        float x[4] = { v[q4 * 4] * p.alpha, v[q4 * 4 + 1] * p.alpha, v[q4 * 4 + 2] * p.alpha, v[q4 * 4 + 3] * p.alpha };
+                        if(use_bias)
+                        {
+                            if(n + 3 < p.N) { const float4 b = ld4(p.bias + n); x[0] += b.x; x[1] += b.y; x[2] += b.z; x[3] += b.w; }
+                            else for(int e = 0; e < 4; e++) if(n + e < p.N) x[e] += p.bias[n + e];
+                        }
+                        if(p.relu) { x[0] = fmaxf(x[0], 0.f); x[1] = fmaxf(x[1], 0.f); x[2] = fmaxf(x[2], 0.f); x[3] = fmaxf(x[3], 0.f); }
+                        // row `lane` of the block is 128 bytes; 16-byte chunk q4 goes to slot q4 ^ (lane % 8): the 128-byte swizzle
+                        const uint32_t dst = block + (uint32_t)lane * 128u + (uint32_t)((q4 ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+                    }
+                    fence_async_shared();                        // generic-proxy writes -> visible to the copy engine
+                    __syncwarp();
+                    if(lane == 0)
+                    {
+                        if(reduce) tma_reduce_add_4d(&map_c, block, (int)n_base, (int)warp_row0, c_zi, c_zo);
+                        else tma_store_4d(&map_c, block, (int)n_base, (int)warp_row0, c_zi, c_zo);
+                        bulk_commit();
+                    }
+                    staged_chunks++;
+                    continue;
+                }
                 if(!row_ok) continue;
 #pragma unroll
                 for(int q4 = 0; q4 < 8; q4++)
@@ -425,6 +502,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             if(lane == 0) mbar_arrive(smem_u32(acc_empty_bar + acc));
         }
+        if(lane == 0) bulk_wait_all();                       // the staging blocks must outlive the copies that read them
     }
 
     tcgen05_fence_before();
@@ -466,7 +544,7 @@ static cuuint64_t stride_bytes(long long elements, long long fallback_elements)
 // 4-D map (d0 = contiguous dimension, d1 = pitched dimension, batch inner, batch outer).
 static bool make_map(CUtensorMap* map, const float* base, long long d0, long long d1, long long pitch,
                      int batch_inner, long long stride_inner, int batch_outer, long long stride_outer,
-                     int box0, int box1, bool mn_major)
+                     int box0, int box1, bool mn_major, bool round_to_tf32 = true)
 {
     EncodeTiledFn fn = encode_tiled();
     if(!fn) return false;
@@ -478,18 +556,39 @@ static bool make_map(CUtensorMap* map, const float* base, long long d0, long lon
                                     stride_bytes(outer_on ? stride_outer : 0, plane) };
     const cuuint32_t box[4] = { (cuuint32_t)box0, (cuuint32_t)box1, 1, 1 };
     const cuuint32_t elem[4] = { 1, 1, 1, 1 };
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, const_cast<float*>(base), dims, strides, box, elem,
+    return fn(map, round_to_tf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, elem,
               CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// MN-major operand whose contiguous extent is a multiple of 32: 5-D view (32 within an atom, reduction
+// rows, atom index, batch inner, batch outer) so ONE copy per stage brings [atoms][32 k-rows][32 floats],
+// the same shared-memory image as `atoms` separate 4 KiB boxes.
+static bool make_wide_map(CUtensorMap* map, const float* base, long long mn, long long kdim, long long pitch,
+                          int batch_inner, long long stride_inner, int batch_outer, long long stride_outer, int atoms)
+{
+    EncodeTiledFn fn = encode_tiled();
+    if(!fn) return false;
+    const bool inner_on = batch_inner > 1 && stride_inner != 0, outer_on = batch_outer > 1 && stride_outer != 0;
+    const cuuint64_t dims[5] = { 32, (cuuint64_t)kdim, (cuuint64_t)(mn / 32), (cuuint64_t)(inner_on ? batch_inner : 1),
+                                 (cuuint64_t)(outer_on ? batch_outer : 1) };
+    const long long plane = pitch * kdim;
+    const cuuint64_t strides[4] = { (cuuint64_t)pitch * 4ull, 128ull, stride_bytes(inner_on ? stride_inner : 0, plane),
+                                    stride_bytes(outer_on ? stride_outer : 0, plane) };
+    const cuuint32_t box[5] = { 32, (cuuint32_t)BK, (cuuint32_t)atoms, 1, 1 };
+    const cuuint32_t elem[5] = { 1, 1, 1, 1, 1 };
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 5, const_cast<float*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 static bool mult4(long long x) { return (x & 3) == 0; }
 
 template <int BN, int STAGES, int A_MN, int B_MN>
-static int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream)
+static int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const Params& p, cudaStream_t stream)
 {
-    constexpr int smem = STAGES * (A_STAGE_BYTES + BN * BK * 4) + 1024 + 256;
+    constexpr int smem = STAGES * (A_STAGE_BYTES + BN * BK * 4) + EPI_BYTES + 1024 + 256;
     static bool configured = false;
     if(!configured)
     {
@@ -499,17 +598,17 @@ static int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, co
     }
     const long long cap = (long long)kSmCount * (BN == 64 ? 2 : 1);
     const int grid = (int)(p.total_work < cap ? p.total_work : cap);
-    gemm_tc_kernel<BN, STAGES, A_MN, B_MN><<<grid, kThreads, smem, stream>>>(map_a, map_b, p);
+    gemm_tc_kernel<BN, STAGES, A_MN, B_MN><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_c, p);
     count_launch();
     return launch_status();
 }
 
 template <int A_MN, int B_MN>
-static int launch_majors(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream)
+static int launch_majors(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const Params& p, cudaStream_t stream)
 {
-    if(bn == 256) return launch_variant<256, 4, A_MN, B_MN>(map_a, map_b, p, stream);
-    if(bn == 128) return launch_variant<128, 6, A_MN, B_MN>(map_a, map_b, p, stream);
-    return launch_variant<64, 4, A_MN, B_MN>(map_a, map_b, p, stream);
+    if(bn == 256) return launch_variant<256, 4, A_MN, B_MN>(map_a, map_b, map_c, p, stream);
+    if(bn == 128) return launch_variant<128, 6, A_MN, B_MN>(map_a, map_b, map_c, p, stream);
+    return launch_variant<64, 3, A_MN, B_MN>(map_a, map_b, map_c, p, stream);
 }
 
 }  // namespace tc
@@ -541,6 +640,10 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
     p.a_batch_inner_on = g.batch_inner > 1 && g.a_stride_inner != 0; p.a_batch_outer_on = g.batch_outer > 1 && g.a_stride_outer != 0;
     p.b_batch_inner_on = g.batch_inner > 1 && g.b_stride_inner != 0; p.b_batch_outer_on = g.batch_outer > 1 && g.b_stride_outer != 0;
+    p.c_batch_inner_on = g.batch_inner > 1 && g.c_stride_inner != 0; p.c_batch_outer_on = g.batch_outer > 1 && g.c_stride_outer != 0;
+
+    p.a_wide = g.a_major == 1 && g.M % 32 == 0;
+    p.b_wide = g.b_major == 1 && g.N % 32 == 0;
 
     const long long k_blocks = (g.K + BK - 1) / BK;
     long long splits = g.split_k > 1 ? g.split_k : 1;
@@ -553,17 +656,21 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.n_blocks = (int)((g.N + bn - 1) / bn);
     p.total_work = (long long)p.m_blocks * p.n_blocks * splits * g.batch_inner * g.batch_outer;
 
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_c;
     bool ok;
     if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, BK, BM, false);
+    else if(p.a_wide) ok = make_wide_map(&map_a, g.A, g.M, g.K, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, BM / 32);
     else ok = make_map(&map_a, g.A, g.M, g.K, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, 32, BK, true);
     if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, BK, bn, false);
+    else if(p.b_wide) ok = ok && make_wide_map(&map_b, g.B, g.N, g.K, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, bn / 32);
     else ok = ok && make_map(&map_b, g.B, g.N, g.K, g.ldb, g.batch_inner, g.b_stride_inner, g.batch_outer, g.b_stride_outer, 32, BK, true);
+    // C: 32 x 32 blocks, plain fp32 (no rounding), 128-byte swizzle to match the staging layout
+    ok = ok && make_map(&map_c, g.C, g.N, g.M, g.ldc, g.batch_inner, g.c_stride_inner, g.batch_outer, g.c_stride_outer, 32, 32, false, false);
     if(!ok) return ONN_ERR_UNSUPPORTED;
 
-    if(g.a_major == 0 && g.b_major == 0) return launch_majors<0, 0>(bn, map_a, map_b, p, stream);
-    if(g.a_major == 0 && g.b_major == 1) return launch_majors<0, 1>(bn, map_a, map_b, p, stream);
-    if(g.a_major == 1 && g.b_major == 1) return launch_majors<1, 1>(bn, map_a, map_b, p, stream);
+    if(g.a_major == 0 && g.b_major == 0) return launch_majors<0, 0>(bn, map_a, map_b, map_c, p, stream);
+    if(g.a_major == 0 && g.b_major == 1) return launch_majors<0, 1>(bn, map_a, map_b, map_c, p, stream);
+    if(g.a_major == 1 && g.b_major == 1) return launch_majors<1, 1>(bn, map_a, map_b, map_c, p, stream);
     return ONN_ERR_UNSUPPORTED;
 }
 

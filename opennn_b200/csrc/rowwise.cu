@@ -255,26 +255,27 @@ layernorm_fwd_generic_kernel(const float* __restrict__ A, const float* __restric
 // rows it visits; the CTA folds its 8 warps through shared memory and writes ONE partial
 // row pair per CTA to `partials` ([gridDim.x][2][E]); colsum_partials_kernel finishes.
 template <int VEC>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 2)
 layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2, const float* __restrict__ dY3,
                      const float* __restrict__ X, const float* __restrict__ mean_in, const float* __restrict__ inv_std_in,
                      const float* __restrict__ gamma, float* __restrict__ dX, float* __restrict__ partials,
                      long long rows, int E)
 {
-    extern __shared__ float smem[];               // [kRowWarps][2][E]
+    // [kRowWarps][2][E]: every warp keeps its running column sums here, and every lane only ever touches
+    // its own columns, so plain loads and stores suffice; registers stay free for two CTAs per SM
+    extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
     const long long warp = (long long)blockIdx.x * kRowWarps + warp_in_block;
     const long long stride = (long long)gridDim.x * kRowWarps;
     const float inv_E = 1.0f / (float)E;
+    float* acc_gamma = smem + (size_t)warp_in_block * 2 * E;
+    float* acc_beta = acc_gamma + E;
 
-    float4 g[VEC], acc_gamma[VEC], acc_beta[VEC];
 #pragma unroll
     for(int i = 0; i < VEC; i++)
     {
         const int e = (i * 32 + lane) * 4;
-        g[i] = e < E ? ld4(gamma + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-        acc_gamma[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        acc_beta[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if(e < E) { st4(acc_gamma + e, make_float4(0.f, 0.f, 0.f, 0.f)); st4(acc_beta + e, make_float4(0.f, 0.f, 0.f, 0.f)); }
     }
 
     for(long long row = warp; row < rows; row += stride)
@@ -295,12 +296,14 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
                 if(dY2) { const float4 t = ld4_stream(dY2 + base + e); dy.x += t.x; dy.y += t.y; dy.z += t.z; dy.w += t.w; }
                 if(dY3) { const float4 t = ld4_stream(dY3 + base + e); dy.x += t.x; dy.y += t.y; dy.z += t.z; dy.w += t.w; }
                 const float4 x = ld4_stream(X + base + e);
+                const float4 g = ld4(gamma + e);
                 xh[i].x = (x.x - mean) * inv_std; xh[i].y = (x.y - mean) * inv_std;
                 xh[i].z = (x.z - mean) * inv_std; xh[i].w = (x.w - mean) * inv_std;
-                acc_gamma[i].x += dy.x * xh[i].x; acc_gamma[i].y += dy.y * xh[i].y;
-                acc_gamma[i].z += dy.z * xh[i].z; acc_gamma[i].w += dy.w * xh[i].w;
-                acc_beta[i].x += dy.x; acc_beta[i].y += dy.y; acc_beta[i].z += dy.z; acc_beta[i].w += dy.w;
-                d[i].x = dy.x * g[i].x; d[i].y = dy.y * g[i].y; d[i].z = dy.z * g[i].z; d[i].w = dy.w * g[i].w;
+                float4 ag = ld4(acc_gamma + e), ab = ld4(acc_beta + e);
+                ag.x += dy.x * xh[i].x; ag.y += dy.y * xh[i].y; ag.z += dy.z * xh[i].z; ag.w += dy.w * xh[i].w;
+                ab.x += dy.x; ab.y += dy.y; ab.z += dy.z; ab.w += dy.w;
+                st4(acc_gamma + e, ag); st4(acc_beta + e, ab);
+                d[i].x = dy.x * g.x; d[i].y = dy.y * g.y; d[i].z = dy.z * g.z; d[i].w = dy.w * g.w;
                 sum_d += (d[i].x + d[i].y) + (d[i].z + d[i].w);
                 sum_dx += (d[i].x * xh[i].x + d[i].y * xh[i].y) + (d[i].z * xh[i].z + d[i].w * xh[i].w);
             }
@@ -323,13 +326,6 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
         }
     }
 
-    float* mine = smem + (size_t)warp_in_block * 2 * E;
-#pragma unroll
-    for(int i = 0; i < VEC; i++)
-    {
-        const int e = (i * 32 + lane) * 4;
-        if(e < E) { st4(mine + e, acc_gamma[i]); st4(mine + E + e, acc_beta[i]); }
-    }
     __syncthreads();
     float* out = partials + (size_t)blockIdx.x * 2 * E;
     for(int c = threadIdx.x; c < 2 * E; c += kRowThreads)
@@ -477,7 +473,7 @@ extern "C" int onn_layernorm_fwd(const float* A, const float* R, const float* ga
 }
 
 // Number of CTAs the backward kernel runs with (= partial row pairs in the workspace).
-static int layernorm_bwd_grid(int64_t rows) { return grid_for(rows, kRowWarps, 2); }
+static int layernorm_bwd_grid(int64_t rows) { return grid_for(rows, kRowWarps, 2); }   // two resident CTAs per SM
 
 extern "C" size_t onn_layernorm_bwd_workspace_floats(int64_t rows, int64_t E)
 {
@@ -502,9 +498,7 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
     {
         const size_t smem = (size_t)kRowWarps * 2 * E * sizeof(float);   // <= 64 KiB at E = 1024
         if(smem > 48 * 1024)
-        {
             cudaFuncSetAttribute(layernorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        }
         switch(vec_count(E))
         {
             case 1: ONN_LN_BWD(1); break;

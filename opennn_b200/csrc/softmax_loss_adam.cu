@@ -79,6 +79,64 @@ attention_softmax_kernel(float* __restrict__ scores, const uint8_t* __restrict__
     }
 }
 
+// 128-bit variant for Sk % 4 == 0: each lane owns VEC float4 of the row (Sk <= 128 * VEC).
+template <int VEC>
+__global__ void __launch_bounds__(256)
+attention_softmax_vec_kernel(float* __restrict__ scores, const uint8_t* __restrict__ key_is_pad,
+                             long long rows, int H, int Sq, int Sk, int causal)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * 8;
+    for(long long row = warp; row < rows; row += stride)
+    {
+        const int q = (int)(row % Sq);
+        const long long b = row / ((long long)Sq * H);
+        const uint8_t* pad = key_is_pad ? key_is_pad + b * Sk : nullptr;
+        float* p = scores + row * (long long)Sk;
+        float4 v[VEC];
+        float row_max = -INFINITY;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            const int k = (i * 32 + lane) * 4;
+            v[i] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            if(k < Sk)
+            {
+                v[i] = ld4_stream(p + k);
+                if(pad)
+                {
+                    const uchar4 f = *reinterpret_cast<const uchar4*>(pad + k);
+                    if(f.x) v[i].x = -1e9f; if(f.y) v[i].y = -1e9f; if(f.z) v[i].z = -1e9f; if(f.w) v[i].w = -1e9f;
+                }
+                if(causal)
+                {
+                    if(k > q) v[i].x = -INFINITY; if(k + 1 > q) v[i].y = -INFINITY;
+                    if(k + 2 > q) v[i].z = -INFINITY; if(k + 3 > q) v[i].w = -INFINITY;
+                }
+            }
+            row_max = fmaxf(row_max, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+        }
+        row_max = warp_max(row_max);
+        float total = 0.f;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            v[i].x = __expf(v[i].x - row_max); v[i].y = __expf(v[i].y - row_max);
+            v[i].z = __expf(v[i].z - row_max); v[i].w = __expf(v[i].w - row_max);
+            total += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+        total = warp_sum(total);
+        const float inv = total > 0.f ? 1.0f / total : 0.f;
+#pragma unroll
+        for(int i = 0; i < VEC; i++)
+        {
+            const int k = (i * 32 + lane) * 4;
+            if(k < Sk) st4(p + k, make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv));
+        }
+    }
+}
+
 // Any Sk: three sweeps through global memory (the row stays in L1/L2).
 __global__ void __launch_bounds__(256)
 attention_softmax_generic_kernel(float* __restrict__ scores, const uint8_t* __restrict__ key_is_pad,
@@ -385,6 +443,48 @@ colsum_accumulate_kernel(const float* __restrict__ D, long long rows, long long 
     }
 }
 
+// Same sums for 16-byte aligned rows: each CTA owns a 128-column strip (one float4 per lane)
+// and a slab of rows; 8 warps stride the slab with four independent loads in flight each.
+__global__ void __launch_bounds__(256)
+colsum_accumulate_vec_kernel(const float* __restrict__ D, long long rows, long long cols, long long ld,
+                             long long rows_per_block, float* __restrict__ out)
+{
+    __shared__ float4 partial[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long c = (long long)blockIdx.x * 128 + lane * 4;
+    const long long r0 = (long long)blockIdx.y * rows_per_block;
+    const long long r1 = min(rows, r0 + rows_per_block);
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a, e = a, f = a;
+    if(c < cols)
+    {
+        long long r = r0 + warp;
+        for(; r + 24 < r1; r += 32)
+        {
+            const float4 x0 = ld4_stream(D + r * ld + c), x1 = ld4_stream(D + (r + 8) * ld + c);
+            const float4 x2 = ld4_stream(D + (r + 16) * ld + c), x3 = ld4_stream(D + (r + 24) * ld + c);
+            a.x += x0.x; a.y += x0.y; a.z += x0.z; a.w += x0.w;
+            b.x += x1.x; b.y += x1.y; b.z += x1.z; b.w += x1.w;
+            e.x += x2.x; e.y += x2.y; e.z += x2.z; e.w += x2.w;
+            f.x += x3.x; f.y += x3.y; f.z += x3.z; f.w += x3.w;
+        }
+        for(; r < r1; r += 8)
+        {
+            const float4 x0 = ld4_stream(D + r * ld + c);
+            a.x += x0.x; a.y += x0.y; a.z += x0.z; a.w += x0.w;
+        }
+    }
+    partial[warp][lane] = make_float4((a.x + b.x) + (e.x + f.x), (a.y + b.y) + (e.y + f.y), (a.z + b.z) + (e.z + f.z), (a.w + b.w) + (e.w + f.w));
+    __syncthreads();
+    if(warp == 0 && c < cols)
+    {
+        float4 total = partial[0][lane];
+#pragma unroll
+        for(int w = 1; w < 8; w++) { const float4 t = partial[w][lane]; total.x += t.x; total.y += t.y; total.z += t.z; total.w += t.w; }
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                     :: "l"(out + c), "f"(total.x), "f"(total.y), "f"(total.z), "f"(total.w) : "memory");
+    }
+}
+
 // delta = dY * (Y > 0), in place over dY.
 __global__ void relu_delta_kernel(float* __restrict__ dY, const float* __restrict__ Y, long long n)
 {
@@ -504,6 +604,17 @@ int launch_attention_softmax(float* scores, const uint8_t* key_is_pad, long long
 {
     const long long rows = B * H * Sq;
     const int grid = grid_for(rows, 8, 8);
+    if((Sk & 3) == 0 && Sk <= 1024 && host_aligned16(scores))
+    {
+#define ONN_SMV(N) attention_softmax_vec_kernel<N><<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal)
+        if(Sk <= 128) ONN_SMV(1);
+        else if(Sk <= 256) ONN_SMV(2);
+        else if(Sk <= 512) ONN_SMV(4);
+        else ONN_SMV(8);
+#undef ONN_SMV
+        count_launch();
+        return launch_status();
+    }
 #define ONN_SM(N) attention_softmax_kernel<N><<<grid, 256, 0, s>>>(scores, key_is_pad, rows, H, Sq, Sk, causal)
     if(Sk <= 32) ONN_SM(1);
     else if(Sk <= 64) ONN_SM(2);
@@ -534,6 +645,19 @@ int launch_attention_softmax_bwd(const float* P, float* dP, long long rows, int 
 
 int launch_colsum_accumulate(const float* D, long long rows, long long cols, long long ld, float* out, cudaStream_t s)
 {
+    if((cols & 3) == 0 && (ld & 3) == 0 && host_aligned16(D) && host_aligned16(out))
+    {
+        const long long strips = (cols + 127) / 128;
+        long long slabs = (4LL * kSmCount + strips - 1) / strips;       // ~4 CTAs per SM overall
+        if(slabs > (rows + 63) / 64) slabs = (rows + 63) / 64;
+        if(slabs < 1) slabs = 1;
+        if(slabs > 65535) slabs = 65535;
+        const long long rows_per_block = (rows + slabs - 1) / slabs;
+        dim3 grid((unsigned)strips, (unsigned)((rows + rows_per_block - 1) / rows_per_block));
+        colsum_accumulate_vec_kernel<<<grid, 256, 0, s>>>(D, rows, cols, ld, rows_per_block, out);
+        count_launch();
+        return launch_status();
+    }
     const long long strips = (cols + 31) / 32;
     long long slabs = (2LL * kSmCount + strips - 1) / strips;          // ~2 CTAs per SM overall
     if(slabs > (rows + 255) / 256) slabs = (rows + 255) / 256;
