@@ -3,7 +3,7 @@
 TEST INFRASTRUCTURE ONLY.  This module is the checker for the CUDA path: only the tests,
 the smoke check and the benchmark's CPU-baseline leg may import it.  No product code does.
 
-Parity is pinned: `oracle/check_against_ref.py` runs the unmodified reference CPU library
+Parity is pinned: `tests/golden/make_golden.py` runs the unmodified reference CPU library
 (built by `oracle/Makefile` into `oracle/_ref/`) on the same seeded inputs and compares
 every function below with it; the outputs it produced are committed under `tests/golden/`.
 
@@ -250,13 +250,16 @@ def ce3d_error(probabilities, targets):
     return F32(total / F32(count)), F32(F32(correct) / F32(count)), count
 
 
-def ce3d_output_gradients(probabilities, targets):
-    """opennn/cross_entropy_error_3d.cpp:154-247: (p - onehot)/active on active tokens, 0 elsewhere."""
+def ce3d_output_gradients(probabilities, targets, active_count=None):
+    """opennn/cross_entropy_error_3d.cpp:154-247: (p - onehot)/active on active tokens, 0 elsewhere.
+    active_count overrides the divisor: a data-parallel rank scales its shard by the count of
+    the WHOLE batch, so that the sum of the ranks' gradients is the gradient of the whole batch."""
     B, S, V = probabilities.shape
     t = token_index(targets)
     active = (t > 0) & (t < V)
     count = int(active.sum())
-    scale = F32(1.0) / F32(count) if count > 0 else F32(0)
+    divisor = count if active_count is None else int(active_count)
+    scale = F32(1.0) / F32(divisor) if divisor > 0 else F32(0)
     grad = np.zeros_like(probabilities, dtype=F32)
     onehot = np.zeros((count, V), dtype=F32)
     onehot[np.arange(count), t[active]] = 1

@@ -1,0 +1,63 @@
+"""CPU, two gloo ranks: the data-parallel rule the GPU driver implements
+(opennn_b200/host/driver_abi.cpp) restated with the numpy oracle.  Each rank takes a contiguous
+slice of the batch, scales its loss gradient by the active-token count of the WHOLE batch
+(summed across ranks first), and the ranks' parameter gradients are summed: the result must be
+the gradient of the whole batch, and Adam on it must give the same parameters on every rank."""
+
+import os
+import tempfile
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import opennn_oracle as O
+from tests.golden.make_golden import network_inputs
+
+
+def _rank_main(rank, world, init_file, out_dir):
+    dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world)
+    net, params, external, targets = network_inputs("tiny_encdec_odd")
+    batch = targets.shape[0]
+    # ragged split on purpose (3 samples over 2 ranks): slices need not be equal
+    bounds = np.linspace(0, batch, world + 1).astype(int)
+    lo, hi = bounds[rank], bounds[rank + 1]
+    shard = {k: v[lo:hi] for k, v in external.items()}
+    shard_targets = targets[lo:hi]
+
+    t = O.token_index(shard_targets)
+    count = torch.tensor([float(((t > 0) & (t < net.layers[-1]["out"])).sum())])
+    dist.all_reduce(count)                                   # (1) global active-token count
+
+    probabilities = net.forward(params, shard)
+    gradient = net.backward(params, O.ce3d_output_gradients(probabilities, shard_targets, active_count=int(count.item())))
+    reduced = torch.from_numpy(gradient.copy())
+    dist.all_reduce(reduced)                                 # (2) sum of the parameter gradients
+
+    arena, m, v = params.copy(), np.zeros_like(params), np.zeros_like(params)
+    O.adam_update(arena, reduced.numpy(), m, v, 2)           # (3) clip + Adam on the reduced gradient, every rank
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), gradient=reduced.numpy(), params=arena, count=count.numpy())
+    dist.destroy_process_group()
+
+
+def test_two_ranks_reproduce_the_whole_batch_step():
+    world = 2
+    with tempfile.TemporaryDirectory() as out_dir:
+        init_file = os.path.join(out_dir, "rendezvous")
+        mp.spawn(_rank_main, args=(world, init_file, out_dir), nprocs=world, join=True)
+        ranks = [np.load(os.path.join(out_dir, f"rank{r}.npz")) for r in range(world)]
+
+    net, params, external, targets = network_inputs("tiny_encdec_odd")
+    probabilities = net.forward(params, external)
+    _, _, count = O.ce3d_error(probabilities, targets)
+    gradient = net.backward(params, O.ce3d_output_gradients(probabilities, targets))
+    arena, m, v = params.copy(), np.zeros_like(params), np.zeros_like(params)
+    O.adam_update(arena, gradient, m, v, 2)
+
+    for r in ranks:
+        assert int(r["count"][0]) == count
+        scale = np.abs(gradient).max()
+        assert np.abs(r["gradient"] - gradient).max() <= 1e-5 * scale
+        assert np.abs(r["params"] - arena).max() <= 2e-6
+    assert np.array_equal(ranks[0]["params"], ranks[1]["params"]), "replicas must stay identical"
