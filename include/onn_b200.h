@@ -148,6 +148,28 @@ int onn_layernorm_bwd(const float* dY, const float* dY2, const float* dY3, const
                       float* dX, float* dgamma, float* dbeta,
                       int64_t rows, int64_t E, float* workspace, uint32_t flags, void* stream);
 
+/* No counterpart in the reference.  The same computation as onn_layernorm_bwd for a caller that
+ * holds nothing but the layer's inputs and outputs and cannot obtain device memory of its own:
+ * code running inside OpenNN's `back_propagate(...) const` overrides sees only the views that the
+ * stock propagation structures linked at set-up time (there is no slot for a scratch view unless
+ * the structures are changed), and hosts that hand out all device memory once at start-up refuse
+ * later cudaMalloc calls.  This entry point therefore takes no workspace and allocates nothing:
+ * its partial column sums go to a fixed 2.3 MiB buffer inside the library (held by every GPU that
+ * loads the library, until exit).
+ *   - E must not exceed ONN_LAYERNORM_BWD_STATIC_MAX_E; larger rows return ONN_ERR_LIMIT.
+ *   - The first call on each device looks up the buffer's device address (one
+ *     cudaGetSymbolAddress with that device current); make that first call before any stream
+ *     capture begins.
+ *   - All calls share the one buffer: two calls whose kernels can overlap on the GPU (different
+ *     streams, no ordering between them) race on it and corrupt each other's dgamma / dbeta.
+ *     Calls on one stream, or ordered by events, are safe.  The buffer keeps the last call's
+ *     partial sums; nothing in it needs clearing between calls. */
+#define ONN_LAYERNORM_BWD_STATIC_MAX_E 1024
+int onn_layernorm_bwd_static(const float* dY, const float* dY2, const float* dY3, const float* X,
+                             const float* mean, const float* inv_std, const float* gamma,
+                             float* dX, float* dgamma, float* dbeta,
+                             int64_t rows, int64_t E, uint32_t flags, void* stream);
+
 /* Addition<3> stand-alone: out = a + b.  Replaces addition_kernel (opennn/kernel.cu:691-699). */
 int onn_add(const float* a, const float* b, float* out, int64_t n, uint32_t flags, void* stream);
 

@@ -51,7 +51,7 @@ class MhaGrads(C.Structure):
 EXPORTS = [
     "onn_status_string", "onn_version", "onn_gemm", "onn_gemm_set_mode", "onn_gemm_device_status",
     "onn_launch_count", "onn_embedding_fwd", "onn_embedding_bwd",
-    "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_add",
+    "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
     "onn_dense_fwd", "onn_dense_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
     "onn_mha_attention_weights", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",

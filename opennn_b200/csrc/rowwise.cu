@@ -1,6 +1,8 @@
 // HBM-bound row kernels: Embedding forward/backward, Normalization3d (+ fused Addition)
 // forward/backward, Addition.  One warp owns one [E]-row; the row lives in
 // registers, reductions are warp shuffles, global access is 128-bit where E % 4 == 0.
+#include <mutex>
+
 #include "common.cuh"
 #include "launch_counter.h"
 
@@ -536,6 +538,57 @@ extern "C" int onn_layernorm_bwd(const float* dY, const float* dY2, const float*
     ONN_CHECK_ARG(dY && X && mean && inv_std && gamma && dX && dgamma && dbeta && rows > 0 && E > 0);
     if(!workspace) return ONN_ERR_WORKSPACE;
     return layernorm_bwd_launch(dY, dY2, dY3, X, mean, inv_std, gamma, dX, dgamma, dbeta, rows, E, workspace, flags,
+                                (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Normalization3d backward for callers that have no way to provide scratch memory
+// ---------------------------------------------------------------------------------------
+
+// Room for the per-CTA partial column sums of the largest supported call:
+// (2 CTAs per SM) x {sum dy*x_hat, sum dy} x ONN_LAYERNORM_BWD_STATIC_MAX_E floats = 2.3 MiB.
+// It lives in the library image, so every GPU that loads the library holds it until exit.
+static __device__ __align__(256) float g_layernorm_bwd_static_partials[2 * kSmCount * 2 * ONN_LAYERNORM_BWD_STATIC_MAX_E];
+
+namespace
+{
+constexpr int kMaxDevices = 64;
+std::mutex g_static_partials_mutex;
+float* g_static_partials_address[kMaxDevices] = {};    // device address of the array above, per device
+
+// In host code the array's name is only a handle: the device address has to be asked for, once per
+// device, with that device current.
+int static_partials_for_current_device(float** address)
+{
+    int device = -1;
+    if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return ONN_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_static_partials_mutex);
+    if(!g_static_partials_address[device])
+    {
+        float* resolved = nullptr;
+        if(cudaGetSymbolAddress(reinterpret_cast<void**>(&resolved), g_layernorm_bwd_static_partials) != cudaSuccess || !resolved)
+            return ONN_ERR_CUDA;
+        g_static_partials_address[device] = resolved;
+    }
+    *address = g_static_partials_address[device];
+    return ONN_OK;
+}
+}  // namespace
+
+extern "C" int onn_layernorm_bwd_static(const float* dY, const float* dY2, const float* dY3, const float* X,
+                                        const float* mean, const float* inv_std, const float* gamma,
+                                        float* dX, float* dgamma, float* dbeta,
+                                        int64_t rows, int64_t E, uint32_t flags, void* stream)
+{
+    ONN_CHECK_ARG(dY && X && mean && inv_std && gamma && dX && dgamma && dbeta && rows > 0 && E > 0);
+    if(E > ONN_LAYERNORM_BWD_STATIC_MAX_E) return ONN_ERR_LIMIT;      // the fixed buffer holds rows of at most this width
+    if(onn_layernorm_bwd_workspace_floats(rows, E) > sizeof(g_layernorm_bwd_static_partials) / sizeof(float)) return ONN_ERR_LIMIT;
+    float* partials = nullptr;
+    const int status = static_partials_for_current_device(&partials);
+    if(status != ONN_OK) return status;
+    // Nothing in the buffer has to start at zero: the row kernel overwrites one partial row pair per CTA
+    // and the column reduction reads exactly those, so whatever an earlier call left behind is never read.
+    return layernorm_bwd_launch(dY, dY2, dY3, X, mean, inv_std, gamma, dX, dgamma, dbeta, rows, E, partials, flags,
                                 (cudaStream_t)stream);
 }
 
