@@ -34,6 +34,7 @@
 // producer drains the copies it still has in flight, TMEM is freed and the kernel returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -514,6 +515,304 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+
+// =========================================================================================
+// Two-CTA variant (cta_group::2) for the large dense GEMMs.
+//
+// A cluster of two CTAs on neighbouring SMs computes one 256 x 256 tile: CTA r owns rows
+// 128r..128r+127 (its own A tile, its own TMEM accumulator) and stages only HALF of the B tile
+// (columns 128r..128r+127); the tensor cores of both SMs read both halves.  Per SM and k-block
+// the copy engine writes 32 KB instead of 48 KB and the MMA reads 32 KB instead of 48 KB, which
+// lifts the shared-memory-bandwidth ceiling of 4-byte operands from 0.68 to 1.0 of the tensor
+// peak, and L2 -> SM operand traffic drops by a third.  No load uses multicast: each CTA copies
+// its own halves, with the completion bytes counted on the leader's barrier.
+//
+// Barriers: full[s] lives in the leader (CTA 0): its producer arms it for the bytes of BOTH
+// CTAs, the peer's copies complete on it remotely.  empty[s] and acc_full[b] exist in both CTAs
+// and are signalled by the leader's tcgen05.commit to both.  acc_empty[b] lives in the leader
+// and counts the epilogue warps of both CTAs.
+// =========================================================================================
+
+constexpr int STAGES2 = 6;
+constexpr int STAGE2_BYTES = A_STAGE_BYTES + 128 * BK * 4;          // A 16 KiB + half of B 16 KiB
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+
+// copies of a CTA pair: data lands in the executing CTA, completion bytes go to the barrier at
+// `bar` (a shared::cluster address, here always the leader's)
+__device__ __forceinline__ void tma2_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void tma2_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_mma2_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n" :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// arrive on the barrier at the same offset in BOTH CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tcgen05_commit2_both(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(bar), "h"((uint16_t)3) : "memory");
+}
+
+__host__ __device__ constexpr uint32_t make_idesc2(int a_mn_major, int b_mn_major)
+{
+    // D = fp32, A = B = tf32, M = 256 (128 rows per CTA), N = 256
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c, const Params p)
+{
+    constexpr int BN = 256;
+    constexpr uint32_t TMEM_COLS = 512;                       // two 256-column accumulator buffers per CTA
+    constexpr uint32_t IDESC = make_idesc2(A_MN, B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* epi_smem = smem + (size_t)STAGES2 * STAGE2_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + EPI_BYTES);
+    uint64_t* full_bar = bars;                                // [STAGES2]  used in the leader only
+    uint64_t* empty_bar = bars + STAGES2;                     // [STAGES2]  both CTAs
+    uint64_t* acc_full_bar = bars + 2 * STAGES2;              // [2]        both CTAs
+    uint64_t* acc_empty_bar = bars + 2 * STAGES2 + 2;         // [2]        used in the leader only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const long long pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if(threadIdx.x == 0)
+    {
+        for(int s = 0; s < STAGES2; s++) { mbar_init(smem_u32(full_bar + s), 1); mbar_init(smem_u32(empty_bar + s), 1); }
+        for(int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full_bar + a), 1); mbar_init(smem_u32(acc_empty_bar + a), 2 * kEpilogueWarps); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if(warp == 1)
+    {
+        // both CTAs of the pair run the allocation with the same destination offset
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();                                           // the peer's barriers exist before anyone signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if(warp == 0)
+    {
+        // ---------------- TMA producer (one per CTA: own A rows, own half of B) ----------------
+        if(lane == 0)
+        {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for(long long w = pair; ok && w < p.total_work; w += pairs)
+            {
+                const WorkItem it = decode_work(p, w);
+                const int m0 = it.m_blk * 256 + (int)rank * 128, n0 = it.n_blk * BN + (int)rank * 128;
+                for(int kb = 0; kb < it.k_blocks; kb++)
+                {
+                    if(!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag, 11)) { ok = false; break; }
+                    const uint32_t bar = map_to_cta(smem_u32(full_bar + stage), 0);      // the leader's barrier
+                    const uint32_t a_dst = smem_u32(smem + (size_t)stage * STAGE2_BYTES);
+                    const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+                    const int k0 = (int)(it.k_begin + (long long)kb * BK);
+                    if(leader) mbar_arrive_expect_tx(smem_u32(full_bar + stage), 2 * STAGE2_BYTES);
+                    if(A_MN) tma2_load_5d(a_dst, &map_a, bar, 0, k0, m0 / 32, 0, 0);
+                    else tma2_load_4d(a_dst, &map_a, bar, k0, m0, 0, 0);
+                    if(B_MN) tma2_load_5d(b_dst, &map_b, bar, 0, k0, n0 / 32, 0, 0);
+                    else tma2_load_4d(b_dst, &map_b, bar, k0, n0, 0, 0);
+                    if(++stage == STAGES2) { stage = 0; phase ^= 1; }
+                }
+            }
+            if(*abort_flag)
+            {
+                // give copies that are still in flight time to land before this CTA's shared memory goes away
+                const unsigned long long start = clock64();
+                while(clock64() - start < 200000ull) { }
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        // ---------------- MMA issuer (leader only) ----------------
+        if(lane == 0 && leader)
+        {
+            uint32_t stage = 0, phase = 0;
+            long long local = 0;
+            bool ok = true;
+            for(long long w = pair; ok && w < p.total_work; w += pairs, local++)
+            {
+                const WorkItem it = decode_work(p, w);
+                const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
+                if(!mbar_wait(smem_u32(acc_empty_bar + acc), acc_phase ^ 1, abort_flag, 12)) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for(int kb = 0; kb < it.k_blocks; kb++)
+                {
+                    if(!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, 13)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE2_BYTES);
+                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+                    const uint64_t a_desc = A_MN ? make_smem_desc(a_addr, 4096, 512, 1) : make_smem_desc(a_addr, 16, 1024, 2);
+                    const uint64_t b_desc = B_MN ? make_smem_desc(b_addr, 4096, 512, 1) : make_smem_desc(b_addr, 16, 1024, 2);
+#pragma unroll
+                    for(int j = 0; j < BK / UMMA_K; j++)
+                    {
+                        const uint64_t a_step = A_MN ? (uint64_t)(j * 1024 >> 4) : (uint64_t)(j * UMMA_K * 4 >> 4);
+                        const uint64_t b_step = B_MN ? (uint64_t)(j * 1024 >> 4) : (uint64_t)(j * UMMA_K * 4 >> 4);
+                        tcgen05_mma2_tf32(d_tmem, a_desc + a_step, b_desc + b_step, IDESC, (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit2_both(smem_u32(empty_bar + stage));     // frees this stage in both CTAs
+                    if(++stage == STAGES2) { stage = 0; phase ^= 1; }
+                }
+                if(!ok) break;
+                tcgen05_commit2_both(smem_u32(acc_full_bar + acc));         // accumulators complete in both CTAs
+            }
+        }
+    }
+    else
+    {
+        // ---------------- epilogue (warps 2..5 of each CTA, its own 128 rows) ----------------
+        const int quadrant = warp & 3;
+        long long local = 0;
+        unsigned int staged_chunks = 0;
+        const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty_bar), 0);
+        for(long long w = pair; w < p.total_work; w += pairs, local++)
+        {
+            const WorkItem it = decode_work(p, w);
+            const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
+            bool ok = true;
+            if(lane == 0) ok = mbar_wait(smem_u32(acc_full_bar + acc), acc_phase, abort_flag, 14);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if(!ok) break;
+            tcgen05_fence_after();
+
+            const long long n0 = (long long)it.n_blk * BN;
+            const bool use_bias = p.bias != nullptr && it.split == 0;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * BN;
+            const long long warp_row0 = (long long)it.m_blk * 256 + (long long)rank * 128 + quadrant * 32;
+            const bool reduce = p.accumulate || p.splits > 1;
+
+#pragma unroll 1
+            for(int c = 0; c < BN / 32; c++)
+            {
+                const long long n_base = n0 + c * 32;
+                if(n_base >= p.N || warp_row0 >= p.M) break;
+                float v[32];
+                __syncwarp();
+                tmem_load_32(taddr + c * 32, v);
+                const uint32_t block = smem_u32(epi_smem + ((warp - 2) * 2 + (int)(staged_chunks & 1)) * EPI_BLOCK_BYTES);
+                if(staged_chunks >= 2) { if(lane == 0) bulk_wait_read_1(); __syncwarp(); }
+#pragma unroll
+                for(int q4 = 0; q4 < 8; q4++)
+                {
+                    const long long n = n_base + q4 * 4;
+                    float x[4] = { v[q4 * 4] * p.alpha, v[q4 * 4 + 1] * p.alpha, v[q4 * 4 + 2] * p.alpha, v[q4 * 4 + 3] * p.alpha };
+                    if(use_bias)
+                    {
+                        if(n + 3 < p.N) { const float4 b = ld4(p.bias + n); x[0] += b.x; x[1] += b.y; x[2] += b.z; x[3] += b.w; }
+                        else for(int e = 0; e < 4; e++) if(n + e < p.N) x[e] += p.bias[n + e];
+                    }
+                    if(p.relu) { x[0] = fmaxf(x[0], 0.f); x[1] = fmaxf(x[1], 0.f); x[2] = fmaxf(x[2], 0.f); x[3] = fmaxf(x[3], 0.f); }
+                    const uint32_t dst = block + (uint32_t)lane * 128u + (uint32_t)((q4 ^ (lane & 7)) << 4);
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+                }
+                if(p.relu_mask)
+                {
+                    // the mask block is read with whole 128-byte rows per 8 lanes (4 rows per pass) and applied
+                    // to the staged values: row = pass * 4 + lane / 8, 16-byte chunk = lane % 8
+                    __syncwarp();
+#pragma unroll
+                    for(int pass = 0; pass < 8; pass++)
+                    {
+                        const int r = pass * 4 + (lane >> 3), chunk = lane & 7;
+                        const long long row = warp_row0 + r, n = n_base + chunk * 4;
+                        if(row < p.M && n + 3 < p.N)
+                        {
+                            const float4 k = ld4(p.relu_mask + row * p.ldc + n);
+                            const uint32_t at = block + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4);
+                            float4 x;
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(at) : "memory");
+                            x.x = k.x > 0.f ? x.x : 0.f; x.y = k.y > 0.f ? x.y : 0.f; x.z = k.z > 0.f ? x.z : 0.f; x.w = k.w > 0.f ? x.w : 0.f;
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(at), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
+                        }
+                    }
+                }
+                fence_async_shared();
+                __syncwarp();
+                if(lane == 0)
+                {
+                    if(reduce) tma_reduce_add_4d(&map_c, block, (int)n_base, (int)warp_row0, 0, 0);
+                    else tma_store_4d(&map_c, block, (int)n_base, (int)warp_row0, 0, 0);
+                    bulk_commit();
+                }
+                staged_chunks++;
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if(lane == 0) mbar_arrive_cluster(leader_acc_empty + acc * 8);     // one arrival per epilogue warp of the pair
+        }
+        if(lane == 0) bulk_wait_all();
+    }
+
+    // nobody leaves while the partner may still read this CTA's shared memory or signal its barriers
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if(warp == 1)
+    {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -611,6 +910,25 @@ static int launch_majors(int bn, const CUtensorMap& map_a, const CUtensorMap& ma
     return launch_variant<64, 3, A_MN, B_MN>(map_a, map_b, map_c, p, stream);
 }
 
+
+template <int A_MN, int B_MN>
+static int launch_pair_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const Params& p, cudaStream_t stream)
+{
+    constexpr int smem = STAGES2 * STAGE2_BYTES + EPI_BYTES + 1024 + 256;
+    static bool configured = false;
+    if(!configured)
+    {
+        if(cudaFuncSetAttribute(gemm_tc2_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return ONN_ERR_CUDA;
+        configured = true;
+    }
+    const long long pairs_cap = kSmCount / 2;
+    const long long pairs = p.total_work < pairs_cap ? p.total_work : pairs_cap;
+    gemm_tc2_kernel<A_MN, B_MN><<<(unsigned)(2 * pairs), kThreads, smem, stream>>>(map_a, map_b, map_c, p);
+    count_launch();
+    return launch_status();
+}
+
 }  // namespace tc
 
 bool gemm_tc_supported(const onn_gemm_args& g)
@@ -658,6 +976,27 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
 
     CUtensorMap map_a, map_b, map_c;
     bool ok;
+
+    // large single GEMMs go to the two-CTA kernel (256 x 256 tiles per CTA pair)
+    static const bool pair_enabled = []{ const char* e = std::getenv("ONN_B200_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    const bool pair = pair_enabled && g.batch_inner == 1 && g.batch_outer == 1 && g.M >= 512 && g.N >= 256 &&
+                      (g.a_major == 0 || p.a_wide) && (g.b_major == 0 || p.b_wide);
+    if(pair)
+    {
+        p.m_blocks = (int)((g.M + 255) / 256);
+        p.n_blocks = (int)((g.N + 255) / 256);
+        p.total_work = (long long)p.m_blocks * p.n_blocks * splits;
+        if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, 1, 0, 1, 0, BK, BM, false);
+        else ok = make_wide_map(&map_a, g.A, g.M, g.K, g.lda, 1, 0, 1, 0, BM / 32);
+        if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, 1, 0, 1, 0, BK, 128, false);
+        else ok = ok && make_wide_map(&map_b, g.B, g.N, g.K, g.ldb, 1, 0, 1, 0, 128 / 32);
+        ok = ok && make_map(&map_c, g.C, g.N, g.M, g.ldc, 1, 0, 1, 0, 32, 32, false, false);
+        if(!ok) return ONN_ERR_UNSUPPORTED;
+        if(g.a_major == 0 && g.b_major == 0) return launch_pair_variant<0, 0>(map_a, map_b, map_c, p, stream);
+        if(g.a_major == 0 && g.b_major == 1) return launch_pair_variant<0, 1>(map_a, map_b, map_c, p, stream);
+        return launch_pair_variant<1, 1>(map_a, map_b, map_c, p, stream);
+    }
+
     if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, BK, BM, false);
     else if(p.a_wide) ok = make_wide_map(&map_a, g.A, g.M, g.K, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, BM / 32);
     else ok = make_map(&map_a, g.A, g.M, g.K, g.lda, g.batch_inner, g.a_stride_inner, g.batch_outer, g.a_stride_outer, 32, BK, true);

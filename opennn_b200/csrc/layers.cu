@@ -36,13 +36,25 @@ static onn_gemm_args plain_gemm(const float* A, int a_major, long long lda, cons
 // gradients: small [in, out] outputs with a reduction over every token).
 static int choose_split_k(long long M, long long N, long long K)
 {
+    // work units: 256 x 256 tiles on CTA pairs (74 of them) for large aligned outputs, else 128 x BN tiles on 148 CTAs
+    const bool pair = M >= 512 && N >= 256 && M % 32 == 0 && N % 32 == 0;
     const long long bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
-    const long long tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
-    if(tiles >= kSmCount || K < 1024) return 1;
-    long long splits = (2LL * kSmCount + tiles - 1) / tiles;
-    const long long max_splits = K / 256;                  // at least 8 k-blocks per split
-    if(splits > max_splits) splits = max_splits;
-    return (int)(splits < 1 ? 1 : splits);
+    const long long tiles = pair ? ((M + 255) / 256) * ((N + 255) / 256) : ((M + 127) / 128) * ((N + bn - 1) / bn);
+    const long long units = pair ? kSmCount / 2 : kSmCount;
+    if(tiles >= 4 * units || K < 1024) return 1;
+    // pick the split count whose last wave is fullest; every extra split costs one more pass of
+    // reduce-adds over the output, so ties go to the smaller count
+    const long long max_splits = K / 512 < 16 ? K / 512 : 16;
+    int best = 1;
+    double best_score = 0.0;
+    for(long long s = 1; s <= max_splits; s++)
+    {
+        const long long work = tiles * s;
+        const long long waves = (work + units - 1) / units;
+        const double score = (double)work / (double)(waves * units) - 0.004 * (double)s;
+        if(score > best_score + 1e-9) { best_score = score; best = (int)s; }
+    }
+    return best;
 }
 
 // dW += X^T D (X [rows, in], D [rows, out]) and db += column sums of D.

@@ -191,7 +191,8 @@ def test_adam_and_norm(capi):
 
 
 @pytest.mark.parametrize("a_major,b_major", [(0, 1), (0, 0), (1, 1)])
-@pytest.mark.parametrize("shape", [(128, 256, 64), (300, 520, 136), (64, 48, 1056), (1000, 72, 40)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (300, 520, 136), (64, 48, 1056), (1000, 72, 40),
+                                   (1000, 520, 136), (1024, 512, 200)])   # the last two reach the two-CTA kernel
 def test_gemm_layouts(capi, gemm_mode, a_major, b_major, shape):
     """The GEMM primitive in every operand layout the layers use, with ragged M, N and K
     (zero-filled TMA boxes, masked epilogue) and each epilogue option."""
