@@ -90,7 +90,7 @@ def run_reference(args):
     w = WORKLOAD
     from oracle import ref_runner
     if not ref_runner.available():
-        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/onn_ref_harness is not built (make -C oracle)"}))
+        emit({"impl": "reference", "unavailable": "oracle/_ref/onn_ref_harness is not built (make -C oracle)"})
         return
     sample_batch = 2
     steps = max(2, min(args.steps + min(args.warmup, 1), 3))
@@ -107,7 +107,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.time() - start,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ---------------------------------------------------------------------------------------
@@ -289,8 +289,8 @@ def run_ours(args):
 
     if args.profile_batch:
         if rank == 0:
-            print(json.dumps({"profiling_only": True, "workload": w["name"], "ms_per_step": 1e3 * seconds / args.steps,
-                              "gpu_launches": int(launches)}))
+            emit({"profiling_only": True, "workload": w["name"], "ms_per_step": 1e3 * seconds / args.steps,
+                  "gpu_launches": int(launches)})
         t.close()
         return
     host_step(0)                                  # warm the host path (staging buffers)
@@ -322,7 +322,7 @@ def run_ours(args):
                     "last_loss": last_stats[0][0] if last_stats[0] else None},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         }
-        print(json.dumps(line))
+        emit(line)
 
     t.close()
     if world > 1:
@@ -340,10 +340,28 @@ def main():
                         help="profiling aid: run the device-resident loop only, on a global batch of this many samples "
                              "(the line it prints is not a benchmark result)")
     args = parser.parse_args()
+    # Libraries (NCCL prints its version) write to file descriptor 1: keep it for the ONE JSON line by
+    # pointing fd 1 at stderr while the benchmark runs and printing the line to the saved descriptor.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    global _result_stream
+    _result_stream = os.fdopen(saved_stdout, "w")
     if args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
+    _result_stream.flush()
+
+
+_result_stream = None
+
+
+def emit(line):
+    """Prints the result line on the process's original stdout."""
+    stream = _result_stream or sys.stdout
+    stream.write(json.dumps(line) + "\n")
+    stream.flush()
 
 
 if __name__ == "__main__":

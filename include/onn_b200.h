@@ -67,7 +67,11 @@ int onn_version(void);
  * of A, B, C (strides in floats; 0 = shared operand).  bias is per output column (N) or NULL.
  * relu_mask (optional, same layout as C): the result is multiplied by (relu_mask > 0),
  * which fuses the ReLU derivative of the consuming Dense layer into a dX GEMM.
- * split_k > 1 splits the reduction over CTAs that accumulate with fp32 atomics; C must
+ * relu_bits (optional) is the same mask at one bit per element -- bit n % 32 of the word
+ * relu_bits[m * relu_bits_ld + n / 32] -- and costs 1/32 of the memory traffic; relu_bits_out
+ * (optional) makes a GEMM write that bit matrix for its own result: bit = (C[m, n] > 0) for the
+ * value it stores.  Both need batch 1 and relu_bits_ld >= ceil(N / 32).
+ * split_k > 1 splits the reduction over CTAs that accumulate with fp32 reductions; C must
  * then hold the value to accumulate into (zero for a plain product).
  * ------------------------------------------------------------------------------------- */
 typedef struct onn_gemm_args
@@ -86,6 +90,13 @@ typedef struct onn_gemm_args
     int32_t relu;               /* apply max(x, 0) after bias */
     int32_t split_k;            /* 0 or 1 = none */
     uint32_t flags;             /* ONN_ACCUMULATE */
+    float* colsum_out;          /* optional [N]: column sums of the values written (after bias / ReLU / mask) are */
+    int64_t colsum_stride_inner;/* ADDED to colsum_out[zi * colsum_stride_inner + n]; not with split_k.  This is  */
+                                /* how a GEMM that produces a layer's delta also produces that layer's bias       */
+                                /* gradient (opennn/dense_layer.h:1339-1349 uses a ones-vector GEMM for it).      */
+    uint32_t* relu_bits_out;    /* optional [M, relu_bits_ld] words, see above; not with split_k or ONN_ACCUMULATE */
+    const uint32_t* relu_bits;  /* optional [M, relu_bits_ld] words, see above; not with split_k */
+    int64_t relu_bits_ld;       /* words per row of relu_bits_out / relu_bits */
 } onn_gemm_args;
 
 int onn_gemm(const onn_gemm_args* args, void* stream);
@@ -98,6 +109,11 @@ int onn_gemm_set_mode(int mode);
 /* 0, or ONN_ERR_DEVICE_TIMEOUT if a tcgen05 GEMM gave up on a bounded barrier wait since
  * the last call (the status word is read back and cleared; synchronises the device). */
 int onn_gemm_device_status(void);
+/* Failure-detection self-test (no counterpart in the reference): runs a one-thread kernel that waits, with a
+ * 1 ms limit, on a barrier nothing ever signals.  *gave_up receives 1 when the wait ran out as it must; the
+ * kernel returns normally, the context stays usable, and the next onn_gemm_device_status() reports
+ * ONN_ERR_DEVICE_TIMEOUT once.  This is the mechanism every wait of the tcgen05 kernels uses (limit ~1 s). */
+int onn_selftest_bounded_wait(int* gave_up);
 /* Number of kernels this library launched since load (all entry points). */
 uint64_t onn_launch_count(void);
 
@@ -179,8 +195,11 @@ int onn_add(const float* a, const float* b, float* out, int64_t n, uint32_t flag
  *   Y = act(X W + b), X [rows, in], W [in, out], b [out].
  * ONN_ACT_SOFTMAX normalises each row unless ONN_DEFER_SOFTMAX is set (then Y holds logits
  * for onn_ce3d_fwd_bwd).
+ * relu_bits (optional, ONN_ACT_RELU only, [rows, onn_relu_bits_words_per_row(out)] words): receives
+ * (Y > 0) at one bit per element, for the onn_dense_bwd call of the layer that consumes Y.
  * ------------------------------------------------------------------------------------- */
-int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y,
+int64_t onn_relu_bits_words_per_row(int64_t features);      /* ceil(features / 32) */
+int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y, uint32_t* relu_bits,
                   int64_t rows, int64_t in, int64_t out, int activation,
                   uint32_t flags, void* stream);
 
@@ -191,9 +210,15 @@ int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y,
  * ONN_DELTA_READY says it already holds delta.  dX may be NULL (ONN_ACCUMULATE adds into it).
  * dW and db are ACCUMULATED into (the gradient arena is zeroed once per step).
  * dX_relu_mask (optional, [rows, in]): dX is multiplied by (mask > 0), i.e. the ReLU
- * derivative of the layer that produced X, saving that layer a pass over its gradient. */
+ * derivative of the layer that produced X, saving that layer a pass over its gradient.
+ * dX_relu_bits (optional): the same mask as written by that layer's onn_dense_fwd(relu_bits);
+ * give one of the two.  The bit form reads 1/32 of the bytes and is the fast one.
+ * dX_colsum (optional, [in]): the column sums of dX (after the mask) are ADDED to it -- that is the
+ * bias gradient of the layer that produced X, which may then pass db = NULL in its own call.
+ * db may be NULL (bias gradient not wanted here). */
 int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
-                  float* dW, float* db, float* dX, const float* dX_relu_mask,
+                  float* dW, float* db, float* dX, const float* dX_relu_mask, const uint32_t* dX_relu_bits,
+                  float* dX_colsum,
                   int64_t rows, int64_t in, int64_t out, int activation,
                   uint32_t flags, void* stream);
 

@@ -37,7 +37,9 @@ class GemmArgs(C.Structure):
                 ("a_stride_inner", C.c_int64), ("a_stride_outer", C.c_int64),
                 ("b_stride_inner", C.c_int64), ("b_stride_outer", C.c_int64),
                 ("c_stride_inner", C.c_int64), ("c_stride_outer", C.c_int64),
-                ("alpha", C.c_float), ("relu", C.c_int32), ("split_k", C.c_int32), ("flags", C.c_uint32)]
+                ("alpha", C.c_float), ("relu", C.c_int32), ("split_k", C.c_int32), ("flags", C.c_uint32),
+                ("colsum_out", C.c_void_p), ("colsum_stride_inner", C.c_int64),
+                ("relu_bits_out", C.c_void_p), ("relu_bits", C.c_void_p), ("relu_bits_ld", C.c_int64)]
 
 
 class MhaParams(C.Structure):
@@ -50,9 +52,9 @@ class MhaGrads(C.Structure):
 
 EXPORTS = [
     "onn_status_string", "onn_version", "onn_gemm", "onn_gemm_set_mode", "onn_gemm_device_status",
-    "onn_launch_count", "onn_embedding_fwd", "onn_embedding_bwd",
+    "onn_launch_count", "onn_selftest_bounded_wait", "onn_embedding_fwd", "onn_embedding_bwd",
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
-    "onn_dense_fwd", "onn_dense_bwd", "onn_softmax_rows",
+    "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
     "onn_mha_attention_weights", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
     "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam",
@@ -70,6 +72,7 @@ def lib():
         L = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
         L.onn_status_string.restype = C.c_char_p
         L.onn_launch_count.restype = C.c_uint64
+        L.onn_relu_bits_words_per_row.restype = C.c_int64
         for name in ("onn_layernorm_bwd_workspace_floats",
                      "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats",
                      "onn_grad_sqnorm_workspace_floats"):
@@ -113,7 +116,8 @@ def _empty(n, dtype=torch.float32):
 # ----------------------------------------------------------------------------------------
 
 def gemm(A, B, Cmat, M, N, K, lda, ldb, ldc, a_major=0, b_major=1, bias=None, relu_mask=None, alpha=1.0,
-         relu=False, split_k=0, flags=0, batch_inner=1, batch_outer=1, a_strides=(0, 0), b_strides=(0, 0), c_strides=(0, 0)):
+         relu=False, split_k=0, flags=0, batch_inner=1, batch_outer=1, a_strides=(0, 0), b_strides=(0, 0), c_strides=(0, 0),
+         colsum_out=None, colsum_stride_inner=0, relu_bits_out=None, relu_bits=None, relu_bits_ld=0):
     g = GemmArgs()
     g.A, g.B, g.C = A.data_ptr(), B.data_ptr(), Cmat.data_ptr()
     g.bias = bias.data_ptr() if bias is not None else None
@@ -125,6 +129,11 @@ def gemm(A, B, Cmat, M, N, K, lda, ldb, ldc, a_major=0, b_major=1, bias=None, re
     g.b_stride_inner, g.b_stride_outer = b_strides
     g.c_stride_inner, g.c_stride_outer = c_strides
     g.alpha, g.relu, g.split_k, g.flags = alpha, int(relu), split_k, flags
+    g.colsum_out = colsum_out.data_ptr() if colsum_out is not None else None
+    g.colsum_stride_inner = colsum_stride_inner
+    g.relu_bits_out = relu_bits_out.data_ptr() if relu_bits_out is not None else None
+    g.relu_bits = relu_bits.data_ptr() if relu_bits is not None else None
+    g.relu_bits_ld = relu_bits_ld
     check(lib().onn_gemm(C.byref(g), stream_ptr()), "onn_gemm")
 
 
@@ -178,24 +187,29 @@ def add(a, b, flags=0):
     return out
 
 
-def dense_fwd(X, W, b, activation, flags=0):
+def relu_bits_words_per_row(features):
+    return (features + 31) // 32
+
+
+def dense_fwd(X, W, b, activation, flags=0, want_relu_bits=False):
     in_f, out_f = W.shape
     rows = X.numel() // in_f
     Y = torch.empty(*X.shape[:-1], out_f, device="cuda")
-    check(lib().onn_dense_fwd(ptr(X), ptr(W), ptr(b), ptr(Y), i64(rows), i64(in_f), i64(out_f), ACTIVATIONS[activation],
+    bits = torch.empty(rows, relu_bits_words_per_row(out_f), dtype=torch.int32, device="cuda") if want_relu_bits else None
+    check(lib().onn_dense_fwd(ptr(X), ptr(W), ptr(b), ptr(Y), ptr(bits), i64(rows), i64(in_f), i64(out_f), ACTIVATIONS[activation],
                               C.c_uint32(flags), stream_ptr()), "onn_dense_fwd")
-    return Y
+    return (Y, bits) if want_relu_bits else Y
 
 
-def dense_bwd(X, W, Y, dY, activation, flags=0, need_dx=True, relu_mask=None):
+def dense_bwd(X, W, Y, dY, activation, flags=0, need_dx=True, relu_mask=None, dx_colsum=None, relu_bits=None):
     in_f, out_f = W.shape
     rows = X.numel() // in_f
     dY = dY.clone()
     dW = torch.zeros_like(W)
     db = torch.zeros(out_f, device="cuda")
     dX = torch.empty_like(X) if need_dx else None
-    check(lib().onn_dense_bwd(ptr(X), ptr(W), ptr(Y), ptr(dY), ptr(dW), ptr(db), ptr(dX), ptr(relu_mask), i64(rows), i64(in_f),
-                              i64(out_f), ACTIVATIONS[activation], C.c_uint32(flags), stream_ptr()), "onn_dense_bwd")
+    check(lib().onn_dense_bwd(ptr(X), ptr(W), ptr(Y), ptr(dY), ptr(dW), ptr(db), ptr(dX), ptr(relu_mask), ptr(relu_bits), ptr(dx_colsum), i64(rows),
+                              i64(in_f), i64(out_f), ACTIVATIONS[activation], C.c_uint32(flags), stream_ptr()), "onn_dense_bwd")
     return dX, dW, db
 
 

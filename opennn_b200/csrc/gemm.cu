@@ -33,7 +33,13 @@ int gemm(const onn_gemm_args& g, cudaStream_t stream)
     ONN_CHECK_ARG(g.ldb >= (g.b_major == 0 ? g.K : g.N));
     ONN_CHECK_ARG(g.ldc >= g.N);
     // split-K partial sums are added atomically: a nonlinear epilogue cannot follow
-    ONN_CHECK_ARG(g.split_k <= 1 || (!g.relu && !g.relu_mask));
+    ONN_CHECK_ARG(g.split_k <= 1 || (!g.relu && !g.relu_mask && !g.colsum_out && !g.relu_bits && !g.relu_bits_out));
+    if(g.relu_bits || g.relu_bits_out)
+    {
+        ONN_CHECK_ARG(g.batch_inner == 1 && g.batch_outer == 1 && g.relu_bits_ld >= (g.N + 31) / 32);
+        ONN_CHECK_ARG(!(g.relu_bits && g.relu_mask));
+        ONN_CHECK_ARG(!(g.relu_bits_out && (g.flags & ONN_ACCUMULATE)));
+    }
 
     const int mode = g_mode.load(std::memory_order_relaxed);
     const bool tc_ok = gemm_tc_supported(g);
@@ -60,6 +66,12 @@ extern "C" int onn_gemm_set_mode(int mode)
 }
 
 extern "C" int onn_gemm_device_status(void) { return gemm_tc_read_status(); }
+
+extern "C" int onn_selftest_bounded_wait(int* gave_up)
+{
+    ONN_CHECK_ARG(gave_up);
+    return gemm_tc_bounded_wait_selftest(gave_up);
+}
 
 extern "C" uint64_t onn_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
 

@@ -12,6 +12,7 @@ int gemm_simt_launch(const onn_gemm_args& g, cudaStream_t stream);
 bool gemm_tc_supported(const onn_gemm_args& g);
 int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream);
 int gemm_tc_read_status();
+int gemm_tc_bounded_wait_selftest(int* gave_up_host);
 
 // Front end used by the layer code (same as onn_gemm).
 int gemm(const onn_gemm_args& g, cudaStream_t stream);

@@ -83,9 +83,13 @@ gemm_simt_kernel(const onn_gemm_args g, int splits, long long k_per_split)
             if(g.bias && split == 0) value += g.bias[n];
             if(g.relu) value = fmaxf(value, 0.f);
             if(mask && !(mask[m * g.ldc + n] > 0.f)) value = 0.f;
+            if(g.relu_bits && !((g.relu_bits[m * g.relu_bits_ld + (n >> 5)] >> (n & 31)) & 1u)) value = 0.f;
+            // the bit matrix was cleared by the launcher; each thread sets the bits of its positive values
+            if(g.relu_bits_out && value > 0.f) atomicOr(g.relu_bits_out + m * g.relu_bits_ld + (n >> 5), 1u << (n & 31));
             float* dst = C + m * g.ldc + n;
             if(splits > 1) atomicAdd(dst, value);
             else *dst = accumulate ? *dst + value : value;
+            if(g.colsum_out) atomicAdd(g.colsum_out + zi * g.colsum_stride_inner + n, value);
         }
     }
 }
@@ -99,6 +103,9 @@ int gemm_simt_launch(const onn_gemm_args& g, cudaStream_t stream)
     if(batch * splits > 65535) return ONN_ERR_UNSUPPORTED;
     dim3 grid((unsigned)((g.N + kTile - 1) / kTile), (unsigned)((g.M + kTile - 1) / kTile), (unsigned)(batch * splits));
     if(grid.y > 65535) return ONN_ERR_UNSUPPORTED;
+    if(g.relu_bits_out &&
+       cudaMemsetAsync(g.relu_bits_out, 0, (size_t)g.M * (size_t)g.relu_bits_ld * sizeof(uint32_t), stream) != cudaSuccess)
+        return ONN_ERR_CUDA;
     gemm_simt_kernel<<<grid, 256, 0, stream>>>(g, splits, k_per_split);
     count_launch();
     return launch_status();

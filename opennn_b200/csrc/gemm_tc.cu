@@ -11,8 +11,8 @@
 //               output rows), alpha / bias / ReLU, stage the 32 x 32 block in shared memory
 //               (128-byte swizzle) and hand it to a TMA store -- or a TMA reduce-add for
 //               accumulation and split-K -- so global writes are whole lines and clipped at the
-//               matrix edge by the copy engine.  (With a ReLU mask operand the epilogue falls
-//               back to direct 128-bit loads and stores.)
+//               matrix edge by the copy engine.  A ReLU-mask operand and column sums of the
+//               output are applied to the staged block.
 //
 // Operand layouts (BK = 32 floats = 128 bytes = one swizzle row, UMMA K = 8):
 //   K-major  (reduction dimension contiguous in memory): one box [rows][32 floats];
@@ -57,6 +57,7 @@ constexpr int EPI_BYTES = kEpilogueWarps * 2 * EPI_BLOCK_BYTES;   // double-buff
 constexpr unsigned long long kWaitCycles = 1ull << 31;     // ~1 s at 2 GHz
 
 __device__ unsigned int g_status;                          // 0 = ok; else first failing wait site
+__device__ int g_selftest_flag;                            // result word of the bounded-wait self-test
 
 struct Params
 {
@@ -66,6 +67,11 @@ struct Params
     float* C;
     const float* bias;
     const float* relu_mask;
+    unsigned int* relu_bits_out;                           // optional: bit n % 32 of word [m][n / 32] = (written value > 0)
+    const unsigned int* relu_bits;                         // optional: the same mask, applied to the result
+    long long relu_bits_ld;                                // words per row of either bit matrix
+    float* colsum;                                         // optional column sums of the written values
+    long long colsum_stride_inner;
     float alpha;
     int relu, accumulate;
     int batch_inner, batch_outer;
@@ -109,7 +115,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  Returns false (and raises the abort flag) if the barrier never completes.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int site)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int site,
+                                          unsigned long long limit_cycles = kWaitCycles)
 {
     if(mbar_try_wait(bar, parity)) return true;
     const unsigned long long start = clock64();
@@ -120,7 +127,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if((++spins & 255u) == 0)
         {
             if(*abort_flag) return false;
-            if(clock64() - start > kWaitCycles)
+            if(clock64() - start > limit_cycles)
             {
                 atomicCAS(&g_status, 0u, site);
                 *abort_flag = 1;
@@ -217,6 +224,62 @@ __host__ __device__ constexpr uint32_t make_idesc(int bn, int a_mn_major, int b_
            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+// Work on a staged 32 x 32 output block (row r at r * 128 bytes, 16-byte chunk c at slot c ^ (r % 8)) before it
+// is handed to the copy engine:
+//   - ReLU mask: the mask block is read with whole 128-byte rows per 8 lanes (4 rows per pass) and applied in place;
+//   - column sums: lane L adds up column L over the block's valid rows and issues one reduction per column.
+__device__ __forceinline__ void staged_block_passes(const Params& p, uint32_t block, long long warp_row0, long long n_base,
+                                                    long long c_offset, int zi, int lane)
+{
+    if(p.relu_mask)
+    {
+        // all eight mask loads are issued before anything waits on them
+        float4 k[8];
+#pragma unroll
+        for(int pass = 0; pass < 8; pass++)
+        {
+            const int r = pass * 4 + (lane >> 3), chunk = lane & 7;
+            const long long row = warp_row0 + r, n = n_base + chunk * 4;
+            k[pass] = make_float4(1.f, 1.f, 1.f, 1.f);
+            if(row < p.M && n < p.N)
+            {
+                const float* k_ptr = p.relu_mask + c_offset + row * p.ldc + n;
+                if(n + 3 < p.N) k[pass] = ld4_stream(k_ptr);
+                else { k[pass].x = k_ptr[0]; k[pass].y = n + 1 < p.N ? k_ptr[1] : 0.f; k[pass].z = n + 2 < p.N ? k_ptr[2] : 0.f; k[pass].w = 0.f; }
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for(int pass = 0; pass < 8; pass++)
+        {
+            const int r = pass * 4 + (lane >> 3), chunk = lane & 7;
+            const uint32_t at = block + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4);
+            float4 x;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(at));
+            x.x = k[pass].x > 0.f ? x.x : 0.f; x.y = k[pass].y > 0.f ? x.y : 0.f;
+            x.z = k[pass].z > 0.f ? x.z : 0.f; x.w = k[pass].w > 0.f ? x.w : 0.f;
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(at), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w));
+        }
+    }
+    if(p.colsum)
+    {
+        __syncwarp();
+        const long long left = p.M - warp_row0;
+        const int rows_valid = left < 32 ? (int)left : 32;
+        float part[4] = { 0.f, 0.f, 0.f, 0.f };
+#pragma unroll
+        for(int r = 0; r < 32; r++)
+        {
+            const uint32_t at = block + (uint32_t)r * 128u + (uint32_t)(((lane >> 2) ^ (r & 7)) << 4) + (uint32_t)(lane & 3) * 4u;
+            float x;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(at));
+            part[r & 3] += r < rows_valid ? x : 0.f;
+        }
+        const float total = (part[0] + part[1]) + (part[2] + part[3]);
+        if(n_base + lane < p.N) atomicAdd(p.colsum + (long long)zi * p.colsum_stride_inner + n_base + lane, total);
+    }
+}
+
 struct WorkItem { int zi, zo, split, m_blk, n_blk; long long k_begin; int k_blocks; };
 
 __device__ __forceinline__ WorkItem decode_work(const Params& p, long long w)
@@ -241,6 +304,103 @@ __device__ __forceinline__ WorkItem decode_work(const Params& p, long long w)
     it.k_blocks = (int)((k_end - it.k_begin + BK - 1) / BK);
     return it;
 }
+
+// What an epilogue warp fetches for a tile BEFORE it waits for the tile's accumulator: the bias values
+// of the tile's columns (lane L holds column 32 j + L) and the ReLU bit words of its rows (lane L holds
+// row L, word j covers columns 32 j .. 32 j + 31).  While the operand pipeline keeps the path from L2
+// to the SM full, a load issued from the epilogue takes microseconds to return; issued here, that
+// time passes behind the tile's MMAs instead of once per 32 x 32 block.
+template <int BN>
+struct TileSideInputs { float bias[BN / 32]; uint32_t bits[BN / 32]; };
+
+template <int BN>
+__device__ __forceinline__ void load_tile_side_inputs(const Params& p, bool use_bias, long long warp_row0, long long n0, int lane,
+                                                      TileSideInputs<BN>& side)
+{
+    const long long row = warp_row0 + lane;
+#pragma unroll
+    for(int j = 0; j < BN / 32; j++)
+    {
+        const long long n = n0 + j * 32 + lane;
+        side.bias[j] = (use_bias && n < p.N) ? __ldg(p.bias + n) : 0.f;
+        side.bits[j] = 0xffffffffu;
+        if(p.relu_bits && row < p.M && n0 + j * 32 < p.N) side.bits[j] = __ldg(p.relu_bits + row * p.relu_bits_ld + (n0 >> 5) + j);
+    }
+}
+
+// One warp's share of one output tile: 32 rows x BN columns from TMEM (lane = row) through the
+// alpha / bias / ReLU / mask arithmetic into this warp's two staging blocks and on to C with the copy
+// engine.  `warp_blocks` is the shared-memory address of the warp's two 4 KiB blocks; `staged_chunks`
+// counts the blocks the warp has handed over so far (it picks the block and tells when to wait).
+template <int BN>
+__device__ __forceinline__ void epilogue_warp_tile(const Params& p, const CUtensorMap* map_c, uint32_t taddr, uint32_t warp_blocks,
+                                                   unsigned int& staged_chunks, long long warp_row0, long long n0,
+                                                   long long c_offset, int zi, int c_zi, int c_zo, bool use_bias, int lane,
+                                                   TileSideInputs<BN>& side)
+{
+    const bool reduce = p.accumulate || p.splits > 1;
+#pragma unroll 1
+    for(int c = 0; c < BN / 32; c++)
+    {
+        const long long n_base = n0 + c * 32;
+        if(n_base >= p.N || warp_row0 >= p.M) break;        // nothing of this block lies inside C
+        float v[32];
+        __syncwarp();                                       // tcgen05.ld is warp-collective: reconverge first
+        tmem_load_32(taddr + c * 32, v);
+        // this warp's two staging blocks alternate; a block is free again once the copy issued from it
+        // two chunks ago has finished READING shared memory
+        const uint32_t block = warp_blocks + (staged_chunks & 1u) * EPI_BLOCK_BYTES;
+        if(staged_chunks >= 2) { if(lane == 0) bulk_wait_read_1(); __syncwarp(); }
+
+        const float bias_lane = side.bias[0];               // this block's values; the rest move up one place
+        const uint32_t keep = side.bits[0];
+#pragma unroll
+        for(int j = 0; j + 1 < BN / 32; j++) { side.bias[j] = side.bias[j + 1]; side.bits[j] = side.bits[j + 1]; }
+
+#pragma unroll
+        for(int i = 0; i < 32; i++) v[i] *= p.alpha;
+        if(use_bias)
+        {
+#pragma unroll
+            for(int i = 0; i < 32; i++) v[i] += __shfl_sync(0xffffffffu, bias_lane, i);
+        }
+        if(p.relu)
+        {
+#pragma unroll
+            for(int i = 0; i < 32; i++) v[i] = fmaxf(v[i], 0.f);
+        }
+        if(p.relu_bits)
+        {
+#pragma unroll
+            for(int i = 0; i < 32; i++) v[i] = (keep >> i) & 1u ? v[i] : 0.f;
+        }
+        if(p.relu_bits_out)
+        {
+            uint32_t positive = 0;
+#pragma unroll
+            for(int i = 0; i < 32; i++) positive |= (v[i] > 0.f ? 1u : 0u) << i;
+            if(warp_row0 + lane < p.M) p.relu_bits_out[(warp_row0 + lane) * p.relu_bits_ld + (n_base >> 5)] = positive;
+        }
+#pragma unroll
+        for(int q4 = 0; q4 < 8; q4++)
+        {
+            // row `lane` of the block is 128 bytes; 16-byte chunk q4 goes to slot q4 ^ (lane % 8): the 128-byte swizzle
+            const uint32_t dst = block + (uint32_t)lane * 128u + (uint32_t)((q4 ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "f"(v[q4 * 4]), "f"(v[q4 * 4 + 1]), "f"(v[q4 * 4 + 2]), "f"(v[q4 * 4 + 3]));
+        }
+        staged_block_passes(p, block, warp_row0, n_base, c_offset, zi, lane);
+        fence_async_shared();                               // generic-proxy writes -> visible to the copy engine
+        __syncwarp();
+        if(lane == 0)
+        {
+            if(reduce) tma_reduce_add_4d(map_c, block, (int)n_base, (int)warp_row0, c_zi, c_zo);
+            else tma_store_4d(map_c, block, (int)n_base, (int)warp_row0, c_zi, c_zo);
+            bulk_commit();
+        }
+        staged_chunks++;
+    }
+}
+
 
 template <int BN, int STAGES, int A_MN, int B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -396,109 +556,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         {
             const WorkItem it = decode_work(p, w);
             const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
+            const long long n0 = (long long)it.n_blk * BN;
+            const long long c_offset = it.zi * p.c_stride_inner + it.zo * p.c_stride_outer;
+            const bool use_bias = p.bias != nullptr && it.split == 0;
+            const long long warp_row0 = (long long)it.m_blk * BM + quadrant * 32;
+            TileSideInputs<BN> side;
+            load_tile_side_inputs<BN>(p, use_bias, warp_row0, n0, lane, side);
+
             bool ok = true;
             if(lane == 0) ok = mbar_wait(smem_u32(acc_full_bar + acc), acc_phase, abort_flag, 4);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if(!ok) break;
             tcgen05_fence_after();
 
-            const long long row = (long long)it.m_blk * BM + quadrant * 32 + lane;
-            const long long n0 = (long long)it.n_blk * BN;
-            const long long c_offset = it.zi * p.c_stride_inner + it.zo * p.c_stride_outer;
-            float* c_row = p.C + c_offset + row * p.ldc;
-            const float* mask_row = p.relu_mask ? p.relu_mask + c_offset + row * p.ldc : nullptr;
-            const bool row_ok = row < p.M;
-            const bool use_bias = p.bias != nullptr && it.split == 0;
             const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * BN;
-            const long long warp_row0 = (long long)it.m_blk * BM + quadrant * 32;
-            const bool staged = p.relu_mask == nullptr;
-            const bool reduce = p.accumulate || p.splits > 1;
             const int c_zi = p.c_batch_inner_on ? it.zi : 0, c_zo = p.c_batch_outer_on ? it.zo : 0;
-
-#pragma unroll 1
-            for(int c = 0; c < BN / 32; c++)
-            {
-                const long long n_base = n0 + c * 32;
-                if(n_base >= p.N || warp_row0 >= p.M) break;    // nothing of this block lies inside C
-                float v[32];
-                __syncwarp();                                   // tcgen05.ld is warp-collective: reconverge first
-                tmem_load_32(taddr + c * 32, v);
-                if(staged)
-                {
-                    // this warp's two staging blocks alternate; a block is free again once the copy
-                    // issued from it two chunks ago has finished READING shared memory
-                    const uint32_t block = smem_u32(epi_smem + ((warp - 2) * 2 + (int)(staged_chunks & 1)) * EPI_BLOCK_BYTES);
-                    if(staged_chunks >= 2) { if(lane == 0) bulk_wait_read_1(); __syncwarp(); }
-#pragma unroll
-                    for(int q4 = 0; q4 < 8; q4++)
-                    {
-                        const long long n = n_base + q4 * 4;
-                        float x[4] = { v[q4 * 4] * p.alpha, v[q4 * 4 + 1] * p.alpha, v[q4 * 4 + 2] * p.alpha, v[q4 * 4 + 3] * p.alpha };
-                        if(use_bias)
-                        {
-                            if(n + 3 < p.N) { const float4 b = ld4(p.bias + n); x[0] += b.x; x[1] += b.y; x[2] += b.z; x[3] += b.w; }
-                            else for(int e = 0; e < 4; e++) if(n + e < p.N) x[e] += p.bias[n + e];
-                        }
-                        if(p.relu) { x[0] = fmaxf(x[0], 0.f); x[1] = fmaxf(x[1], 0.f); x[2] = fmaxf(x[2], 0.f); x[3] = fmaxf(x[3], 0.f); }
-                        // row `lane` of the block is 128 bytes; 16-byte chunk q4 goes to slot q4 ^ (lane % 8): the 128-byte swizzle
-                        const uint32_t dst = block + (uint32_t)lane * 128u + (uint32_t)((q4 ^ (lane & 7)) << 4);
-                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
-                    }
-                    fence_async_shared();                        // generic-proxy writes -> visible to the copy engine
-                    __syncwarp();
-                    if(lane == 0)
-                    {
-                        if(reduce) tma_reduce_add_4d(&map_c, block, (int)n_base, (int)warp_row0, c_zi, c_zo);
-                        else tma_store_4d(&map_c, block, (int)n_base, (int)warp_row0, c_zi, c_zo);
-                        bulk_commit();
-                    }
-                    staged_chunks++;
-                    continue;
-                }
-                if(!row_ok) continue;
-#pragma unroll
-                for(int q4 = 0; q4 < 8; q4++)
-                {
-                    const long long n = n_base + q4 * 4;
-                    if(n >= p.N) break;
-                    float x[4] = { v[q4 * 4] * p.alpha, v[q4 * 4 + 1] * p.alpha, v[q4 * 4 + 2] * p.alpha, v[q4 * 4 + 3] * p.alpha };
-                    if(n + 3 < p.N)
-                    {
-                        if(use_bias) { const float4 b = ld4(p.bias + n); x[0] += b.x; x[1] += b.y; x[2] += b.z; x[3] += b.w; }
-                        if(p.relu) { x[0] = fmaxf(x[0], 0.f); x[1] = fmaxf(x[1], 0.f); x[2] = fmaxf(x[2], 0.f); x[3] = fmaxf(x[3], 0.f); }
-                        if(mask_row)
-                        {
-                            const float4 k = ld4(mask_row + n);
-                            x[0] = k.x > 0.f ? x[0] : 0.f; x[1] = k.y > 0.f ? x[1] : 0.f;
-                            x[2] = k.z > 0.f ? x[2] : 0.f; x[3] = k.w > 0.f ? x[3] : 0.f;
-                        }
-                        if(p.splits > 1)
-                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-                                         :: "l"(c_row + n), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
-                        else
-                        {
-                            if(p.accumulate) { const float4 o = ld4(c_row + n); x[0] += o.x; x[1] += o.y; x[2] += o.z; x[3] += o.w; }
-                            st4(c_row + n, make_float4(x[0], x[1], x[2], x[3]));
-                        }
-                    }
-                    else
-                    {
-                        for(int e = 0; e < 4 && n + e < p.N; e++)
-                        {
-                            float y = x[e];
-                            if(use_bias) y += p.bias[n + e];
-                            if(p.relu) y = fmaxf(y, 0.f);
-                            if(mask_row && !(mask_row[n + e] > 0.f)) y = 0.f;
-                            if(p.splits > 1) atomicAdd(c_row + n + e, y);
-                            else
-                            {
-                                if(p.accumulate) y += c_row[n + e];
-                                c_row[n + e] = y;
-                            }
-                        }
-                    }
-                }
-            }
+            epilogue_warp_tile<BN>(p, &map_c, taddr, smem_u32(epi_smem + (warp - 2) * 2 * EPI_BLOCK_BYTES), staged_chunks, warp_row0, n0,
+                                   c_offset, it.zi, c_zi, c_zo, use_bias, lane, side);
             tcgen05_fence_before();
             __syncwarp();
             if(lane == 0) mbar_arrive(smem_u32(acc_empty_bar + acc));
@@ -728,73 +802,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         {
             const WorkItem it = decode_work(p, w);
             const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
+            const long long n0 = (long long)it.n_blk * BN;
+            const bool use_bias = p.bias != nullptr && it.split == 0;
+            const long long warp_row0 = (long long)it.m_blk * 256 + (long long)rank * 128 + quadrant * 32;
+            TileSideInputs<BN> side;
+            load_tile_side_inputs<BN>(p, use_bias, warp_row0, n0, lane, side);
+
             bool ok = true;
             if(lane == 0) ok = mbar_wait(smem_u32(acc_full_bar + acc), acc_phase, abort_flag, 14);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if(!ok) break;
             tcgen05_fence_after();
 
-            const long long n0 = (long long)it.n_blk * BN;
-            const bool use_bias = p.bias != nullptr && it.split == 0;
             const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * BN;
-            const long long warp_row0 = (long long)it.m_blk * 256 + (long long)rank * 128 + quadrant * 32;
-            const bool reduce = p.accumulate || p.splits > 1;
-
-#pragma unroll 1
-            for(int c = 0; c < BN / 32; c++)
-            {
-                const long long n_base = n0 + c * 32;
-                if(n_base >= p.N || warp_row0 >= p.M) break;
-                float v[32];
-                __syncwarp();
-                tmem_load_32(taddr + c * 32, v);
-                const uint32_t block = smem_u32(epi_smem + ((warp - 2) * 2 + (int)(staged_chunks & 1)) * EPI_BLOCK_BYTES);
-                if(staged_chunks >= 2) { if(lane == 0) bulk_wait_read_1(); __syncwarp(); }
-#pragma unroll
-                for(int q4 = 0; q4 < 8; q4++)
-                {
-                    const long long n = n_base + q4 * 4;
-                    float x[4] = { v[q4 * 4] * p.alpha, v[q4 * 4 + 1] * p.alpha, v[q4 * 4 + 2] * p.alpha, v[q4 * 4 + 3] * p.alpha };
-                    if(use_bias)
-                    {
-                        if(n + 3 < p.N) { const float4 b = ld4(p.bias + n); x[0] += b.x; x[1] += b.y; x[2] += b.z; x[3] += b.w; }
-                        else for(int e = 0; e < 4; e++) if(n + e < p.N) x[e] += p.bias[n + e];
-                    }
-                    if(p.relu) { x[0] = fmaxf(x[0], 0.f); x[1] = fmaxf(x[1], 0.f); x[2] = fmaxf(x[2], 0.f); x[3] = fmaxf(x[3], 0.f); }
-                    const uint32_t dst = block + (uint32_t)lane * 128u + (uint32_t)((q4 ^ (lane & 7)) << 4);
-                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
-                }
-                if(p.relu_mask)
-                {
-                    // the mask block is read with whole 128-byte rows per 8 lanes (4 rows per pass) and applied
-                    // to the staged values: row = pass * 4 + lane / 8, 16-byte chunk = lane % 8
-                    __syncwarp();
-#pragma unroll
-                    for(int pass = 0; pass < 8; pass++)
-                    {
-                        const int r = pass * 4 + (lane >> 3), chunk = lane & 7;
-                        const long long row = warp_row0 + r, n = n_base + chunk * 4;
-                        if(row < p.M && n + 3 < p.N)
-                        {
-                            const float4 k = ld4(p.relu_mask + row * p.ldc + n);
-                            const uint32_t at = block + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4);
-                            float4 x;
-                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(at) : "memory");
-                            x.x = k.x > 0.f ? x.x : 0.f; x.y = k.y > 0.f ? x.y : 0.f; x.z = k.z > 0.f ? x.z : 0.f; x.w = k.w > 0.f ? x.w : 0.f;
-                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(at), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
-                        }
-                    }
-                }
-                fence_async_shared();
-                __syncwarp();
-                if(lane == 0)
-                {
-                    if(reduce) tma_reduce_add_4d(&map_c, block, (int)n_base, (int)warp_row0, 0, 0);
-                    else tma_store_4d(&map_c, block, (int)n_base, (int)warp_row0, 0, 0);
-                    bulk_commit();
-                }
-                staged_chunks++;
-            }
+            epilogue_warp_tile<BN>(p, &map_c, taddr, smem_u32(epi_smem + (warp - 2) * 2 * EPI_BLOCK_BYTES), staged_chunks, warp_row0, n0,
+                                   0, 0, 0, 0, use_bias, lane, side);
             tcgen05_fence_before();
             __syncwarp();
             if(lane == 0) mbar_arrive_cluster(leader_acc_empty + acc * 8);     // one arrival per epilogue warp of the pair
@@ -810,6 +832,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+
+// Self-test of the bounded wait: a barrier that nothing ever arrives on, waited for with a 1 ms limit.
+// The wait must give up, record its site in the status word and let the kernel return normally.
+__global__ void bounded_wait_selftest_kernel(int* gave_up)
+{
+    __shared__ uint64_t never_signalled;
+    __shared__ int abort_flag;
+    if(threadIdx.x == 0)
+    {
+        abort_flag = 0;
+        mbar_init(smem_u32(&never_signalled), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool completed = mbar_wait(smem_u32(&never_signalled), 0, &abort_flag, 99, 1ull << 21);
+        *gave_up = completed ? 0 : 1;
     }
 }
 
@@ -954,6 +993,8 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.M = g.M; p.N = g.N; p.K = g.K; p.ldc = g.ldc;
     p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
     p.C = g.C; p.bias = g.bias; p.relu_mask = g.relu_mask; p.alpha = g.alpha;
+    p.relu_bits_out = g.relu_bits_out; p.relu_bits = g.relu_bits; p.relu_bits_ld = g.relu_bits_ld;
+    p.colsum = g.colsum_out; p.colsum_stride_inner = g.colsum_stride_inner;
     p.relu = g.relu; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
     p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
     p.a_batch_inner_on = g.batch_inner > 1 && g.a_stride_inner != 0; p.a_batch_outer_on = g.batch_outer > 1 && g.a_stride_outer != 0;
@@ -1011,6 +1052,17 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     if(g.a_major == 0 && g.b_major == 1) return launch_majors<0, 1>(bn, map_a, map_b, map_c, p, stream);
     if(g.a_major == 1 && g.b_major == 1) return launch_majors<1, 1>(bn, map_a, map_b, map_c, p, stream);
     return ONN_ERR_UNSUPPORTED;
+}
+
+int gemm_tc_bounded_wait_selftest(int* gave_up_host)
+{
+    int* flag = nullptr;
+    if(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), tc::g_selftest_flag) != cudaSuccess) return ONN_ERR_CUDA;
+    tc::bounded_wait_selftest_kernel<<<1, 32>>>(flag);
+    count_launch();
+    if(cudaDeviceSynchronize() != cudaSuccess) return ONN_ERR_CUDA;
+    if(cudaMemcpy(gave_up_host, flag, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ONN_ERR_CUDA;
+    return ONN_OK;
 }
 
 int gemm_tc_read_status()

@@ -77,23 +77,29 @@ using namespace onn;
 // Dense<3>
 // ---------------------------------------------------------------------------------------
 
-extern "C" int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y,
+extern "C" int64_t onn_relu_bits_words_per_row(int64_t features) { return (features + 31) / 32; }
+
+extern "C" int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y, uint32_t* relu_bits,
                              int64_t rows, int64_t in, int64_t out, int activation,
                              uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(X && W && Y && rows > 0 && in > 0 && out > 0);
     ONN_CHECK_ARG(activation == ONN_ACT_LINEAR || activation == ONN_ACT_RELU || activation == ONN_ACT_SOFTMAX);
+    ONN_CHECK_ARG(!relu_bits || activation == ONN_ACT_RELU);
     cudaStream_t s = (cudaStream_t)stream;
     onn_gemm_args g = plain_gemm(X, 0, in, W, 1, out, Y, out, rows, out, in);
     g.bias = b;
     g.relu = activation == ONN_ACT_RELU;
+    g.relu_bits_out = relu_bits;
+    g.relu_bits_ld = onn_relu_bits_words_per_row(out);
     ONN_TRY(gemm(g, s));
     if(activation == ONN_ACT_SOFTMAX && !(flags & ONN_DEFER_SOFTMAX)) ONN_TRY(onn_softmax_rows(Y, rows, out, stream));
     return ONN_OK;
 }
 
 extern "C" int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
-                             float* dW, float* db, float* dX, const float* dX_relu_mask,
+                             float* dW, float* db, float* dX, const float* dX_relu_mask, const uint32_t* dX_relu_bits,
+                             float* dX_colsum,
                              int64_t rows, int64_t in, int64_t out, int activation,
                              uint32_t flags, void* stream)
 {
@@ -111,7 +117,10 @@ extern "C" int onn_dense_bwd(const float* X, const float* W, const float* Y, flo
     if(dX)
     {
         onn_gemm_args g = plain_gemm(delta, 0, out, W, 0, out, dX, in, rows, in, out);
-        g.relu_mask = dX_relu_mask;
+        g.relu_mask = dX_relu_bits ? nullptr : dX_relu_mask;
+        g.relu_bits = dX_relu_bits;
+        g.relu_bits_ld = onn_relu_bits_words_per_row(in);
+        g.colsum_out = dX_colsum;
         g.flags = flags & ONN_ACCUMULATE;
         ONN_TRY(gemm(g, s));
     }
@@ -278,7 +287,6 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
     ONN_TRY(weight_gradients(ctx, dY, grads->dWo, grads->dbo, rows_q, E, E, s));
     {
         onn_gemm_args g = plain_gemm(dY, 0, E, Wo, 0, E, dctx, E, rows_q, E, E);
-       
         ONN_TRY(gemm(g, s));
     }
     // dV = P^T dO
@@ -286,7 +294,7 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         onn_gemm_args g = plain_gemm(p, 1, Sk, dctx, 1, E, dv, E, Sk, hd, Sq);
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sq, E, hd); head_strides(g, 'c', Sk, E, hd);
-       
+        g.colsum_out = grads->dbv; g.colsum_stride_inner = hd;      // dbv = column sums of dV, taken in the epilogue
         ONN_TRY(gemm(g, s));
     }
     // dP = dO V^T
@@ -304,6 +312,7 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sk, E, hd); head_strides(g, 'c', Sq, E, hd);
         g.alpha = scale;
+        g.colsum_out = grads->dbq; g.colsum_stride_inner = hd;      // dbq = column sums of dQ, taken in the epilogue
         ONN_TRY(gemm(g, s));
     }
     // dK = scale * dS^T Q
@@ -312,12 +321,13 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sq, E, hd); head_strides(g, 'c', Sk, E, hd);
         g.alpha = scale;
+        g.colsum_out = grads->dbk; g.colsum_stride_inner = hd;
         ONN_TRY(gemm(g, s));
     }
-    // input projections
-    ONN_TRY(weight_gradients(Xq, dq, grads->dWq, grads->dbq, rows_q, E, E, s));
-    ONN_TRY(weight_gradients(Xs, dk, grads->dWk, grads->dbk, rows_s, E, E, s));
-    ONN_TRY(weight_gradients(Xs, dv, grads->dWv, grads->dbv, rows_s, E, E, s));
+    // input projections (their bias gradients were taken by the epilogues above)
+    ONN_TRY(weight_gradients(Xq, dq, grads->dWq, nullptr, rows_q, E, E, s));
+    ONN_TRY(weight_gradients(Xs, dk, grads->dWk, nullptr, rows_s, E, E, s));
+    ONN_TRY(weight_gradients(Xs, dv, grads->dWv, nullptr, rows_s, E, E, s));
 
     {
         onn_gemm_args g = plain_gemm(dq, 0, E, Wq, 0, E, dXq, E, rows_q, E, E);

@@ -383,16 +383,28 @@ layernorm_bwd_generic_kernel(const float* __restrict__ dY, const float* __restri
     for(int c = threadIdx.x; c < 2 * E; c += kRowThreads) out[c] = smem[c];
 }
 
-// out[c] (+)= sum over p of partials[p][c]; one thread per column, coalesced across threads.
-__global__ void colsum_partials_kernel(const float* __restrict__ partials, int count, int columns,
-                                       float* __restrict__ out_a, float* __restrict__ out_b, int split, int accumulate)
+// out[c] (+)= sum over p of partials[p][c].  A CTA of 32 x 8 threads owns 32 columns: the 8 thread rows
+// stride the partial rows (eight independent, coalesced 128-byte reads in flight), shared memory folds them.
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partials, int count, int columns,
+                       float* __restrict__ out_a, float* __restrict__ out_b, int split, int accumulate)
 {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if(c >= columns) return;
+    __shared__ float fold[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + tx;
     float total = 0.f;
-    for(int p = 0; p < count; p++) total += partials[(size_t)p * columns + c];
-    float* dst = c < split ? out_a + c : out_b + (c - split);
-    *dst = accumulate ? *dst + total : total;
+    if(c < columns)
+        for(int p = ty; p < count; p += 8) total += partials[(size_t)p * columns + c];
+    fold[ty][tx] = total;
+    __syncthreads();
+    if(ty == 0 && c < columns)
+    {
+        float sum = 0.f;
+#pragma unroll
+        for(int w = 0; w < 8; w++) sum += fold[w][tx];
+        float* dst = c < split ? out_a + c : out_b + (c - split);
+        *dst = accumulate ? *dst + sum : sum;
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -523,7 +535,7 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
     count_launch();
     if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
     const int columns = (int)(2 * E);
-    colsum_partials_kernel<<<(columns + 127) / 128, 128, 0, s>>>(partials, grid, columns, dgamma, dbeta, (int)E,
+    colsum_partials_kernel<<<(columns + 31) / 32, 256, 0, s>>>(partials, grid, columns, dgamma, dbeta, (int)E,
                                                                   (flags & ONN_ACCUMULATE) != 0);
     count_launch();
     return launch_status();

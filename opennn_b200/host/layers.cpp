@@ -411,6 +411,14 @@ void Dense3dForwardPropagationCuda::initialize()
 {
     const Dense3d* dense = static_cast<const Dense3d*>(layer);
     outputs.shape = {batch_size, dense->get_sequence_length(), dense->get_neurons_number()};
+    relu_bits.shape = {batch_size * dense->get_sequence_length(), Index(onn_relu_bits_words_per_row(dense->get_neurons_number()))};
+}
+
+vector<TensorViewCuda*> Dense3dForwardPropagationCuda::get_workspace_views()
+{
+    vector<TensorViewCuda*> views = LayerForwardPropagationCuda::get_workspace_views();
+    if(wants_relu_bits) views.push_back(&relu_bits);
+    return views;
 }
 
 void Dense3dBackPropagationCuda::initialize()
@@ -430,7 +438,8 @@ void Dense3d::forward_propagate(unique_ptr<LayerForwardPropagationCuda>& forward
     Dense3dForwardPropagationCuda* this_forward = static_cast<Dense3dForwardPropagationCuda*>(forward.get());
     const Index rows = forward->batch_size * sequence_length;
     const uint32_t flags = (is_training && this_forward->defer_softmax) ? ONN_DEFER_SOFTMAX : 0;
-    check_onn(onn_dense_fwd(forward->inputs[0].data, weights_device.data, biases_device.data, forward->outputs.data,
+    uint32_t* relu_bits = (is_training && this_forward->wants_relu_bits) ? reinterpret_cast<uint32_t*>(this_forward->relu_bits.data) : nullptr;
+    check_onn(onn_dense_fwd(forward->inputs[0].data, weights_device.data, biases_device.data, forward->outputs.data, relu_bits,
                             rows, inputs_number, neurons_number, get_activation_code(), flags, stream()),
               "Dense3d::forward_propagate");
 }
@@ -442,8 +451,9 @@ void Dense3d::back_propagate(unique_ptr<LayerForwardPropagationCuda>& forward, u
     fold_extra_gradients(back->output_gradients, 1);
     const uint32_t flags = this_back->delta_is_ready ? ONN_DELTA_READY : 0;
     check_onn(onn_dense_bwd(forward->inputs[0].data, weights_device.data, forward->outputs.data, back->output_gradients[0].data,
-                            this_back->weight_gradients.data, this_back->bias_gradients.data,
+                            this_back->weight_gradients.data, this_back->bias_gradient_is_ready ? nullptr : this_back->bias_gradients.data,
                             this_back->skip_input_gradient ? nullptr : back->input_gradients[0].data, this_back->input_relu_mask,
+                            this_back->input_relu_bits, this_back->input_bias_gradients,
                             rows, inputs_number, neurons_number, get_activation_code(), flags, stream()),
               "Dense3d::back_propagate");
 }

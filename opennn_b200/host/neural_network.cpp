@@ -238,6 +238,17 @@ void ForwardPropagationCuda::set(Index new_samples_number, NeuralNetwork* new_ne
         if(producer == "Embedding" || producer == "Normalization3d") layers[size_t(source)]->wants_row_flags = true;
     }
 
+    // plan: a Dense "RectifiedLinear" read by one Dense layer only also writes its ReLU mask as bits; that consumer's
+    // input-gradient GEMM applies the mask (see NeuralNetworkBackPropagationCuda::set, which makes the same test)
+    for(size_t i = 0; i < layers_number; i++)
+    {
+        const Dense3d* dense = dynamic_cast<const Dense3d*>(network_layers[i].get());
+        if(!dense || dense->get_activation_function() != "RectifiedLinear" || output_indices[i].size() != 1) continue;
+        const size_t consumer = size_t(output_indices[i][0]);
+        if(network_layers[consumer]->get_name() != "Dense3d" || input_indices[consumer].size() != 1) continue;
+        static_cast<Dense3dForwardPropagationCuda*>(layers[i].get())->wants_relu_bits = true;
+    }
+
     vector<vector<TensorViewCuda*>> views(layers_number);
     for(size_t i = 0; i < layers_number; i++) views[i] = layers[i]->get_workspace_views();
     workspace.resize(get_size(views));
@@ -340,6 +351,7 @@ void NeuralNetworkBackPropagationCuda::set(Index new_batch_size, NeuralNetwork* 
     }
 
     // plan 3: Dense "Linear" fed by a Dense "RectifiedLinear" that nobody else reads
+    vector<std::pair<size_t, size_t>> fused_relu_pairs;
     for(size_t i = 0; i < layers_number; i++)
     {
         if(network_layers[i]->get_name() != "Dense3d" || input_indices[i].size() != 1 || input_indices[i][0] < 0) continue;
@@ -348,7 +360,19 @@ void NeuralNetworkBackPropagationCuda::set(Index new_batch_size, NeuralNetwork* 
         if(!producer_dense || producer_dense->get_activation_function() != "RectifiedLinear" || output_indices[producer].size() != 1) continue;
         if(!forward_propagation) continue;
         static_cast<Dense3dBackPropagationCuda*>(layers[i].get())->input_relu_mask = forward_propagation->layers[producer]->outputs.data;
+        const auto* producer_forward = static_cast<const Dense3dForwardPropagationCuda*>(forward_propagation->layers[producer].get());
+        if(producer_forward->wants_relu_bits)
+            static_cast<Dense3dBackPropagationCuda*>(layers[i].get())->input_relu_bits = reinterpret_cast<const uint32_t*>(producer_forward->relu_bits.data);
         static_cast<Dense3dBackPropagationCuda*>(layers[producer].get())->delta_is_ready = true;
+        fused_relu_pairs.push_back({i, producer});
+    }
+
+    for(const auto& pair : fused_relu_pairs)
+    {
+        auto* consumer = static_cast<Dense3dBackPropagationCuda*>(layers[pair.first].get());
+        auto* producer = static_cast<Dense3dBackPropagationCuda*>(layers[pair.second].get());
+        consumer->input_bias_gradients = producer->bias_gradients.data;     // the gradient arena is linked by now
+        producer->bias_gradient_is_ready = true;
     }
 
     // workspace: the input gradients each layer owns, plus per-layer scratch

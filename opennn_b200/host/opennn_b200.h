@@ -299,7 +299,10 @@ private:
 struct Dense3dForwardPropagationCuda final : LayerForwardPropagationCuda
 {
     void initialize() override;
+    vector<TensorViewCuda*> get_workspace_views() override;
     bool defer_softmax = false;              // training with CrossEntropyError3d: outputs hold logits
+    TensorViewCuda relu_bits;                // (outputs > 0) at one bit per element, 32-bit words held in a float view
+    bool wants_relu_bits = false;            // the only consumer is a Dense3d whose dX epilogue applies this layer's ReLU derivative
 };
 
 struct Dense3dBackPropagationCuda final : LayerBackPropagationCuda
@@ -309,7 +312,10 @@ struct Dense3dBackPropagationCuda final : LayerBackPropagationCuda
     TensorViewCuda bias_gradients, weight_gradients;
     bool delta_is_ready = false;             // the consumer's dX epilogue already applied this layer's ReLU derivative
     const type* input_relu_mask = nullptr;   // outputs of the ReLU layer that produced this layer's input
+    const uint32_t* input_relu_bits = nullptr;   // the same mask as bits, written by that layer's forward pass
     bool skip_input_gradient = false;
+    type* input_bias_gradients = nullptr;    // bias gradients of that ReLU layer: column sums of this layer's dX
+    bool bias_gradient_is_ready = false;     // the consumer's dX epilogue already accumulated this layer's bias gradient
 };
 
 

@@ -117,6 +117,37 @@ def test_dense(capi, gemm_mode, name):
     assert_close(host(db), expected["db"], TOL, "db")
 
 
+@pytest.mark.parametrize("rows,features,hidden", [(96, 40, 72), (1024, 256, 512)])
+def test_dense_pair_relu_bits(capi, gemm_mode, rows, features, hidden):
+    """Feed-forward pair Dense(ReLU) -> Dense(Linear): the first layer's forward pass writes (y > 0) as bits, the
+    second layer's backward pass applies them to its input gradient and takes the first layer's bias gradient
+    from the column sums.  The result must be the one the float mask gives, and match the layer-by-layer oracle."""
+    from oracle import opennn_oracle as O
+    rng = np.random.default_rng(rows + hidden)
+    x = rng.standard_normal((rows, features)).astype(np.float32)
+    W1 = (rng.standard_normal((features, hidden)) / np.sqrt(features)).astype(np.float32)
+    b1 = (0.1 * rng.standard_normal(hidden)).astype(np.float32)
+    W2 = (rng.standard_normal((hidden, features)) / np.sqrt(hidden)).astype(np.float32)
+    b2 = (0.1 * rng.standard_normal(features)).astype(np.float32)
+    delta = rng.standard_normal((rows, features)).astype(np.float32)
+
+    y1, bits = capi.dense_fwd(dev(x), dev(W1), dev(b1), "RectifiedLinear", want_relu_bits=True)
+    y2 = capi.dense_fwd(y1, dev(W2), dev(b2), "Linear")
+    db1_bits = torch.zeros(hidden, device="cuda")
+    dx_bits, dW2, db2 = capi.dense_bwd(y1, dev(W2), y2, dev(delta), "Linear", relu_bits=bits, dx_colsum=db1_bits)
+    db1_mask = torch.zeros(hidden, device="cuda")
+    dx_mask, _, _ = capi.dense_bwd(y1, dev(W2), y2, dev(delta), "Linear", relu_mask=y1, dx_colsum=db1_mask)
+    assert np.array_equal(host(dx_bits), host(dx_mask)), "bit mask and float mask must select the same elements"
+    assert_close(host(db1_bits), host(db1_mask), 1e-5, "db1 from column sums")
+
+    device_mask = (host(y1) > 0).astype(np.float32)
+    dy1, dW2_e, db2_e = O.dense_backward(host(y1), W2, delta, np.ones_like(delta), "Linear")
+    assert_close(host(dx_bits), dy1 * device_mask, TOL, "delta of the ReLU layer")
+    assert_close(host(dW2), dW2_e, TOL, "dW2")
+    assert_close(host(db2), db2_e, TOL, "db2")
+    assert_close(host(db1_bits), (dy1 * device_mask).sum(axis=0), TOL, "db1", floor=1e-3 * np.abs(dy1).sum(axis=0).max())
+
+
 @pytest.mark.parametrize("name", names("mha_"))
 def test_mha(capi, gemm_mode, name):
     g = golden(name)
@@ -213,8 +244,11 @@ def test_gemm_layouts(capi, gemm_mode, a_major, b_major, shape):
     assert_close(host(out), reference, TOL, "plain")
 
     out = torch.zeros(M, N, device="cuda")
-    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, bias=dev(bias), relu=True, alpha=0.5)
-    assert_close(host(out), np.maximum(0.5 * reference + bias, 0), TOL, "alpha + bias + relu")
+    sums = torch.ones(N, device="cuda")
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, bias=dev(bias), relu=True, alpha=0.5, colsum_out=sums)
+    expected = np.maximum(0.5 * reference + bias, 0)
+    assert_close(host(out), expected, TOL, "alpha + bias + relu")
+    assert_close(host(sums), 1.0 + expected.sum(axis=0), TOL, "column sums of the written values")
 
     start = rng.standard_normal((M, N)).astype(np.float32)
     out = dev(start)
@@ -224,6 +258,27 @@ def test_gemm_layouts(capi, gemm_mode, a_major, b_major, shape):
     out = dev(start)
     capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, split_k=5)
     assert_close(host(out), start + reference, TOL, "split-K")
+
+    # the ReLU mask as one bit per element: written by a ReLU GEMM for its own result, applied by another GEMM
+    words = (N + 31) // 32
+    bits = torch.full((M, words), -1, dtype=torch.int32, device="cuda")
+    out = torch.zeros(M, N, device="cuda")
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, bias=dev(bias), relu=True, relu_bits_out=bits, relu_bits_ld=words)
+    written = host(out)
+    positive = np.zeros((M, words * 32), dtype=bool)
+    positive[:, :N] = written > 0
+    expected_bits = (positive.reshape(M, words, 32).astype(np.uint64) << np.arange(32, dtype=np.uint64)).sum(axis=2).astype(np.uint32)
+    valid = np.full((M, words), 0xFFFFFFFF, dtype=np.uint32)
+    if N % 32: valid[:, -1] = (1 << (N % 32)) - 1            # bits past column N are unspecified
+    got_bits = bits.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got_bits & valid, expected_bits & valid), "bits must equal (stored value > 0)"
+
+    out = dev(start)
+    sums = torch.zeros(N, device="cuda")
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, relu_bits=bits, relu_bits_ld=words, colsum_out=sums)
+    expected = reference * (written > 0)
+    assert_close(host(out), expected, TOL, "bit mask")
+    assert_close(host(sums), expected.sum(axis=0), TOL, "column sums after the bit mask", floor=1e-3 * np.abs(expected).sum(axis=0).max())
 
 
 def test_gemm_batched_heads(capi, gemm_mode):
@@ -265,3 +320,20 @@ def test_gemm_large_linearity(capi):
     rows = torch.arange(0, M, 511, device="cuda")
     expected = A1[rows].double() @ W.double()
     assert_close(host(outs[0][rows]), host(expected), TOL, "sampled rows vs fp64")
+
+
+def test_bounded_wait_gives_up_and_reports(capi):
+    """Failure detection without a fault: a wait on a barrier nothing signals runs out after its
+    limit, the kernel returns, the status word reports it once, and the context keeps working."""
+    import ctypes
+    assert capi.lib().onn_gemm_device_status() == 0
+    gave_up = ctypes.c_int(-1)
+    capi.check(capi.lib().onn_selftest_bounded_wait(ctypes.byref(gave_up)))
+    assert gave_up.value == 1
+    assert capi.lib().onn_gemm_device_status() == -5        # ONN_ERR_DEVICE_TIMEOUT, then cleared
+    assert capi.lib().onn_gemm_device_status() == 0
+    a = torch.randn(256, 64, device="cuda")
+    b = torch.randn(64, 256, device="cuda")
+    out = torch.empty(256, 256, device="cuda")
+    capi.gemm(a, b, out, 256, 256, 64, 64, 256, 256, 0, 1)
+    assert_close(host(out), host(a).astype(np.float64) @ host(b).astype(np.float64), TOL, "GEMM after the self-test")
