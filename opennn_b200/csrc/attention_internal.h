@@ -1,0 +1,16 @@
+// Internal interface between the MultiHeadAttention front end and the fused attention-core kernel.
+#pragma once
+#include <cuda_runtime.h>
+#include "../../include/onn_b200.h"
+
+namespace onn
+{
+// q [B, Sq, E], k and v [B, Sk, E] (head h = columns h * 64 ..), weights [B, H, Sq, Sk], context [B, Sq, E].
+// Supported: head size 64, Sk <= 256 and a multiple of 4, 16-byte aligned bases.
+bool attention_fwd_fused_supported(const float* q, const float* k, const float* v, const float* weights, const float* context,
+                                   long long B, long long Sq, long long Sk, long long E, long long H);
+int attention_fwd_fused_launch(const float* q, const float* k, const float* v, const unsigned char* key_is_pad,
+                               float* weights, float* context, long long B, long long Sq, long long Sk, long long E, long long H,
+                               int causal, float scale, cudaStream_t stream);
+int attention_tc_read_status();
+}

@@ -1,0 +1,472 @@
+// Attention core on the Blackwell tensor cores: scores, masks, softmax and context in ONE kernel.
+//
+// For one (batch, head, 128-query tile) a CTA computes
+//     S = Q K^T (tcgen05.mma, kind::tf32, accumulator in tensor memory, 128 lanes x up to 256 columns)
+//     P = softmax(scale * S with the key-padding and causal masks)
+//     O = P V   (second MMA: A operand read straight from tensor memory, V from shared memory)
+// and writes P (the attention weights the layer keeps for back-propagation) and O (its head's column
+// slice of the concatenated context) once.  The score matrix never makes the round trips through HBM
+// that separate GEMM / softmax / GEMM launches need: traffic per (batch, head) drops from ~7 passes
+// over the [Sq, Sk] matrix to the single write of P.
+//
+// Shapes: head size 64, source length <= 256 (one accumulator holds a whole row of scores), any query
+// length (tiles of 128 rows, ragged tiles are zero-filled on load and clipped on store by the copy engine).
+// The layer front end falls back to the separate kernels for anything else.
+//
+// Roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2..9 = softmax and
+// output.  A warp may read only the 32 accumulator lanes (query rows) its id selects, so warps w and
+// w + 4 share a quadrant and split its columns: each thread holds 128 scores of one row in registers
+// from ONE tensor-memory load (a round trip costs ~500 cycles, so the row is never re-read), the two
+// halves exchange row maximum and row sum through shared memory, the unnormalised exponentials go
+// back to tensor memory (rounded to tf32) for the context MMA, and the normalised weights leave from
+// the registers through swizzled staging blocks and TMA stores while that MMA runs.
+// CTAs are persistent: the producer fetches the next item's Q/K as soon as the score MMAs have read the
+// current ones, V as soon as the context MMAs have, and the next item's scores are computed while this
+// item's weights are still being written.  All barrier waits are bounded (tcgen05.cuh).
+#include <cmath>
+#include <cstdlib>
+
+#include "attention_internal.h"
+#include "common.cuh"
+#include "launch_counter.h"
+#include "tcgen05.cuh"
+
+namespace onn
+{
+namespace tc
+{
+
+constexpr int kSoftmaxWarps = 8;
+constexpr int kAttnThreads = 64 + 32 * kSoftmaxWarps;     // 320
+constexpr int kQRows = 128;                               // query rows per tile = accumulator lanes
+constexpr int kMaxKeys = 256;                             // accumulator columns of one score row
+constexpr int kHalfKeys = kMaxKeys / 2;                   // columns one softmax thread owns
+constexpr int kBlock = 32 * 32 * 4;                       // one warp's 32 x 32 staging block
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams
+{
+    const unsigned char* key_is_pad;                      // [B, Sk] or null
+    int B, H, Sq, Sk;
+    int q_tiles;                                          // ceil(Sq / 128)
+    int key_blocks;                                       // ceil(Sk / 32)
+    int causal;
+    float scale;
+    long long items;                                      // B * H * q_tiles
+};
+
+#define ONN_LIST8(M, v, o) M(v[(o)]), M(v[(o) + 1]), M(v[(o) + 2]), M(v[(o) + 3]), M(v[(o) + 4]), M(v[(o) + 5]), M(v[(o) + 6]), M(v[(o) + 7])
+#define ONN_LIST32(M, v) ONN_LIST8(M, v, 0), ONN_LIST8(M, v, 8), ONN_LIST8(M, v, 16), ONN_LIST8(M, v, 24)
+#define ONN_OUT_F(x) "=f"(x)
+#define ONN_INOUT_F(x) "+f"(x)
+#define ONN_IN_F(x) "f"(x)
+
+// Issues a 32-column tensor-memory load WITHOUT waiting for it: several can be in flight at once.
+__device__ __forceinline__ void tmem_load_32_issue(uint32_t taddr, float* v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : ONN_LIST32(ONN_OUT_F, v) : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// After the wait: an empty volatile statement that "rewrites" the loaded registers, so that no instruction
+// consuming them can be scheduled above the wait.
+__device__ __forceinline__ void tmem_load_pin_32(float* v) { asm volatile("" : ONN_LIST32(ONN_INOUT_F, v) :: "memory"); }
+
+__device__ __forceinline__ void tmem_store_32_issue(uint32_t taddr, const float* v)
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :: "r"(taddr), ONN_LIST32(ONN_IN_F, v) : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tcgen05_mma_tf32_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+        "}\n" :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// fp32 -> nearest tf32 (ties away from zero) for finite x, as the bits of an fp32 value: add half a tf32 ulp to the
+// magnitude and drop the 13 low mantissa bits.  Two integer instructions at full rate; the conversion instruction
+// would share the quarter-rate unit with the exponentials.
+__device__ __forceinline__ float round_tf32(float x)
+{
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+}
+
+__device__ __forceinline__ float exp2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void pair_barrier(int quadrant)
+{
+    // the two warps that share accumulator quadrant `quadrant` (64 threads); barrier 0 is __syncthreads
+    asm volatile("bar.sync %0, 64;" :: "r"(1 + quadrant) : "memory");
+}
+
+struct AttnItem { int b, h, q_tile; };
+
+__device__ __forceinline__ AttnItem decode_item(const AttnParams& p, long long w)
+{
+    // the query tiles of one head are neighbours, so the second one finds K and V in L2
+    AttnItem it;
+    it.q_tile = (int)(w % p.q_tiles); w /= p.q_tiles;
+    it.h = (int)(w % p.H);
+    it.b = (int)(w / p.H);
+    return it;
+}
+
+// hands one staged 32 x 32 block (this warp's rows) to the copy engine
+__device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint32_t warp_blocks, unsigned int& staged, const float* v, float factor,
+                                                int lane, int c0, int c1, int c2, int c3)
+{
+    const uint32_t block = warp_blocks + (staged & 1u) * kBlock;
+    // a block is free again once the copy issued from it two blocks ago has finished READING shared memory
+    if(staged >= 2) { if(lane == 0) bulk_wait_read_1(); __syncwarp(); }
+#pragma unroll
+    for(int q4 = 0; q4 < 8; q4++)
+    {
+        // row `lane` of the block is 128 bytes; 16-byte chunk q4 goes to slot q4 ^ (lane % 8): the 128-byte swizzle
+        const uint32_t dst = block + (uint32_t)lane * 128u + (uint32_t)((q4 ^ (lane & 7)) << 4);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "f"(v[q4 * 4] * factor), "f"(v[q4 * 4 + 1] * factor),
+                     "f"(v[q4 * 4 + 2] * factor), "f"(v[q4 * 4 + 3] * factor));
+    }
+    fence_async_shared();
+    __syncwarp();
+    if(lane == 0) { tma_store_4d(map, block, c0, c1, c2, c3); bulk_commit(); }
+    staged++;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_p,
+                     const __grid_constant__ CUtensorMap map_ctx, const AttnParams p)
+{
+    constexpr int KB = HD / 32;                             // 32-float k-blocks of the head dimension
+    constexpr int Q_BYTES = KB * kQRows * 128;              // K-major [128 rows][32 floats] per k-block
+    constexpr int K_BYTES = KB * kMaxKeys * 128;            // K-major [256 rows][32 floats] per k-block
+    constexpr int V_BYTES = KB * kMaxKeys * 128;            // MN-major [HD / 32 atoms][256 key rows][32 floats]
+    constexpr uint32_t TMEM_COLS = 512;                     // scores 0..255, context 256..256+HD
+    constexpr uint32_t O_COL = kMaxKeys;
+    // D = fp32, A = B = tf32; context MMA: A from tensor memory (K-major), B = V MN-major, N = HD
+    constexpr uint32_t IDESC_O = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_smem = smem;
+    uint8_t* k_smem = q_smem + Q_BYTES;
+    uint8_t* v_smem = k_smem + K_BYTES;
+    uint8_t* stage_smem = v_smem + V_BYTES;
+    float* exchange = reinterpret_cast<float*>(stage_smem + kSoftmaxWarps * 2 * kBlock);     // [2 halves][128 rows]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(exchange + 2 * kQRows);
+    uint64_t* qk_full = bars + 0;
+    uint64_t* v_full = bars + 1;
+    uint64_t* qk_empty = bars + 2;
+    uint64_t* v_empty = bars + 3;
+    uint64_t* s_full = bars + 4;
+    uint64_t* p_ready = bars + 5;
+    uint64_t* o_full = bars + 6;
+    uint64_t* o_free = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if(threadIdx.x == 0)
+    {
+        mbar_init(smem_u32(qk_full), 1); mbar_init(smem_u32(v_full), 1);
+        mbar_init(smem_u32(qk_empty), 1); mbar_init(smem_u32(v_empty), 1);
+        mbar_init(smem_u32(s_full), 1); mbar_init(smem_u32(o_full), 1);
+        mbar_init(smem_u32(p_ready), kSoftmaxWarps); mbar_init(smem_u32(o_free), kSoftmaxWarps);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if(warp == 1)
+    {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if(warp == 0)
+    {
+        // ---------------- TMA producer ----------------
+        if(lane == 0)
+        {
+            uint32_t ph = 0;
+            for(long long w = blockIdx.x; w < p.items; w += gridDim.x, ph ^= 1)
+            {
+                const AttnItem it = decode_item(p, w);
+                if(!mbar_wait(smem_u32(qk_empty), ph ^ 1, abort_flag, 21)) break;
+                mbar_arrive_expect_tx(smem_u32(qk_full), Q_BYTES + K_BYTES);
+#pragma unroll
+                for(int kb = 0; kb < KB; kb++)
+                {
+                    tma_load_4d(smem_u32(q_smem + kb * kQRows * 128), &map_q, smem_u32(qk_full), it.h * HD + kb * 32, it.q_tile * kQRows, 0, it.b);
+                    tma_load_4d(smem_u32(k_smem + kb * kMaxKeys * 128), &map_k, smem_u32(qk_full), it.h * HD + kb * 32, 0, 0, it.b);
+                }
+                if(!mbar_wait(smem_u32(v_empty), ph ^ 1, abort_flag, 22)) break;
+                mbar_arrive_expect_tx(smem_u32(v_full), V_BYTES);
+                tma_load_5d(smem_u32(v_smem), &map_v, smem_u32(v_full), 0, 0, it.h * KB, 0, it.b);
+            }
+            if(*abort_flag)
+            {
+                const unsigned long long start = clock64();
+                while(clock64() - start < 200000ull) { }    // let copies in flight land before shared memory goes away
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        // ---------------- MMA issuer ----------------
+        if(lane == 0)
+        {
+            const uint32_t idesc_s = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)((p.key_blocks * 32) >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
+            uint32_t ph = 0;
+            for(long long w = blockIdx.x; w < p.items; w += gridDim.x, ph ^= 1)
+            {
+                // scores: the previous item's context MMAs were issued before these and the tensor pipe runs in order,
+                // and every softmax thread had its scores in registers before those MMAs were released (p_ready)
+                if(!mbar_wait(smem_u32(qk_full), ph, abort_flag, 23)) break;
+                tcgen05_fence_after();
+#pragma unroll
+                for(int kb = 0; kb < KB; kb++)
+                {
+                    const uint64_t a_desc = make_smem_desc(smem_u32(q_smem + kb * kQRows * 128), 16, 1024, 2);
+                    const uint64_t b_desc = make_smem_desc(smem_u32(k_smem + kb * kMaxKeys * 128), 16, 1024, 2);
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                        tcgen05_mma_tf32(tmem_base, a_desc + (uint64_t)(j * 32 >> 4), b_desc + (uint64_t)(j * 32 >> 4), idesc_s, (kb > 0 || j > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(smem_u32(qk_empty));           // Q and K may be overwritten
+                tcgen05_commit(smem_u32(s_full));             // scores complete
+
+                if(!mbar_wait(smem_u32(v_full), ph, abort_flag, 25)) break;
+                if(!mbar_wait(smem_u32(p_ready), ph, abort_flag, 26)) break;
+                if(!mbar_wait(smem_u32(o_free), ph ^ 1, abort_flag, 27)) break;
+                tcgen05_fence_after();
+                const uint64_t v_desc = make_smem_desc(smem_u32(v_smem), kMaxKeys * 128, 512, 1);
+                const int k_steps = p.key_blocks * 4;        // 8 keys per MMA
+                for(int kk = 0; kk < k_steps; kk++)
+                    tcgen05_mma_tf32_a_tmem(tmem_base + O_COL, tmem_base + (uint32_t)(kk * 8), v_desc + (uint64_t)(kk * 1024 >> 4), IDESC_O, kk > 0 ? 1u : 0u);
+                tcgen05_commit(smem_u32(v_empty));
+                tcgen05_commit(smem_u32(o_full));
+            }
+        }
+    }
+    else
+    {
+        // ---------------- softmax and output (warps 2..9) ----------------
+        const int quadrant = warp & 3;                       // accumulator lanes 32 * quadrant .. + 31
+        const int half = (warp - 2) >> 2;                    // 0: key columns 0..127, 1: 128..255
+        const int r_local = quadrant * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quadrant * 32) << 16);
+        const uint32_t warp_blocks = smem_u32(stage_smem + (warp - 2) * 2 * kBlock);
+        const float to_log2 = p.scale * kLog2e;
+        unsigned int staged = 0;
+        uint32_t ph = 0;
+        for(long long w = blockIdx.x; w < p.items; w += gridDim.x, ph ^= 1)
+        {
+            const AttnItem it = decode_item(p, w);
+            const int row0 = it.q_tile * kQRows + quadrant * 32;      // first query row of this warp
+            const int q_row = row0 + lane;
+
+            // key-padding flags of this thread's four 32-key blocks, one word per block (the same in every lane)
+            uint32_t pad_word[4];
+#pragma unroll
+            for(int j = 0; j < 4; j++)
+            {
+                const int key = half * kHalfKeys + j * 32 + lane;
+                const bool flag = p.key_is_pad && key < p.Sk && p.key_is_pad[(long long)it.b * p.Sk + key] != 0;
+                pad_word[j] = __ballot_sync(0xffffffffu, flag);
+            }
+
+            bool ok = true;
+            if(lane == 0) ok = mbar_wait(smem_u32(s_full), ph, abort_flag, 28);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if(!ok) break;
+            tcgen05_fence_after();
+
+            // this thread's 128 scores, one round trip
+            float v[kHalfKeys];
+#pragma unroll
+            for(int j = 0; j < 4; j++) tmem_load_32_issue(lane_base + half * kHalfKeys + j * 32, v + j * 32);
+            tmem_load_wait();
+#pragma unroll
+            for(int j = 0; j < 4; j++) tmem_load_pin_32(v + j * 32);
+
+            // scores in the log2 domain with the layer's masks: padded keys are OVERWRITTEN with -1e9, keys after the
+            // query (causal) and keys past the source length drop out; blocks that need no per-element test take the short path
+            float row_max = -INFINITY;
+#pragma unroll
+            for(int j = 0; j < 4; j++)
+            {
+                const int key0 = half * kHalfKeys + j * 32;
+                const bool dead = key0 >= p.Sk || (p.causal && key0 > row0 + 31);
+                const bool special = pad_word[j] != 0 || key0 + 31 >= p.Sk || (p.causal && key0 + 31 > row0);
+                if(dead)
+                {
+#pragma unroll
+                    for(int i = 0; i < 32; i++) v[j * 32 + i] = -INFINITY;
+                }
+                else if(!special)
+                {
+#pragma unroll
+                    for(int i = 0; i < 32; i++) { v[j * 32 + i] *= to_log2; row_max = fmaxf(row_max, v[j * 32 + i]); }
+                }
+                else
+                {
+#pragma unroll
+                    for(int i = 0; i < 32; i++)
+                    {
+                        const int key = key0 + i;
+                        float t = v[j * 32 + i] * to_log2;
+                        if((pad_word[j] >> i) & 1u) t = -1e9f * kLog2e;
+                        if((p.causal && key > q_row) || key >= p.Sk) t = -INFINITY;
+                        v[j * 32 + i] = t;
+                        row_max = fmaxf(row_max, t);
+                    }
+                }
+            }
+            exchange[half * kQRows + r_local] = row_max;
+            pair_barrier(quadrant);
+            row_max = fmaxf(row_max, exchange[(half ^ 1) * kQRows + r_local]);
+            pair_barrier(quadrant);                          // both have read: the slots may be rewritten
+
+            // exponentials, unnormalised and rounded to tf32 for the tensor core
+            float total = 0.f;
+#pragma unroll
+            for(int i = 0; i < kHalfKeys; i++)
+            {
+                const float e = round_tf32(exp2_approx(v[i] - row_max));
+                total += e;
+                v[i] = e;
+            }
+#pragma unroll
+            for(int j = 0; j < 4; j++) tmem_store_32_issue(lane_base + half * kHalfKeys + j * 32, v + j * 32);
+            tmem_store_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if(lane == 0) mbar_arrive(smem_u32(p_ready));    // the context MMAs may start
+
+            exchange[half * kQRows + r_local] = total;
+            pair_barrier(quadrant);
+            total += exchange[(half ^ 1) * kQRows + r_local];
+            const float inv = total > 0.f ? 1.0f / total : 0.f;
+
+            // the attention weights leave from the registers while the context MMAs run
+#pragma unroll
+            for(int j = 0; j < 4; j++)
+            {
+                const int block = half * 4 + j;
+                if(block < p.key_blocks && row0 < p.Sq) stage_and_store(&map_p, warp_blocks, staged, v + j * 32, inv, lane, block * 32, row0, it.h, it.b);
+            }
+
+            if(lane == 0) ok = mbar_wait(smem_u32(o_full), ph, abort_flag, 29);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if(!ok) break;
+            tcgen05_fence_after();
+#pragma unroll
+            for(int c = 0; c < KB; c++)
+            {
+                if((c & 1) != half) continue;                // the two warps of a quadrant take alternate 32-column blocks
+                float o[32];
+                __syncwarp();
+                tmem_load_32_issue(lane_base + O_COL + c * 32, o);
+                tmem_load_wait();
+                tmem_load_pin_32(o);
+                if(row0 < p.Sq) stage_and_store(&map_ctx, warp_blocks, staged, o, inv, lane, it.h * HD + c * 32, row0, 0, it.b);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if(lane == 0) mbar_arrive(smem_u32(o_free));
+        }
+        if(lane == 0) bulk_wait_all();                       // the staging blocks must outlive the copies that read them
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if(warp == 1)
+    {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace tc
+
+bool attention_fwd_fused_supported(const float* q, const float* k, const float* v, const float* weights, const float* context,
+                                   long long B, long long Sq, long long Sk, long long E, long long H)
+{
+    if(H <= 0 || E % H != 0 || E / H != 64) return false;
+    if(Sk > tc::kMaxKeys || (Sk & 3) != 0) return false;              // one accumulator row; 16-byte pitch of the weights
+    if(B >= 65536 || Sq >= (1LL << 30)) return false;
+    if(!host_aligned16(q) || !host_aligned16(k) || !host_aligned16(v) || !host_aligned16(weights) || !host_aligned16(context)) return false;
+    return tc::encode_tiled() != nullptr;
+}
+
+int attention_fwd_fused_launch(const float* q, const float* k, const float* v, const unsigned char* key_is_pad,
+                               float* weights, float* context, long long B, long long Sq, long long Sk, long long E, long long H,
+                               int causal, float scale, cudaStream_t stream)
+{
+    using namespace tc;
+    constexpr int HD = 64;
+    AttnParams p;
+    p.key_is_pad = key_is_pad;
+    p.B = (int)B; p.H = (int)H; p.Sq = (int)Sq; p.Sk = (int)Sk;
+    p.q_tiles = (int)((Sq + kQRows - 1) / kQRows);
+    p.key_blocks = (int)((Sk + 31) / 32);
+    p.causal = causal;
+    p.scale = scale;
+    p.items = B * H * p.q_tiles;
+
+    CUtensorMap map_q, map_k, map_v, map_p, map_ctx;
+    bool ok = make_map(&map_q, q, E, Sq, E, 1, 0, (int)B, Sq * E, 32, kQRows, false);
+    ok = ok && make_map(&map_k, k, E, Sk, E, 1, 0, (int)B, Sk * E, 32, kMaxKeys, false);
+    ok = ok && make_wide_map(&map_v, v, E, Sk, E, 1, 0, (int)B, Sk * E, HD / 32, kMaxKeys);
+    ok = ok && make_map(&map_p, weights, Sk, Sq, Sk, (int)H, Sq * Sk, (int)B, H * Sq * Sk, 32, 32, false, false);
+    ok = ok && make_map(&map_ctx, context, E, Sq, E, 1, 0, (int)B, Sq * E, 32, 32, false, false);
+    if(!ok) return ONN_ERR_UNSUPPORTED;
+
+    // operands, staging blocks, exchange array, alignment slack, barriers
+    constexpr int smem = (HD / 32) * (kQRows + 2 * kMaxKeys) * 128 + kSoftmaxWarps * 2 * kBlock + 2 * kQRows * 4 + 1024 + 256;
+    static_assert(smem <= 232448, "beyond the shared memory of one CTA");
+    static bool configured = false;
+    if(!configured)
+    {
+        if(cudaFuncSetAttribute(attention_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return ONN_ERR_CUDA;
+        configured = true;
+    }
+    const int grid = (int)(p.items < kSmCount ? p.items : kSmCount);
+    attention_fwd_kernel<HD><<<grid, kAttnThreads, smem, stream>>>(map_q, map_k, map_v, map_p, map_ctx, p);
+    count_launch();
+    return launch_status();
+}
+
+int attention_tc_read_status()
+{
+    unsigned int status = 0;
+    if(tc::read_and_clear_status(&status) != 0) return ONN_ERR_CUDA;
+    return status == 0 ? ONN_OK : ONN_ERR_DEVICE_TIMEOUT;
+}
+
+}  // namespace onn

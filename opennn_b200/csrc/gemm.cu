@@ -6,6 +6,7 @@
 
 #include "common.cuh"
 #include "gemm_internal.h"
+#include "attention_internal.h"
 #include "launch_counter.h"
 
 namespace onn
@@ -22,6 +23,8 @@ static int initial_mode()
 }
 
 static std::atomic<int> g_mode{initial_mode()};
+
+int gemm_mode() { return g_mode.load(std::memory_order_relaxed); }
 
 int gemm(const onn_gemm_args& g, cudaStream_t stream)
 {
@@ -65,7 +68,12 @@ extern "C" int onn_gemm_set_mode(int mode)
     return ONN_OK;
 }
 
-extern "C" int onn_gemm_device_status(void) { return gemm_tc_read_status(); }
+extern "C" int onn_gemm_device_status(void)
+{
+    const int gemm_status = gemm_tc_read_status();
+    const int attention_status = attention_tc_read_status();
+    return gemm_status != ONN_OK ? gemm_status : attention_status;
+}
 
 extern "C" int onn_selftest_bounded_wait(int* gave_up)
 {

@@ -16,4 +16,6 @@ int gemm_tc_bounded_wait_selftest(int* gave_up_host);
 
 // Front end used by the layer code (same as onn_gemm).
 int gemm(const onn_gemm_args& g, cudaStream_t stream);
+// 0 = automatic, 1 = CUDA-core kernels only, 2 = tensor cores required (onn_gemm_set_mode).
+int gemm_mode();
 }

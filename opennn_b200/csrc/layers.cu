@@ -1,9 +1,11 @@
 // Layer-level entry points built from the GEMM primitive and the row kernels:
 // Dense<3> forward/backward and MultiHeadAttention forward/backward.
 #include <math.h>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "gemm_internal.h"
+#include "attention_internal.h"
 #include "launch_counter.h"
 
 namespace onn
@@ -236,22 +238,32 @@ extern "C" int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_param
         g.bias = params->bv;
         ONN_TRY(gemm(g, s));
     }
-    // scores = scale * Q K^T per (b, h)
+    // attention core: one fused kernel where the shapes allow (head size 64, source length <= 256), else
+    // scores GEMM -> mask + softmax -> context GEMM
+    static const bool fused_enabled = []{ const char* e = std::getenv("ONN_B200_ATTENTION_FUSED"); return !(e && e[0] == '0'); }();
+    if(fused_enabled && gemm_mode() != 1 && attention_fwd_fused_supported(q, k, v, p, ctx, B, Sq, Sk, E, H))
     {
-        onn_gemm_args g = plain_gemm(q, 0, E, k, 0, E, p, Sk, Sq, Sk, hd);
-        g.batch_inner = (int)H; g.batch_outer = (int)B;
-        head_strides(g, 'a', Sq, E, hd); head_strides(g, 'b', Sk, E, hd); score_strides(g, 'c', H, Sq, Sk);
-        g.alpha = scale;
-        ONN_TRY(gemm(g, s));
+        ONN_TRY(attention_fwd_fused_launch(q, k, v, pad_flags, p, ctx, B, Sq, Sk, E, H, causal, scale, s));
     }
-    ONN_TRY(launch_attention_softmax(p, pad_flags, B, (int)H, (int)Sq, (int)Sk, causal, s));
-    // context = P V per (b, h), written straight into the concatenated [B, Sq, E] layout
+    else
     {
-        onn_gemm_args g = plain_gemm(p, 0, Sk, v, 1, E, ctx, E, Sq, hd, Sk);
-        g.batch_inner = (int)H; g.batch_outer = (int)B;
-        score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sk, E, hd); head_strides(g, 'c', Sq, E, hd);
+        // scores = scale * Q K^T per (b, h)
+        {
+            onn_gemm_args g = plain_gemm(q, 0, E, k, 0, E, p, Sk, Sq, Sk, hd);
+            g.batch_inner = (int)H; g.batch_outer = (int)B;
+            head_strides(g, 'a', Sq, E, hd); head_strides(g, 'b', Sk, E, hd); score_strides(g, 'c', H, Sq, Sk);
+            g.alpha = scale;
+            ONN_TRY(gemm(g, s));
+        }
+        ONN_TRY(launch_attention_softmax(p, pad_flags, B, (int)H, (int)Sq, (int)Sk, causal, s));
+        // context = P V per (b, h), written straight into the concatenated [B, Sq, E] layout
+        {
+            onn_gemm_args g = plain_gemm(p, 0, Sk, v, 1, E, ctx, E, Sq, hd, Sk);
+            g.batch_inner = (int)H; g.batch_outer = (int)B;
+            score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sk, E, hd); head_strides(g, 'c', Sq, E, hd);
        
-        ONN_TRY(gemm(g, s));
+            ONN_TRY(gemm(g, s));
+        }
     }
     {
         onn_gemm_args g = plain_gemm(ctx, 0, E, Wo, 1, E, Y, E, B * Sq, E, E);

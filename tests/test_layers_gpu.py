@@ -281,6 +281,51 @@ def test_gemm_layouts(capi, gemm_mode, a_major, b_major, shape):
     assert_close(host(sums), expected.sum(axis=0), TOL, "column sums after the bit mask", floor=1e-3 * np.abs(expected).sum(axis=0).max())
 
 
+@pytest.mark.parametrize("B,H,Sq,Sk,causal,cross", [(2, 2, 256, 256, True, False), (2, 2, 256, 256, False, True),
+                                                      (1, 3, 200, 136, False, True), (3, 1, 40, 72, False, True),
+                                                      (2, 2, 72, 72, True, False)])
+def test_mha_head64(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
+    """MultiHeadAttention at head size 64, the shapes the fused attention-core kernel serves (whole and ragged
+    query tiles, source lengths up to 256, causal and key-padding masks), forward and backward against the oracle."""
+    from oracle import opennn_oracle as O
+    E = 64 * H
+    rng = np.random.default_rng(B * 1000 + Sq + Sk)
+    limit = np.sqrt(6.0 / (2 * E))
+    p = {n: rng.uniform(-limit, limit, (E, E)).astype(np.float32) for n in ("Wq", "Wk", "Wv", "Wo")}
+    p.update({n: (0.05 * rng.standard_normal(E)).astype(np.float32) for n in ("bq", "bk", "bv", "bo")})
+    xq = rng.standard_normal((B, Sq, E)).astype(np.float32)
+    xs = rng.standard_normal((B, Sk, E)).astype(np.float32) if cross else xq
+    if cross:
+        xs[0, Sk - 5:] = 0.0                                  # padded source rows: masked keys
+        if B > 1: xs[1, Sk // 2:] = 0.0
+    delta = rng.standard_normal((B, Sq, E)).astype(np.float32)
+    y_e, saved = O.mha_forward(xq, xs, p, H, causal)
+    grads_e, dxq_e, dxs_e = O.mha_backward(xq, xs, p, H, saved, delta, not cross)
+
+    pd = {k: dev(v) for k, v in p.items()}
+    xq_d = dev(xq)
+    xs_d = dev(xs) if cross else xq_d
+    y, ws = capi.mha_fwd(xq_d, xs_d, pd, H, causal)
+    weights = capi.mha_attention_weights(ws, B, Sq, Sk, E, H)
+    # tf32 operands: the L2 error of every tensor stays within the tolerance; a single element of a reduction over
+    # only 64 terms may exceed it (one product carries up to 9.8e-4), so the largest element error gets twice that
+    def check(device, reference, what, floor=0.0):
+        max_err, l2_err = errors(device, reference, floor)
+        assert np.all(np.isfinite(device)), what
+        assert l2_err <= TOL and max_err <= (TOL if gemm_mode == "simt" else 2 * TOL), f"{what}: max-rel {max_err:.3e}, l2-rel {l2_err:.3e}"
+
+    check(host(weights), saved["weights"], "attention weights")
+    assert_close(host(weights).sum(axis=-1), np.ones((B, H, Sq)), 1e-3, "rows of the attention weights sum to one")
+    check(host(y), y_e, "y")
+    grads, dxq, dxs = capi.mha_bwd(xq_d, xs_d, pd, H, causal, ws, dev(delta))
+    check(host(dxq), dxq_e, "dxq")
+    if cross:
+        check(host(dxs), dxs_e, "dxs")
+    for name in ("dWq", "dWk", "dWv", "dWo", "dbq", "dbv", "dbo"):
+        check(host(grads[name]), grads_e[name], name, floor=1e-6)
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
 def test_gemm_batched_heads(capi, gemm_mode):
     """Per-(batch, head) products addressed by strides inside [B, S, E] tensors, as attention uses them."""
     Bn, H, Sq, Sk, hd = 3, 4, 40, 72, 16
