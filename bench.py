@@ -197,7 +197,10 @@ def time_dominant_kernel(capi, torch, w, peaks, copies=4, launches=24, with_cubl
             "shape": {"M": M, "N": N, "K": K}, "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
             "frac": achieved / peaks["tflops"], "peak_source": "dense bf16 burst, " + peaks["source"] +
             "; tf32 operands have half the bf16 rate, so 0.5 is this kernel's ceiling on this scale",
-            "us_per_launch": seconds * 1e6, "cublas_tf32_same_shape_tflops": cublas_tf32, "traffic": None}
+            "us_per_launch": seconds * 1e6, "cublas_tf32_same_shape_tflops": cublas_tf32,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised in
+            # profiles/gemm_tc2_ffn_up_M16384_N4096_K1024_ncu.md (algorithmic bytes: 84 MB in + 268 MB out)
+            "traffic": 328.9e6}
 
 
 def run_ours(args):
