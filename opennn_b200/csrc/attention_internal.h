@@ -12,5 +12,13 @@ bool attention_fwd_fused_supported(const float* q, const float* k, const float* 
 int attention_fwd_fused_launch(const float* q, const float* k, const float* v, const unsigned char* key_is_pad,
                                float* weights, float* context, long long B, long long Sq, long long Sk, long long E, long long H,
                                int causal, float scale, cudaStream_t stream);
+// Backward of the same core up to the query gradient: d_scores = P * (dP - rowsum(P * dP)) with dP = dO V^T, and
+// d_q = scale * d_scores K (+ its column sums into d_bias_q).  The key and value gradients follow from d_scores
+// and the weights with two batched GEMMs.
+bool attention_bwd_fused_supported(const float* k, const float* v, const float* weights, const float* context, const float* d_context,
+                                   const float* d_scores, const float* d_q, long long B, long long Sq, long long Sk, long long E, long long H);
+int attention_bwd_fused_launch(const float* k, const float* v, const float* weights, const float* context, const float* d_context,
+                               float* d_scores, float* d_q, float* d_bias_q, long long B, long long Sq, long long Sk, long long E, long long H,
+                               float scale, cudaStream_t stream);
 int attention_tc_read_status();
 }

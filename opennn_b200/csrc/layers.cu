@@ -309,23 +309,32 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         g.colsum_out = grads->dbv; g.colsum_stride_inner = hd;      // dbv = column sums of dV, taken in the epilogue
         ONN_TRY(gemm(g, s));
     }
-    // dP = dO V^T
+    // dP, dS and dQ: one fused kernel where the shapes allow, else GEMM -> softmax backward -> GEMM
+    static const bool fused_enabled = []{ const char* e = std::getenv("ONN_B200_ATTENTION_FUSED"); return !(e && e[0] == '0'); }();
+    if(fused_enabled && gemm_mode() != 1 && attention_bwd_fused_supported(k, v, p, ctx, dctx, dp, dq, B, Sq, Sk, E, H))
     {
-        onn_gemm_args g = plain_gemm(dctx, 0, E, v, 0, E, dp, Sk, Sq, Sk, hd);
-        g.batch_inner = (int)H; g.batch_outer = (int)B;
-        head_strides(g, 'a', Sq, E, hd); head_strides(g, 'b', Sk, E, hd); score_strides(g, 'c', H, Sq, Sk);
-        ONN_TRY(gemm(g, s));
+        ONN_TRY(attention_bwd_fused_launch(k, v, p, ctx, dctx, dp, dq, grads->dbq, B, Sq, Sk, E, H, scale, s));
     }
-    // dS = P * (dP - rowsum(P * dP)), in place
-    ONN_TRY(launch_attention_softmax_bwd(p, dp, B * H * Sq, (int)Sk, s));
-    // dQ = scale * dS K
+    else
     {
-        onn_gemm_args g = plain_gemm(dp, 0, Sk, k, 1, E, dq, E, Sq, hd, Sk);
-        g.batch_inner = (int)H; g.batch_outer = (int)B;
-        score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sk, E, hd); head_strides(g, 'c', Sq, E, hd);
-        g.alpha = scale;
-        g.colsum_out = grads->dbq; g.colsum_stride_inner = hd;      // dbq = column sums of dQ, taken in the epilogue
-        ONN_TRY(gemm(g, s));
+        // dP = dO V^T
+        {
+            onn_gemm_args g = plain_gemm(dctx, 0, E, v, 0, E, dp, Sk, Sq, Sk, hd);
+            g.batch_inner = (int)H; g.batch_outer = (int)B;
+            head_strides(g, 'a', Sq, E, hd); head_strides(g, 'b', Sk, E, hd); score_strides(g, 'c', H, Sq, Sk);
+            ONN_TRY(gemm(g, s));
+        }
+        // dS = P * (dP - rowsum(P * dP)), in place
+        ONN_TRY(launch_attention_softmax_bwd(p, dp, B * H * Sq, (int)Sk, s));
+        // dQ = scale * dS K
+        {
+            onn_gemm_args g = plain_gemm(dp, 0, Sk, k, 1, E, dq, E, Sq, hd, Sk);
+            g.batch_inner = (int)H; g.batch_outer = (int)B;
+            score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sk, E, hd); head_strides(g, 'c', Sq, E, hd);
+            g.alpha = scale;
+            g.colsum_out = grads->dbq; g.colsum_stride_inner = hd;      // dbq = column sums of dQ, taken in the epilogue
+            ONN_TRY(gemm(g, s));
+        }
     }
     // dK = scale * dS^T Q
     {
