@@ -157,11 +157,14 @@ int onn_layernorm_fwd(const float* A, const float* R, const float* gamma, const 
  * sum; CPU semantics opennn/normalization_layer_3d.cpp:128-188.  dY2, dY3 (optional) are
  * further consumer gradients summed on load.  X is the layer input (A + R).  dX is the
  * gradient for the layer input; with the Addition fused both addends receive this same
- * tensor (opennn/addition_layer.h:79-90).  workspace: onn_layernorm_bwd_workspace_floats. */
+ * tensor (opennn/addition_layer.h:79-90).  workspace: onn_layernorm_bwd_workspace_floats.
+ * dX_colsum (optional, [E]): the column sums of dX are ADDED to it.  When one addend of the fused Addition is
+ * the output of a Dense or MultiHeadAttention layer with no other consumer, that layer's output gradient IS dX
+ * and these sums are its (projection) bias gradient, which then needs no pass of its own over dX. */
 size_t onn_layernorm_bwd_workspace_floats(int64_t rows, int64_t E);
 int onn_layernorm_bwd(const float* dY, const float* dY2, const float* dY3, const float* X,
                       const float* mean, const float* inv_std, const float* gamma,
-                      float* dX, float* dgamma, float* dbeta,
+                      float* dX, float* dgamma, float* dbeta, float* dX_colsum,
                       int64_t rows, int64_t E, float* workspace, uint32_t flags, void* stream);
 
 /* No counterpart in the reference.  The same computation as onn_layernorm_bwd for a caller that

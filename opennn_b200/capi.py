@@ -168,7 +168,7 @@ def layernorm_fwd(A, gamma, beta, R=None, eps=None, flags=0, want_sum=False):
     return Y, mean, inv_std, total
 
 
-def layernorm_bwd(dY, X, mean, inv_std, gamma, dY2=None, dY3=None, flags=0):
+def layernorm_bwd(dY, X, mean, inv_std, gamma, dY2=None, dY3=None, flags=0, dx_colsum=None):
     E = X.shape[-1]
     rows = X.numel() // E
     dX = torch.empty_like(X)
@@ -176,7 +176,7 @@ def layernorm_bwd(dY, X, mean, inv_std, gamma, dY2=None, dY3=None, flags=0):
     dbeta = torch.zeros(E, device="cuda")
     ws = _empty(lib().onn_layernorm_bwd_workspace_floats(i64(rows), i64(E)))
     check(lib().onn_layernorm_bwd(ptr(dY), ptr(dY2), ptr(dY3), ptr(X), ptr(mean), ptr(inv_std), ptr(gamma), ptr(dX),
-                                  ptr(dgamma), ptr(dbeta), i64(rows), i64(E), ptr(ws), C.c_uint32(flags), stream_ptr()),
+                                  ptr(dgamma), ptr(dbeta), ptr(dx_colsum), i64(rows), i64(E), ptr(ws), C.c_uint32(flags), stream_ptr()),
           "onn_layernorm_bwd")
     return dX, dgamma, dbeta
 

@@ -256,7 +256,9 @@ layernorm_fwd_generic_kernel(const float* __restrict__ A, const float* __restric
 // Each warp keeps running per-column sums of dy * x_hat and dy in registers across all the
 // rows it visits; the CTA folds its 8 warps through shared memory and writes ONE partial
 // row pair per CTA to `partials` ([gridDim.x][2][E]); colsum_partials_kernel finishes.
-template <int VEC>
+// DX_SUM adds a third running sum, of dx itself: the bias gradient of the layer whose output the
+// normalised sum contains (its output gradient IS dx), so partials become [gridDim.x][3][E].
+template <int VEC, bool DX_SUM>
 __global__ void __launch_bounds__(kRowThreads, 2)
 layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2, const float* __restrict__ dY3,
                      const float* __restrict__ X, const float* __restrict__ mean_in, const float* __restrict__ inv_std_in,
@@ -270,14 +272,20 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
     const long long warp = (long long)blockIdx.x * kRowWarps + warp_in_block;
     const long long stride = (long long)gridDim.x * kRowWarps;
     const float inv_E = 1.0f / (float)E;
-    float* acc_gamma = smem + (size_t)warp_in_block * 2 * E;
+    constexpr int SETS = DX_SUM ? 3 : 2;
+    float* acc_gamma = smem + (size_t)warp_in_block * SETS * E;
     float* acc_beta = acc_gamma + E;
+    float* acc_dx = acc_beta + E;                            // only touched with DX_SUM
 
 #pragma unroll
     for(int i = 0; i < VEC; i++)
     {
         const int e = (i * 32 + lane) * 4;
-        if(e < E) { st4(acc_gamma + e, make_float4(0.f, 0.f, 0.f, 0.f)); st4(acc_beta + e, make_float4(0.f, 0.f, 0.f, 0.f)); }
+        if(e < E)
+        {
+            st4(acc_gamma + e, make_float4(0.f, 0.f, 0.f, 0.f)); st4(acc_beta + e, make_float4(0.f, 0.f, 0.f, 0.f));
+            if(DX_SUM) st4(acc_dx + e, make_float4(0.f, 0.f, 0.f, 0.f));
+        }
     }
 
     for(long long row = warp; row < rows; row += stride)
@@ -324,17 +332,23 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
                 o.z = ((d[i].z - sum_d - xh[i].z * sum_dx) * inv_std);
                 o.w = ((d[i].w - sum_d - xh[i].w * sum_dx) * inv_std);
                 st4(dX + base + e, o);
+                if(DX_SUM)
+                {
+                    float4 ax = ld4(acc_dx + e);
+                    ax.x += o.x; ax.y += o.y; ax.z += o.z; ax.w += o.w;
+                    st4(acc_dx + e, ax);
+                }
             }
         }
     }
 
     __syncthreads();
-    float* out = partials + (size_t)blockIdx.x * 2 * E;
-    for(int c = threadIdx.x; c < 2 * E; c += kRowThreads)
+    float* out = partials + (size_t)blockIdx.x * SETS * E;
+    for(int c = threadIdx.x; c < SETS * E; c += kRowThreads)
     {
         float total = 0.f;
 #pragma unroll
-        for(int w = 0; w < kRowWarps; w++) total += smem[(size_t)w * 2 * E + c];
+        for(int w = 0; w < kRowWarps; w++) total += smem[(size_t)w * SETS * E + c];
         out[c] = total;
     }
 }
@@ -387,7 +401,7 @@ layernorm_bwd_generic_kernel(const float* __restrict__ dY, const float* __restri
 // stride the partial rows (eight independent, coalesced 128-byte reads in flight), shared memory folds them.
 __global__ void __launch_bounds__(256)
 colsum_partials_kernel(const float* __restrict__ partials, int count, int columns,
-                       float* __restrict__ out_a, float* __restrict__ out_b, int split, int accumulate)
+                       float* __restrict__ out_a, float* __restrict__ out_b, float* __restrict__ out_c, int split, int accumulate)
 {
     __shared__ float fold[8][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -402,8 +416,13 @@ colsum_partials_kernel(const float* __restrict__ partials, int count, int column
         float sum = 0.f;
 #pragma unroll
         for(int w = 0; w < 8; w++) sum += fold[w][tx];
-        float* dst = c < split ? out_a + c : out_b + (c - split);
-        *dst = accumulate ? *dst + sum : sum;
+        // columns [0, split) -> out_a, [split, 2 split) -> out_b, the rest is ADDED to out_c (a bias gradient)
+        if(c >= 2 * split) out_c[c - 2 * split] += sum;
+        else
+        {
+            float* dst = c < split ? out_a + c : out_b + (c - split);
+            *dst = accumulate ? *dst + sum : sum;
+        }
     }
 }
 
@@ -489,30 +508,43 @@ extern "C" int onn_layernorm_fwd(const float* A, const float* R, const float* ga
 // Number of CTAs the backward kernel runs with (= partial row pairs in the workspace).
 static int layernorm_bwd_grid(int64_t rows) { return grid_for(rows, kRowWarps, 2); }   // two resident CTAs per SM
 
-extern "C" size_t onn_layernorm_bwd_workspace_floats(int64_t rows, int64_t E)
+// floats of partial sums for `sets` running sums per CTA
+static size_t layernorm_bwd_partial_floats(int64_t rows, int64_t E, int sets)
 {
     if(rows <= 0 || E <= 0) return 0;
-    return (size_t)layernorm_bwd_grid(rows) * 2 * (size_t)E;
+    return (size_t)layernorm_bwd_grid(rows) * (size_t)sets * (size_t)E;
 }
+
+extern "C" size_t onn_layernorm_bwd_workspace_floats(int64_t rows, int64_t E) { return layernorm_bwd_partial_floats(rows, E, 3); }
 
 namespace onn
 {
+int launch_colsum_accumulate(const float* D, long long rows, long long cols, long long ld, float* out, cudaStream_t s);
+
+static bool fast_path_sums_dx(const float* dX_colsum, int64_t E) { return dX_colsum != nullptr && E <= 128 * kMaxVec; }
+
 // Shared by the workspace entry point and any other front end: launches the row kernel
 // into `partials` and the column reduction into dgamma / dbeta.
 int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, const float* X,
                          const float* mean, const float* inv_std, const float* gamma,
-                         float* dX, float* dgamma, float* dbeta, int64_t rows, int64_t E,
+                         float* dX, float* dgamma, float* dbeta, float* dX_colsum, int64_t rows, int64_t E,
                          float* partials, uint32_t flags, cudaStream_t s)
 {
     const int grid = layernorm_bwd_grid(rows);
     const bool fast = (E & 3) == 0 && E <= 128 * kMaxVec && host_aligned16(dY) && host_aligned16(X) && host_aligned16(dX) &&
                       host_aligned16(gamma) && (!dY2 || host_aligned16(dY2)) && (!dY3 || host_aligned16(dY3));
-#define ONN_LN_BWD(V) layernorm_bwd_kernel<V><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E)
+    const bool dx_sum = fast_path_sums_dx(dX_colsum, E);
+    const int sets = dx_sum ? 3 : 2;
+#define ONN_LN_BWD(V) do { if(dx_sum) layernorm_bwd_kernel<V, true><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E); \
+                           else layernorm_bwd_kernel<V, false><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E); } while(0)
     if(fast)
     {
-        const size_t smem = (size_t)kRowWarps * 2 * E * sizeof(float);   // <= 64 KiB at E = 1024
+        const size_t smem = (size_t)kRowWarps * sets * E * sizeof(float);   // 64 KiB (96 KiB with the dx sums) at E = 1024
         if(smem > 48 * 1024)
-            cudaFuncSetAttribute(layernorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        {
+            cudaFuncSetAttribute(layernorm_bwd_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+            cudaFuncSetAttribute(layernorm_bwd_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        }
         switch(vec_count(E))
         {
             case 1: ONN_LN_BWD(1); break;
@@ -534,22 +566,25 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
 #undef ONN_LN_BWD
     count_launch();
     if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
-    const int columns = (int)(2 * E);
-    colsum_partials_kernel<<<(columns + 31) / 32, 256, 0, s>>>(partials, grid, columns, dgamma, dbeta, (int)E,
+    const int columns = (int)(((fast && dx_sum) ? 3 : 2) * E);
+    colsum_partials_kernel<<<(columns + 31) / 32, 256, 0, s>>>(partials, grid, columns, dgamma, dbeta, dX_colsum, (int)E,
                                                                   (flags & ONN_ACCUMULATE) != 0);
     count_launch();
-    return launch_status();
+    if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    // rows the vector kernel cannot take: the column sums of dX come from a pass of their own
+    if(dX_colsum && !(fast && dx_sum)) return launch_colsum_accumulate(dX, rows, E, E, dX_colsum, s);
+    return ONN_OK;
 }
 }  // namespace onn
 
 extern "C" int onn_layernorm_bwd(const float* dY, const float* dY2, const float* dY3, const float* X,
                                  const float* mean, const float* inv_std, const float* gamma,
-                                 float* dX, float* dgamma, float* dbeta,
+                                 float* dX, float* dgamma, float* dbeta, float* dX_colsum,
                                  int64_t rows, int64_t E, float* workspace, uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(dY && X && mean && inv_std && gamma && dX && dgamma && dbeta && rows > 0 && E > 0);
     if(!workspace) return ONN_ERR_WORKSPACE;
-    return layernorm_bwd_launch(dY, dY2, dY3, X, mean, inv_std, gamma, dX, dgamma, dbeta, rows, E, workspace, flags,
+    return layernorm_bwd_launch(dY, dY2, dY3, X, mean, inv_std, gamma, dX, dgamma, dbeta, dX_colsum, rows, E, workspace, flags,
                                 (cudaStream_t)stream);
 }
 
@@ -594,13 +629,13 @@ extern "C" int onn_layernorm_bwd_static(const float* dY, const float* dY2, const
 {
     ONN_CHECK_ARG(dY && X && mean && inv_std && gamma && dX && dgamma && dbeta && rows > 0 && E > 0);
     if(E > ONN_LAYERNORM_BWD_STATIC_MAX_E) return ONN_ERR_LIMIT;      // the fixed buffer holds rows of at most this width
-    if(onn_layernorm_bwd_workspace_floats(rows, E) > sizeof(g_layernorm_bwd_static_partials) / sizeof(float)) return ONN_ERR_LIMIT;
+    if(layernorm_bwd_partial_floats(rows, E, 2) > sizeof(g_layernorm_bwd_static_partials) / sizeof(float)) return ONN_ERR_LIMIT;
     float* partials = nullptr;
     const int status = static_partials_for_current_device(&partials);
     if(status != ONN_OK) return status;
     // Nothing in the buffer has to start at zero: the row kernel overwrites one partial row pair per CTA
     // and the column reduction reads exactly those, so whatever an earlier call left behind is never read.
-    return layernorm_bwd_launch(dY, dY2, dY3, X, mean, inv_std, gamma, dX, dgamma, dbeta, rows, E, partials, flags,
+    return layernorm_bwd_launch(dY, dY2, dY3, X, mean, inv_std, gamma, dX, dgamma, dbeta, nullptr, rows, E, partials, flags,
                                 (cudaStream_t)stream);
 }
 

@@ -361,7 +361,8 @@ void MultiHeadAttention::back_propagate(unique_ptr<LayerForwardPropagationCuda>&
     const onn_mha_grads grads = {this_back->query_weight_gradients.data, this_back->query_bias_gradients.data,
                                  this_back->key_weight_gradients.data, this_back->key_bias_gradients.data,
                                  this_back->value_weight_gradients.data, this_back->value_bias_gradients.data,
-                                 this_back->projection_weight_gradients.data, this_back->projection_bias_gradients.data};
+                                 this_back->projection_weight_gradients.data,
+                                 this_back->projection_bias_gradient_is_ready ? nullptr : this_back->projection_bias_gradients.data};
     uint32_t flags = 0;
     if(!self_attention && back->accumulate_input_gradient.size() > 1 && back->accumulate_input_gradient[1]) flags |= ONN_ACCUMULATE;
     check_onn(onn_mha_bwd(query_input, source_input, &params, this_forward->attention_state.data, back->output_gradients[0].data, &grads,
@@ -542,6 +543,7 @@ void Normalization3d::back_propagate(unique_ptr<LayerForwardPropagationCuda>& fo
                                 gradients.size() > 2 ? gradients[2].data : nullptr, forward->inputs[0].data,
                                 this_forward->means.data, this_forward->inverse_standard_deviations.data, gammas_device.data,
                                 back->input_gradients[0].data, this_back->gamma_gradients.data, this_back->beta_gradients.data,
+                                this_back->input_bias_gradients,
                                 rows, embedding_dimension, this_back->partial_sums.data, ONN_ACCUMULATE, stream()),
               "Normalization3d::back_propagate");
 }

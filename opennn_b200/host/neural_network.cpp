@@ -375,6 +375,34 @@ void NeuralNetworkBackPropagationCuda::set(Index new_batch_size, NeuralNetwork* 
         producer->bias_gradient_is_ready = true;
     }
 
+    // plan 4: Normalization3d over a fused Addition<3> one of whose addends comes from a Dense "Linear" or a
+    // MultiHeadAttention layer that nobody else reads: that layer's output gradient IS the normalisation's input
+    // gradient, so its (projection) bias gradient is the column sum of that tensor, which the normalisation kernel takes
+    for(size_t i = 0; i < layers_number; i++)
+    {
+        if(network_layers[i]->get_name() != "Normalization3d" || input_indices[i].size() != 1 || input_indices[i][0] < 0) continue;
+        const size_t addition = size_t(input_indices[i][0]);
+        if(!layers[addition]->fused_into_consumer) continue;
+        for(const Index addend : input_indices[addition])
+        {
+            if(addend < 0 || output_indices[size_t(addend)].size() != 1) continue;
+            auto* norm = static_cast<Normalization3dBackPropagationCuda*>(layers[i].get());
+            if(norm->input_bias_gradients) break;
+            if(auto* dense = dynamic_cast<Dense3dBackPropagationCuda*>(layers[size_t(addend)].get()))
+            {
+                const Dense3d* dense_layer = static_cast<const Dense3d*>(network_layers[size_t(addend)].get());
+                if(dense_layer->get_activation_function() != "Linear" || dense->bias_gradient_is_ready) continue;
+                norm->input_bias_gradients = dense->bias_gradients.data;
+                dense->bias_gradient_is_ready = true;
+            }
+            else if(auto* attention = dynamic_cast<MultiHeadAttentionBackPropagationCuda*>(layers[size_t(addend)].get()))
+            {
+                norm->input_bias_gradients = attention->projection_bias_gradients.data;
+                attention->projection_bias_gradient_is_ready = true;
+            }
+        }
+    }
+
     // workspace: the input gradients each layer owns, plus per-layer scratch
     vector<vector<TensorViewCuda*>> workspace_views(layers_number);
     for(size_t i = 0; i < layers_number; i++) workspace_views[i] = layers[i]->get_workspace_views();

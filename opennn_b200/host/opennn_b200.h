@@ -262,6 +262,7 @@ struct MultiHeadAttentionBackPropagationCuda final : LayerBackPropagationCuda
                    value_weight_gradients, value_bias_gradients, projection_weight_gradients, projection_bias_gradients;
     TensorViewCuda scratch;                  // shared by all attention layers (NeuralNetworkBackPropagationCuda owns it)
     Index scratch_floats = 0;
+    bool projection_bias_gradient_is_ready = false;   // taken by the following Normalization3d as column sums of its dx
 };
 
 
@@ -363,6 +364,7 @@ struct Normalization3dBackPropagationCuda final : LayerBackPropagationCuda
     vector<TensorViewCuda*> get_workspace_views() override;
     TensorViewCuda gamma_gradients, beta_gradients;
     TensorViewCuda partial_sums;
+    type* input_bias_gradients = nullptr;    // bias gradient of the layer whose output gradient is this layer's input gradient
 };
 
 class Addition3d final : public Layer

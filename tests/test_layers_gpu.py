@@ -78,6 +78,13 @@ def test_layernorm(capi, name):
     assert_close(host(dx), g["dx"], 5e-5, "dx")
     assert_close(host(dgamma), g["dgamma"], 5e-5, "dgamma")
     assert_close(host(dbeta), g["dbeta"], 5e-5, "dbeta")
+    # column sums of dx, ADDED to a caller's vector: the bias gradient of the layer whose output was normalised
+    E = g["x"].shape[-1]
+    sums = torch.ones(E, device="cuda")
+    dx_again, _, _ = capi.layernorm_bwd(delta, x, mean, inv_std, gamma, dx_colsum=sums)
+    assert np.array_equal(host(dx_again), host(dx))
+    expected_sums = 1.0 + g["dx"].reshape(-1, E).astype(np.float64).sum(axis=0)
+    assert_close(host(sums), expected_sums, 5e-5, "column sums of dx", floor=float(np.abs(g["dx"]).reshape(-1, E).sum(axis=0).max()) * 1e-1)
     # fused residual add: A + R = x, and the sum comes back as the Addition layer's output
     a = dev(g["x"] * 0.25)
     r = dev(g["x"] - g["x"] * 0.25)
