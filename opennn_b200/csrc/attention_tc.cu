@@ -220,6 +220,8 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();                                               // set-up done; global memory only from here on
 
     if(warp == 0)
     {
@@ -675,9 +677,9 @@ static int launch_attention_core(const CUtensorMap& a, const CUtensorMap& b1, co
         configured = true;
     }
     const int grid = (int)(p.items < kSmCount ? p.items : kSmCount);
-    attention_core_kernel<kAttnHeadSize, BACKWARD><<<grid, kAttnThreads, kAttnSmem, stream>>>(a, b1, b2, w, o, in, p);
+    const cudaError_t launched = launch_overlapped(attention_core_kernel<kAttnHeadSize, BACKWARD>, dim3(grid), dim3(kAttnThreads), kAttnSmem, stream, a, b1, b2, w, o, in, p);
     count_launch();
-    return launch_status();
+    return launched == cudaSuccess ? launch_status() : ONN_ERR_CUDA;
 }
 }  // namespace tc
 

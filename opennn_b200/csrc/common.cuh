@@ -5,6 +5,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <utility>
+
 #include "../../include/onn_b200.h"
 
 namespace onn
@@ -26,6 +29,37 @@ inline int grid_for(long long work_items, int items_per_block, int blocks_per_sm
     if(blocks > cap) blocks = cap;
     if(blocks < 1) blocks = 1;
     return (int)blocks;
+}
+
+// Programmatic dependent launch.  A kernel launched with launch_overlapped() may become resident while the kernel in
+// front of it on the stream is still finishing: its CTAs take the SMs that kernel's CTAs have left, run their set-up
+// (barrier initialisation, tensor-memory allocation) and then block in pdl_wait() until the whole preceding grid has
+// completed and its memory is visible.  So every kernel launched that way calls pdl_wait() in ALL its threads before
+// it reads or writes global memory, and pdl_launch_dependents() to let its own successor do the same.  Kernels launched
+// the ordinary way keep the ordinary full serialisation on both sides.  ONN_B200_PDL=0 turns the attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled()
+{
+    static const bool enabled = []{ const char* e = std::getenv("ONN_B200_PDL"); return !(e && e[0] == '0'); }();
+    return enabled;
+}
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args)
+{
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 
 __device__ __forceinline__ float warp_sum(float v)

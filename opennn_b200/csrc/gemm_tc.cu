@@ -305,6 +305,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();                                               // set-up done; global memory only from here on
 
     if(warp == 0)
     {
@@ -582,6 +584,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     cluster_sync();                                           // the peer's barriers exist before anyone signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();                                               // set-up done; global memory only from here on
 
     if(warp == 0)
     {
@@ -733,9 +737,9 @@ static int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, co
     }
     const long long cap = (long long)kSmCount * (BN == 64 ? 2 : 1);
     const int grid = (int)(p.total_work < cap ? p.total_work : cap);
-    gemm_tc_kernel<BN, STAGES, A_MN, B_MN><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_c, p);
+    const cudaError_t launched = launch_overlapped(gemm_tc_kernel<BN, STAGES, A_MN, B_MN>, dim3(grid), dim3(kThreads), smem, stream, map_a, map_b, map_c, p);
     count_launch();
-    return launch_status();
+    return launched == cudaSuccess ? launch_status() : ONN_ERR_CUDA;
 }
 
 template <int A_MN, int B_MN>
@@ -760,9 +764,9 @@ static int launch_pair_variant(const CUtensorMap& map_a, const CUtensorMap& map_
     }
     const long long pairs_cap = kSmCount / 2;
     const long long pairs = p.total_work < pairs_cap ? p.total_work : pairs_cap;
-    gemm_tc2_kernel<A_MN, B_MN><<<(unsigned)(2 * pairs), kThreads, smem, stream>>>(map_a, map_b, map_c, p);
+    const cudaError_t launched = launch_overlapped(gemm_tc2_kernel<A_MN, B_MN>, dim3((unsigned)(2 * pairs)), dim3(kThreads), smem, stream, map_a, map_b, map_c, p);
     count_launch();
-    return launch_status();
+    return launched == cudaSuccess ? launch_status() : ONN_ERR_CUDA;
 }
 
 }  // namespace tc

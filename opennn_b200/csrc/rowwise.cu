@@ -136,6 +136,8 @@ layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
                      float* __restrict__ mean_out, float* __restrict__ inv_std_out, uint8_t* __restrict__ row_is_zero,
                      long long rows, int E, float eps)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
     const long long stride = (long long)gridDim.x * kRowWarps;
@@ -265,6 +267,8 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
                      const float* __restrict__ gamma, float* __restrict__ dX, float* __restrict__ partials,
                      long long rows, int E)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     // [kRowWarps][2][E]: every warp keeps its running column sums here, and every lane only ever touches
     // its own columns, so plain loads and stores suffice; registers stay free for two CTAs per SM
     extern __shared__ float smem[];
@@ -403,6 +407,8 @@ __global__ void __launch_bounds__(256)
 colsum_partials_kernel(const float* __restrict__ partials, int count, int columns,
                        float* __restrict__ out_a, float* __restrict__ out_b, float* __restrict__ out_c, int split, int accumulate)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float fold[8][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + tx;
@@ -487,7 +493,7 @@ extern "C" int onn_layernorm_fwd(const float* A, const float* R, const float* ga
     cudaStream_t s = (cudaStream_t)stream;
     const bool fast = (E & 3) == 0 && E <= 128 * kMaxVec && host_aligned16(A) && host_aligned16(Y) &&
                       host_aligned16(gamma) && host_aligned16(beta) && (!R || host_aligned16(R)) && (!sum || host_aligned16(sum));
-#define ONN_LN_FWD(V) layernorm_fwd_kernel<V><<<grid, kRowThreads, 0, s>>>(A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, rows, (int)E, eps)
+#define ONN_LN_FWD(V) launch_overlapped(layernorm_fwd_kernel<V>, dim3(grid), dim3(kRowThreads), 0, s, A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, (long long)rows, (int)E, eps)
     if(fast)
     {
         switch(vec_count(E))
@@ -535,8 +541,8 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
                       host_aligned16(gamma) && (!dY2 || host_aligned16(dY2)) && (!dY3 || host_aligned16(dY3));
     const bool dx_sum = fast_path_sums_dx(dX_colsum, E);
     const int sets = dx_sum ? 3 : 2;
-#define ONN_LN_BWD(V) do { if(dx_sum) layernorm_bwd_kernel<V, true><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E); \
-                           else layernorm_bwd_kernel<V, false><<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E); } while(0)
+#define ONN_LN_BWD(V) do { if(dx_sum) launch_overlapped(layernorm_bwd_kernel<V, true>, dim3(grid), dim3(kRowThreads), smem, s, dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, (long long)rows, (int)E); \
+                           else launch_overlapped(layernorm_bwd_kernel<V, false>, dim3(grid), dim3(kRowThreads), smem, s, dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, (long long)rows, (int)E); } while(0)
     if(fast)
     {
         const size_t smem = (size_t)kRowWarps * sets * E * sizeof(float);   // 64 KiB (96 KiB with the dx sums) at E = 1024
@@ -567,8 +573,8 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
     count_launch();
     if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
     const int columns = (int)(((fast && dx_sum) ? 3 : 2) * E);
-    colsum_partials_kernel<<<(columns + 31) / 32, 256, 0, s>>>(partials, grid, columns, dgamma, dbeta, dX_colsum, (int)E,
-                                                                  (flags & ONN_ACCUMULATE) != 0);
+    launch_overlapped(colsum_partials_kernel, dim3((columns + 31) / 32), dim3(256), 0, s, (const float*)partials, grid, columns, dgamma, dbeta, dX_colsum,
+                      (int)E, (int)((flags & ONN_ACCUMULATE) != 0));
     count_launch();
     if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
     // rows the vector kernel cannot take: the column sums of dX come from a pass of their own
