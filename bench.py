@@ -39,6 +39,10 @@ sys.path.insert(0, ROOT)
 
 WORKLOAD = dict(name="config5_large_encdec", S_in=256, S_dec=256, V_in=32000, V_out=32000, E=1024, H=16, F=4096, L=6,
                 global_batch=512, micro_batch=64, seed=3, min_len=64, max_len=256)
+# reference config 2 (1+1 layers, E 64): every kernel is tiny, the step is bound by launching ~190 of them; only
+# reachable with --workload config2, which prints a profiling line (step time with and without CUDA-graph replay)
+SMALL_WORKLOAD = dict(name="config2_small_encdec", S_in=32, S_dec=32, V_in=1000, V_out=1000, E=64, H=4, F=128, L=1,
+                      global_batch=32, micro_batch=32, seed=3, min_len=8, max_len=32)
 METRIC = "train tokens/s (fwd+bwd+Adam)"
 UNIT = "tokens/s"
 
@@ -227,6 +231,8 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
+    if args.workload == "config2":
+        w = SMALL_WORKLOAD
     peaks = measured_peaks()
     if args.profile_kernel:
         # small stand-alone case for an ncu capture of the dominant kernel: 2 warm-up + 2 timed launches, 0.7 GB on the device
@@ -295,10 +301,15 @@ def run_ours(args):
     launches = capi.lib().onn_launch_count() - launches_before
     clocks = sampler.stop() if sampler else None
 
-    if args.profile_batch:
+    if args.profile_batch or args.workload != "config5":
+        line = {"profiling_only": True, "workload": w["name"], "ms_per_step": 1e3 * seconds / args.steps, "gpu_launches": int(launches)}
+        if args.workload != "config5":
+            # the same steps launched kernel by kernel, to show what the graph replay of the micro-batch saves
+            t.set_graph_capture(False)
+            device_step(0)
+            line["ms_per_step_without_graphs"] = 1e3 * timed(device_step, args.steps) / args.steps
         if rank == 0:
-            emit({"profiling_only": True, "workload": w["name"], "ms_per_step": 1e3 * seconds / args.steps,
-                  "gpu_launches": int(launches)})
+            emit(line)
         t.close()
         return
     host_step(0)                                  # warm the host path (staging buffers)
@@ -347,6 +358,8 @@ def main():
     parser.add_argument("--profile-batch", type=int, default=0,
                         help="profiling aid: run the device-resident loop only, on a global batch of this many samples "
                              "(the line it prints is not a benchmark result)")
+    parser.add_argument("--workload", default="config5", choices=["config5", "config2"],
+                        help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network")
     parser.add_argument("--profile-kernel", action="store_true",
                         help="profiling aid: launch only the dominant GEMM (FFN-up shape) four times on buffers larger than L2")
     args = parser.parse_args()

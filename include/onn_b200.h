@@ -116,6 +116,9 @@ int onn_gemm_device_status(void);
 int onn_selftest_bounded_wait(int* gave_up);
 /* Number of kernels this library launched since load (all entry points). */
 uint64_t onn_launch_count(void);
+/* For a caller that replays launches it captured into a CUDA graph: the library only sees the capture, so the
+ * caller adds the captured count on each replay to keep the figure above true. */
+void onn_launch_count_add(uint64_t launches);
 
 /* ---------------------------------------------------------------------------------------
  * Embedding.  Forward replaces embedding_forward_kernel (opennn/kernel.cu:714-761, called

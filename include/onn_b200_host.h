@@ -57,6 +57,13 @@ int onn_trainer_set_iteration(onn_trainer* trainer, int64_t iteration);
  * batch; gradients and the active-token count are summed across ranks (onn_dp_*). */
 int onn_trainer_set_dp(onn_trainer* trainer, onn_dp_comm* comm, int world);
 
+/* CUDA-graph replay of the micro-batch (forward, loss, back-propagation), on by default (ONN_B200_GRAPHS=0 or
+ * enabled = 0 turns it off).  The first step runs eagerly; after that every micro-batch index is captured once
+ * (opennn/adaptive_moment_estimation.cpp:697-721 launches its ~500 kernels one by one every step) and replayed
+ * with its ids copied to fixed device buffers.  The data-parallel rank's last micro-batch, whose back-propagation
+ * hands gradient buckets to the all-reduce as it goes, always runs eagerly.  Results do not change. */
+int onn_trainer_set_graph_capture(onn_trainer* trainer, int enabled);
+
 /* One optimiser step on a batch of `batch` samples (a multiple of micro_batch).
  * ids and targets are floats holding integers, [batch, sequence]; encoder_ids is NULL for
  * the decoder-only network.  update = 0 stops after back-propagation (gradients stay in the

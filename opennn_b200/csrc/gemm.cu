@@ -82,6 +82,7 @@ extern "C" int onn_selftest_bounded_wait(int* gave_up)
 }
 
 extern "C" uint64_t onn_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+extern "C" void onn_launch_count_add(uint64_t launches) { g_launch_count.fetch_add(launches, std::memory_order_relaxed); }
 
 extern "C" int onn_version(void) { return 100; }
 

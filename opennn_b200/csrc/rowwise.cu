@@ -546,10 +546,12 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
     if(fast)
     {
         const size_t smem = (size_t)kRowWarps * sets * E * sizeof(float);   // 64 KiB (96 KiB with the dx sums) at E = 1024
-        if(smem > 48 * 1024)
+        static bool configured = false;                          // once: attribute calls do not belong inside a stream capture
+        if(smem > 48 * 1024 && !configured)
         {
             cudaFuncSetAttribute(layernorm_bwd_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
             cudaFuncSetAttribute(layernorm_bwd_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            configured = true;
         }
         switch(vec_count(E))
         {
@@ -565,7 +567,12 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
         if(smem > 48 * 1024)
         {
             if(smem > 200 * 1024) return ONN_ERR_UNSUPPORTED;
-            cudaFuncSetAttribute(layernorm_bwd_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            static size_t configured_bytes = 0;
+            if(smem > configured_bytes)
+            {
+                cudaFuncSetAttribute(layernorm_bwd_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                configured_bytes = smem;
+            }
         }
         layernorm_bwd_generic_kernel<<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E);
     }

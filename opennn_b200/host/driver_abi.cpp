@@ -8,6 +8,8 @@
 #include <cstring>
 
 #include "../../include/onn_b200_host.h"
+#include <cstdlib>
+
 #include "opennn_b200.h"
 
 using namespace opennn_b200;
@@ -37,8 +39,17 @@ struct onn_trainer
     TensorCuda staged_decoder, staged_encoder, staged_targets;
     type* pinned_scalars = nullptr;       // {square norm, global active tokens}
 
+    // CUDA-graph replay of the micro-batch: one executable graph per micro-batch index (the statistics slot the
+    // loss kernel writes is part of the captured arguments), ids read from fixed buffers
+    struct MicroGraph { cudaGraphExec_t executable = nullptr; uint64_t launches = 0; };
+    vector<MicroGraph> micro_graphs;
+    TensorCuda micro_decoder, micro_encoder, micro_targets;
+    bool graphs_enabled = true;
+    Index eager_steps = 0;                // graphs are captured only after one eager step has configured every kernel
+
     ~onn_trainer()
     {
+        for(MicroGraph& g : micro_graphs) if(g.executable) cudaGraphExecDestroy(g.executable);
         if(pinned_scalars) cudaFreeHost(pinned_scalars);
         if(stream) cudaStreamDestroy(stream);
     }
@@ -88,6 +99,7 @@ extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
         t->forward = std::make_unique<ForwardPropagationCuda>(micro_batch, t->network.get());
         t->back = std::make_unique<BackPropagationCuda>(micro_batch, t->loss.get(), t->forward.get());
         t->optimization = std::make_unique<ADAMOptimizationDataCuda>(t->adam.get());
+        if(const char* e = std::getenv("ONN_B200_GRAPHS")) t->graphs_enabled = e[0] != '0';
         check_cuda(cudaMallocHost(reinterpret_cast<void**>(&t->pinned_scalars), 8 * sizeof(type)), "pinned scalars");
 
         Index offset = 0;
@@ -187,6 +199,74 @@ static void gradient_ready(void* context, Index layer)
     }
 }
 
+// Replays (capturing it first if need be) the forward pass, loss and back-propagation of micro-batch number `chunk`.
+// Returns false if graphs cannot be used; the caller then runs the micro-batch eagerly.
+static bool replay_micro_batch(onn_trainer* t, const BatchCuda& source, Index chunk)
+{
+    const Index S_dec = t->decoder_sequence_length, S_in = t->input_sequence_length;
+    if(t->micro_decoder.size() == 0)
+    {
+        t->micro_decoder.resize(t->micro_batch * S_dec);
+        t->micro_targets.resize(t->micro_batch * S_dec);
+        if(!t->decoder_only) t->micro_encoder.resize(t->micro_batch * S_in);
+    }
+    if(size_t(chunk) >= t->micro_graphs.size()) t->micro_graphs.resize(size_t(chunk) + 1);
+    onn_trainer::MicroGraph& graph = t->micro_graphs[size_t(chunk)];
+
+    // the captured kernels read their ids from these fixed buffers
+    const size_t decoder_bytes = size_t(t->micro_batch * S_dec) * sizeof(type);
+    check_cuda(cudaMemcpyAsync(t->micro_decoder.data, source.decoder.data, decoder_bytes, cudaMemcpyDeviceToDevice, t->stream), "micro ids");
+    check_cuda(cudaMemcpyAsync(t->micro_targets.data, source.target.data, decoder_bytes, cudaMemcpyDeviceToDevice, t->stream), "micro targets");
+    if(!t->decoder_only)
+        check_cuda(cudaMemcpyAsync(t->micro_encoder.data, source.input.data, size_t(t->micro_batch * S_in) * sizeof(type),
+                                   cudaMemcpyDeviceToDevice, t->stream), "micro ids");
+
+    if(!graph.executable)
+    {
+        BatchCuda micro;
+        micro.samples_number = t->micro_batch;
+        micro.decoder = TensorViewCuda(t->micro_decoder.data, {t->micro_batch, S_dec});
+        if(!t->decoder_only) micro.input = TensorViewCuda(t->micro_encoder.data, {t->micro_batch, S_in});
+        micro.target = TensorViewCuda(t->micro_targets.data, {t->micro_batch, S_dec});
+
+        const Index slot_before = t->back->statistics_slot;
+        const uint64_t launches_before = onn_launch_count();
+        cudaGraph_t captured = nullptr;
+        bool ok = cudaStreamBeginCapture(t->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if(ok)
+        {
+            try
+            {
+                t->network->forward_propagate(micro.get_inputs_device(), *t->forward, true);
+                t->loss->back_propagate(micro, *t->forward, *t->back, chunk > 0);
+            }
+            catch(...) { ok = false; }
+            ok = (cudaStreamEndCapture(t->stream, &captured) == cudaSuccess) && ok && captured != nullptr;
+        }
+        if(ok) ok = cudaGraphInstantiate(&graph.executable, captured, 0) == cudaSuccess;
+        if(captured) cudaGraphDestroy(captured);
+        if(!ok)
+        {
+            // nothing of the micro-batch has run; give up on graphs for this trainer and let the caller run it eagerly
+            cudaGetLastError();
+            graph.executable = nullptr;
+            t->graphs_enabled = false;
+            t->back->statistics_slot = slot_before;
+            return false;
+        }
+        graph.launches = onn_launch_count() - launches_before;    // counted at capture; the first replay below is that launch
+        t->back->statistics_slot = slot_before;
+        onn_launch_count_add(0 - graph.launches);
+    }
+
+    // host-side bookkeeping the captured code did when it ran eagerly
+    if(chunk == 0) t->back->statistics_slot = 0;
+    t->back->statistics_slot++;
+    check_cuda(cudaGraphLaunch(graph.executable, t->stream), "micro-batch graph launch");
+    onn_launch_count_add(graph.launches);
+    return true;
+}
+
 static void run_step(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,
                      Index batch, bool update, float* statistics)
 {
@@ -220,10 +300,13 @@ static void run_step(onn_trainer* t, const float* decoder_ids, const float* enco
         if(!t->decoder_only) micro.input = TensorViewCuda(const_cast<float*>(encoder_ids) + first * S_in, {t->micro_batch, S_in});
         micro.target = TensorViewCuda(const_cast<float*>(targets) + first * S_dec, {t->micro_batch, S_dec});
 
+        const bool last = chunk == chunks - 1;
+        const bool hands_out_gradients = t->comm && last;     // bucketed all-reduces are issued from inside back-propagation
+        if(t->graphs_enabled && t->eager_steps > 0 && !hands_out_gradients && replay_micro_batch(t, micro, chunk)) continue;
+
         t->network->forward_propagate(micro.get_inputs_device(), *t->forward, true);
 
-        const bool last = chunk == chunks - 1;
-        if(t->comm && last)
+        if(hands_out_gradients)
         {
             t->pending_high = gradients.size();
             t->loss->gradient_ready_hook = gradient_ready;
@@ -232,6 +315,7 @@ static void run_step(onn_trainer* t, const float* decoder_ids, const float* enco
         t->loss->back_propagate(micro, *t->forward, *t->back, chunk > 0);
         t->loss->gradient_ready_hook = nullptr;
     }
+    t->eager_steps++;
 
     if(t->comm)
     {
@@ -266,6 +350,13 @@ static void run_step(onn_trainer* t, const float* decoder_ids, const float* enco
         statistics[2] = float(active);
         statistics[3] = std::sqrt(t->pinned_scalars[0]);
     }
+}
+
+extern "C" int onn_trainer_set_graph_capture(onn_trainer* t, int enabled)
+{
+    if(!t) return ONN_ERR_INVALID_ARGUMENT;
+    t->graphs_enabled = enabled != 0;
+    return ONN_OK;
 }
 
 extern "C" int onn_trainer_step_device(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,

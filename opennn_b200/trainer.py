@@ -23,7 +23,7 @@ HOST_EXPORTS = [
     "onn_trainer_layers_number", "onn_trainer_layer_info", "onn_trainer_set_parameters", "onn_trainer_get_parameters",
     "onn_trainer_get_gradients", "onn_trainer_set_learning_rate", "onn_trainer_set_iteration", "onn_trainer_set_dp",
     "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_forward", "onn_trainer_get_layer_output",
-    "onn_trainer_synchronize", "onn_trainer_stream",
+    "onn_trainer_synchronize", "onn_trainer_stream", "onn_trainer_set_graph_capture",
 ]
 
 _host = None
@@ -99,6 +99,10 @@ class Trainer:
 
     def set_learning_rate(self, lr):
         _check(host_lib().onn_trainer_set_learning_rate(self._handle, C.c_float(lr)), "set_learning_rate")
+
+    def set_graph_capture(self, enabled):
+        """CUDA-graph replay of the micro-batches (on by default); results do not depend on it."""
+        _check(host_lib().onn_trainer_set_graph_capture(self._handle, int(bool(enabled))), "set_graph_capture")
 
     def set_dp(self, comm_handle, world):
         _check(host_lib().onn_trainer_set_dp(self._handle, comm_handle, int(world)), "set_dp")

@@ -150,6 +150,40 @@ def test_micro_batches_match_one_batch(libs):
     assert_close(results[1][1], results[0][1], 1e-4, "gradient, 4 micro-batches vs 1")
 
 
+def test_graph_replay_matches_eager_steps(libs):
+    """Steps whose micro-batches are replayed from captured CUDA graphs (the default after the first step) train
+    exactly like steps launched kernel by kernel: same losses, same gradients, same parameters, and the launch
+    counter keeps counting the replayed kernels."""
+    capi, trainer = libs
+    capi.check(capi.lib().onn_gemm_set_mode(0))
+    name = "config2_tiny"
+    net, params, external, targets = network_inputs(name)
+    dec, enc, tgt = device_batch(external, targets)
+    outcomes = []
+    for graphs in (False, True):
+        t = make_trainer(trainer, name, micro_batch=8)            # 4 micro-batches per step
+        t.set_graph_capture(graphs)
+        t.set_parameters(params)
+        history = []
+        counts = []
+        for step in range(4):
+            before = capi.lib().onn_launch_count()
+            history.append(t.step_device(dec, enc, tgt, update=True))
+            counts.append(capi.lib().onn_launch_count() - before)
+        stats = t.step_device(dec, enc, tgt, update=False)
+        outcomes.append((history, stats, t.get_gradients(), t.get_parameters(), counts))
+        t.close()
+    eager, replayed = outcomes
+    for a, b in zip(eager[0] + [eager[1]], replayed[0] + [replayed[1]]):
+        assert abs(a[0] - b[0]) <= 1e-5 * abs(a[0]) and a[2] == b[2], (a, b)
+    # the two runs differ only in the order of floating-point atomics (embedding and bias gradients), which four Adam
+    # steps amplify a little: the bounds are those of two eager runs
+    assert_close(replayed[2], eager[2], 1e-3, "gradient after four steps")
+    assert_close(replayed[3], eager[3], 1e-4, "parameters after four steps")
+    assert len(set(eager[4])) == 1 and replayed[4][1:] == eager[4][1:], (eager[4], replayed[4])
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
 def test_host_step_matches_device_step(libs):
     """The host-buffer entry point (pinned ids copied inside the step) gives the same step."""
     capi, trainer = libs
