@@ -244,7 +244,8 @@ def run_ours(args):
     micro = min(w["micro_batch"], local_batch)
     t = trainer.Trainer(trainer.TRANSFORMER, w["S_in"], w["S_dec"], w["V_in"], w["V_out"], w["E"], w["H"], w["F"], w["L"], micro)
     if world > 1:
-        comm = trainer.dp_init_from_torch()
+        # host-side check first: every rank present, same parameter arena and micro-batch on all of them
+        comm = trainer.dp_init_from_torch(signature={"parameters": t.parameters_number, "micro_batch": micro, "workload": w["name"]})
         t.set_dp(comm, world)
 
     # synthetic batches: the same global stream on every rank, each rank keeps its contiguous slice

@@ -149,12 +149,48 @@ class Trainer:
         _check(host_lib().onn_trainer_synchronize(self._handle), "synchronize")
 
 
-def dp_init_from_torch():
+class DpRendezvousError(RuntimeError):
+    """A data-parallel job that must not start: a rank is missing or the replicas differ."""
+
+
+def dp_check_replicas(signature, timeout_s=60.0):
+    """Failure detection on the host, before any NCCL call or kernel launch (the reference has no multi-GPU path, so
+    there is no counterpart): every rank of the initialised torch.distributed group publishes `signature` (anything
+    picklable that must be equal on all replicas: parameter count, micro-batch, network shape) in the group's store
+    and waits at most `timeout_s` seconds for the others.  Raises DpRendezvousError naming the ranks that never
+    arrived, or the first rank whose signature differs from rank 0's.  Every rank sees the same data, so every rank
+    that arrived raises the same error and none of them goes on to wait in a collective for the others."""
+    import datetime
+    import pickle
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(), dist.get_rank()
+    store = dist.distributed_c10d._get_default_store()
+    generation = dp_check_replicas.generation = getattr(dp_check_replicas, "generation", 0) + 1
+    keys = [f"onn_b200/replica/{generation}/{r}" for r in range(world)]
+    store.set(keys[rank], pickle.dumps(signature))
+    try:
+        store.wait(keys, datetime.timedelta(seconds=float(timeout_s)))
+    except Exception as error:                                   # the store raises its own timeout type
+        missing = [r for r in range(world) if not store.check([keys[r]])]
+        raise DpRendezvousError(f"rank {rank}: ranks {missing} did not join within {timeout_s} s") from error
+    published = [pickle.loads(store.get(key)) for key in keys]
+    for r, other in enumerate(published):
+        if other != published[0]:
+            raise DpRendezvousError(f"rank {rank}: replica {r} differs from replica 0: {other!r} != {published[0]!r}")
+    return published[0]
+
+
+def dp_init_from_torch(signature=None, timeout_s=60.0):
     """Creates the NCCL communicator of libonn_b200 for the ranks of an initialised
-    torch.distributed process group (the 128-byte unique id travels through it)."""
+    torch.distributed process group (the 128-byte unique id travels through it).  With a `signature`
+    the ranks first check on the host that all of them are present and hold the same replica
+    (dp_check_replicas), so a missing rank or a mismatched parameter arena ends the job with an
+    error instead of a hang inside ncclCommInitRank or a corrupted all-reduce."""
     import torch
     import torch.distributed as dist
     world, rank = dist.get_world_size(), dist.get_rank()
+    if signature is not None:
+        dp_check_replicas(signature, timeout_s)
     uid = (C.c_char * 128)()
     if rank == 0:
         capi.check(capi.lib().onn_dp_unique_id(uid), "onn_dp_unique_id")

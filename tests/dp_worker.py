@@ -31,7 +31,7 @@ def main(out_path):
 
     t = trainer.Trainer(trainer.TRANSFORMER, S_in, S_dec, V_in, V_out, E, H, F, L, share // 2)   # two micro-batches per rank
     t.set_parameters(params)
-    comm = trainer.dp_init_from_torch()
+    comm = trainer.dp_init_from_torch(signature={"parameters": t.parameters_number, "micro_batch": share // 2})
     t.set_dp(comm, world)
     stats = t.step_device(dec, enc, tgt, update=False)
     gradient = t.get_gradients()

@@ -61,3 +61,50 @@ def test_two_ranks_reproduce_the_whole_batch_step():
         assert np.abs(r["gradient"] - gradient).max() <= 1e-5 * scale
         assert np.abs(r["params"] - arena).max() <= 2e-6
     assert np.array_equal(ranks[0]["params"], ranks[1]["params"]), "replicas must stay identical"
+
+
+# ---------------------------------------------------------------------------------------
+# Failure detection, on the host: no GPU, no NCCL, nothing faults or hangs
+# ---------------------------------------------------------------------------------------
+
+def _rendezvous_main(rank, world, init_file, out_dir, scenario):
+    import datetime
+    from opennn_b200 import trainer
+    dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=60))
+    outcome = "ok"
+    try:
+        if scenario == "missing" and rank == 1:
+            outcome = "left before the rendezvous"                 # a rank that exits between steps and never joins
+        else:
+            parameters = 276712 if not (scenario == "mismatch" and rank == 1) else 276704
+            trainer.dp_check_replicas({"parameters": parameters, "micro_batch": 8}, timeout_s=3.0)
+    except trainer.DpRendezvousError as error:
+        outcome = f"refused: {error}"
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(outcome)
+    if scenario != "missing":
+        dist.destroy_process_group()
+
+
+def _run_rendezvous(scenario):
+    world = 2
+    with tempfile.TemporaryDirectory() as out_dir:
+        init_file = os.path.join(out_dir, "rendezvous")
+        mp.spawn(_rendezvous_main, args=(world, init_file, out_dir, scenario), nprocs=world, join=True)
+        return [open(os.path.join(out_dir, f"rank{r}.txt")).read() for r in range(world)]
+
+
+def test_replicas_that_agree_may_start():
+    assert _run_rendezvous("agree") == ["ok", "ok"]
+
+
+def test_mismatched_parameter_arena_is_refused_on_every_rank_before_any_launch():
+    outcomes = _run_rendezvous("mismatch")
+    assert all(o.startswith("refused") and "replica 1 differs" in o for o in outcomes), outcomes
+
+
+def test_missing_rank_ends_the_rendezvous_with_a_timeout_not_a_hang():
+    outcomes = _run_rendezvous("missing")
+    assert outcomes[1] == "left before the rendezvous"
+    assert outcomes[0].startswith("refused") and "[1] did not join" in outcomes[0], outcomes
