@@ -128,8 +128,10 @@ embedding_bwd_kernel(const float* __restrict__ ids, const float* __restrict__ dY
 
 // Register-resident row path (E % 4 == 0, E <= 1024).  Statistics are two passes over the
 // registers: mean first, then the mean of centred squares (the reference's formulation).
+// gamma and beta are read per row (8 KiB, they stay in L1): keeping them in registers as well would cost 64 registers
+// per thread and halve the rows in flight per SM, which is what the memory system is fed by.
 template <int VEC>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 4)
 layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
                      const float* __restrict__ gamma, const float* __restrict__ beta,
                      float* __restrict__ Y, float* __restrict__ sum_out,
@@ -142,15 +144,6 @@ layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
     const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
     const long long stride = (long long)gridDim.x * kRowWarps;
     const float inv_E = 1.0f / (float)E;
-
-    float4 g[VEC], b[VEC];
-#pragma unroll
-    for(int i = 0; i < VEC; i++)
-    {
-        const int e = (i * 32 + lane) * 4;
-        g[i] = e < E ? ld4(gamma + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-        b[i] = e < E ? ld4(beta + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
 
     for(long long row = warp; row < rows; row += stride)
     {
@@ -191,11 +184,12 @@ layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
             const int e = (i * 32 + lane) * 4;
             if(e < E)
             {
+                const float4 g = ld4(gamma + e), b = ld4(beta + e);
                 float4 y;
-                y.x = (x[i].x * inv_std * g[i].x + b[i].x);
-                y.y = (x[i].y * inv_std * g[i].y + b[i].y);
-                y.z = (x[i].z * inv_std * g[i].z + b[i].z);
-                y.w = (x[i].w * inv_std * g[i].w + b[i].w);
+                y.x = (x[i].x * inv_std * g.x + b.x);
+                y.y = (x[i].y * inv_std * g.y + b.y);
+                y.z = (x[i].z * inv_std * g.z + b.z);
+                y.w = (x[i].w * inv_std * g.w + b.w);
                 all_zero = all_zero && fabsf(y.x) <= 1e-7f && fabsf(y.y) <= 1e-7f && fabsf(y.z) <= 1e-7f && fabsf(y.w) <= 1e-7f;
                 st4(Y + row * (long long)E + e, y);
             }
