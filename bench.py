@@ -199,7 +199,7 @@ def time_dominant_kernel(capi, torch, w, peaks, copies=4, launches=24, with_cubl
 
     return {"bound": "tensor", "kernel": "gemm_tc2_kernel<0,1> (Dense forward with bias + ReLU, two-CTA tcgen05, tf32 operands, fp32 accumulate)",
             "shape": {"M": M, "N": N, "K": K}, "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-            "frac": achieved / peaks["tflops"], "peak_source": "dense bf16 burst, " + peaks["source"] +
+            "frac": achieved / peaks["tflops"], "frac_of_tf32_rate": achieved / (0.5 * peaks["tflops"]), "peak_source": "dense bf16 burst, " + peaks["source"] +
             "; tf32 operands have half the bf16 rate, so 0.5 is this kernel's ceiling on this scale",
             "us_per_launch": seconds * 1e6, "cublas_tf32_same_shape_tflops": cublas_tf32,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised in
