@@ -11,8 +11,10 @@
 //               output rows), alpha / bias / ReLU, stage the 32 x 32 block in shared memory
 //               (128-byte swizzle) and hand it to a TMA store -- or a TMA reduce-add for
 //               accumulation and split-K -- so global writes are whole lines and clipped at the
-//               matrix edge by the copy engine.  A ReLU-mask operand and column sums of the
-//               output are applied to the staged block.
+//               matrix edge by the copy engine.  What the epilogue reads from global memory (bias
+//               values, the ReLU mask as one bit per element) is fetched once per tile BEFORE the
+//               wait for the accumulator, so its latency passes behind the MMAs; a float ReLU-mask
+//               operand and column sums of the output are applied to the staged block.
 //
 // Operand layouts (BK = 32 floats = 128 bytes = one swizzle row, UMMA K = 8):
 //   K-major  (reduction dimension contiguous in memory): one box [rows][32 floats];
