@@ -36,6 +36,7 @@
 // producer drains the copies it still has in flight, TMEM is freed and the kernel returns.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -81,6 +82,11 @@ struct Params
     long long k_per_split;                                 // multiple of BK
     int m_blocks, n_blocks;
     long long total_work;
+    // two-CTA kernel only: the last `tail_tiles` tiles of the tile order are each split into two halves of the
+    // reduction that two different CTA pairs add into C (see the kernel's header); 0 = no split
+    int tail_tiles;
+    unsigned long long tail_token;                         // this launch's value of "zeroed" in tail_flags
+    unsigned long long* tail_flags;                        // [tail tile][8 epilogue warps of a pair]
 };
 
 // Instruction descriptor: D = fp32, A = B = tf32, M = 128, N = BN, majors as given.
@@ -146,18 +152,41 @@ __device__ __forceinline__ void staged_block_passes(const Params& p, uint32_t bl
     }
 }
 
-struct WorkItem { int zi, zo, split, m_blk, n_blk; long long k_begin; int k_blocks; };
+struct WorkItem { int zi, zo, split, m_blk, n_blk; long long k_begin; int k_blocks; int tail; };   // tail: index of a split tail tile, or -1
 
 __device__ __forceinline__ WorkItem decode_work(const Params& p, long long w)
 {
     constexpr int kGroup = 8;                               // M blocks per raster group (L2 reuse of B panels)
     const long long tiles = (long long)p.m_blocks * p.n_blocks;
-    const long long t = w % tiles;
-    long long rest = w / tiles;
+    long long t;
     WorkItem it;
-    it.split = (int)(rest % p.splits); rest /= p.splits;
-    it.zi = (int)(rest % p.batch_inner);
-    it.zo = (int)(rest / p.batch_inner);
+    it.tail = -1;
+    if(p.tail_tiles > 0)
+    {
+        // batch 1, no split-K: whole tiles first, then the two reduction halves of each tail tile, the halves of one
+        // tile `tail_tiles` work items apart so that they land on different CTA pairs of the same wave
+        const long long whole = tiles - p.tail_tiles;
+        it.zi = 0; it.zo = 0;
+        const int k_blocks = (int)((p.K + BK - 1) / BK), first_half = (k_blocks + 1) / 2;
+        if(w < whole) { t = w; it.split = 0; it.k_begin = 0; it.k_blocks = k_blocks; }
+        else
+        {
+            const long long u = w - whole;
+            it.tail = (int)(u % p.tail_tiles);
+            it.split = (int)(u / p.tail_tiles);
+            t = whole + it.tail;
+            it.k_begin = it.split == 0 ? 0 : (long long)first_half * BK;
+            it.k_blocks = it.split == 0 ? first_half : k_blocks - first_half;
+        }
+    }
+    else
+    {
+        t = w % tiles;
+        long long rest = w / tiles;
+        it.split = (int)(rest % p.splits); rest /= p.splits;
+        it.zi = (int)(rest % p.batch_inner);
+        it.zo = (int)(rest / p.batch_inner);
+    }
     const long long per_group = (long long)kGroup * p.n_blocks;
     const int group = (int)(t / per_group);
     const int first_m = group * kGroup;
@@ -165,9 +194,12 @@ __device__ __forceinline__ WorkItem decode_work(const Params& p, long long w)
     const int in_group = (int)(t % per_group);
     it.m_blk = first_m + in_group % group_size;
     it.n_blk = in_group / group_size;
-    it.k_begin = it.split * p.k_per_split;
-    const long long k_end = min(p.K, it.k_begin + p.k_per_split);
-    it.k_blocks = (int)((k_end - it.k_begin + BK - 1) / BK);
+    if(p.tail_tiles == 0)
+    {
+        it.k_begin = it.split * p.k_per_split;
+        const long long k_end = min(p.K, it.k_begin + p.k_per_split);
+        it.k_blocks = (int)((k_end - it.k_begin + BK - 1) / BK);
+    }
     return it;
 }
 
@@ -201,10 +233,10 @@ __device__ __forceinline__ void load_tile_side_inputs(const Params& p, bool use_
 template <int BN>
 __device__ __forceinline__ void epilogue_warp_tile(const Params& p, const CUtensorMap* map_c, uint32_t taddr, uint32_t warp_blocks,
                                                    unsigned int& staged_chunks, long long warp_row0, long long n0,
-                                                   long long c_offset, int zi, int c_zi, int c_zo, bool use_bias, int lane,
+                                                   long long c_offset, int zi, int c_zi, int c_zo, bool use_bias, bool add_to_c, int lane,
                                                    TileSideInputs<BN>& side)
 {
-    const bool reduce = p.accumulate || p.splits > 1;
+    const bool reduce = p.accumulate || p.splits > 1 || add_to_c;
 #pragma unroll 1
     for(int c = 0; c < BN / 32; c++)
     {
@@ -440,7 +472,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * BN;
             const int c_zi = p.c_batch_inner_on ? it.zi : 0, c_zo = p.c_batch_outer_on ? it.zo : 0;
             epilogue_warp_tile<BN>(p, &map_c, taddr, smem_u32(epi_smem + (warp - 2) * 2 * EPI_BLOCK_BYTES), staged_chunks, warp_row0, n0,
-                                   c_offset, it.zi, c_zi, c_zo, use_bias, lane, side);
+                                   c_offset, it.zi, c_zi, c_zo, use_bias, false, lane, side);
             tcgen05_fence_before();
             __syncwarp();
             if(lane == 0) mbar_arrive(smem_u32(acc_empty_bar + acc));
@@ -668,6 +700,46 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         long long local = 0;
         unsigned int staged_chunks = 0;
         const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty_bar), 0);
+        const uint32_t warp_blocks = smem_u32(epi_smem + (warp - 2) * 2 * EPI_BLOCK_BYTES);
+        const int flag_slot = (int)rank * 4 + quadrant;      // this warp's place among the 8 epilogue warps of a pair
+
+        // Split tail tiles are ADDED into by two pairs, so C must hold zeros there first (unless the caller's values
+        // are to be kept).  Pair j zeroes tail tile j while its first tile's MMAs run -- each warp its own 32 rows,
+        // from one zero-filled staging block -- and publishes that under this launch's token; the adding warps look
+        // the token up before their first reduce (three waves later: the look-up never waits in practice, it is
+        // there so that the order is guaranteed rather than likely).
+        if(p.tail_tiles > 0 && !p.accumulate)
+        {
+            const long long whole = (long long)p.m_blocks * p.n_blocks - p.tail_tiles;
+            for(long long j = pair; j < p.tail_tiles; j += pairs)
+            {
+                Params q = p;                                   // decode the tile itself, not one of its halves
+                q.tail_tiles = 0; q.splits = 1; q.batch_inner = 1; q.k_per_split = p.K;
+                const WorkItem tile = decode_work(q, whole + j);
+                const long long rows0 = (long long)tile.m_blk * 256 + (long long)rank * 128 + quadrant * 32;
+#pragma unroll
+                for(int q4 = 0; q4 < 8; q4++)
+                {
+                    const uint32_t dst = warp_blocks + (uint32_t)lane * 128u + (uint32_t)(q4 << 4);
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %1, %1, %1};" :: "r"(dst), "f"(0.f));
+                }
+                fence_async_shared();
+                __syncwarp();
+                if(lane == 0)
+                {
+                    if(rows0 < p.M)
+                        for(int c = 0; c < BN / 32; c++)
+                            if((long long)tile.n_blk * BN + c * 32 < p.N) tma_store_4d(&map_c, warp_blocks, tile.n_blk * BN + c * 32, (int)rows0, 0, 0);
+                    bulk_commit();
+                    bulk_wait_all();                            // the zeros are in memory, not just on their way
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.u64 [%0], %1;" :: "l"(p.tail_flags + j * 8 + flag_slot), "l"(p.tail_token) : "memory");
+                }
+                __syncwarp();
+            }
+        }
+
         for(long long w = pair; w < p.total_work; w += pairs, local++)
         {
             const WorkItem it = decode_work(p, w);
@@ -677,6 +749,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const long long warp_row0 = (long long)it.m_blk * 256 + (long long)rank * 128 + quadrant * 32;
             TileSideInputs<BN> side;
             load_tile_side_inputs<BN>(p, use_bias, warp_row0, n0, lane, side);
+            if(it.tail >= 0 && !p.accumulate)
+            {
+                // this strip of the tail tile has been zeroed (see above) before anything is added to it
+                bool zeroed = true;
+                if(lane == 0)
+                {
+                    const unsigned long long* flag = p.tail_flags + (long long)it.tail * 8 + flag_slot;
+                    const unsigned long long start = clock64();
+                    unsigned long long seen;
+                    while(true)
+                    {
+                        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(flag) : "memory");
+                        if(seen == p.tail_token) break;
+                        if(*abort_flag || clock64() - start > kWaitCycles) { atomicCAS(&g_status, 0u, 15u); *abort_flag = 1; zeroed = false; break; }
+                    }
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
+                zeroed = __shfl_sync(0xffffffffu, zeroed, 0);
+                if(!zeroed) break;
+            }
 
             bool ok = true;
             if(lane == 0) ok = mbar_wait(smem_u32(acc_full_bar + acc), acc_phase, abort_flag, 14);
@@ -685,8 +777,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tcgen05_fence_after();
 
             const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * BN;
-            epilogue_warp_tile<BN>(p, &map_c, taddr, smem_u32(epi_smem + (warp - 2) * 2 * EPI_BLOCK_BYTES), staged_chunks, warp_row0, n0,
-                                   0, 0, 0, 0, use_bias, lane, side);
+            epilogue_warp_tile<BN>(p, &map_c, taddr, warp_blocks, staged_chunks, warp_row0, n0,
+                                   0, 0, 0, 0, use_bias, it.tail >= 0, lane, side);
             tcgen05_fence_before();
             __syncwarp();
             if(lane == 0) mbar_arrive_cluster(leader_acc_empty + acc * 8);     // one arrival per epilogue warp of the pair
@@ -773,6 +865,32 @@ static int launch_pair_variant(const CUtensorMap& map_a, const CUtensorMap& map_
 
 }  // namespace tc
 
+namespace tc
+{
+// "zeroed" tokens of split tail tiles: kTailFlagSets launches may be in flight at once without sharing a set
+constexpr int kTailFlagSets = 16;
+constexpr int kTailFlagsPerSet = (kSmCount / 2) * 8;
+static __device__ unsigned long long g_tail_flags[kTailFlagSets * kTailFlagsPerSet];
+
+static int tail_flags_for_current_device(unsigned long long** address)
+{
+    constexpr int kMaxDevices = 64;
+    static std::mutex mutex;
+    static unsigned long long* resolved[kMaxDevices] = {};
+    int device = -1;
+    if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return ONN_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mutex);
+    if(!resolved[device])
+    {
+        unsigned long long* found = nullptr;
+        if(cudaGetSymbolAddress(reinterpret_cast<void**>(&found), g_tail_flags) != cudaSuccess || !found) return ONN_ERR_CUDA;
+        resolved[device] = found;
+    }
+    *address = resolved[device];
+    return ONN_OK;
+}
+}  // namespace tc
+
 bool gemm_tc_supported(const onn_gemm_args& g)
 {
     using tc::mult4;
@@ -798,6 +916,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.C = g.C; p.bias = g.bias; p.relu_mask = g.relu_mask; p.alpha = g.alpha;
     p.relu_bits_out = g.relu_bits_out; p.relu_bits = g.relu_bits; p.relu_bits_ld = g.relu_bits_ld;
     p.colsum = g.colsum_out; p.colsum_stride_inner = g.colsum_stride_inner;
+    p.tail_tiles = 0; p.tail_token = 0; p.tail_flags = nullptr;
     p.relu = g.relu; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
     p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
     p.a_batch_inner_on = g.batch_inner > 1 && g.a_stride_inner != 0; p.a_batch_outer_on = g.batch_outer > 1 && g.a_stride_outer != 0;
@@ -830,6 +949,23 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
         p.m_blocks = (int)((g.M + 255) / 256);
         p.n_blocks = (int)((g.N + 255) / 256);
         p.total_work = (long long)p.m_blocks * p.n_blocks * splits;
+        // a last wave that is at most half full is split in two along the reduction (linear epilogues only)
+        static const bool tail_split_enabled = []{ const char* e = std::getenv("ONN_B200_GEMM_TAIL_SPLIT"); return !(e && e[0] == '0'); }();
+        const long long tiles = (long long)p.m_blocks * p.n_blocks, pairs_cap = kSmCount / 2, tail = tiles % pairs_cap;
+        if(tail_split_enabled && splits == 1 && tiles > pairs_cap && tail > 0 && 2 * tail <= pairs_cap && k_blocks >= 16 &&
+           !g.relu && !g.relu_mask && !g.relu_bits && !g.relu_bits_out)
+        {
+            unsigned long long* flags = nullptr;
+            if(tail_flags_for_current_device(&flags) == ONN_OK)
+            {
+                static std::atomic<unsigned long long> sequence{0};
+                const unsigned long long token = ++sequence;
+                p.tail_tiles = (int)tail;
+                p.tail_token = token;
+                p.tail_flags = flags + (token % kTailFlagSets) * kTailFlagsPerSet;
+                p.total_work = tiles + tail;
+            }
+        }
         if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, 1, 0, 1, 0, BK, BM, false);
         else ok = make_wide_map(&map_a, g.A, g.M, g.K, g.lda, 1, 0, 1, 0, BM / 32, BK);
         if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, 1, 0, 1, 0, BK, 128, false);

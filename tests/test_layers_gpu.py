@@ -333,6 +333,41 @@ def test_mha_head64(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
     assert capi.lib().onn_gemm_device_status() == 0
 
 
+@pytest.mark.parametrize("a_major,b_major", [(0, 1), (0, 0), (1, 1)])
+@pytest.mark.parametrize("M", [4864, 4800])
+def test_gemm_split_tail_wave(capi, a_major, b_major, M):
+    """76 tile pairs on 74 CTA pairs: the two tiles of the last wave are each split along the reduction between two
+    pairs that ADD their halves into C, which the kernel zeroes first (or, with ONN_ACCUMULATE, adds to the caller's
+    values).  Bias is added once, column sums see every element once, ragged M is clipped."""
+    N, K = 1024, 1024
+    rng = np.random.default_rng(M)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) / 32).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    A_store = dev(A if a_major == 0 else A.T)
+    B_store = dev(B.T if b_major == 0 else B)
+    lda = K if a_major == 0 else M
+    ldb = K if b_major == 0 else N
+    reference = A.astype(np.float64) @ B.astype(np.float64)
+
+    out = torch.full((M, N), 7.0, device="cuda")                 # stale values the kernel must not add to
+    sums = torch.zeros(N, device="cuda")
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, bias=dev(bias), alpha=0.5, colsum_out=sums)
+    expected = 0.5 * reference + bias
+    assert_close(host(out), expected, TOL, "alpha + bias over a split tail")
+    assert_close(host(sums), expected.sum(axis=0), TOL, "column sums over a split tail", floor=1e-3 * np.abs(expected).sum(axis=0).max())
+
+    start = rng.standard_normal((M, N)).astype(np.float32)
+    out = dev(start)
+    capi.gemm(A_store, B_store, out, M, N, K, lda, ldb, N, a_major, b_major, flags=capi.ACCUMULATE)
+    assert_close(host(out), start + reference, TOL, "accumulate over a split tail")
+    for _ in range(3):                                           # repeated launches take fresh tokens
+        out2 = torch.full((M, N), -3.0, device="cuda")
+        capi.gemm(A_store, B_store, out2, M, N, K, lda, ldb, N, a_major, b_major)
+        assert_close(host(out2), reference, TOL, "plain product over a split tail")
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
 def test_gemm_batched_heads(capi, gemm_mode):
     """Per-(batch, head) products addressed by strides inside [B, S, E] tensors, as attention uses them."""
     Bn, H, Sq, Sk, hd = 3, 4, 40, 72, 16
