@@ -207,6 +207,29 @@ def time_dominant_kernel(capi, torch, w, peaks, copies=4, launches=24, with_cubl
             "traffic": 328.9e6}
 
 
+def time_attention_core(capi, torch, w):
+    """One MultiHeadAttention layer of the benchmark's shape on 32 samples (attention weights 134 MB: larger than
+    L2), forward and backward, timed with CUDA events: the fused attention-core kernels with their projections."""
+    B, S, E, H = 32, w["S_dec"], w["E"], w["H"]
+    torch.manual_seed(0)
+    p = {n: torch.randn(E, E, device="cuda") * 0.03 for n in ("Wq", "Wk", "Wv", "Wo")}
+    p.update({n: torch.zeros(E, device="cuda") for n in ("bq", "bk", "bv", "bo")})
+    x = torch.randn(B, S, E, device="cuda")
+    dy = torch.randn(B, S, E, device="cuda")
+    y, ws = capi.mha_fwd(x, x, p, H, True)
+    capi.mha_bwd(x, x, p, H, True, ws, dy)
+    torch.cuda.synchronize()
+    start, middle, stop = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    start.record()
+    y, ws = capi.mha_fwd(x, x, p, H, True)
+    middle.record()
+    capi.mha_bwd(x, x, p, H, True, ws, dy)
+    stop.record()
+    torch.cuda.synchronize()
+    return {"kernel": "attention_core_kernel<64,false|true> inside onn_mha_fwd / onn_mha_bwd", "shape": {"B": B, "H": H, "Sq": S, "Sk": S, "E": E},
+            "mha_fwd_us": start.elapsed_time(middle) * 1e3, "mha_bwd_us": middle.elapsed_time(stop) * 1e3}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -234,9 +257,12 @@ def run_ours(args):
     if args.workload == "config2":
         w = SMALL_WORKLOAD
     peaks = measured_peaks()
-    if args.profile_kernel:
+    if args.profile_kernel == "gemm":
         # small stand-alone case for an ncu capture of the dominant kernel: 2 warm-up + 2 timed launches, 0.7 GB on the device
         emit(dict(time_dominant_kernel(capi, torch, w, peaks, copies=2, launches=2, with_cublas=False), profiling_only=True))
+        return
+    if args.profile_kernel == "attention":
+        emit(dict(time_attention_core(capi, torch, w), profiling_only=True))
         return
     if args.profile_batch:
         w = dict(w, global_batch=args.profile_batch, name=w["name"] + f" (profiling batch {args.profile_batch})")
@@ -361,8 +387,9 @@ def main():
                              "(the line it prints is not a benchmark result)")
     parser.add_argument("--workload", default="config5", choices=["config5", "config2"],
                         help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network")
-    parser.add_argument("--profile-kernel", action="store_true",
-                        help="profiling aid: launch only the dominant GEMM (FFN-up shape) four times on buffers larger than L2")
+    parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention"],
+                        help="profiling aid: launch only the dominant GEMM (FFN-up shape) four times on buffers larger than L2, "
+                             "or only one attention layer (forward and backward, 32 samples) twice")
     args = parser.parse_args()
     # Libraries (NCCL prints its version) write to file descriptor 1: keep it for the ONE JSON line by
     # pointing fd 1 at stderr while the benchmark runs and printing the line to the saved descriptor.
