@@ -305,6 +305,7 @@ def test_mha_head64(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
     if cross:
         xs[0, Sk - 5:] = 0.0                                  # padded source rows: masked keys
         if B > 1: xs[1, Sk // 2:] = 0.0
+        if B > 2: xs[2, :] = 0.0                               # a source of nothing but padding: uniform weights
     delta = rng.standard_normal((B, Sq, E)).astype(np.float32)
     y_e, saved = O.mha_forward(xq, xs, p, H, causal)
     grads_e, dxq_e, dxs_e = O.mha_backward(xq, xs, p, H, saved, delta, not cross)
