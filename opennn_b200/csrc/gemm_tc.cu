@@ -87,6 +87,7 @@ struct Params
     int tail_tiles;
     unsigned long long tail_token;                         // this launch's value of "zeroed" in tail_flags
     unsigned long long* tail_flags;                        // [tail tile][8 epilogue warps of a pair]
+    unsigned int* tail_visits;                             // same shape: adders that have seen the token (0, 1, back to 0)
 };
 
 // Instruction descriptor: D = fp32, A = B = tf32, M = 128, N = BN, majors as given.
@@ -765,6 +766,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if(*abort_flag || clock64() - start > kWaitCycles) { atomicCAS(&g_status, 0u, 15u); *abort_flag = 1; zeroed = false; break; }
                     }
                     asm volatile("fence.proxy.async;" ::: "memory");
+                    // the second of the strip's two adders to get here clears the token, so that a replay of this very
+                    // launch (a captured graph carries the same token) starts from "not zeroed" again
+                    unsigned int* visits = p.tail_visits + (long long)it.tail * 8 + flag_slot;
+                    if(zeroed && atomicAdd(visits, 1u) == 1u)
+                    {
+                        *visits = 0u;
+                        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(flag), "l"(0ull) : "memory");
+                    }
                 }
                 zeroed = __shfl_sync(0xffffffffu, zeroed, 0);
                 if(!zeroed) break;
@@ -871,22 +880,28 @@ namespace tc
 constexpr int kTailFlagSets = 16;
 constexpr int kTailFlagsPerSet = (kSmCount / 2) * 8;
 static __device__ unsigned long long g_tail_flags[kTailFlagSets * kTailFlagsPerSet];
+static __device__ unsigned int g_tail_visits[kTailFlagSets * kTailFlagsPerSet];
 
-static int tail_flags_for_current_device(unsigned long long** address)
+static int tail_flags_for_current_device(unsigned long long** flags, unsigned int** visits)
 {
     constexpr int kMaxDevices = 64;
     static std::mutex mutex;
-    static unsigned long long* resolved[kMaxDevices] = {};
+    static unsigned long long* resolved_flags[kMaxDevices] = {};
+    static unsigned int* resolved_visits[kMaxDevices] = {};
     int device = -1;
     if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return ONN_ERR_CUDA;
     std::lock_guard<std::mutex> lock(mutex);
-    if(!resolved[device])
+    if(!resolved_flags[device])
     {
-        unsigned long long* found = nullptr;
-        if(cudaGetSymbolAddress(reinterpret_cast<void**>(&found), g_tail_flags) != cudaSuccess || !found) return ONN_ERR_CUDA;
-        resolved[device] = found;
+        unsigned long long* found_flags = nullptr;
+        unsigned int* found_visits = nullptr;
+        if(cudaGetSymbolAddress(reinterpret_cast<void**>(&found_flags), g_tail_flags) != cudaSuccess || !found_flags) return ONN_ERR_CUDA;
+        if(cudaGetSymbolAddress(reinterpret_cast<void**>(&found_visits), g_tail_visits) != cudaSuccess || !found_visits) return ONN_ERR_CUDA;
+        resolved_flags[device] = found_flags;
+        resolved_visits[device] = found_visits;
     }
-    *address = resolved[device];
+    *flags = resolved_flags[device];
+    *visits = resolved_visits[device];
     return ONN_OK;
 }
 }  // namespace tc
@@ -916,7 +931,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.C = g.C; p.bias = g.bias; p.relu_mask = g.relu_mask; p.alpha = g.alpha;
     p.relu_bits_out = g.relu_bits_out; p.relu_bits = g.relu_bits; p.relu_bits_ld = g.relu_bits_ld;
     p.colsum = g.colsum_out; p.colsum_stride_inner = g.colsum_stride_inner;
-    p.tail_tiles = 0; p.tail_token = 0; p.tail_flags = nullptr;
+    p.tail_tiles = 0; p.tail_token = 0; p.tail_flags = nullptr; p.tail_visits = nullptr;
     p.relu = g.relu; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
     p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
     p.a_batch_inner_on = g.batch_inner > 1 && g.a_stride_inner != 0; p.a_batch_outer_on = g.batch_outer > 1 && g.a_stride_outer != 0;
@@ -956,13 +971,15 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
            !g.relu && !g.relu_mask && !g.relu_bits && !g.relu_bits_out)
         {
             unsigned long long* flags = nullptr;
-            if(tail_flags_for_current_device(&flags) == ONN_OK)
+            unsigned int* visits = nullptr;
+            if(tail_flags_for_current_device(&flags, &visits) == ONN_OK)
             {
                 static std::atomic<unsigned long long> sequence{0};
                 const unsigned long long token = ++sequence;
                 p.tail_tiles = (int)tail;
                 p.tail_token = token;
                 p.tail_flags = flags + (token % kTailFlagSets) * kTailFlagsPerSet;
+                p.tail_visits = visits + (token % kTailFlagSets) * kTailFlagsPerSet;
                 p.total_work = tiles + tail;
             }
         }
