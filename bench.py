@@ -256,6 +256,8 @@ def run_ours(args):
 
     if args.workload == "config2":
         w = SMALL_WORKLOAD
+    if args.micro_batch:
+        w = dict(w, micro_batch=args.micro_batch)
     peaks = measured_peaks()
     if args.profile_kernel == "gemm":
         # small stand-alone case for an ncu capture of the dominant kernel: 2 warm-up + 2 timed launches, 0.7 GB on the device
@@ -385,6 +387,7 @@ def main():
     parser.add_argument("--profile-batch", type=int, default=0,
                         help="profiling aid: run the device-resident loop only, on a global batch of this many samples "
                              "(the line it prints is not a benchmark result)")
+    parser.add_argument("--micro-batch", type=int, default=0, help="samples per micro-batch (default: the workload's own)")
     parser.add_argument("--workload", default="config5", choices=["config5", "config2"],
                         help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network")
     parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention"],
