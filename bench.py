@@ -282,8 +282,7 @@ def run_ours(args):
     host_batches, device_batches = [], []
     for _ in range(pool):
         enc, dec, tgt = synthetic_batch(rng, w["global_batch"], w)
-        lo, hi = rank * local_batch, (rank + 1) * local_batch
-        pinned = [torch.from_numpy(np.ascontiguousarray(x[lo:hi])).pin_memory() for x in (dec, enc, tgt)]
+        pinned = [torch.from_numpy(np.ascontiguousarray(x)).pin_memory() for x in trainer.shard_batch((dec, enc, tgt), rank, world)]
         host_batches.append(pinned)
         device_batches.append([x.cuda() for x in pinned])
 

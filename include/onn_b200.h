@@ -135,6 +135,10 @@ int onn_embedding_fwd(const float* ids, const float* W, const float* PE, float* 
                       int64_t B, int64_t S, int64_t E, int64_t V,
                       int scale, int add_pe, uint32_t flags, void* stream);
 
+/* Token ids as 32-bit integers (what a data feed holds; opennn/dataset.cpp:4397-4494 stages them as floats) to the
+ * floats-holding-integers the layers and the loss read.  Exact for |id| < 2^24. */
+int onn_ids_to_float(const int32_t* ids, float* out, int64_t n, void* stream);
+
 /* Backward replaces embedding_backward_kernel (opennn/kernel.cu:764-800) plus the fan-in
  * sum Layer::add_gradients (opennn/layer.cpp:447-457); CPU semantics
  * opennn/embedding_layer.cpp:193-226:  dW[id,:] += (dY + dY2)[b,s,:] * sqrt(E) for 0 < id < V.

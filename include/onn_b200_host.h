@@ -76,6 +76,12 @@ int onn_trainer_step_device(onn_trainer* trainer, const float* decoder_ids, cons
                             int64_t batch, int update, float* statistics);
 int onn_trainer_step_host(onn_trainer* trainer, const float* decoder_ids, const float* encoder_ids, const float* targets,
                           int64_t batch, int update, float* statistics);
+/* The same step fed with 32-bit integer ids in (pinned) host memory, as a data feed holds them
+ * (opennn/dataset.cpp:4363-4494 converts to float on the host and copies on the compute path).  The copies go through
+ * a copy stream into one of two sets of device buffers, so with statistics = NULL the next call's ids cross PCIe
+ * while this call's step computes; the conversion to the floats the layers read is a kernel on the trainer's stream. */
+int onn_trainer_step_host_i32(onn_trainer* trainer, const int32_t* decoder_ids, const int32_t* encoder_ids, const int32_t* targets,
+                              int64_t batch, int update, float* statistics);
 
 /* NeuralNetwork::forward_propagate on one micro-batch of device-resident ids
  * (is_training = 0: the output layer holds probabilities). */

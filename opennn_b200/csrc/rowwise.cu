@@ -646,6 +646,22 @@ extern "C" int onn_layernorm_bwd_static(const float* dY, const float* dY2, const
                                 (cudaStream_t)stream);
 }
 
+// Token ids arrive from the data feed as 32-bit integers; the layers read them as floats holding integers
+// (the reference's convention), which is exact up to 2^24.
+__global__ void ids_to_float_kernel(const int32_t* __restrict__ ids, float* __restrict__ out, long long n)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for(long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = (float)ids[i];
+}
+
+extern "C" int onn_ids_to_float(const int32_t* ids, float* out, int64_t n, void* stream)
+{
+    ONN_CHECK_ARG(ids && out && n > 0);
+    ids_to_float_kernel<<<grid_for(n, 256, 8), 256, 0, (cudaStream_t)stream>>>(ids, out, n);
+    count_launch();
+    return launch_status();
+}
+
 extern "C" int onn_add(const float* a, const float* b, float* out, int64_t n, uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(a && b && out && n > 0);

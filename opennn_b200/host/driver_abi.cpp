@@ -37,6 +37,14 @@ struct onn_trainer
     Index bucket_floats = 16 << 20;       // 64 MiB buckets: large enough for NVLink bandwidth, small enough to overlap
 
     TensorCuda staged_decoder, staged_encoder, staged_targets;
+
+    // int32 feed (onn_trainer_step_host_i32): two sets of device buffers filled by a copy stream, so the ids of the
+    // next step cross PCIe while this step computes
+    struct IdBuffers { int32_t *decoder = nullptr, *encoder = nullptr, *targets = nullptr; Index capacity = 0;
+                       cudaEvent_t copied = nullptr, consumed = nullptr; };
+    IdBuffers id_buffers[2];
+    cudaStream_t copy_stream = nullptr;
+    int id_flip = 0;
     type* pinned_scalars = nullptr;       // {square norm, global active tokens}
 
     // CUDA-graph replay of the micro-batch: one executable graph per micro-batch index (the statistics slot the
@@ -50,6 +58,15 @@ struct onn_trainer
     ~onn_trainer()
     {
         for(MicroGraph& g : micro_graphs) if(g.executable) cudaGraphExecDestroy(g.executable);
+        for(IdBuffers& b : id_buffers)
+        {
+            if(b.decoder) cudaFree(b.decoder);
+            if(b.encoder) cudaFree(b.encoder);
+            if(b.targets) cudaFree(b.targets);
+            if(b.copied) cudaEventDestroy(b.copied);
+            if(b.consumed) cudaEventDestroy(b.consumed);
+        }
+        if(copy_stream) cudaStreamDestroy(copy_stream);
         if(pinned_scalars) cudaFreeHost(pinned_scalars);
         if(stream) cudaStreamDestroy(stream);
     }
@@ -382,6 +399,52 @@ extern "C" int onn_trainer_step_host(onn_trainer* t, const float* decoder_ids, c
             if(!encoder_ids) throw std::runtime_error("step: missing encoder ids");
             check_cuda(cudaMemcpyAsync(t->staged_encoder.data, encoder_ids, size_t(encoder_count) * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
         }
+        run_step(t, t->staged_decoder.data, t->decoder_only ? nullptr : t->staged_encoder.data, t->staged_targets.data, batch, update != 0, statistics);
+    });
+}
+
+extern "C" int onn_trainer_step_host_i32(onn_trainer* t, const int32_t* decoder_ids, const int32_t* encoder_ids, const int32_t* targets,
+                                         int64_t batch, int update, float* statistics)
+{
+    if(!t || !decoder_ids || !targets || batch <= 0) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        if(!t->decoder_only && !encoder_ids) throw std::runtime_error("step: missing encoder ids");
+        const Index decoder_count = batch * t->decoder_sequence_length, encoder_count = batch * t->input_sequence_length;
+        if(!t->copy_stream) check_cuda(cudaStreamCreateWithFlags(&t->copy_stream, cudaStreamNonBlocking), "copy stream");
+        onn_trainer::IdBuffers& ids = t->id_buffers[t->id_flip];
+        t->id_flip ^= 1;
+        const Index wanted = std::max(decoder_count, encoder_count);
+        if(ids.capacity < wanted)
+        {
+            if(ids.copied) check_cuda(cudaEventSynchronize(ids.copied), "id buffers");       // nothing may still use the old ones
+            if(ids.consumed) check_cuda(cudaEventSynchronize(ids.consumed), "id buffers");
+            for(int32_t** pointer : {&ids.decoder, &ids.encoder, &ids.targets})
+            {
+                if(*pointer) cudaFree(*pointer);
+                check_cuda(cudaMalloc(reinterpret_cast<void**>(pointer), size_t(wanted) * sizeof(int32_t)), "id buffers");
+            }
+            ids.capacity = wanted;
+            if(!ids.copied) check_cuda(cudaEventCreateWithFlags(&ids.copied, cudaEventDisableTiming), "id event");
+            if(!ids.consumed) check_cuda(cudaEventCreateWithFlags(&ids.consumed, cudaEventDisableTiming), "id event");
+        }
+        if(t->staged_decoder.size() < decoder_count) { t->staged_decoder.resize(decoder_count); t->staged_targets.resize(decoder_count); }
+        if(!t->decoder_only && t->staged_encoder.size() < encoder_count) t->staged_encoder.resize(encoder_count);
+
+        // copy stream: wait until the conversion kernels that last read this set are done, then bring the new ids over
+        check_cuda(cudaStreamWaitEvent(t->copy_stream, ids.consumed, 0), "id buffers: wait for consumer");
+        check_cuda(cudaMemcpyAsync(ids.decoder, decoder_ids, size_t(decoder_count) * sizeof(int32_t), cudaMemcpyHostToDevice, t->copy_stream), "ids H2D");
+        check_cuda(cudaMemcpyAsync(ids.targets, targets, size_t(decoder_count) * sizeof(int32_t), cudaMemcpyHostToDevice, t->copy_stream), "targets H2D");
+        if(!t->decoder_only)
+            check_cuda(cudaMemcpyAsync(ids.encoder, encoder_ids, size_t(encoder_count) * sizeof(int32_t), cudaMemcpyHostToDevice, t->copy_stream), "ids H2D");
+        check_cuda(cudaEventRecord(ids.copied, t->copy_stream), "id buffers: copied");
+
+        // compute stream: ids as the floats the layers read
+        check_cuda(cudaStreamWaitEvent(t->stream, ids.copied, 0), "id buffers: wait for copy");
+        check_onn(onn_ids_to_float(ids.decoder, t->staged_decoder.data, decoder_count, t->stream), "ids to float");
+        check_onn(onn_ids_to_float(ids.targets, t->staged_targets.data, decoder_count, t->stream), "ids to float");
+        if(!t->decoder_only) check_onn(onn_ids_to_float(ids.encoder, t->staged_encoder.data, encoder_count, t->stream), "ids to float");
+        check_cuda(cudaEventRecord(ids.consumed, t->stream), "id buffers: consumed");
         run_step(t, t->staged_decoder.data, t->decoder_only ? nullptr : t->staged_encoder.data, t->staged_targets.data, batch, update != 0, statistics);
     });
 }

@@ -22,7 +22,7 @@ HOST_EXPORTS = [
     "onn_trainer_last_error", "onn_trainer_create", "onn_trainer_destroy", "onn_trainer_parameters_number",
     "onn_trainer_layers_number", "onn_trainer_layer_info", "onn_trainer_set_parameters", "onn_trainer_get_parameters",
     "onn_trainer_get_gradients", "onn_trainer_set_learning_rate", "onn_trainer_set_iteration", "onn_trainer_set_dp",
-    "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_forward", "onn_trainer_get_layer_output",
+    "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_step_host_i32", "onn_trainer_forward", "onn_trainer_get_layer_output",
     "onn_trainer_synchronize", "onn_trainer_stream", "onn_trainer_set_graph_capture",
 ]
 
@@ -130,6 +130,21 @@ class Trainer:
                                                 C.c_int64(batch), int(update), stats if want_statistics else None), "step_host")
         return tuple(stats) if want_statistics else None
 
+    def step_host_i32(self, dec_ids, enc_ids, targets, update=True, want_statistics=True):
+        """Same, fed with int32 ids in host memory (torch CPU tensors, pinned for full copy speed): the ids are copied
+        on a copy stream into one of two sets of device buffers and converted on the device."""
+        import torch
+        stats = (C.c_float * 4)()
+        for x in (dec_ids, enc_ids, targets):
+            if x is not None and (x.dtype != torch.int32 or not x.is_contiguous() or x.is_cuda):
+                raise ValueError("step_host_i32 takes contiguous int32 CPU tensors")
+        batch = dec_ids.shape[0]
+        _check(host_lib().onn_trainer_step_host_i32(self._handle, C.c_void_p(dec_ids.data_ptr()),
+                                                    C.c_void_p(enc_ids.data_ptr() if enc_ids is not None else 0),
+                                                    C.c_void_p(targets.data_ptr()), C.c_int64(batch), int(update),
+                                                    stats if want_statistics else None), "step_host_i32")
+        return tuple(stats) if want_statistics else None
+
     def forward(self, dec_ids, enc_ids, is_training=False):
         _check(host_lib().onn_trainer_forward(self._handle, capi.ptr(dec_ids), capi.ptr(enc_ids), int(is_training)), "forward")
 
@@ -147,6 +162,22 @@ class Trainer:
 
     def synchronize(self):
         _check(host_lib().onn_trainer_synchronize(self._handle), "synchronize")
+
+
+def shard_batch(arrays, rank, world):
+    """The data-parallel rule of the trainer for a batch every rank can see: rank r of `world` takes the r-th of
+    `world` equal contiguous slices of each array's first dimension (the global batch must divide evenly, so that
+    every rank runs the same number of micro-batches and joins the same collectives)."""
+    shards = []
+    for a in arrays:
+        if a is None:
+            shards.append(None)
+            continue
+        if a.shape[0] % world != 0:
+            raise ValueError(f"batch of {a.shape[0]} samples does not split evenly over {world} ranks")
+        share = a.shape[0] // world
+        shards.append(a[rank * share:(rank + 1) * share])
+    return shards
 
 
 class DpRendezvousError(RuntimeError):

@@ -108,3 +108,17 @@ def test_missing_rank_ends_the_rendezvous_with_a_timeout_not_a_hang():
     outcomes = _run_rendezvous("missing")
     assert outcomes[1] == "left before the rendezvous"
     assert outcomes[0].startswith("refused") and "[1] did not join" in outcomes[0], outcomes
+
+
+def test_shard_batch_gives_every_rank_an_equal_contiguous_slice():
+    from opennn_b200 import trainer
+    ids = np.arange(24).reshape(8, 3)
+    parts = [trainer.shard_batch([ids, None], rank, 4) for rank in range(4)]
+    assert all(p[1] is None for p in parts)
+    assert np.array_equal(np.concatenate([p[0] for p in parts]), ids)
+    assert all(p[0].shape[0] == 2 for p in parts)
+    try:
+        trainer.shard_batch([ids], 0, 3)
+        raise AssertionError("a batch that does not divide must be refused")
+    except ValueError:
+        pass

@@ -150,6 +150,29 @@ def test_micro_batches_match_one_batch(libs):
     assert_close(results[1][1], results[0][1], 1e-4, "gradient, 4 micro-batches vs 1")
 
 
+def test_int32_feed_matches_float_feed(libs):
+    """Ids fed as int32 from pinned host memory (copy stream, two buffer sets, conversion on the device) give the very
+    step the float feed gives, call after call."""
+    capi, trainer = libs
+    name = "tiny_encdec_odd"
+    net, params, external, targets = network_inputs(name)
+    as_float = [torch.from_numpy(x).pin_memory() for x in (external[-1], external[-2], targets)]
+    as_int = [torch.from_numpy(x.astype(np.int32)).pin_memory() for x in (external[-1], external[-2], targets)]
+    t = make_trainer(trainer, name)
+    t.set_parameters(params)
+    a = t.step_host(*as_float, update=False)
+    ga = t.get_gradients()
+    for _ in range(3):                                              # both buffer sets get used
+        b = t.step_host_i32(*as_int, update=False)
+        gb = t.get_gradients()
+        assert a[:3] == b[:3]
+        assert_close(gb, ga, 1e-5, "gradient")
+    for _ in range(3):                                              # without statistics the host runs ahead of the copies
+        t.step_host_i32(*as_int, update=False, want_statistics=False)
+    assert_close(t.get_gradients(), ga, 1e-5, "gradient after queued steps")
+    t.close()
+
+
 def test_graph_replay_matches_eager_steps(libs):
     """Steps whose micro-batches are replayed from captured CUDA graphs (the default after the first step) train
     exactly like steps launched kernel by kernel: same losses, same gradients, same parameters, and the launch
