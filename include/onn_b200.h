@@ -232,6 +232,24 @@ int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
                   int64_t rows, int64_t in, int64_t out, int activation,
                   uint32_t flags, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Pooling3d: pooling over the sequence in front of a classification head.  Replaces
+ * pooling3d_{max,avg}_{forward,backward}_kernel (opennn/kernel.cu:995-1136, called from
+ * opennn/pooling_layer_3d.cpp:235-300); CPU semantics opennn/pooling_layer_3d.cpp:77-232.
+ * x [B, S, E] -> y [B, E].  method 0 = MaxPooling: the maximum over the sequence, the first position winning ties;
+ * argmax ([B, E], optional for inference) keeps that position for the backward pass.  method 1 = AveragePooling:
+ * the mean over the rows that are not padding (a padding row has every feature exactly zero), zeros for a sample
+ * of nothing but padding; row_is_valid ([B * S] bytes) and valid_count ([B]) are written by the forward pass and read
+ * by the backward pass.  The backward pass writes all of dx (zeros where nothing flows).  Results are bit-identical to
+ * the CPU path (same order of additions, same division).
+ * ------------------------------------------------------------------------------------- */
+#define ONN_POOL_MAX      0
+#define ONN_POOL_AVERAGE  1
+int onn_pooling3d_fwd(const float* x, float* y, int32_t* argmax, uint8_t* row_is_valid, int32_t* valid_count,
+                      int64_t B, int64_t S, int64_t E, int method, void* stream);
+int onn_pooling3d_bwd(const float* dy, const int32_t* argmax, const uint8_t* row_is_valid, const int32_t* valid_count,
+                      float* dx, int64_t B, int64_t S, int64_t E, int method, void* stream);
+
 /* Row softmax over the last dimension, in place (opennn/layer.cpp:338-371). */
 int onn_softmax_rows(float* Y, int64_t rows, int64_t cols, void* stream);
 

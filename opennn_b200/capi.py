@@ -54,7 +54,7 @@ EXPORTS = [
     "onn_status_string", "onn_version", "onn_gemm", "onn_gemm_set_mode", "onn_gemm_device_status",
     "onn_launch_count", "onn_launch_count_add", "onn_selftest_bounded_wait", "onn_embedding_fwd", "onn_embedding_bwd", "onn_ids_to_float",
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
-    "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_softmax_rows",
+    "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_pooling3d_fwd", "onn_pooling3d_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
     "onn_mha_attention_weights", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
     "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam",
@@ -211,6 +211,29 @@ def dense_bwd(X, W, Y, dY, activation, flags=0, need_dx=True, relu_mask=None, dx
     check(lib().onn_dense_bwd(ptr(X), ptr(W), ptr(Y), ptr(dY), ptr(dW), ptr(db), ptr(dX), ptr(relu_mask), ptr(relu_bits), ptr(dx_colsum), i64(rows),
                               i64(in_f), i64(out_f), ACTIVATIONS[activation], C.c_uint32(flags), stream_ptr()), "onn_dense_bwd")
     return dX, dW, db
+
+
+POOLING_METHODS = {"MaxPooling": 0, "AveragePooling": 1}
+
+
+def pooling3d_fwd(x, method):
+    B, S, E = x.shape
+    y = torch.empty(B, E, device="cuda")
+    argmax = torch.empty(B, E, dtype=torch.int32, device="cuda")
+    valid = torch.empty(B * S, dtype=torch.uint8, device="cuda")
+    count = torch.empty(B, dtype=torch.int32, device="cuda")
+    check(lib().onn_pooling3d_fwd(ptr(x), ptr(y), ptr(argmax), ptr(valid), ptr(count), i64(B), i64(S), i64(E),
+                                  POOLING_METHODS[method], stream_ptr()), "onn_pooling3d_fwd")
+    return y, (argmax, valid, count)
+
+
+def pooling3d_bwd(dy, saved, S, method):
+    B, E = dy.shape
+    argmax, valid, count = saved
+    dx = torch.empty(B, S, E, device="cuda")
+    check(lib().onn_pooling3d_bwd(ptr(dy), ptr(argmax), ptr(valid), ptr(count), ptr(dx), i64(B), i64(S), i64(E),
+                                  POOLING_METHODS[method], stream_ptr()), "onn_pooling3d_bwd")
+    return dx
 
 
 def softmax_rows(Y):

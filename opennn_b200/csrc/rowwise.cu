@@ -646,6 +646,122 @@ extern "C" int onn_layernorm_bwd_static(const float* dY, const float* dY2, const
                                 (cudaStream_t)stream);
 }
 
+// ---------------------------------------------------------------------------------------
+// Pooling3d: [B, S, E] -> [B, E] over the sequence
+// ---------------------------------------------------------------------------------------
+
+// One CTA per sample: a row is padding when every feature is exactly zero; flags per row, count per sample.
+__global__ void __launch_bounds__(kRowThreads)
+pooling_valid_rows_kernel(const float* __restrict__ x, uint8_t* __restrict__ row_is_valid, int32_t* __restrict__ valid_count, int S, int E)
+{
+    __shared__ int warp_counts[kRowWarps];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long b = blockIdx.x;
+    int mine = 0;
+    for(int s = warp; s < S; s += kRowWarps)
+    {
+        const float* row = x + (b * S + s) * (long long)E;
+        bool any = false;
+        for(int e = lane; e < E; e += 32) any = any || row[e] != 0.f;
+        any = __any_sync(0xffffffffu, any);
+        if(lane == 0) { row_is_valid[b * S + s] = any ? 1 : 0; mine += any ? 1 : 0; }
+    }
+    if(lane == 0) warp_counts[warp] = mine;
+    __syncthreads();
+    if(threadIdx.x == 0)
+    {
+        int total = 0;
+        for(int w = 0; w < kRowWarps; w++) total += warp_counts[w];
+        valid_count[b] = total;
+    }
+}
+
+// One thread per (sample, feature), walking the sequence in order (the reference's order of additions and its
+// first-position-wins rule for ties of the maximum); neighbouring threads read neighbouring features.
+__global__ void pooling_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ argmax,
+                                   const uint8_t* __restrict__ row_is_valid, const int32_t* __restrict__ valid_count,
+                                   long long B, int S, int E, int method)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for(long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < B * E; i += stride)
+    {
+        const long long b = i / E;
+        const int f = (int)(i % E);
+        const float* column = x + b * S * (long long)E + f;
+        if(method == 0)
+        {
+            float best = -INFINITY;
+            int where = 0;
+            for(int s = 0; s < S; s++)
+            {
+                const float value = column[(long long)s * E];
+                if(value > best) { best = value; where = s; }
+            }
+            y[i] = best;
+            if(argmax) argmax[i] = where;
+        }
+        else
+        {
+            float total = 0.f;
+            for(int s = 0; s < S; s++)
+                if(row_is_valid[b * S + s]) total += column[(long long)s * E];
+            const int count = valid_count[b];
+            y[i] = count > 0 ? total / (float)count : total;
+        }
+    }
+}
+
+__global__ void pooling_bwd_kernel(const float* __restrict__ dy, const int32_t* __restrict__ argmax, const uint8_t* __restrict__ row_is_valid,
+                                   const int32_t* __restrict__ valid_count, float* __restrict__ dx, long long B, int S, int E, int method)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for(long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < B * E; i += stride)
+    {
+        const long long b = i / E;
+        const int f = (int)(i % E);
+        float* column = dx + b * S * (long long)E + f;
+        const float delta = dy[i];
+        if(method == 0)
+        {
+            const int where = argmax[i];
+            for(int s = 0; s < S; s++) column[(long long)s * E] = s == where ? delta : 0.f;
+        }
+        else
+        {
+            const int count = valid_count[b];
+            const float share = count > 0 ? delta * (1.0f / (float)count) : 0.f;
+            for(int s = 0; s < S; s++) column[(long long)s * E] = (count > 0 && row_is_valid[b * S + s]) ? share : 0.f;
+        }
+    }
+}
+
+extern "C" int onn_pooling3d_fwd(const float* x, float* y, int32_t* argmax, uint8_t* row_is_valid, int32_t* valid_count,
+                                 int64_t B, int64_t S, int64_t E, int method, void* stream)
+{
+    ONN_CHECK_ARG(x && y && B > 0 && S > 0 && E > 0 && S < (1LL << 31) && E < (1LL << 31) && (method == 0 || method == 1));
+    ONN_CHECK_ARG(method == 0 || (row_is_valid && valid_count));
+    cudaStream_t s = (cudaStream_t)stream;
+    if(method == 1)
+    {
+        pooling_valid_rows_kernel<<<(unsigned)B, kRowThreads, 0, s>>>(x, row_is_valid, valid_count, (int)S, (int)E);
+        count_launch();
+        if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    }
+    pooling_fwd_kernel<<<grid_for(B * E, 256, 8), 256, 0, s>>>(x, y, argmax, row_is_valid, valid_count, B, (int)S, (int)E, method);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_pooling3d_bwd(const float* dy, const int32_t* argmax, const uint8_t* row_is_valid, const int32_t* valid_count,
+                                 float* dx, int64_t B, int64_t S, int64_t E, int method, void* stream)
+{
+    ONN_CHECK_ARG(dy && dx && B > 0 && S > 0 && E > 0 && S < (1LL << 31) && E < (1LL << 31) && (method == 0 || method == 1));
+    ONN_CHECK_ARG(method == 0 ? argmax != nullptr : (row_is_valid && valid_count));
+    pooling_bwd_kernel<<<grid_for(B * E, 256, 8), 256, 0, (cudaStream_t)stream>>>(dy, argmax, row_is_valid, valid_count, dx, B, (int)S, (int)E, method);
+    count_launch();
+    return launch_status();
+}
+
 // Token ids arrive from the data feed as 32-bit integers; the layers read them as floats holding integers
 // (the reference's convention), which is exact up to 2^24.
 __global__ void ids_to_float_kernel(const int32_t* __restrict__ ids, float* __restrict__ out, long long n)

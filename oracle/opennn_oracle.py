@@ -155,6 +155,46 @@ def dense_backward(x, weights, d_y, activation_derivatives, activation):
 
 
 # --------------------------------------------------------------------------------------
+# Pooling3d (sequence pooling in front of a classification head)
+# --------------------------------------------------------------------------------------
+
+def pooling3d_forward(x, method):
+    """opennn/pooling_layer_3d.cpp:77-148.  x [B,S,E] -> y [B,E].  MaxPooling: maximum over the sequence, the FIRST
+    position winning ties (strict >, :101-108), its index kept for the backward pass.  AveragePooling: mean over the
+    rows that are not padding, a padding row being one whose features are all exactly zero (:119-141); a sample of
+    nothing but padding gives zeros."""
+    if method == "MaxPooling":
+        indices = np.argmax(x, axis=1)                                    # first occurrence of the maximum
+        return np.take_along_axis(x, indices[:, None, :], axis=1)[:, 0, :].astype(F32), indices
+    valid = np.any(x != 0, axis=2)                                        # [B,S]
+    y = np.zeros((x.shape[0], x.shape[2]), dtype=F32)
+    for b in range(x.shape[0]):
+        for s in range(x.shape[1]):                                       # sequential float accumulation, as :134-135
+            if valid[b, s]:
+                y[b] += x[b, s]
+        count = int(valid[b].sum())
+        if count > 0:
+            y[b] /= F32(count)
+    return y, valid
+
+
+def pooling3d_backward(x, d_y, method, saved):
+    """opennn/pooling_layer_3d.cpp:151-232.  MaxPooling routes each output gradient to the stored position, zeros
+    elsewhere; AveragePooling gives every non-padding row d_y / count and padding rows zero."""
+    d_x = np.zeros_like(x, dtype=F32)
+    if method == "MaxPooling":
+        np.put_along_axis(d_x, saved[:, None, :], d_y[:, None, :].astype(F32), axis=1)
+        return d_x
+    for b in range(x.shape[0]):
+        count = int(saved[b].sum())
+        if count == 0:
+            continue
+        inverse = F32(1.0) / F32(count)
+        d_x[b, saved[b]] = (d_y[b] * inverse).astype(F32)
+    return d_x
+
+
+# --------------------------------------------------------------------------------------
 # MultiHeadAttention
 # --------------------------------------------------------------------------------------
 

@@ -138,6 +138,15 @@ unique_ptr<Layer> make_layer(const string& kind, Index& inputs_count, vector<Sha
         return make_unique<opennn::Dense<3>>(S, E, F, spec_string("activation", "Linear"), "dense");
     }
 
+    if(kind == "pooling3d")
+    {
+        inputs_count = 1;
+        input_shapes = {Shape{batch, S, E}};
+        const Pooling3d::PoolingMethod method = spec_string("method", "MaxPooling") == "MaxPooling"
+            ? Pooling3d::PoolingMethod::MaxPooling : Pooling3d::PoolingMethod::AveragePooling;
+        return make_unique<Pooling3d>(Shape{S, E}, method);
+    }
+
     throw runtime_error("unknown layer kind " + kind);
 }
 
@@ -154,10 +163,12 @@ void run_layer()
     vector<TensorView*> parameter_views = layer->get_parameter_views();
     VectorR parameters(get_size(parameter_views));
     parameters.setZero();
-    link(parameters.data(), parameter_views);
-
-    const vector<type> parameters_in = read_bin("params", parameters.size());
-    memcpy(parameters.data(), parameters_in.data(), parameters_in.size() * sizeof(type));
+    if(parameters.size() > 0)                                   // Pooling3d has none
+    {
+        link(parameters.data(), parameter_views);
+        const vector<type> parameters_in = read_bin("params", parameters.size());
+        memcpy(parameters.data(), parameters_in.data(), parameters_in.size() * sizeof(type));
+    }
 
     vector<VectorR> inputs(inputs_count);
     for(Index i = 0; i < inputs_count; i++)
@@ -197,7 +208,7 @@ void run_layer()
     vector<TensorView*> gradient_views = back->get_gradient_views();
     VectorR gradients(get_size(gradient_views));
     gradients.setZero();
-    link(gradients.data(), gradient_views);
+    if(gradients.size() > 0) link(gradients.data(), gradient_views);
 
     vector<TensorView*> back_workspace_views = back->get_workspace_views();
     VectorR back_workspace(get_size(back_workspace_views));

@@ -194,6 +194,30 @@ def make_layernorm(seed=2):
              y=ref["y"], dx=ref["dx0"], dgamma=ref["grads"][:E], dbeta=ref["grads"][O.padded(E):O.padded(E) + E])
 
 
+POOLING_CASES = [("pooling_max_3_7_16", 3, 7, 16, "MaxPooling"), ("pooling_max_2_33_200", 2, 33, 200, "MaxPooling"),
+                 ("pooling_avg_4_9_24", 4, 9, 24, "AveragePooling"), ("pooling_avg_2_40_136", 2, 40, 136, "AveragePooling")]
+
+
+def make_pooling(seed=6):
+    for name, B, S, E, method in POOLING_CASES:
+        print(f"  {name}")
+        rng = np.random.default_rng(seed)
+        x = rng.standard_normal((B, S, E)).astype(F32)
+        x[:, S - 2:, :] = 0                                       # trailing padding rows
+        x[0, 1, :] = 0                                            # one in the middle
+        if B > 2:
+            x[2] = 0                                              # a sample of nothing but padding
+        x[1, 0, 3] = x[1, 2, 3] = 7.5                             # a tie for the maximum: the first position wins
+        delta = rng.standard_normal((B, E)).astype(F32)
+        spec = dict(mode="layer", kind="pooling3d", B=B, S=S, E=E, method=method)
+        ref, _ = ref_runner.run(spec, {"params": np.zeros(0, dtype=F32), "x0": x, "delta": delta}, ["y", "dx0"])
+        y, saved = O.pooling3d_forward(x, method)
+        dx = O.pooling3d_backward(x, delta, method, saved)
+        check("y", y, ref["y"], 1e-6)
+        check("dx", dx, ref["dx0"], 1e-6)
+        save(name, spec=np.array([B, S, E]), method=np.array(method), x=x, delta=delta, y=ref["y"].reshape(B, E), dx=ref["dx0"].reshape(B, S, E))
+
+
 DENSE_CASES = [("dense_linear_2_5_6_9", 2, 5, 6, 9, "Linear"), ("dense_relu_3_8_16_40", 3, 8, 16, 40, "RectifiedLinear"),
                ("dense_softmax_4_5_6_8", 4, 5, 6, 8, "Softmax"), ("dense_relu_2_33_64_136", 2, 33, 64, 136, "RectifiedLinear"),
                ("dense_linear_2_17_200_72", 2, 17, 200, 72, "Linear")]
@@ -350,7 +374,7 @@ def main():
     if not ref_runner.available():
         raise SystemExit("build the reference first: make -C oracle REF=/path/to/opennn")
     groups = {"mha": make_mha, "embedding": make_embedding, "layernorm": make_layernorm,
-              "dense": make_dense, "ce3d": make_ce3d}
+              "dense": make_dense, "ce3d": make_ce3d, "pooling": make_pooling}
     for group, fn in groups.items():
         if args.only and args.only != group:
             continue

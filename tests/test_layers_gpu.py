@@ -98,6 +98,19 @@ def test_layernorm(capi, name):
     assert_close(host(dgamma3), g["dgamma"], 5e-5, "dgamma (three consumers)")
 
 
+@pytest.mark.parametrize("name", names("pooling_"))
+def test_pooling3d(capi, name):
+    """Sequence pooling against the reference's outputs: padding rows, a sample of nothing but padding, a tie for the
+    maximum.  Element-wise work in the reference's order: bit-exact."""
+    g = golden(name)
+    method = str(g["method"])
+    x = dev(g["x"])
+    y, saved = capi.pooling3d_fwd(x, method)
+    assert np.array_equal(host(y), g["y"]), "y"
+    dx = capi.pooling3d_bwd(dev(g["delta"]), saved, g["x"].shape[1], method)
+    assert np.array_equal(host(dx), g["dx"]), "dx"
+
+
 @pytest.mark.parametrize("name", names("dense_"))
 def test_dense(capi, gemm_mode, name):
     g = golden(name)

@@ -40,6 +40,15 @@ def test_layernorm(name):
     assert_close(db, g["dbeta"], 2e-5, "dbeta")
 
 
+@pytest.mark.parametrize("name", names("pooling_"))
+def test_pooling3d(name):
+    g = golden(name)
+    method = str(g["method"])
+    y, saved = O.pooling3d_forward(g["x"], method)
+    dx = O.pooling3d_backward(g["x"], g["delta"], method, saved)
+    assert np.array_equal(y, g["y"]) and np.array_equal(dx, g["dx"])
+
+
 @pytest.mark.parametrize("name", names("dense_"))
 def test_dense(name):
     g = golden(name)
