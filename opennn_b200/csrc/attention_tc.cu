@@ -524,7 +524,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
                 // scores in the log2 domain with the layer's masks: padded keys are OVERWRITTEN with -1e9, keys after the
                 // query (causal) and keys past the source length drop out; blocks that need no per-element test take the short path
-                float row_max = -INFINITY;
+                float part_max[4] = { -INFINITY, -INFINITY, -INFINITY, -INFINITY };   // four chains instead of one long one
 #pragma unroll
                 for(int j = 0; j < 4; j++)
                 {
@@ -539,7 +539,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     else if(!special)
                     {
 #pragma unroll
-                        for(int i = 0; i < 32; i++) { v[j * 32 + i] *= to_log2; row_max = fmaxf(row_max, v[j * 32 + i]); }
+                        for(int i = 0; i < 32; i++) { v[j * 32 + i] *= to_log2; part_max[i & 3] = fmaxf(part_max[i & 3], v[j * 32 + i]); }
                     }
                     else
                     {
@@ -551,24 +551,26 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             if((pad_word[j] >> i) & 1u) t = -1e9f * kLog2e;
                             if((p.causal && key > q_row) || key >= p.Sk) t = -INFINITY;
                             v[j * 32 + i] = t;
-                            row_max = fmaxf(row_max, t);
+                            part_max[i & 3] = fmaxf(part_max[i & 3], t);
                         }
                     }
                 }
+                float row_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
                 exchange[half * kQRows + r_local] = row_max;
                 pair_barrier(quadrant);
                 row_max = fmaxf(row_max, exchange[(half ^ 1) * kQRows + r_local]);
                 pair_barrier(quadrant);                          // both have read: the slots may be rewritten
 
                 // exponentials, unnormalised and rounded to tf32 for the tensor core
-                float total = 0.f;
+                float part_sum[4] = { 0.f, 0.f, 0.f, 0.f };
 #pragma unroll
                 for(int i = 0; i < kHalfKeys; i++)
                 {
                     const float e = round_tf32(exp2_approx(v[i] - row_max));
-                    total += e;
+                    part_sum[i & 3] += e;
                     v[i] = e;
                 }
+                float total = (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
 #pragma unroll
                 for(int j = 0; j < 4; j++) tmem_store_32_issue(lane_base + half * kHalfKeys + j * 32, v + j * 32);
                 tmem_store_wait();
