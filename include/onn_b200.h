@@ -326,6 +326,13 @@ int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_co
                      int64_t rows, int64_t V, int inputs_are_probabilities,
                      uint32_t flags, void* stream);
 
+/* Greedy decoding step (the body of the loop at opennn/standard_networks.cpp:1016-1034, which reads the distribution
+ * back to the host and scans it there): for each of B samples the arg-max -- first index on ties -- of
+ * probabilities[b, position, :] ([B, S, V]) becomes ids[b, position + 1] (floats holding integers, [B, S]) unless
+ * finished[b] is set; finished[b] is set when that token is end_id. */
+int onn_greedy_next_token(const float* probabilities, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
+                          int64_t position, int end_id, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * AdaptiveMomentEstimation.  Replaces adam_update_kernel (opennn/kernel.cu:6-68) and adds
  * the global-norm clip only the CPU path has (opennn/adaptive_moment_estimation.cpp:444-473):

@@ -86,6 +86,12 @@ int onn_trainer_step_host_i32(onn_trainer* trainer, const int32_t* decoder_ids, 
 /* NeuralNetwork::forward_propagate on one micro-batch of device-resident ids
  * (is_training = 0: the output layer holds probabilities). */
 int onn_trainer_forward(onn_trainer* trainer, const float* decoder_ids, const float* encoder_ids, int is_training);
+/* Greedy decoding on token ids: the loop of Transformer::calculate_outputs (opennn/standard_networks.cpp:1002-1035)
+ * without the tokeniser and vocabulary maps around it.  encoder_ids (host, [micro_batch, input_sequence_length]) are
+ * decoded independently row by row; decoded_ids (host, [micro_batch, decoder_sequence_length]) receives
+ * [start_id, token 1, ..., end_id, PAD ...].  The encoder side runs once, the decoder side once per token, the
+ * arg-max stays on the device (onn_greedy_next_token); there is no key/value cache. */
+int onn_trainer_greedy_decode(onn_trainer* trainer, const float* encoder_ids, float* decoded_ids, int start_id, int end_id);
 int onn_trainer_get_layer_output(onn_trainer* trainer, int layer, float* host_output, int64_t count);
 int onn_trainer_synchronize(onn_trainer* trainer);
 /* The cudaStream_t every kernel of this trainer is launched on (for event timing by the caller). */

@@ -688,6 +688,54 @@ extern "C" int onn_softmax_rows(float* Y, int64_t rows, int64_t cols, void* stre
     return launch_status();
 }
 
+// Greedy decoding step: per sample the arg-max (first index on ties) of the distribution at `position`, written as a
+// float id into ids[b, position + 1] unless the sample already produced END; finished[b] is set on END.
+__global__ void __launch_bounds__(256)
+greedy_next_token_kernel(const float* __restrict__ probabilities, float* __restrict__ ids, int* __restrict__ finished,
+                         int S, int V, int position, int end_id)
+{
+    __shared__ float best_value[256];
+    __shared__ int best_index[256];
+    const int b = blockIdx.x;
+    const float* row = probabilities + ((long long)b * S + position) * V;
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    for(int k = threadIdx.x; k < V; k += blockDim.x)
+        if(row[k] > value) { value = row[k]; index = k; }        // strided scan keeps the smallest index of each thread's maximum
+    best_value[threadIdx.x] = value;
+    best_index[threadIdx.x] = index;
+    __syncthreads();
+    for(int step = blockDim.x / 2; step > 0; step >>= 1)
+    {
+        if(threadIdx.x < step)
+        {
+            const float other = best_value[threadIdx.x + step];
+            const int other_index = best_index[threadIdx.x + step];
+            if(other > best_value[threadIdx.x] || (other == best_value[threadIdx.x] && other_index < best_index[threadIdx.x]))
+            {
+                best_value[threadIdx.x] = other;
+                best_index[threadIdx.x] = other_index;
+            }
+        }
+        __syncthreads();
+    }
+    if(threadIdx.x == 0 && !finished[b])
+    {
+        const int token = best_index[0] == 0x7fffffff ? 0 : best_index[0];
+        ids[(long long)b * S + position + 1] = (float)token;
+        if(token == end_id) finished[b] = 1;
+    }
+}
+
+extern "C" int onn_greedy_next_token(const float* probabilities, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
+                                     int64_t position, int end_id, void* stream)
+{
+    ONN_CHECK_ARG(probabilities && ids && finished && B > 0 && S > 1 && V > 0 && position >= 0 && position + 1 < S && V < (1LL << 31));
+    greedy_next_token_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(probabilities, ids, finished, (int)S, (int)V, (int)position, end_id);
+    count_launch();
+    return launch_status();
+}
+
 extern "C" int onn_ce3d_count_active(const float* targets, int64_t rows, int64_t V, float* counts, void* stream)
 {
     ONN_CHECK_ARG(targets && counts && rows > 0 && V > 0);

@@ -463,6 +463,53 @@ extern "C" int onn_trainer_forward(onn_trainer* t, const float* decoder_ids, con
     });
 }
 
+extern "C" int onn_trainer_greedy_decode(onn_trainer* t, const float* encoder_ids, float* decoded_ids, int start_id, int end_id)
+{
+    if(!t || !encoder_ids || !decoded_ids || t->decoder_only) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        Device::instance().set_compute_stream(t->stream);
+        const Index B = t->micro_batch, S_in = t->input_sequence_length, S_dec = t->decoder_sequence_length;
+        if(t->staged_encoder.size() < B * S_in) t->staged_encoder.resize(B * S_in);
+        if(t->staged_decoder.size() < B * S_dec) { t->staged_decoder.resize(B * S_dec); t->staged_targets.resize(B * S_dec); }
+        TensorCuda finished_device;
+        finished_device.resize(B);                                  // zero-filled; read as int
+
+        // target ids start as [START, PAD, ...] (opennn/standard_networks.cpp:1002-1004)
+        vector<type> target(size_t(B * S_dec), type(0));
+        for(Index b = 0; b < B; b++) target[size_t(b * S_dec)] = type(start_id);
+        check_cuda(cudaMemcpyAsync(t->staged_encoder.data, encoder_ids, size_t(B * S_in) * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
+        check_cuda(cudaMemcpyAsync(t->staged_decoder.data, target.data(), target.size() * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
+        check_cuda(cudaStreamSynchronize(t->stream), "decode: ids");   // `target` is pageable host memory
+
+        BatchCuda batch;
+        batch.samples_number = B;
+        batch.decoder = TensorViewCuda(t->staged_decoder.data, {B, S_dec});
+        batch.input = TensorViewCuda(t->staged_encoder.data, {B, S_in});
+        // the reference re-runs the whole network for every token; the encoder side sees the same ids each time, so it
+        // runs once here and only the layers that depend on the decoder ids run per token
+        const vector<char> decoder_side = t->network->layers_depending_on_input(1);
+        vector<int> finished(size_t(B), 0);
+        for(Index i = 1; i < S_dec; i++)
+        {
+            t->network->forward_propagate(batch.get_inputs_device(), *t->forward, false, i == 1 ? nullptr : &decoder_side);
+            const TensorViewCuda outputs = t->forward->get_outputs();
+            check_onn(onn_greedy_next_token(outputs.data, t->staged_decoder.data, reinterpret_cast<int*>(finished_device.data), B, S_dec,
+                                            t->vocabulary_size, i - 1, end_id, t->stream), "greedy step");
+            if(i % 8 == 0 || i + 1 == S_dec)
+            {
+                check_cuda(cudaMemcpyAsync(finished.data(), finished_device.data, size_t(B) * sizeof(int), cudaMemcpyDeviceToHost, t->stream), "decode: flags");
+                check_cuda(cudaStreamSynchronize(t->stream), "decode: flags");
+                bool all = true;
+                for(const int f : finished) all = all && f != 0;
+                if(all) break;
+            }
+        }
+        check_cuda(cudaMemcpyAsync(decoded_ids, t->staged_decoder.data, size_t(B * S_dec) * sizeof(type), cudaMemcpyDeviceToHost, t->stream), "decode: ids D2H");
+        check_cuda(cudaStreamSynchronize(t->stream), "decode: ids D2H");
+    });
+}
+
 extern "C" int onn_trainer_get_layer_output(onn_trainer* t, int layer, float* host_output, int64_t count)
 {
     if(!t || !host_output || layer < 0 || layer >= int(t->network->get_layers_number())) return ONN_ERR_INVALID_ARGUMENT;

@@ -73,11 +73,22 @@ void NeuralNetwork::copy_parameters_host()
                "copy_parameters_host");
 }
 
-void NeuralNetwork::forward_propagate(const vector<TensorViewCuda>& input_views, ForwardPropagationCuda& forward_propagation, bool is_training)
+vector<char> NeuralNetwork::layers_depending_on_input(Index external) const
+{
+    vector<char> depends(layers.size(), 0);
+    for(size_t i = 0; i < layers.size(); i++)                  // layers are stored in topological order
+        for(const Index source : layer_input_indices[i])
+            if(source == -external || (source >= 0 && depends[size_t(source)])) depends[i] = 1;
+    return depends;
+}
+
+void NeuralNetwork::forward_propagate(const vector<TensorViewCuda>& input_views, ForwardPropagationCuda& forward_propagation, bool is_training,
+                                      const vector<char>* run_layer)
 {
     // neural_network.cpp:1889-1943: external input -k is input_views[k-1]
     for(size_t i = 0; i < layers.size(); i++)
     {
+        if(run_layer && !(*run_layer)[i]) continue;
         unique_ptr<LayerForwardPropagationCuda>& state = forward_propagation.layers[i];
         for(size_t port = 0; port < layer_input_indices[i].size(); port++)
         {

@@ -427,7 +427,12 @@ public:
 
     // neural_network.cpp:1889-1943.  input_views: {decoder ids, encoder ids} for the Transformer
     // (external input -1 = first, -2 = second: standard_networks.cpp:669-704).
-    void forward_propagate(const vector<TensorViewCuda>& input_views, ForwardPropagationCuda& forward_propagation, bool is_training);
+    // run_layer (optional, one flag per layer): layers whose flag is 0 keep the outputs of an earlier pass -- the decoding
+    // loop runs the encoder side once and only the layers that depend on the decoder ids afterwards
+    void forward_propagate(const vector<TensorViewCuda>& input_views, ForwardPropagationCuda& forward_propagation, bool is_training,
+                           const vector<char>* run_layer = nullptr);
+    // 1 for every layer whose output depends on external input number `external` (1 = decoder ids, 2 = encoder ids)
+    vector<char> layers_depending_on_input(Index external) const;
 
 protected:
     vector<unique_ptr<Layer>> layers;

@@ -483,6 +483,30 @@ def _encoder_block(net, S, E, H, F, source):
     return net.add("Normalization3d", S=S, E=E)
 
 
+def greedy_decode(net, arena, source_ids, S_dec, start=2, end=3):
+    """The decoding loop of opennn/standard_networks.cpp:1002-1035 on token ids (the tokeniser and the vocabulary
+    maps around it are not part of this path): the target starts as [START, PAD, ...]; step i runs the whole network
+    on it (inference: the last layer gives probabilities), takes the arg-max of the distribution at position i - 1
+    (first index on ties, opennn/tensor_utilities.cpp maximal_index) as token i and stops after END.  source_ids
+    [B, S_in]; every row is decoded independently.  Returns ids [B, S_dec] (PAD after END)."""
+    B = source_ids.shape[0]
+    target = np.zeros((B, S_dec), dtype=F32)
+    target[:, 0] = start
+    finished = np.zeros(B, dtype=bool)
+    for i in range(1, S_dec):
+        probabilities = net.forward(arena, {-1: target, -2: source_ids})
+        best = np.argmax(probabilities[:, i - 1, :], axis=-1)
+        for b in range(B):
+            if finished[b]:
+                continue
+            target[b, i] = best[b]
+            if best[b] == end:
+                finished[b] = True
+        if finished.all():
+            break
+    return target
+
+
 def build_transformer(S_in, S_dec, V_in, V_out, E, H, F, L):
     """opennn/standard_networks.cpp:638-907: post-norm encoder-decoder, 2 + 7L + 10L + 1 layers."""
     net = Network()

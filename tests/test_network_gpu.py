@@ -150,6 +150,46 @@ def test_micro_batches_match_one_batch(libs):
     assert_close(results[1][1], results[0][1], 1e-4, "gradient, 4 micro-batches vs 1")
 
 
+@pytest.mark.parametrize("gemm", ["simt", "auto"])
+def test_greedy_decode(libs, gemm):
+    """The decoding loop on token ids against the oracle's restatement of the reference loop: same tokens (fp32 GEMMs),
+    END stops a row and leaves PAD behind it, rows are independent.  With tf32 GEMMs a step may pick the other of two
+    nearly tied tokens; a row may then differ from the oracle only from a position where the oracle's two best
+    probabilities lie within 2e-3 of each other."""
+    from oracle import opennn_oracle as O
+    capi, trainer = libs
+    capi.check(capi.lib().onn_gemm_set_mode(1 if gemm == "simt" else 0))
+    name = "tiny_encdec_odd"
+    mode, B, S_in, S_dec, V_in, V_out, E, H, F, L, steps, seed, lo, hi = CONFIGS[name]
+    net, params, external, targets = network_inputs(name)
+    source = external[-2]
+    free_run = O.greedy_decode(net, params, source, S_dec, start=2, end=-1)          # no END: full-length rows
+    end_id = int(free_run[0, min(4, S_dec - 1)])                                      # make a token that really occurs the END
+    expected = O.greedy_decode(net, params, source, S_dec, start=2, end=end_id)
+    assert (expected[0] == 0).any(), "the chosen END must cut row 0 short"
+
+    t = make_trainer(trainer, name)
+    t.set_parameters(params)
+    decoded = t.greedy_decode(source, start_id=2, end_id=end_id)
+    t.close()
+    capi.check(capi.lib().onn_gemm_set_mode(0))
+    assert decoded.shape == expected.shape and (decoded[:, 0] == 2).all()
+    if gemm == "simt":
+        assert np.array_equal(decoded, expected)
+        return
+    for b in range(decoded.shape[0]):
+        differing = np.nonzero(decoded[b] != expected[b])[0]
+        if differing.size == 0:
+            continue
+        i = int(differing[0])                                                          # the rows agree up to token i - 1
+        prefix = np.zeros_like(expected)
+        prefix[:, 0] = 2
+        prefix[b, :i] = expected[b, :i]
+        distribution = net.forward(params, {-1: prefix, -2: source})[b, i - 1]
+        top = np.sort(distribution)[-2:]
+        assert top[1] - top[0] <= 2e-3 * top[1], f"row {b} leaves the oracle at token {i} without a near-tie"
+
+
 def test_int32_feed_matches_float_feed(libs):
     """Ids fed as int32 from pinned host memory (copy stream, two buffer sets, conversion on the device) give the very
     step the float feed gives, call after call."""
