@@ -97,6 +97,9 @@ typedef struct onn_gemm_args
     uint32_t* relu_bits_out;    /* optional [M, relu_bits_ld] words, see above; not with split_k or ONN_ACCUMULATE */
     const uint32_t* relu_bits;  /* optional [M, relu_bits_ld] words, see above; not with split_k */
     int64_t relu_bits_ld;       /* words per row of relu_bits_out / relu_bits */
+    int32_t k_parts;            /* 0 or 1 = none; P > 1: C = alpha * sum over p < P of opA(A + p * a_stride_part) * opB(B + p * */
+    int64_t a_stride_part;      /* b_stride_part) -- one product whose reduction runs through P operand pairs of equal     */
+    int64_t b_stride_part;      /* shape, e.g. dX = dQ Wq^T + dK Wk^T + dV Wv^T in one pass over dX.  Batch 1, no split_k. */
 } onn_gemm_args;
 
 int onn_gemm(const onn_gemm_args* args, void* stream);

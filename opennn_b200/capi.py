@@ -39,7 +39,8 @@ class GemmArgs(C.Structure):
                 ("c_stride_inner", C.c_int64), ("c_stride_outer", C.c_int64),
                 ("alpha", C.c_float), ("relu", C.c_int32), ("split_k", C.c_int32), ("flags", C.c_uint32),
                 ("colsum_out", C.c_void_p), ("colsum_stride_inner", C.c_int64),
-                ("relu_bits_out", C.c_void_p), ("relu_bits", C.c_void_p), ("relu_bits_ld", C.c_int64)]
+                ("relu_bits_out", C.c_void_p), ("relu_bits", C.c_void_p), ("relu_bits_ld", C.c_int64),
+                ("k_parts", C.c_int32), ("a_stride_part", C.c_int64), ("b_stride_part", C.c_int64)]
 
 
 class MhaParams(C.Structure):
@@ -117,7 +118,8 @@ def _empty(n, dtype=torch.float32):
 
 def gemm(A, B, Cmat, M, N, K, lda, ldb, ldc, a_major=0, b_major=1, bias=None, relu_mask=None, alpha=1.0,
          relu=False, split_k=0, flags=0, batch_inner=1, batch_outer=1, a_strides=(0, 0), b_strides=(0, 0), c_strides=(0, 0),
-         colsum_out=None, colsum_stride_inner=0, relu_bits_out=None, relu_bits=None, relu_bits_ld=0):
+         colsum_out=None, colsum_stride_inner=0, relu_bits_out=None, relu_bits=None, relu_bits_ld=0,
+         k_parts=0, part_strides=(0, 0)):
     g = GemmArgs()
     g.A, g.B, g.C = A.data_ptr(), B.data_ptr(), Cmat.data_ptr()
     g.bias = bias.data_ptr() if bias is not None else None
@@ -134,6 +136,8 @@ def gemm(A, B, Cmat, M, N, K, lda, ldb, ldc, a_major=0, b_major=1, bias=None, re
     g.relu_bits_out = relu_bits_out.data_ptr() if relu_bits_out is not None else None
     g.relu_bits = relu_bits.data_ptr() if relu_bits is not None else None
     g.relu_bits_ld = relu_bits_ld
+    g.k_parts = k_parts
+    g.a_stride_part, g.b_stride_part = part_strides
     check(lib().onn_gemm(C.byref(g), stream_ptr()), "onn_gemm")
 
 

@@ -45,6 +45,24 @@ int gemm(const onn_gemm_args& g, cudaStream_t stream)
     }
 
     const int mode = g_mode.load(std::memory_order_relaxed);
+    if(g.k_parts > 1)
+    {
+        ONN_CHECK_ARG(g.batch_inner == 1 && g.batch_outer == 1 && g.split_k <= 1);
+        ONN_CHECK_ARG(!g.relu && !g.relu_mask && !g.relu_bits && !g.relu_bits_out);
+        if(mode != 1 && gemm_tc_takes_parts(g)) return gemm_tc_launch(g, stream);
+        // anywhere else: one product per operand pair, the later ones added to the first
+        onn_gemm_args part = g;
+        part.k_parts = 0;
+        for(int p = 0; p < g.k_parts; p++)
+        {
+            part.A = g.A + p * g.a_stride_part;
+            part.B = g.B + p * g.b_stride_part;
+            if(p > 0) { part.flags |= ONN_ACCUMULATE; part.bias = nullptr; }
+            const int status = gemm(part, stream);
+            if(status != ONN_OK) return status;
+        }
+        return ONN_OK;
+    }
     const bool tc_ok = gemm_tc_supported(g);
     if(mode == 2 && !tc_ok) return ONN_ERR_UNSUPPORTED;
     if(mode != 1 && tc_ok) return gemm_tc_launch(g, stream);

@@ -11,6 +11,8 @@ int gemm_simt_launch(const onn_gemm_args& g, cudaStream_t stream);
 // tcgen05 (kind::tf32) path.  Needs 16-byte aligned bases, pitches and batch strides.
 bool gemm_tc_supported(const onn_gemm_args& g);
 int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream);
+// k_parts > 1: true when the two-CTA kernel can run the product in one launch (else the front end adds up P launches).
+bool gemm_tc_takes_parts(const onn_gemm_args& g);
 int gemm_tc_read_status();
 int gemm_tc_bounded_wait_selftest(int* gave_up_host);
 

@@ -78,6 +78,7 @@ struct Params
     int batch_inner, batch_outer;
     int a_batch_inner_on, a_batch_outer_on, b_batch_inner_on, b_batch_outer_on, c_batch_inner_on, c_batch_outer_on;
     int a_wide, b_wide;                                    // MN-major operand loaded with one 5-D box per stage
+    int k_parts, k_part_blocks;                            // reduction through k_parts operand pairs of k_part_blocks k-blocks each (two-CTA kernel)
     int splits;
     long long k_per_split;                                 // multiple of BK
     int m_blocks, n_blocks;
@@ -639,12 +640,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t bar = map_to_cta(smem_u32(full_bar + stage), 0);      // the leader's barrier
                     const uint32_t a_dst = smem_u32(smem + (size_t)stage * STAGE2_BYTES);
                     const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-                    const int k0 = (int)(it.k_begin + (long long)kb * BK);
+                    // with several operand pairs the reduction index runs through them one after the other; the pair is the
+                    // third coordinate of both maps
+                    const int k_block = (int)(it.k_begin / BK) + kb;
+                    const int part = p.k_parts > 1 ? k_block / p.k_part_blocks : 0;
+                    const int k0 = (p.k_parts > 1 ? k_block % p.k_part_blocks : k_block) * BK;
                     if(leader) mbar_arrive_expect_tx(smem_u32(full_bar + stage), 2 * STAGE2_BYTES);
-                    if(A_MN) tma2_load_5d(a_dst, &map_a, bar, 0, k0, m0 / 32, 0, 0);
-                    else tma2_load_4d(a_dst, &map_a, bar, k0, m0, 0, 0);
-                    if(B_MN) tma2_load_5d(b_dst, &map_b, bar, 0, k0, n0 / 32, 0, 0);
-                    else tma2_load_4d(b_dst, &map_b, bar, k0, n0, 0, 0);
+                    if(A_MN) tma2_load_5d(a_dst, &map_a, bar, 0, k0, m0 / 32, part, 0);
+                    else tma2_load_4d(a_dst, &map_a, bar, k0, m0, part, 0);
+                    if(B_MN) tma2_load_5d(b_dst, &map_b, bar, 0, k0, n0 / 32, part, 0);
+                    else tma2_load_4d(b_dst, &map_b, bar, k0, n0, part, 0);
                     if(++stage == STAGES2) { stage = 0; phase ^= 1; }
                 }
             }
@@ -920,13 +925,29 @@ bool gemm_tc_supported(const onn_gemm_args& g)
     return tc::encode_tiled() != nullptr;
 }
 
+static bool pair_kernel_takes(const onn_gemm_args& g)
+{
+    static const bool pair_enabled = []{ const char* e = std::getenv("ONN_B200_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    return pair_enabled && g.batch_inner == 1 && g.batch_outer == 1 && g.M >= 512 && g.N >= 256 &&
+           (g.a_major == 0 || g.M % 32 == 0) && (g.b_major == 0 || g.N % 32 == 0);
+}
+
+bool gemm_tc_takes_parts(const onn_gemm_args& g)
+{
+    using tc::mult4;
+    return gemm_tc_supported(g) && pair_kernel_takes(g) && g.K % tc::BK == 0 && g.a_stride_part != 0 && g.b_stride_part != 0 &&
+           mult4(g.a_stride_part) && mult4(g.b_stride_part);
+}
+
 int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
 {
     using namespace tc;
     const int bn = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
 
+    const int parts = g.k_parts > 1 ? g.k_parts : 1;
     Params p;
-    p.M = g.M; p.N = g.N; p.K = g.K; p.ldc = g.ldc;
+    p.M = g.M; p.N = g.N; p.K = g.K * parts; p.ldc = g.ldc;
+    p.k_parts = parts; p.k_part_blocks = (int)(g.K / BK);
     p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
     p.C = g.C; p.bias = g.bias; p.relu_mask = g.relu_mask; p.alpha = g.alpha;
     p.relu_bits_out = g.relu_bits_out; p.relu_bits = g.relu_bits; p.relu_bits_ld = g.relu_bits_ld;
@@ -941,7 +962,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.a_wide = g.a_major == 1 && g.M % 32 == 0;
     p.b_wide = g.b_major == 1 && g.N % 32 == 0;
 
-    const long long k_blocks = (g.K + BK - 1) / BK;
+    const long long k_blocks = (p.K + BK - 1) / BK;
     long long splits = g.split_k > 1 ? g.split_k : 1;
     if(splits > k_blocks) splits = k_blocks;
     const long long blocks_per_split = (k_blocks + splits - 1) / splits;
@@ -956,9 +977,8 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     bool ok;
 
     // large single GEMMs go to the two-CTA kernel (256 x 256 tiles per CTA pair)
-    static const bool pair_enabled = []{ const char* e = std::getenv("ONN_B200_GEMM_PAIR"); return !(e && e[0] == '0'); }();
-    const bool pair = pair_enabled && g.batch_inner == 1 && g.batch_outer == 1 && g.M >= 512 && g.N >= 256 &&
-                      (g.a_major == 0 || p.a_wide) && (g.b_major == 0 || p.b_wide);
+    const bool pair = pair_kernel_takes(g);
+    if(!pair && parts > 1) return ONN_ERR_UNSUPPORTED;       // the front end only sends operand pairs the two-CTA kernel takes
     if(pair)
     {
         p.m_blocks = (int)((g.M + 255) / 256);
@@ -983,10 +1003,10 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
                 p.total_work = tiles + tail;
             }
         }
-        if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, 1, 0, 1, 0, BK, BM, false);
-        else ok = make_wide_map(&map_a, g.A, g.M, g.K, g.lda, 1, 0, 1, 0, BM / 32, BK);
-        if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, 1, 0, 1, 0, BK, 128, false);
-        else ok = ok && make_wide_map(&map_b, g.B, g.N, g.K, g.ldb, 1, 0, 1, 0, 128 / 32, BK);
+        if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, parts, g.a_stride_part, 1, 0, BK, BM, false);
+        else ok = make_wide_map(&map_a, g.A, g.M, g.K, g.lda, parts, g.a_stride_part, 1, 0, BM / 32, BK);
+        if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, parts, g.b_stride_part, 1, 0, BK, 128, false);
+        else ok = ok && make_wide_map(&map_b, g.B, g.N, g.K, g.ldb, parts, g.b_stride_part, 1, 0, 128 / 32, BK);
         ok = ok && make_map(&map_c, g.C, g.N, g.M, g.ldc, 1, 0, 1, 0, 32, 32, false, false);
         if(!ok) return ONN_ERR_UNSUPPORTED;
         if(g.a_major == 0 && g.b_major == 0) return launch_pair_variant<0, 0>(map_a, map_b, map_c, p, stream);

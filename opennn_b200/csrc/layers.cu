@@ -350,18 +350,41 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
     ONN_TRY(weight_gradients(Xs, dk, grads->dWk, nullptr, rows_s, E, E, s));
     ONN_TRY(weight_gradients(Xs, dv, grads->dWv, nullptr, rows_s, E, E, s));
 
+    // Input gradients.  Where the operand pairs lie at equal distances (dQ, dK, dV in the scratch arena; Wq, Wk, Wv in
+    // the parameter arena) the sum dQ Wq^T + dK Wk^T + dV Wv^T is ONE product whose reduction runs through the pairs:
+    // one pass over the result instead of a store and two read-modify-write passes.
+    const long long kv_step = dv - dk, w_kv_step = Wv - Wk;                 // between the key and value operand pairs
+    const bool pair_kv = kv_step > 0 && w_kv_step > 0;
+    const bool triple = pair_kv && dk - dq == kv_step && Wk - Wq == w_kv_step; // and the same again from query to key
+    float* source_grad = self_attention ? dXq : dXs;
+    if(self_attention && triple)
     {
         onn_gemm_args g = plain_gemm(dq, 0, E, Wq, 0, E, dXq, E, rows_q, E, E);
+        g.k_parts = 3; g.a_stride_part = kv_step; g.b_stride_part = w_kv_step;
         ONN_TRY(gemm(g, s));
     }
-    float* source_grad = self_attention ? dXq : dXs;
+    else
     {
-        onn_gemm_args g = plain_gemm(dk, 0, E, Wk, 0, E, source_grad, E, rows_s, E, E);
-        if(self_attention || (flags & ONN_ACCUMULATE)) g.flags = ONN_ACCUMULATE;
-        ONN_TRY(gemm(g, s));
-        g = plain_gemm(dv, 0, E, Wv, 0, E, source_grad, E, rows_s, E, E);
-        g.flags = ONN_ACCUMULATE;
-        ONN_TRY(gemm(g, s));
+        {
+            onn_gemm_args g = plain_gemm(dq, 0, E, Wq, 0, E, dXq, E, rows_q, E, E);
+            ONN_TRY(gemm(g, s));
+        }
+        if(pair_kv)
+        {
+            onn_gemm_args g = plain_gemm(dk, 0, E, Wk, 0, E, source_grad, E, rows_s, E, E);
+            g.k_parts = 2; g.a_stride_part = kv_step; g.b_stride_part = w_kv_step;
+            if(self_attention || (flags & ONN_ACCUMULATE)) g.flags = ONN_ACCUMULATE;
+            ONN_TRY(gemm(g, s));
+        }
+        else
+        {
+            onn_gemm_args g = plain_gemm(dk, 0, E, Wk, 0, E, source_grad, E, rows_s, E, E);
+            if(self_attention || (flags & ONN_ACCUMULATE)) g.flags = ONN_ACCUMULATE;
+            ONN_TRY(gemm(g, s));
+            g = plain_gemm(dv, 0, E, Wv, 0, E, source_grad, E, rows_s, E, E);
+            g.flags = ONN_ACCUMULATE;
+            ONN_TRY(gemm(g, s));
+        }
     }
     return ONN_OK;
 }

@@ -382,6 +382,33 @@ def test_gemm_split_tail_wave(capi, a_major, b_major, M):
     assert capi.lib().onn_gemm_device_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(1024, 512, 128), (300, 72, 40), (4864, 1024, 256)])
+def test_gemm_reduction_through_operand_pairs(capi, gemm_mode, shape):
+    """C = sum over p of A_p B_p^T for three operand pairs at equal distances (how dX = dQ Wq^T + dK Wk^T + dV Wv^T is
+    computed): one launch of the two-CTA kernel where it applies, a store and two accumulating launches elsewhere."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N)
+    a_gap, b_gap = M * K + 64, N * K + 8                        # the pairs need not be contiguous
+    A = rng.standard_normal((3, M, K)).astype(np.float32)
+    B = (rng.standard_normal((3, N, K)) / np.sqrt(3 * K)).astype(np.float32)
+    A_store = torch.zeros(3 * a_gap, device="cuda")
+    B_store = torch.zeros(3 * b_gap, device="cuda")
+    for part in range(3):
+        A_store[part * a_gap:part * a_gap + M * K] = dev(A[part]).reshape(-1)
+        B_store[part * b_gap:part * b_gap + N * K] = dev(B[part]).reshape(-1)
+    reference = sum(A[part].astype(np.float64) @ B[part].astype(np.float64).T for part in range(3))
+    bias = rng.standard_normal(N).astype(np.float32)
+    out = torch.full((M, N), 5.0, device="cuda")
+    capi.gemm(A_store, B_store, out, M, N, K, K, K, N, 0, 0, bias=dev(bias), k_parts=3, part_strides=(a_gap, b_gap))
+    assert_close(host(out), reference + bias, TOL, "three operand pairs")
+    start = rng.standard_normal((M, N)).astype(np.float32)
+    out = dev(start)
+    capi.gemm(A_store, B_store, out, M, N, K, K, K, N, 0, 0, flags=capi.ACCUMULATE, k_parts=2, part_strides=(a_gap, b_gap))
+    two = sum(A[part].astype(np.float64) @ B[part].astype(np.float64).T for part in range(2))
+    assert_close(host(out), start + two, TOL, "two operand pairs, accumulated")
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
 def test_gemm_batched_heads(capi, gemm_mode):
     """Per-(batch, head) products addressed by strides inside [B, S, E] tensors, as attention uses them."""
     Bn, H, Sq, Sk, hd = 3, 4, 40, 72, 16
