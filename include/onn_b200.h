@@ -335,6 +335,21 @@ int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_co
  * finished[b] is set; finished[b] is set when that token is end_id. */
 int onn_greedy_next_token(const float* probabilities, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
                           int64_t position, int end_id, void* stream);
+/* The same step when only the current position was computed: probabilities is [B, V] and the token goes to
+ * ids[b, write_position]. */
+int onn_greedy_next_token_rows(const float* probabilities, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
+                               int64_t write_position, int end_id, void* stream);
+
+/* Attention of ONE query row per sample against keys and values kept from earlier decoding steps (no counterpart in
+ * the reference, whose decoding loop recomputes every position for every token): q [B, E] (projected), k_cache and
+ * v_cache [B, S_cache, E] of which the first `length` rows are valid, key_is_pad [B, S_cache] bytes or NULL (a set flag
+ * overwrites the score with -1e9 as in onn_mha_fwd), out [B, E] = concatenated head outputs before the output
+ * projection.  Scale 1/sqrt(E/H).  fp32 throughout. */
+int onn_decode_attention(const float* q, const float* k_cache, const float* v_cache, const uint8_t* key_is_pad, float* out,
+                         int64_t B, int64_t S_cache, int64_t length, int64_t E, int64_t H, void* stream);
+/* flags[r] = 1 where every feature of row r has |x| <= 1e-7: the key-padding rule of MultiHeadAttention
+ * (opennn/multihead_attention_layer.cpp:574-603) for a caller that keeps its own key cache. */
+int onn_rows_are_zero(const float* X, uint8_t* flags, int64_t rows, int64_t E, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * AdaptiveMomentEstimation.  Replaces adam_update_kernel (opennn/kernel.cu:6-68) and adds

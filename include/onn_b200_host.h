@@ -92,6 +92,11 @@ int onn_trainer_forward(onn_trainer* trainer, const float* decoder_ids, const fl
  * [start_id, token 1, ..., end_id, PAD ...].  The encoder side runs once, the decoder side once per token, the
  * arg-max stays on the device (onn_greedy_next_token); there is no key/value cache. */
 int onn_trainer_greedy_decode(onn_trainer* trainer, const float* encoder_ids, float* decoded_ids, int start_id, int end_id);
+/* The same decoding with cached keys and values: the encoder side runs once, every decoder-side layer then sees ONE
+ * target position per token ([micro_batch, 1, features]); self-attention layers append that position's key and value
+ * rows to a cache and attend over it (onn_decode_attention), cross-attention layers attend over keys and values
+ * projected once from the encoder output.  Work per token is O(length) instead of O(length^2). */
+int onn_trainer_greedy_decode_cached(onn_trainer* trainer, const float* encoder_ids, float* decoded_ids, int start_id, int end_id);
 int onn_trainer_get_layer_output(onn_trainer* trainer, int layer, float* host_output, int64_t count);
 int onn_trainer_synchronize(onn_trainer* trainer);
 /* The cudaStream_t every kernel of this trainer is launched on (for event timing by the caller). */

@@ -688,16 +688,16 @@ extern "C" int onn_softmax_rows(float* Y, int64_t rows, int64_t cols, void* stre
     return launch_status();
 }
 
-// Greedy decoding step: per sample the arg-max (first index on ties) of the distribution at `position`, written as a
-// float id into ids[b, position + 1] unless the sample already produced END; finished[b] is set on END.
+// Greedy decoding step: per sample the arg-max (first index on ties) of one distribution, written as a float id into
+// the sample's id row unless the sample already produced END; finished[b] is set on END.
 __global__ void __launch_bounds__(256)
-greedy_next_token_kernel(const float* __restrict__ probabilities, float* __restrict__ ids, int* __restrict__ finished,
-                         int S, int V, int position, int end_id)
+greedy_next_token_kernel(const float* __restrict__ probabilities, long long sample_stride, float* __restrict__ ids, long long ids_stride,
+                         int write_position, int* __restrict__ finished, int V, int end_id)
 {
     __shared__ float best_value[256];
     __shared__ int best_index[256];
     const int b = blockIdx.x;
-    const float* row = probabilities + ((long long)b * S + position) * V;
+    const float* row = probabilities + (long long)b * sample_stride;
     float value = -INFINITY;
     int index = 0x7fffffff;
     for(int k = threadIdx.x; k < V; k += blockDim.x)
@@ -722,7 +722,7 @@ greedy_next_token_kernel(const float* __restrict__ probabilities, float* __restr
     if(threadIdx.x == 0 && !finished[b])
     {
         const int token = best_index[0] == 0x7fffffff ? 0 : best_index[0];
-        ids[(long long)b * S + position + 1] = (float)token;
+        ids[(long long)b * ids_stride + write_position] = (float)token;
         if(token == end_id) finished[b] = 1;
     }
 }
@@ -731,9 +731,95 @@ extern "C" int onn_greedy_next_token(const float* probabilities, float* ids, int
                                      int64_t position, int end_id, void* stream)
 {
     ONN_CHECK_ARG(probabilities && ids && finished && B > 0 && S > 1 && V > 0 && position >= 0 && position + 1 < S && V < (1LL << 31));
-    greedy_next_token_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(probabilities, ids, finished, (int)S, (int)V, (int)position, end_id);
+    greedy_next_token_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(probabilities + position * V, S * V, ids, S, (int)position + 1,
+                                                                             finished, (int)V, end_id);
     count_launch();
     return launch_status();
+}
+
+extern "C" int onn_greedy_next_token_rows(const float* probabilities, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
+                                          int64_t write_position, int end_id, void* stream)
+{
+    ONN_CHECK_ARG(probabilities && ids && finished && B > 0 && S > 1 && V > 0 && write_position > 0 && write_position < S && V < (1LL << 31));
+    greedy_next_token_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(probabilities, V, ids, S, (int)write_position, finished, (int)V, end_id);
+    count_launch();
+    return launch_status();
+}
+
+// One query row per (sample, head) against the keys and values cached so far: scores, softmax and weighted sum in one
+// warp.  Lanes own keys for the scores (each a full dot product over the head) and head features for the output.
+__global__ void __launch_bounds__(128)
+decode_attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache, const float* __restrict__ v_cache,
+                        const uint8_t* __restrict__ key_is_pad, float* __restrict__ out,
+                        int B, int H, int S_cache, int length, int E, float scale)
+{
+    extern __shared__ float shared[];                          // per warp: hd query values, then `length` scores
+    const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
+    const int hd = E / H;
+    const long long item = (long long)blockIdx.x * 4 + warp_in_block;
+    if(item >= (long long)B * H) return;
+    const int b = (int)(item / H), h = (int)(item % H);
+    float* q_shared = shared + (size_t)warp_in_block * (hd + S_cache);
+    float* scores = q_shared + hd;
+    const float* q_row = q + (long long)b * E + h * hd;
+    for(int d = lane; d < hd; d += 32) q_shared[d] = q_row[d];
+    __syncwarp();
+
+    float row_max = -INFINITY;
+    for(int j = lane; j < length; j += 32)
+    {
+        const float* k_row = k_cache + ((long long)b * S_cache + j) * E + h * hd;
+        float dot = 0.f;
+        for(int d = 0; d < hd; d++) dot = fmaf(q_shared[d], k_row[d], dot);
+        float s = dot * scale;
+        if(key_is_pad && key_is_pad[(long long)b * S_cache + j]) s = -1e9f;     // overwrite, as the training path
+        scores[j] = s;
+        row_max = fmaxf(row_max, s);
+    }
+    row_max = warp_max(row_max);
+    float total = 0.f;
+    for(int j = lane; j < length; j += 32)
+    {
+        const float e = __expf(scores[j] - row_max);
+        scores[j] = e;
+        total += e;
+    }
+    total = warp_sum(total);
+    const float inv = total > 0.f ? 1.0f / total : 0.f;
+    __syncwarp();
+    for(int d = lane; d < hd; d += 32)
+    {
+        float acc = 0.f;
+        for(int j = 0; j < length; j++) acc = fmaf(scores[j], v_cache[((long long)b * S_cache + j) * E + h * hd + d], acc);
+        out[(long long)b * E + h * hd + d] = acc * inv;
+    }
+}
+
+extern "C" int onn_decode_attention(const float* q, const float* k_cache, const float* v_cache, const uint8_t* key_is_pad, float* out,
+                                    int64_t B, int64_t S_cache, int64_t length, int64_t E, int64_t H, void* stream)
+{
+    ONN_CHECK_ARG(q && k_cache && v_cache && out && B > 0 && H > 0 && E > 0 && E % H == 0 && length > 0 && length <= S_cache);
+    const int hd = (int)(E / H);
+    const size_t shared = 4 * (size_t)(hd + S_cache) * sizeof(float);
+    if(shared > 200 * 1024) return ONN_ERR_UNSUPPORTED;
+    static size_t configured = 48 * 1024;
+    if(shared > configured)
+    {
+        if(cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess) return ONN_ERR_CUDA;
+        configured = shared;
+    }
+    const long long items = B * H;
+    decode_attention_kernel<<<(unsigned)((items + 3) / 4), 128, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, out, (int)B, (int)H,
+                                                                                             (int)S_cache, (int)length, (int)E,
+                                                                                             1.0f / sqrtf((float)hd));
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int onn_rows_are_zero(const float* X, uint8_t* flags, int64_t rows, int64_t E, void* stream)
+{
+    ONN_CHECK_ARG(X && flags && rows > 0 && E > 0 && E < (1LL << 31));
+    return launch_source_row_is_zero(X, flags, rows, (int)E, (cudaStream_t)stream);
 }
 
 extern "C" int onn_ce3d_count_active(const float* targets, int64_t rows, int64_t V, float* counts, void* stream)

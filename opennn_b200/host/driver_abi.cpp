@@ -24,6 +24,7 @@ struct onn_trainer
     unique_ptr<ForwardPropagationCuda> forward;
     unique_ptr<BackPropagationCuda> back;
     unique_ptr<ADAMOptimizationDataCuda> optimization;
+    unique_ptr<IncrementalDecoder> decoder;             // created by the first cached decode
 
     bool decoder_only = false;
     Index micro_batch = 0, input_sequence_length = 0, decoder_sequence_length = 0, vocabulary_size = 0;
@@ -496,6 +497,55 @@ extern "C" int onn_trainer_greedy_decode(onn_trainer* t, const float* encoder_id
             const TensorViewCuda outputs = t->forward->get_outputs();
             check_onn(onn_greedy_next_token(outputs.data, t->staged_decoder.data, reinterpret_cast<int*>(finished_device.data), B, S_dec,
                                             t->vocabulary_size, i - 1, end_id, t->stream), "greedy step");
+            if(i % 8 == 0 || i + 1 == S_dec)
+            {
+                check_cuda(cudaMemcpyAsync(finished.data(), finished_device.data, size_t(B) * sizeof(int), cudaMemcpyDeviceToHost, t->stream), "decode: flags");
+                check_cuda(cudaStreamSynchronize(t->stream), "decode: flags");
+                bool all = true;
+                for(const int f : finished) all = all && f != 0;
+                if(all) break;
+            }
+        }
+        check_cuda(cudaMemcpyAsync(decoded_ids, t->staged_decoder.data, size_t(B * S_dec) * sizeof(type), cudaMemcpyDeviceToHost, t->stream), "decode: ids D2H");
+        check_cuda(cudaStreamSynchronize(t->stream), "decode: ids D2H");
+    });
+}
+
+extern "C" int onn_trainer_greedy_decode_cached(onn_trainer* t, const float* encoder_ids, float* decoded_ids, int start_id, int end_id)
+{
+    if(!t || !encoder_ids || !decoded_ids || t->decoder_only) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        Device::instance().set_compute_stream(t->stream);
+        const Index B = t->micro_batch, S_in = t->input_sequence_length, S_dec = t->decoder_sequence_length;
+        if(t->staged_encoder.size() < B * S_in) t->staged_encoder.resize(B * S_in);
+        if(t->staged_decoder.size() < B * S_dec) { t->staged_decoder.resize(B * S_dec); t->staged_targets.resize(B * S_dec); }
+        TensorCuda finished_device;
+        finished_device.resize(B);
+
+        vector<type> target(size_t(B * S_dec), type(0));
+        for(Index b = 0; b < B; b++) target[size_t(b * S_dec)] = type(start_id);
+        check_cuda(cudaMemcpyAsync(t->staged_encoder.data, encoder_ids, size_t(B * S_in) * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
+        check_cuda(cudaMemcpyAsync(t->staged_decoder.data, target.data(), target.size() * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
+        check_cuda(cudaStreamSynchronize(t->stream), "decode: ids");
+
+        // encoder side once, through the ordinary forward pass
+        BatchCuda batch;
+        batch.samples_number = B;
+        batch.decoder = TensorViewCuda(t->staged_decoder.data, {B, S_dec});
+        batch.input = TensorViewCuda(t->staged_encoder.data, {B, S_in});
+        vector<char> encoder_side = t->network->layers_depending_on_input(1);
+        for(char& flag : encoder_side) flag = !flag;
+        t->network->forward_propagate(batch.get_inputs_device(), *t->forward, false, &encoder_side);
+
+        if(!t->decoder) t->decoder = std::make_unique<IncrementalDecoder>(t->network.get(), t->forward.get(), B);
+        t->decoder->start();
+        vector<int> finished(size_t(B), 0);
+        for(Index i = 1; i < S_dec; i++)
+        {
+            const type* probabilities = t->decoder->step(t->staged_decoder.data, S_dec, i - 1);
+            check_onn(onn_greedy_next_token_rows(probabilities, t->staged_decoder.data, reinterpret_cast<int*>(finished_device.data), B, S_dec,
+                                                 t->vocabulary_size, i, end_id, t->stream), "greedy step");
             if(i % 8 == 0 || i + 1 == S_dec)
             {
                 check_cuda(cudaMemcpyAsync(finished.data(), finished_device.data, size_t(B) * sizeof(int), cudaMemcpyDeviceToHost, t->stream), "decode: flags");

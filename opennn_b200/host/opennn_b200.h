@@ -163,8 +163,11 @@ protected:
 // Embedding (opennn/embedding_layer.h)
 // ---------------------------------------------------------------------------------------
 
+class IncrementalDecoder;
+
 class Embedding final : public Layer
 {
+    friend class IncrementalDecoder;
 public:
     Embedding(const Shape& input_shape = {0, 0}, Index embedding_dimension = 0, const string& label = "embedding_layer");
 
@@ -214,6 +217,7 @@ struct EmbeddingBackPropagationCuda final : LayerBackPropagationCuda
 
 class MultiHeadAttention final : public Layer
 {
+    friend class IncrementalDecoder;
 public:
     MultiHeadAttention(const Shape& query_shape = {0, 0}, Index heads_number = 0, const string& label = "multihead_attention_layer");
     MultiHeadAttention(const Shape& query_shape, const Shape& source_shape, Index heads_number, const string& label = "multihead_attention_layer");
@@ -272,6 +276,7 @@ struct MultiHeadAttentionBackPropagationCuda final : LayerBackPropagationCuda
 
 class Dense3d final : public Layer
 {
+    friend class IncrementalDecoder;
 public:
     Dense3d(Index sequence_length, Index input_features, Index neurons, const string& activation, const string& label);
 
@@ -326,6 +331,7 @@ struct Dense3dBackPropagationCuda final : LayerBackPropagationCuda
 
 class Normalization3d final : public Layer
 {
+    friend class IncrementalDecoder;
 public:
     Normalization3d(const Shape& input_shape = {0, 0}, const string& label = "normalization_layer_3d");
 
@@ -594,6 +600,40 @@ public:
 private:
     CrossEntropyError3d* loss = nullptr;
     type learning_rate = type(0.001), beta_1 = type(0.9), beta_2 = type(0.999), gradient_clip_norm = type(1.0);   // .h:86-92
+};
+
+
+// ---------------------------------------------------------------------------------------
+// Decoding one token at a time with cached keys and values.  Transformer::calculate_outputs
+// (opennn/standard_networks.cpp:1002-1035) runs the whole network on the whole target for every new
+// token; here the encoder side runs once, each decoder-side layer sees ONE position per step
+// ([batch, 1, features]), self-attention layers append that position's key and value rows to a
+// cache and attend over it (causality is what the cache holds), cross-attention layers attend over
+// keys and values projected once from the encoder output.
+// ---------------------------------------------------------------------------------------
+
+class IncrementalDecoder
+{
+public:
+    IncrementalDecoder(NeuralNetwork* network, ForwardPropagationCuda* forward_propagation, Index batch_size);
+
+    // After the encoder side has been run by NeuralNetwork::forward_propagate (its outputs are in
+    // forward_propagation): projects the cross-attention keys and values and clears the self-attention caches.
+    void start();
+    // Feeds the decoder ids of `position` (device, one float per sample at ids[b * ids_stride + position]) through the
+    // decoder side and returns the device pointer of the last layer's output for that position: [batch, vocabulary].
+    const type* step(const type* ids, Index ids_stride, Index position);
+
+private:
+    struct AttentionCache { TensorCuda keys, values, key_is_pad; Index capacity = 0; };
+
+    NeuralNetwork* network = nullptr;
+    ForwardPropagationCuda* forward_propagation = nullptr;
+    Index batch_size = 0;
+    vector<char> decoder_side;
+    vector<unique_ptr<TensorCuda>> outputs;       // per decoder-side layer: [batch, width] of the current position
+    vector<unique_ptr<AttentionCache>> caches;    // per decoder-side MultiHeadAttention layer
+    TensorCuda query, context, step_ids;
 };
 
 }  // namespace opennn_b200

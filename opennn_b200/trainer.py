@@ -24,7 +24,7 @@ HOST_EXPORTS = [
     "onn_trainer_get_gradients", "onn_trainer_set_learning_rate", "onn_trainer_set_iteration", "onn_trainer_set_dp",
     "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_step_host_i32", "onn_trainer_forward", "onn_trainer_get_layer_output",
     "onn_trainer_synchronize", "onn_trainer_stream", "onn_trainer_set_graph_capture",
-    "onn_trainer_greedy_decode",
+    "onn_trainer_greedy_decode", "onn_trainer_greedy_decode_cached",
 ]
 
 _host = None
@@ -149,12 +149,13 @@ class Trainer:
     def forward(self, dec_ids, enc_ids, is_training=False):
         _check(host_lib().onn_trainer_forward(self._handle, capi.ptr(dec_ids), capi.ptr(enc_ids), int(is_training)), "forward")
 
-    def greedy_decode(self, encoder_ids, start_id=2, end_id=3):
-        """encoder_ids: float32 numpy [micro_batch, S_in]; returns float32 numpy [micro_batch, S_dec]."""
+    def greedy_decode(self, encoder_ids, start_id=2, end_id=3, cached=False):
+        """encoder_ids: float32 numpy [micro_batch, S_in]; returns float32 numpy [micro_batch, S_dec].
+        cached=True decodes one position per step with cached keys and values."""
         encoder_ids = np.ascontiguousarray(encoder_ids, dtype=np.float32)
         decoded = np.zeros((encoder_ids.shape[0], self.S_dec), dtype=np.float32)
-        _check(host_lib().onn_trainer_greedy_decode(self._handle, _f32_ptr(encoder_ids), _f32_ptr(decoded), int(start_id), int(end_id)),
-               "greedy_decode")
+        entry = host_lib().onn_trainer_greedy_decode_cached if cached else host_lib().onn_trainer_greedy_decode
+        _check(entry(self._handle, _f32_ptr(encoder_ids), _f32_ptr(decoded), int(start_id), int(end_id)), "greedy_decode")
         return decoded
 
     def layer_output(self, i, count=None):

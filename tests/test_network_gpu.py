@@ -171,23 +171,28 @@ def test_greedy_decode(libs, gemm):
     t = make_trainer(trainer, name)
     t.set_parameters(params)
     decoded = t.greedy_decode(source, start_id=2, end_id=end_id)
+    cached = t.greedy_decode(source, start_id=2, end_id=end_id, cached=True)     # one position per step, keys and values cached
+    cached_again = t.greedy_decode(source, start_id=2, end_id=end_id, cached=True)
     t.close()
     capi.check(capi.lib().onn_gemm_set_mode(0))
     assert decoded.shape == expected.shape and (decoded[:, 0] == 2).all()
+    assert np.array_equal(cached, cached_again), "the caches must start clean"
     if gemm == "simt":
         assert np.array_equal(decoded, expected)
+        assert np.array_equal(cached, expected)
         return
-    for b in range(decoded.shape[0]):
-        differing = np.nonzero(decoded[b] != expected[b])[0]
-        if differing.size == 0:
-            continue
-        i = int(differing[0])                                                          # the rows agree up to token i - 1
-        prefix = np.zeros_like(expected)
-        prefix[:, 0] = 2
-        prefix[b, :i] = expected[b, :i]
-        distribution = net.forward(params, {-1: prefix, -2: source})[b, i - 1]
-        top = np.sort(distribution)[-2:]
-        assert top[1] - top[0] <= 2e-3 * top[1], f"row {b} leaves the oracle at token {i} without a near-tie"
+    for decoded in (decoded, cached):
+      for b in range(decoded.shape[0]):
+          differing = np.nonzero(decoded[b] != expected[b])[0]
+          if differing.size == 0:
+              continue
+          i = int(differing[0])                                                          # the rows agree up to token i - 1
+          prefix = np.zeros_like(expected)
+          prefix[:, 0] = 2
+          prefix[b, :i] = expected[b, :i]
+          distribution = net.forward(params, {-1: prefix, -2: source})[b, i - 1]
+          top = np.sort(distribution)[-2:]
+          assert top[1] - top[0] <= 2e-3 * top[1], f"row {b} leaves the oracle at token {i} without a near-tie"
 
 
 def test_int32_feed_matches_float_feed(libs):
