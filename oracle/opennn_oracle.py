@@ -271,6 +271,23 @@ def mha_backward(xq, xs, p, H, saved, d_y, self_attention):
 
 
 # --------------------------------------------------------------------------------------
+# CrossEntropyError2d (several classes)
+# --------------------------------------------------------------------------------------
+
+def ce2d_error(probabilities, targets):
+    """opennn/cross_entropy_error.cpp:58-77: -sum(t * log(y + eps)) / samples, eps = FLT_EPSILON."""
+    samples = probabilities.shape[0]
+    terms = (targets * np.log(probabilities + EPSILON)).astype(F32)
+    return F32(terms.sum(dtype=F32) / F32(-samples))
+
+
+def ce2d_output_gradients(probabilities, targets):
+    """opennn/cross_entropy_error.cpp:114-134: (y - t) / samples -- the softmax Jacobian is folded in, the Softmax
+    Dense layer passes it on unchanged (dense_layer.h:834-840)."""
+    return ((probabilities - targets) / F32(probabilities.shape[0])).astype(F32)
+
+
+# --------------------------------------------------------------------------------------
 # CrossEntropyError3d
 # --------------------------------------------------------------------------------------
 
@@ -341,6 +358,8 @@ PARAMETER_SHAPES = {
     "Addition3d": lambda l: [],
     "Normalization3d": lambda l: [("gammas", (l["E"],)), ("betas", (l["E"],))],  # normalization_layer_3d.cpp:49
     "Dense3d": lambda l: [("biases", (l["out"],)), ("weights", (l["in"], l["out"]))],  # dense_layer.h:484
+    "Dense2d": lambda l: [("biases", (l["out"],)), ("weights", (l["in"], l["out"]))],  # the same template, rank 2
+    "Pooling3d": lambda l: [],
 }
 
 
@@ -394,7 +413,7 @@ class Network:
                     v[name][:] = rng.uniform(-0.1, 0.1, v[name].shape).astype(F32)
             elif kind == "Normalization3d":
                 v["gammas"][:] = 1
-            elif kind == "Dense3d":
+            elif kind in ("Dense3d", "Dense2d"):
                 v["weights"][:] = rng.uniform(-0.1, 0.1, v["weights"].shape).astype(F32)
         return arena
 
@@ -416,8 +435,10 @@ class Network:
             elif kind == "Normalization3d":
                 y, mean, std, x_hat = layernorm_forward(ins[0], p["gammas"], p["betas"])
                 self.outputs[i], self.saved[i] = y, (std, x_hat)
-            elif kind == "Dense3d":
+            elif kind in ("Dense3d", "Dense2d"):
                 self.outputs[i], self.saved[i] = dense_forward(ins[0], p["weights"], p["biases"], layer["activation"])
+            elif kind == "Pooling3d":
+                self.outputs[i], self.saved[i] = pooling3d_forward(ins[0], layer["method"])
             self.layers[i]["_ins"] = ins
         return self.outputs[-1]
 
@@ -457,10 +478,21 @@ class Network:
                 std, x_hat = self.saved[i]
                 d_x, g["gammas"][:], g["betas"][:] = layernorm_backward(d_y, x_hat, std, p["gammas"])
                 input_grads[i][0] = d_x
-            elif kind == "Dense3d":
+            elif kind in ("Dense3d", "Dense2d"):
                 d_x, g["weights"][:], g["biases"][:] = dense_backward(ins[0], p["weights"], d_y, self.saved[i], layer["activation"])
                 input_grads[i][0] = d_x
+            elif kind == "Pooling3d":
+                input_grads[i][0] = pooling3d_backward(ins[0], d_y, layer["method"], self.saved[i])
         return gradient
+
+    def train_step_2d(self, arena, m, v, iteration, ids, targets, lr=1e-3):
+        """The same loop body with CrossEntropyError2d on a classifier: targets are one-hot rows [B, classes]."""
+        probabilities = self.forward(arena, {-1: ids})
+        error = ce2d_error(probabilities, targets)
+        gradient = self.backward(arena, ce2d_output_gradients(probabilities, targets))
+        iteration += 1
+        adam_update(arena, gradient, m, v, iteration, lr=lr)
+        return error, gradient, iteration
 
     def train_step(self, arena, m, v, iteration, external, targets, lr=1e-3):
         """Loop body of opennn/adaptive_moment_estimation.cpp:249-284 (regularisation "None").
@@ -481,6 +513,21 @@ def _encoder_block(net, S, E, H, F, source):
     dense = net.add("Dense3d", **{"in": F, "out": E, "activation": "Linear"})
     net.add("Addition3d", [norm_1, dense], E=E)
     return net.add("Normalization3d", S=S, E=E)
+
+
+def build_text_classifier(V, S, E, H, hidden, classes):
+    """opennn/standard_networks.cpp:575-615: Embedding (scaled, with positions) -> self-attention -> max pooling over
+    the sequence -> Dense<2> ReLU layers -> Dense<2> Softmax (Sigmoid for a single output, not restated here)."""
+    net = Network()
+    net.add("Embedding", [-1], V=V, S=S, E=E)
+    net.add("MultiHeadAttention", Sq=S, Sk=S, E=E, H=H, causal=False)
+    net.add("Pooling3d", method="MaxPooling")
+    width = E
+    for size in hidden:
+        net.add("Dense2d", **{"in": width, "out": size, "activation": "RectifiedLinear"})
+        width = size
+    net.add("Dense2d", **{"in": width, "out": classes, "activation": "Softmax"})
+    return net.compile()
 
 
 def greedy_decode(net, arena, source_ids, S_dec, start=2, end=3):

@@ -435,6 +435,78 @@ void run_network(bool decoder_only)
     for(const double seconds : step_seconds) timing << seconds << "\n";
 }
 
+
+
+// Text classifier (Embedding -> MultiHeadAttention -> Pooling3d -> Dense<2>... -> Softmax) with CrossEntropyError2d.
+
+void run_classifier()
+{
+    const Index B = spec_index("B");
+    const Index S = spec_index("S");
+    const Index V = spec_index("V");
+    const Index E = spec_index("E");
+    const Index H = spec_index("H");
+    const Index hidden = spec_index("hidden");
+    const Index classes = spec_index("classes");
+    const Index steps = spec_index("steps", 1);
+
+    Shape complexity;
+    if(hidden > 0) complexity.push_back(hidden);
+    TextClassificationNetwork network(Shape{V, S, E, H}, complexity, Shape{classes});
+
+    VectorR& parameters = network.get_parameters();
+    {
+        const type count[2] = { type(parameters.size()), type(network.get_layers_number()) };
+        write_bin("param_count", count, 2);
+        ofstream names(dir_path + "/layers.txt");
+        for(const unique_ptr<Layer>& layer : network.get_layers())
+            names << layer->get_name() << " " << layer->get_label() << " " << get_size(layer->get_parameter_views()) << "\n";
+    }
+    if(spec_index("structure_only") != 0) return;
+
+    const vector<type> parameters_in = read_bin("params", parameters.size());
+    memcpy(parameters.data(), parameters_in.data(), parameters_in.size() * sizeof(type));
+
+    CrossEntropyError2d loss(&network, nullptr);
+    loss.set_regularization_method("None");
+
+    Batch batch;
+    batch.samples_number = B;
+    const vector<type> ids = read_bin("ids", B * S);
+    batch.input_shape = {B, S};
+    batch.input_vector.resize(B * S);
+    memcpy(batch.input_vector.data(), ids.data(), ids.size() * sizeof(type));
+    const vector<type> targets = read_bin("targets", B * classes);
+    batch.target_shape = {B, classes};
+    batch.target_vector.resize(B * classes);
+    memcpy(batch.target_vector.data(), targets.data(), targets.size() * sizeof(type));
+
+    ForwardPropagation forward(B, &network);
+    BackPropagation back(B, &loss);
+    AdaptiveMomentEstimation adam(&loss);
+    adam.set_learning_rate(type(spec_double("lr", 1e-3)));
+    AdaptiveMomentEstimationData optimization_data(&adam);
+    optimization_data.iteration = 1;
+
+    vector<type> history;
+    for(Index step = 0; step < steps; step++)
+    {
+        back.neural_network.gradient.setZero();
+        network.forward_propagate(batch.get_inputs(), forward, true);
+        loss.back_propagate(batch, forward, back);
+        if(step == 0)
+        {
+            write_bin("grad_step0", back.neural_network.gradient.data(), back.neural_network.gradient.size());
+            const TensorView outputs = forward.get_outputs();
+            write_bin("probabilities", outputs.data, outputs.size());
+        }
+        adam.update_parameters(back, optimization_data);
+        history.push_back(back.error);
+    }
+    write_bin("loss", history.data(), history.size());
+    write_bin("params_out", parameters.data(), parameters.size());
+}
+
 }
 
 
@@ -461,6 +533,7 @@ int main(int argc, char** argv)
         else if(mode == "ce3d") run_ce3d();
         else if(mode == "transformer") run_network(false);
         else if(mode == "decoder") run_network(true);
+        else if(mode == "classifier") run_classifier();
         else throw runtime_error("unknown mode " + mode);
     }
     catch(const exception& e)

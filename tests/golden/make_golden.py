@@ -218,6 +218,47 @@ def make_pooling(seed=6):
         save(name, spec=np.array([B, S, E]), method=np.array(method), x=x, delta=delta, y=ref["y"].reshape(B, E), dx=ref["dx0"].reshape(B, S, E))
 
 
+CLASSIFIER_CASES = {
+    # name: B, S, V, E, H, hidden, classes, steps
+    "classifier_tiny": (6, 12, 50, 16, 2, 24, 3, 3),
+    "classifier_head64": (8, 72, 200, 128, 2, 256, 5, 3),
+}
+
+
+def classifier_inputs(name):
+    """Seeded parameters, ids and one-hot targets of a classifier case (shared by the generator and the tests)."""
+    B, S, V, E, H, hidden, classes, steps = CLASSIFIER_CASES[name]
+    rng = np.random.default_rng(11 + B + S)
+    net = O.build_text_classifier(V, S, E, H, [hidden], classes)
+    params = net.default_parameters(rng)
+    ids = O.synthetic_ids(rng, B, S, V, max(2, S // 3), S)
+    labels = rng.integers(0, classes, B)
+    targets = np.eye(classes, dtype=F32)[labels]
+    return net, params, ids, targets
+
+
+def make_classifier():
+    for name, (B, S, V, E, H, hidden, classes, steps) in CLASSIFIER_CASES.items():
+        print(f"  {name}")
+        net, params, ids, targets = classifier_inputs(name)
+        spec = dict(mode="classifier", B=B, S=S, V=V, E=E, H=H, hidden=hidden, classes=classes, steps=steps)
+        ref, _ = ref_runner.run(spec, {"params": params, "ids": ids, "targets": targets},
+                                ["param_count", "grad_step0", "loss", "params_out", "probabilities"])
+        assert int(ref["param_count"][0]) == net.parameters_size
+        arena, m, v = params.copy(), np.zeros_like(params), np.zeros_like(params)
+        iteration, losses = 1, []
+        for step in range(steps):
+            if step == 0:
+                check("probabilities", net.forward(arena, {-1: ids}), ref["probabilities"], 1e-5)
+            error, gradient, iteration = net.train_step_2d(arena, m, v, iteration, ids, targets)
+            if step == 0:
+                check("gradient", gradient, ref["grad_step0"], 1e-5)
+            losses.append(error)
+        check("loss history", np.array(losses), ref["loss"], 1e-6)
+        check("params_out", arena, ref["params_out"], 1e-4)       # Adam turns rounding differences of tiny gradients into steps
+        save(name, probabilities=ref["probabilities"].reshape(B, classes), gradient=ref["grad_step0"], loss=ref["loss"], params_out=ref["params_out"])
+
+
 DENSE_CASES = [("dense_linear_2_5_6_9", 2, 5, 6, 9, "Linear"), ("dense_relu_3_8_16_40", 3, 8, 16, 40, "RectifiedLinear"),
                ("dense_softmax_4_5_6_8", 4, 5, 6, 8, "Softmax"), ("dense_relu_2_33_64_136", 2, 33, 64, 136, "RectifiedLinear"),
                ("dense_linear_2_17_200_72", 2, 17, 200, 72, "Linear")]
@@ -374,7 +415,8 @@ def main():
     if not ref_runner.available():
         raise SystemExit("build the reference first: make -C oracle REF=/path/to/opennn")
     groups = {"mha": make_mha, "embedding": make_embedding, "layernorm": make_layernorm,
-              "dense": make_dense, "ce3d": make_ce3d, "pooling": make_pooling}
+              "dense": make_dense, "ce3d": make_ce3d, "pooling": make_pooling,
+              "classifier": make_classifier}
     for group, fn in groups.items():
         if args.only and args.only != group:
             continue

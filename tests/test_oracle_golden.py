@@ -110,6 +110,26 @@ def test_network_training_steps(name):
     assert_close(arena, g["params_out_sample"], 1e-4, "parameters after Adam")
 
 
+@pytest.mark.parametrize("name", ["classifier_tiny", "classifier_head64"])
+def test_text_classifier_training_steps(name):
+    """Embedding -> attention -> max pooling -> Dense<2> head with the 2-D cross-entropy, against the reference's
+    probabilities, first gradient, loss history and parameters after three Adam steps."""
+    from tests.golden.make_golden import CLASSIFIER_CASES, classifier_inputs
+    g = golden(name)
+    steps = CLASSIFIER_CASES[name][-1]
+    net, params, ids, targets = classifier_inputs(name)
+    arena, m, v = params.copy(), np.zeros_like(params), np.zeros_like(params)
+    assert_close(net.forward(arena, {-1: ids}), g["probabilities"], 1e-5, "probabilities")
+    iteration, losses = 1, []
+    for step in range(steps):
+        error, gradient, iteration = net.train_step_2d(arena, m, v, iteration, ids, targets)
+        if step == 0:
+            assert_close(gradient, g["gradient"], 1e-5, "gradient")
+        losses.append(error)
+    assert_close(np.array(losses), g["loss"], 1e-6, "loss history")
+    assert_close(arena, g["params_out"], 1e-4, "parameters after Adam")
+
+
 def test_transformer_structure():
     """Layer count and order of the reference's Transformer builder: 2 + 7L + 10L + 1 layers
     (20 for L = 1, the figure the reference's own structural test checks)."""
