@@ -329,6 +329,15 @@ int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_co
                      int64_t rows, int64_t V, int inputs_are_probabilities,
                      uint32_t flags, void* stream);
 
+/* CrossEntropyError2d with several classes (the loss of the text-classification network).  Replaces
+ * calculate_multiple_cross_entropy_cuda + the gradient kernel (opennn/cross_entropy_error.cpp:217-300); CPU semantics
+ * opennn/cross_entropy_error.cpp:58-77 and 114-134: error = -sum(t * log(y + FLT_EPSILON)) / rows, gradient
+ * (y - t) / rows (the softmax Jacobian is folded in; the Softmax Dense layer passes it on unchanged).
+ * probabilities [rows, classes] are overwritten with the gradient; targets [rows, classes] (one-hot or soft);
+ * stats (device, 2 floats) receives {error, rows}; row_scratch is [rows] floats. */
+int onn_ce2d_fwd_bwd(float* probabilities, const float* targets, float* stats, float* row_scratch,
+                     int64_t rows, int64_t classes, void* stream);
+
 /* Greedy decoding step (the body of the loop at opennn/standard_networks.cpp:1016-1034, which reads the distribution
  * back to the host and scans it there): for each of B samples the arg-max -- first index on ties -- of
  * probabilities[b, position, :] ([B, S, V]) becomes ids[b, position + 1] (floats holding integers, [B, S]) unless

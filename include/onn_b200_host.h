@@ -102,6 +102,31 @@ int onn_trainer_synchronize(onn_trainer* trainer);
 /* The cudaStream_t every kernel of this trainer is launched on (for event timing by the caller). */
 void* onn_trainer_stream(onn_trainer* trainer);
 
+/* -------------------------------------------------------------------------------------
+ * Text classification (opennn/standard_networks.cpp:575-615, TextClassificationNetwork): Embedding (scaled, with
+ * positions) -> self-attention -> max Pooling3d over the sequence -> Dense<2> "RectifiedLinear" layers ->
+ * Dense<2> "Softmax", trained with CrossEntropyError2d (opennn/cross_entropy_error.cpp:58-77, 114-134) and Adam
+ * (lr 1e-3, betas 0.9 / 0.999, clip norm 1, iteration 1).  One GPU, one batch per step of exactly `batch` samples.
+ * ids [batch, sequence_length] (token ids as floats, 0 = padding) and targets [batch, classes] (one-hot) are DEVICE
+ * pointers.  statistics (host, 2 floats, optional) receives {error, gradient norm}.  classes >= 2.
+ * ------------------------------------------------------------------------------------- */
+typedef struct onn_classifier onn_classifier;
+const char* onn_classifier_last_error(void);
+int onn_classifier_create(onn_classifier** out, int64_t vocabulary_size, int64_t sequence_length, int64_t embedding_dimension,
+                          int64_t heads_number, const int64_t* hidden_sizes, int hidden_layers, int64_t classes, int64_t batch);
+void onn_classifier_destroy(onn_classifier* classifier);
+int64_t onn_classifier_parameters_number(const onn_classifier* classifier);
+int onn_classifier_layers_number(const onn_classifier* classifier);
+int onn_classifier_layer_info(const onn_classifier* classifier, int layer, char* name, char* label, int capacity, int64_t* parameters);
+int onn_classifier_set_parameters(onn_classifier* classifier, const float* host_parameters);
+int onn_classifier_get_parameters(onn_classifier* classifier, float* host_parameters);
+int onn_classifier_get_gradients(onn_classifier* classifier, float* host_gradients);
+int onn_classifier_set_learning_rate(onn_classifier* classifier, float learning_rate);
+/* calculate_outputs: probabilities [batch, classes] to the host (optional) */
+int onn_classifier_forward(onn_classifier* classifier, const float* ids, float* host_probabilities);
+/* forward pass, loss, back-propagation and (update != 0) the Adam update */
+int onn_classifier_step_device(onn_classifier* classifier, const float* ids, const float* targets, int update, float* statistics);
+
 #ifdef __cplusplus
 }
 #endif

@@ -57,7 +57,7 @@ EXPORTS = [
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
     "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_pooling3d_fwd", "onn_pooling3d_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
-    "onn_mha_attention_weights", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
+    "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
     "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam",
     "onn_dp_unique_id", "onn_dp_init", "onn_dp_allreduce", "onn_dp_wait", "onn_dp_finalize",
 ]
@@ -305,6 +305,17 @@ def ce3d(logits, targets, inputs_are_probabilities=False, want_probabilities=Fal
     error = loss_sum / active if active > 0 else 0.0
     accuracy = correct / active if active > 0 else 0.0
     return error, accuracy, logits, probabilities
+
+
+def ce2d(probabilities, targets):
+    """CrossEntropyError2d with several classes.  Returns (error, gradient); `probabilities` is consumed (overwritten)."""
+    classes = probabilities.shape[-1]
+    rows = probabilities.numel() // classes
+    stats = torch.empty(2, device="cuda")
+    scratch = torch.empty(rows, device="cuda")
+    check(lib().onn_ce2d_fwd_bwd(ptr(probabilities), ptr(targets), ptr(stats), ptr(scratch), i64(rows), i64(classes), stream_ptr()),
+          "onn_ce2d_fwd_bwd")
+    return float(stats[0]), probabilities
 
 
 def grad_sqnorm(g):

@@ -822,6 +822,52 @@ extern "C" int onn_rows_are_zero(const float* X, uint8_t* flags, int64_t rows, i
     return launch_source_row_is_zero(X, flags, rows, (int)E, (cudaStream_t)stream);
 }
 
+// CrossEntropyError2d for several classes: one warp per sample; the gradient overwrites the probabilities.
+__global__ void __launch_bounds__(256)
+ce2d_fwd_bwd_kernel(float* __restrict__ probabilities, const float* __restrict__ targets, float* __restrict__ row_terms, long long rows, int classes)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * 8;
+    const float inv_rows = 1.0f / (float)rows;
+    for(long long row = warp; row < rows; row += stride)
+    {
+        float* p = probabilities + row * classes;
+        const float* t = targets + row * classes;
+        float term = 0.f;
+        for(int c = lane; c < classes; c += 32)
+        {
+            const float y = p[c], target = t[c];
+            term += target * logf(y + 1.1920929e-07f);
+            p[c] = (y - target) * inv_rows;
+        }
+        term = warp_sum(term);
+        if(lane == 0) row_terms[row] = term;
+    }
+}
+
+__global__ void ce2d_finish_kernel(const float* __restrict__ row_terms, long long rows, float* __restrict__ stats)
+{
+    __shared__ float scratch[32];
+    float mine = 0.f;
+    for(long long i = threadIdx.x; i < rows; i += blockDim.x) mine += row_terms[i];
+    const float total = block_sum(mine, scratch);
+    if(threadIdx.x == 0) { stats[0] = total / (float)(-rows); stats[1] = (float)rows; }
+}
+
+extern "C" int onn_ce2d_fwd_bwd(float* probabilities, const float* targets, float* stats, float* row_scratch,
+                                int64_t rows, int64_t classes, void* stream)
+{
+    ONN_CHECK_ARG(probabilities && targets && stats && row_scratch && rows > 0 && classes > 1 && classes < (1LL << 31));
+    cudaStream_t s = (cudaStream_t)stream;
+    ce2d_fwd_bwd_kernel<<<grid_for(rows, 8, 8), 256, 0, s>>>(probabilities, targets, row_scratch, rows, (int)classes);
+    count_launch();
+    if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    ce2d_finish_kernel<<<1, 1024, 0, s>>>(row_scratch, rows, stats);
+    count_launch();
+    return launch_status();
+}
+
 extern "C" int onn_ce3d_count_active(const float* targets, int64_t rows, int64_t V, float* counts, void* stream)
 {
     ONN_CHECK_ARG(targets && counts && rows > 0 && V > 0);

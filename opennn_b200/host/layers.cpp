@@ -464,6 +464,77 @@ void Dense3d::back_propagate(unique_ptr<LayerForwardPropagationCuda>& forward, u
 // Normalization3d and Addition<3>
 // ---------------------------------------------------------------------------------------
 
+unique_ptr<Dense3d> Dense3d::make_rank2(Index input_features, Index neurons, const string& activation, const string& new_label)
+{
+    unique_ptr<Dense3d> layer = std::make_unique<Dense3d>(1, input_features, neurons, activation, new_label);
+    layer->name = "Dense2d";
+    return layer;
+}
+
+
+// ---------------------------------------------------------------------------------------
+// Pooling3d
+// ---------------------------------------------------------------------------------------
+
+Pooling3d::Pooling3d(const Shape& input_shape, PoolingMethod method, const string& new_label)
+{
+    name = "Pooling3d";
+    label = new_label;
+    sequence_length = input_shape[0];
+    features = input_shape[1];
+    pooling_method = method;
+}
+
+void Pooling3dForwardPropagationCuda::initialize()
+{
+    const Shape input = layer->get_input_shape();
+    outputs.shape = {batch_size, input[1]};
+    maximal_indices.shape = {batch_size, input[1]};
+    row_is_valid.shape = {(batch_size * input[0] + 3) / 4};
+    valid_count.shape = {batch_size};
+}
+
+vector<TensorViewCuda*> Pooling3dForwardPropagationCuda::get_workspace_views()
+{
+    vector<TensorViewCuda*> views = LayerForwardPropagationCuda::get_workspace_views();
+    views.push_back(&maximal_indices);
+    views.push_back(&row_is_valid);
+    views.push_back(&valid_count);
+    return views;
+}
+
+void Pooling3dBackPropagationCuda::initialize()
+{
+    const Shape input = layer->get_input_shape();
+    input_gradients.resize(1);
+    input_gradients[0].shape = {batch_size, input[0], input[1]};
+}
+
+unique_ptr<LayerForwardPropagationCuda> Pooling3d::create_forward_propagation() const { return std::make_unique<Pooling3dForwardPropagationCuda>(); }
+unique_ptr<LayerBackPropagationCuda> Pooling3d::create_back_propagation() const { return std::make_unique<Pooling3dBackPropagationCuda>(); }
+
+void Pooling3d::forward_propagate(unique_ptr<LayerForwardPropagationCuda>& forward, bool)
+{
+    Pooling3dForwardPropagationCuda* state = static_cast<Pooling3dForwardPropagationCuda*>(forward.get());
+    check_onn(onn_pooling3d_fwd(forward->inputs[0].data, forward->outputs.data, reinterpret_cast<int32_t*>(state->maximal_indices.data),
+                                reinterpret_cast<uint8_t*>(state->row_is_valid.data), reinterpret_cast<int32_t*>(state->valid_count.data),
+                                forward->batch_size, sequence_length, features,
+                                pooling_method == PoolingMethod::MaxPooling ? ONN_POOL_MAX : ONN_POOL_AVERAGE, stream()),
+              "Pooling3d::forward_propagate");
+}
+
+void Pooling3d::back_propagate(unique_ptr<LayerForwardPropagationCuda>& forward, unique_ptr<LayerBackPropagationCuda>& back) const
+{
+    Pooling3dForwardPropagationCuda* state = static_cast<Pooling3dForwardPropagationCuda*>(forward.get());
+    fold_extra_gradients(back->output_gradients, 1);
+    check_onn(onn_pooling3d_bwd(back->output_gradients[0].data, reinterpret_cast<const int32_t*>(state->maximal_indices.data),
+                                reinterpret_cast<const uint8_t*>(state->row_is_valid.data), reinterpret_cast<const int32_t*>(state->valid_count.data),
+                                back->input_gradients[0].data, forward->batch_size, sequence_length, features,
+                                pooling_method == PoolingMethod::MaxPooling ? ONN_POOL_MAX : ONN_POOL_AVERAGE, stream()),
+              "Pooling3d::back_propagate");
+}
+
+
 Normalization3d::Normalization3d(const Shape& input_shape, const string& new_label)
 {
     name = "Normalization3d";

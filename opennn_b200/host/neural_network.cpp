@@ -178,6 +178,28 @@ Transformer::Transformer(Index input_sequence_length, Index decoder_sequence_len
     set_parameters_random();
 }
 
+TextClassificationNetwork::TextClassificationNetwork(Index vocabulary_size, Index sequence_length, Index embedding_dimension, Index heads_number,
+                                                     const vector<Index>& complexity_dimensions, Index classes)
+{
+    if(classes < 2) throw std::runtime_error("TextClassificationNetwork: the single-output (Sigmoid) variant is not implemented on this path.");
+    auto embedding = std::make_unique<Embedding>(Shape{vocabulary_size, sequence_length}, embedding_dimension, "embedding_layer");
+    embedding->set_scale_embedding(true);
+    embedding->set_add_positional_encoding(true);
+    add_layer(std::move(embedding), {-1});
+    add_layer(std::make_unique<MultiHeadAttention>(Shape{sequence_length, embedding_dimension}, heads_number, "multihead_attention_layer"), {0});
+    add_layer(std::make_unique<Pooling3d>(Shape{sequence_length, embedding_dimension}, Pooling3d::PoolingMethod::MaxPooling), {1});
+    Index width = embedding_dimension;
+    for(size_t i = 0; i < complexity_dimensions.size(); i++)
+    {
+        add_layer(Dense3d::make_rank2(width, complexity_dimensions[i], "RectifiedLinear", "dense2d_layer_" + std::to_string(i + 1)),
+                  {get_layers_number() - 1});
+        width = complexity_dimensions[i];
+    }
+    add_layer(Dense3d::make_rank2(width, classes, "Softmax", "classification_layer"), {get_layers_number() - 1});
+    compile();
+    set_parameters_random();
+}
+
 unique_ptr<NeuralNetwork> make_decoder_only_network(Index sequence_length, Index vocabulary_size, Index embedding_dimension,
                                                     Index heads_number, Index feed_forward_dimension, Index layers_number)
 {

@@ -279,6 +279,9 @@ class Dense3d final : public Layer
     friend class IncrementalDecoder;
 public:
     Dense3d(Index sequence_length, Index input_features, Index neurons, const string& activation, const string& label);
+    // Dense<2> (opennn/dense_layer.h with Rank = 2): the same layer on [batch, features] rows; it reports the name
+    // "Dense2d" as the reference does, and takes no part in the set-up plans written for the transformer's Dense3d pairs
+    static unique_ptr<Dense3d> make_rank2(Index input_features, Index neurons, const string& activation, const string& label);
 
     Index get_sequence_length() const { return sequence_length; }
     Index get_input_features_number() const { return inputs_number; }
@@ -401,6 +404,43 @@ struct Addition3dBackPropagationCuda final : LayerBackPropagationCuda
 
 
 // ---------------------------------------------------------------------------------------
+// Pooling3d (opennn/pooling_layer_3d.h): pooling over the sequence in front of a classification head
+// ---------------------------------------------------------------------------------------
+
+class Pooling3d final : public Layer
+{
+public:
+    enum class PoolingMethod { MaxPooling, AveragePooling };
+    Pooling3d(const Shape& input_shape = {0, 0}, PoolingMethod method = PoolingMethod::MaxPooling, const string& label = "sequence_pooling_layer");
+    PoolingMethod get_pooling_method() const { return pooling_method; }
+    Shape get_input_shape() const override { return {sequence_length, features}; }
+    Shape get_output_shape() const override { return {features}; }
+
+    void forward_propagate(unique_ptr<LayerForwardPropagationCuda>&, bool) override;
+    void back_propagate(unique_ptr<LayerForwardPropagationCuda>&, unique_ptr<LayerBackPropagationCuda>&) const override;
+    unique_ptr<LayerForwardPropagationCuda> create_forward_propagation() const override;
+    unique_ptr<LayerBackPropagationCuda> create_back_propagation() const override;
+
+private:
+    Index sequence_length = 0, features = 0;
+    PoolingMethod pooling_method = PoolingMethod::MaxPooling;
+};
+
+struct Pooling3dForwardPropagationCuda final : LayerForwardPropagationCuda
+{
+    void initialize() override;
+    vector<TensorViewCuda*> get_workspace_views() override;
+    TensorViewCuda maximal_indices;          // int32 [batch, features], held in a float view
+    TensorViewCuda row_is_valid;             // bytes [batch * sequence], held in a float view
+    TensorViewCuda valid_count;              // int32 [batch]
+};
+
+struct Pooling3dBackPropagationCuda final : LayerBackPropagationCuda
+{
+    void initialize() override;
+};
+
+// ---------------------------------------------------------------------------------------
 // NeuralNetwork (opennn/neural_network.h) and the Transformer builder (opennn/standard_networks.h)
 // ---------------------------------------------------------------------------------------
 
@@ -454,6 +494,15 @@ public:
     Transformer(Index input_sequence_length, Index decoder_sequence_length, Index input_vocabulary_size,
                 Index output_vocabulary_size, Index embedding_dimension, Index heads_number,
                 Index feed_forward_dimension, Index layers_number);
+};
+
+// standard_networks.cpp:575-615: Embedding (scaled, with positions) -> self-attention -> max pooling over the sequence ->
+// Dense<2> "RectifiedLinear" layers -> Dense<2> "Softmax" (more than one class)
+class TextClassificationNetwork final : public NeuralNetwork
+{
+public:
+    TextClassificationNetwork(Index vocabulary_size, Index sequence_length, Index embedding_dimension, Index heads_number,
+                              const vector<Index>& complexity_dimensions, Index classes);
 };
 
 // Decoder-only stack assembled with add_layer the way Transformer assembles its decoder,
@@ -565,6 +614,22 @@ private:
 // AdaptiveMomentEstimation (opennn/adaptive_moment_estimation.h)
 // ---------------------------------------------------------------------------------------
 
+// CrossEntropyError2d with several classes (opennn/cross_entropy_error.cpp:58-77, 114-134, CUDA :217-300): the loss
+// of a classification head whose last layer is a Dense<2> "Softmax".  error = -sum(t log(y + eps)) / samples; the
+// output gradient (y - t) / samples replaces the probabilities in the last layer's output buffer and goes through
+// that layer's back-propagation unchanged.
+class CrossEntropyError2d
+{
+public:
+    explicit CrossEntropyError2d(NeuralNetwork* network = nullptr) : neural_network(network) {}
+    NeuralNetwork* get_neural_network() const { return neural_network; }
+    // targets [samples, classes]; statistics (device, 2 floats) receives {error, samples}; row_scratch [samples]
+    void back_propagate(const TensorViewCuda& targets, ForwardPropagationCuda& forward_propagation,
+                        NeuralNetworkBackPropagationCuda& back_propagation, type* statistics, type* row_scratch) const;
+private:
+    NeuralNetwork* neural_network = nullptr;
+};
+
 class AdaptiveMomentEstimation;
 
 // adaptive_moment_estimation.h:139-160
@@ -572,6 +637,7 @@ struct ADAMOptimizationDataCuda
 {
     explicit ADAMOptimizationDataCuda(AdaptiveMomentEstimation* optimizer = nullptr);
     void set(AdaptiveMomentEstimation* optimizer);
+    void set(Index parameters_number);
 
     AdaptiveMomentEstimation* adaptive_moment_estimation = nullptr;
     TensorCuda gradient_exponential_decay;           // m
@@ -595,6 +661,9 @@ public:
     // adaptive_moment_estimation.cpp:855-883 with the CPU path's global-norm clip (:462-466).
     // gradient_scale multiplies the gradient first (1 unless the caller averaged an all-reduce).
     void update_parameters(BackPropagationCuda& back_propagation, ADAMOptimizationDataCuda& optimization_data,
+                           type gradient_scale = 1) const;
+    // the same update on any network and gradient arena (used with CrossEntropyError2d)
+    void update_parameters(NeuralNetwork* network, TensorCuda& gradients, ADAMOptimizationDataCuda& optimization_data,
                            type gradient_scale = 1) const;
 
 private:

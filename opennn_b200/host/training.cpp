@@ -137,6 +137,29 @@ void CrossEntropyError3d::read_error(BackPropagationCuda& back_propagation, type
 
 
 // ---------------------------------------------------------------------------------------
+// CrossEntropyError2d
+// ---------------------------------------------------------------------------------------
+
+void CrossEntropyError2d::back_propagate(const TensorViewCuda& targets, ForwardPropagationCuda& forward_propagation,
+                                         NeuralNetworkBackPropagationCuda& back_propagation, type* statistics, type* row_scratch) const
+{
+    const vector<unique_ptr<Layer>>& layers = neural_network->get_layers();
+    const Index last = neural_network->get_last_trainable_layer_index();
+    const Index first = neural_network->get_first_trainable_layer_index();
+    const TensorViewCuda outputs = forward_propagation.layers[size_t(last)]->outputs;
+    const Index classes = outputs.shape.back();
+    const Index samples = outputs.size() / classes;
+    if(classes < 2) throw std::runtime_error("CrossEntropyError2d: the binary (one output) variant is not implemented on this path.");
+    if(targets.size() != samples * classes) throw std::runtime_error("CrossEntropyError2d: targets must be [samples, classes]");
+    check_onn(onn_ce2d_fwd_bwd(outputs.data, targets.data, statistics, row_scratch, samples, classes, stream()),
+              "CrossEntropyError2d::back_propagate");
+    back_propagation.layers[size_t(last)]->output_gradients[0] = outputs;
+    for(Index i = last; i >= first; i--)
+        layers[size_t(i)]->back_propagate(forward_propagation.layers[size_t(i)], back_propagation.layers[size_t(i)]);
+}
+
+
+// ---------------------------------------------------------------------------------------
 // AdaptiveMomentEstimation
 // ---------------------------------------------------------------------------------------
 
@@ -148,7 +171,11 @@ ADAMOptimizationDataCuda::ADAMOptimizationDataCuda(AdaptiveMomentEstimation* opt
 void ADAMOptimizationDataCuda::set(AdaptiveMomentEstimation* optimizer)
 {
     adaptive_moment_estimation = optimizer;
-    const Index parameters_number = optimizer->get_loss()->get_neural_network()->get_parameters_number();
+    set(optimizer->get_loss()->get_neural_network()->get_parameters_number());
+}
+
+void ADAMOptimizationDataCuda::set(Index parameters_number)
+{
     gradient_exponential_decay.resize(parameters_number);
     square_gradient_exponential_decay.resize(parameters_number);
     square_norm.resize(8);
@@ -159,13 +186,17 @@ void ADAMOptimizationDataCuda::set(AdaptiveMomentEstimation* optimizer)
 void AdaptiveMomentEstimation::update_parameters(BackPropagationCuda& back_propagation, ADAMOptimizationDataCuda& optimization_data,
                                                  type gradient_scale) const
 {
-    NeuralNetwork* network = loss->get_neural_network();
+    update_parameters(loss->get_neural_network(), back_propagation.neural_network.gradients, optimization_data, gradient_scale);
+}
+
+void AdaptiveMomentEstimation::update_parameters(NeuralNetwork* network, TensorCuda& gradients, ADAMOptimizationDataCuda& optimization_data,
+                                                 type gradient_scale) const
+{
     optimization_data.iteration++;
     const type iteration = type(optimization_data.iteration);
     const type bias_correction_1 = type(1) - std::pow(beta_1, iteration);
     const type bias_correction_2 = type(1) - std::pow(beta_2, iteration);
 
-    TensorCuda& gradients = back_propagation.neural_network.gradients;
     const Index n = network->get_parameters_number();
     check_onn(onn_grad_sqnorm(gradients.data, n, optimization_data.square_norm.data, optimization_data.norm_workspace.data, stream()),
               "AdaptiveMomentEstimation: gradient norm");

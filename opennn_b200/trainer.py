@@ -25,6 +25,9 @@ HOST_EXPORTS = [
     "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_step_host_i32", "onn_trainer_forward", "onn_trainer_get_layer_output",
     "onn_trainer_synchronize", "onn_trainer_stream", "onn_trainer_set_graph_capture",
     "onn_trainer_greedy_decode", "onn_trainer_greedy_decode_cached",
+    "onn_classifier_last_error", "onn_classifier_create", "onn_classifier_destroy", "onn_classifier_parameters_number",
+    "onn_classifier_layers_number", "onn_classifier_layer_info", "onn_classifier_set_parameters", "onn_classifier_get_parameters",
+    "onn_classifier_get_gradients", "onn_classifier_set_learning_rate", "onn_classifier_forward", "onn_classifier_step_device",
 ]
 
 _host = None
@@ -41,6 +44,9 @@ def host_lib():
         L.onn_trainer_parameters_number.restype = C.c_int64
         L.onn_trainer_destroy.restype = None
         L.onn_trainer_stream.restype = C.c_void_p
+        L.onn_classifier_last_error.restype = C.c_char_p
+        L.onn_classifier_parameters_number.restype = C.c_int64
+        L.onn_classifier_destroy.restype = None
         _host = L
     return _host
 
@@ -172,6 +178,75 @@ class Trainer:
 
     def synchronize(self):
         _check(host_lib().onn_trainer_synchronize(self._handle), "synchronize")
+
+
+class TextClassifier:
+    """TextClassificationNetwork + CrossEntropyError2d + Adam on the current CUDA device: Embedding -> self-attention ->
+    max pooling over the sequence -> Dense<2> ReLU layers -> Dense<2> Softmax."""
+
+    def __init__(self, V, S, E, H, hidden, classes, batch):
+        self.S, self.classes, self.batch = S, classes, batch
+        self._handle = C.c_void_p()
+        i64 = C.c_int64
+        sizes = (i64 * max(len(hidden), 1))(*hidden)
+        status = host_lib().onn_classifier_create(C.byref(self._handle), i64(V), i64(S), i64(E), i64(H), sizes, len(hidden), i64(classes), i64(batch))
+        self._check(status, "onn_classifier_create")
+        self.parameters_number = int(host_lib().onn_classifier_parameters_number(self._handle))
+        self.layers_number = int(host_lib().onn_classifier_layers_number(self._handle))
+
+    @staticmethod
+    def _check(status, what):
+        if status != 0:
+            raise capi.OnnError(f"{what}: {host_lib().onn_classifier_last_error().decode()} ({status})")
+
+    def close(self):
+        if self._handle:
+            host_lib().onn_classifier_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def layer_info(self, i):
+        name, label = C.create_string_buffer(128), C.create_string_buffer(128)
+        params = C.c_int64()
+        self._check(host_lib().onn_classifier_layer_info(self._handle, int(i), name, label, 128, C.byref(params)), "layer_info")
+        return name.value.decode(), label.value.decode(), params.value
+
+    def set_parameters(self, host_array):
+        a = np.ascontiguousarray(host_array, dtype=np.float32)
+        assert a.size == self.parameters_number
+        self._check(host_lib().onn_classifier_set_parameters(self._handle, _f32_ptr(a)), "set_parameters")
+
+    def get_parameters(self):
+        a = np.empty(self.parameters_number, dtype=np.float32)
+        self._check(host_lib().onn_classifier_get_parameters(self._handle, _f32_ptr(a)), "get_parameters")
+        return a
+
+    def get_gradients(self):
+        a = np.empty(self.parameters_number, dtype=np.float32)
+        self._check(host_lib().onn_classifier_get_gradients(self._handle, _f32_ptr(a)), "get_gradients")
+        return a
+
+    def set_learning_rate(self, lr):
+        self._check(host_lib().onn_classifier_set_learning_rate(self._handle, C.c_float(lr)), "set_learning_rate")
+
+    def forward(self, ids):
+        """ids: torch CUDA float tensor [batch, S].  Returns the class probabilities [batch, classes] (numpy)."""
+        assert tuple(ids.shape) == (self.batch, self.S)
+        out = np.empty((self.batch, self.classes), dtype=np.float32)
+        self._check(host_lib().onn_classifier_forward(self._handle, capi.ptr(ids), _f32_ptr(out)), "forward")
+        return out
+
+    def step_device(self, ids, targets, update=True):
+        """ids [batch, S], targets [batch, classes] one-hot: torch CUDA float tensors.  Returns (error, gradient norm)."""
+        assert tuple(ids.shape) == (self.batch, self.S) and tuple(targets.shape) == (self.batch, self.classes)
+        stats = (C.c_float * 2)()
+        self._check(host_lib().onn_classifier_step_device(self._handle, capi.ptr(ids), capi.ptr(targets), int(update), stats), "step_device")
+        return tuple(stats)
 
 
 def shard_batch(arrays, rank, world):
