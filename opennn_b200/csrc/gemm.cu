@@ -63,6 +63,7 @@ int gemm(const onn_gemm_args& g, cudaStream_t stream)
         }
         return ONN_OK;
     }
+    if(mode == 0 && gemm_skinny_takes(g)) return gemm_skinny_launch(g, stream);
     const bool tc_ok = gemm_tc_supported(g);
     if(mode == 2 && !tc_ok) return ONN_ERR_UNSUPPORTED;
     if(mode != 1 && tc_ok) return gemm_tc_launch(g, stream);

@@ -16,6 +16,11 @@ bool gemm_tc_takes_parts(const onn_gemm_args& g);
 int gemm_tc_read_status();
 int gemm_tc_bounded_wait_selftest(int* gave_up_host);
 
+// fp32 CUDA-core kernel for M <= 64 rows against a [K, N] row-major matrix (one decoding step): streams the matrix with
+// 8 x N/32 CTAs, cluster reduction over K.  ONN_B200_GEMM_SKINNY=0 turns it off.
+bool gemm_skinny_takes(const onn_gemm_args& g);
+int gemm_skinny_launch(const onn_gemm_args& g, cudaStream_t stream);
+
 // Front end used by the layer code (same as onn_gemm).
 int gemm(const onn_gemm_args& g, cudaStream_t stream);
 // 0 = automatic, 1 = CUDA-core kernels only, 2 = tensor cores required (onn_gemm_set_mode).

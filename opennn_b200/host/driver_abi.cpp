@@ -56,9 +56,18 @@ struct onn_trainer
     bool graphs_enabled = true;
     Index eager_steps = 0;                // graphs are captured only after one eager step has configured every kernel
 
+    // cached greedy decoding: one executable graph per target position (the position is part of the captured pointers
+    // and arguments), captured from the second call on; ids and END flags live in buffers that never move
+    vector<cudaGraphExec_t> decode_graphs;
+    vector<uint64_t> decode_graph_launches;
+    TensorCuda decode_ids, decode_finished;
+    Index cached_decodes = 0;
+    int decode_end_id = -1;               // the END id the graphs were captured with (it is a captured argument)
+
     ~onn_trainer()
     {
         for(MicroGraph& g : micro_graphs) if(g.executable) cudaGraphExecDestroy(g.executable);
+        for(cudaGraphExec_t g : decode_graphs) if(g) cudaGraphExecDestroy(g);
         for(IdBuffers& b : id_buffers)
         {
             if(b.decoder) cudaFree(b.decoder);
@@ -511,6 +520,52 @@ extern "C" int onn_trainer_greedy_decode(onn_trainer* t, const float* encoder_id
     });
 }
 
+// One target position of the cached decoding loop: the decoder side on that position, then the arg-max into the next slot.
+static void decode_position(onn_trainer* t, Index i, int end_id)
+{
+    const Index B = t->micro_batch, S_dec = t->decoder_sequence_length;
+    const type* probabilities = t->decoder->step(t->decode_ids.data, S_dec, i - 1);
+    check_onn(onn_greedy_next_token_rows(probabilities, t->decode_ids.data, reinterpret_cast<int*>(t->decode_finished.data), B, S_dec,
+                                         t->vocabulary_size, i, end_id, t->stream), "greedy step");
+}
+
+// Replays position i from its graph, capturing it first if need be.  Returns false (nothing has run) if graphs cannot be used.
+static bool replay_decode_position(onn_trainer* t, Index i, int end_id)
+{
+    if(t->decode_graphs.size() < size_t(t->decoder_sequence_length))
+    {
+        t->decode_graphs.resize(size_t(t->decoder_sequence_length), nullptr);
+        t->decode_graph_launches.resize(size_t(t->decoder_sequence_length), 0);
+    }
+    cudaGraphExec_t& executable = t->decode_graphs[size_t(i)];
+    if(!executable)
+    {
+        const uint64_t launches_before = onn_launch_count();
+        cudaGraph_t captured = nullptr;
+        bool ok = cudaStreamBeginCapture(t->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if(ok)
+        {
+            try { decode_position(t, i, end_id); }
+            catch(...) { ok = false; }
+            ok = (cudaStreamEndCapture(t->stream, &captured) == cudaSuccess) && ok && captured != nullptr;
+        }
+        if(ok) ok = cudaGraphInstantiate(&executable, captured, 0) == cudaSuccess;
+        if(captured) cudaGraphDestroy(captured);
+        const uint64_t counted = onn_launch_count() - launches_before;
+        onn_launch_count_add(0 - counted);                          // counted at capture, launched below
+        if(!ok)
+        {
+            cudaGetLastError();
+            executable = nullptr;
+            return false;
+        }
+        t->decode_graph_launches[size_t(i)] = counted;
+    }
+    check_cuda(cudaGraphLaunch(executable, t->stream), "decode graph launch");
+    onn_launch_count_add(t->decode_graph_launches[size_t(i)]);
+    return true;
+}
+
 extern "C" int onn_trainer_greedy_decode_cached(onn_trainer* t, const float* encoder_ids, float* decoded_ids, int start_id, int end_id)
 {
     if(!t || !encoder_ids || !decoded_ids || t->decoder_only) return ONN_ERR_INVALID_ARGUMENT;
@@ -519,20 +574,19 @@ extern "C" int onn_trainer_greedy_decode_cached(onn_trainer* t, const float* enc
         Device::instance().set_compute_stream(t->stream);
         const Index B = t->micro_batch, S_in = t->input_sequence_length, S_dec = t->decoder_sequence_length;
         if(t->staged_encoder.size() < B * S_in) t->staged_encoder.resize(B * S_in);
-        if(t->staged_decoder.size() < B * S_dec) { t->staged_decoder.resize(B * S_dec); t->staged_targets.resize(B * S_dec); }
-        TensorCuda finished_device;
-        finished_device.resize(B);
+        if(t->decode_ids.size() == 0) { t->decode_ids.resize(B * S_dec); t->decode_finished.resize(B); }
+        t->decode_finished.fill(0);                                    // read as int
 
         vector<type> target(size_t(B * S_dec), type(0));
         for(Index b = 0; b < B; b++) target[size_t(b * S_dec)] = type(start_id);
         check_cuda(cudaMemcpyAsync(t->staged_encoder.data, encoder_ids, size_t(B * S_in) * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
-        check_cuda(cudaMemcpyAsync(t->staged_decoder.data, target.data(), target.size() * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
+        check_cuda(cudaMemcpyAsync(t->decode_ids.data, target.data(), target.size() * sizeof(type), cudaMemcpyHostToDevice, t->stream), "ids H2D");
         check_cuda(cudaStreamSynchronize(t->stream), "decode: ids");
 
         // encoder side once, through the ordinary forward pass
         BatchCuda batch;
         batch.samples_number = B;
-        batch.decoder = TensorViewCuda(t->staged_decoder.data, {B, S_dec});
+        batch.decoder = TensorViewCuda(t->decode_ids.data, {B, S_dec});
         batch.input = TensorViewCuda(t->staged_encoder.data, {B, S_in});
         vector<char> encoder_side = t->network->layers_depending_on_input(1);
         for(char& flag : encoder_side) flag = !flag;
@@ -540,22 +594,31 @@ extern "C" int onn_trainer_greedy_decode_cached(onn_trainer* t, const float* enc
 
         if(!t->decoder) t->decoder = std::make_unique<IncrementalDecoder>(t->network.get(), t->forward.get(), B);
         t->decoder->start();
+        // the first call runs eagerly (it configures every kernel); later calls replay one graph per position.  The END id
+        // is a captured argument: another one drops the graphs
+        bool use_graphs = t->graphs_enabled && t->cached_decodes > 0;
+        if(t->decode_end_id != end_id)
+            for(cudaGraphExec_t& g : t->decode_graphs) { if(g) cudaGraphExecDestroy(g); g = nullptr; }
+        t->decode_end_id = end_id;
         vector<int> finished(size_t(B), 0);
         for(Index i = 1; i < S_dec; i++)
         {
-            const type* probabilities = t->decoder->step(t->staged_decoder.data, S_dec, i - 1);
-            check_onn(onn_greedy_next_token_rows(probabilities, t->staged_decoder.data, reinterpret_cast<int*>(finished_device.data), B, S_dec,
-                                                 t->vocabulary_size, i, end_id, t->stream), "greedy step");
+            if(!use_graphs || !replay_decode_position(t, i, end_id))
+            {
+                use_graphs = false;
+                decode_position(t, i, end_id);
+            }
             if(i % 8 == 0 || i + 1 == S_dec)
             {
-                check_cuda(cudaMemcpyAsync(finished.data(), finished_device.data, size_t(B) * sizeof(int), cudaMemcpyDeviceToHost, t->stream), "decode: flags");
+                check_cuda(cudaMemcpyAsync(finished.data(), t->decode_finished.data, size_t(B) * sizeof(int), cudaMemcpyDeviceToHost, t->stream), "decode: flags");
                 check_cuda(cudaStreamSynchronize(t->stream), "decode: flags");
                 bool all = true;
                 for(const int f : finished) all = all && f != 0;
                 if(all) break;
             }
         }
-        check_cuda(cudaMemcpyAsync(decoded_ids, t->staged_decoder.data, size_t(B * S_dec) * sizeof(type), cudaMemcpyDeviceToHost, t->stream), "decode: ids D2H");
+        t->cached_decodes++;
+        check_cuda(cudaMemcpyAsync(decoded_ids, t->decode_ids.data, size_t(B * S_dec) * sizeof(type), cudaMemcpyDeviceToHost, t->stream), "decode: ids D2H");
         check_cuda(cudaStreamSynchronize(t->stream), "decode: ids D2H");
     });
 }

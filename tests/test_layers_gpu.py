@@ -241,6 +241,38 @@ def test_adam_and_norm(capi):
         assert not host(g).any(), "zero_grad must clear the gradient"
 
 
+@pytest.mark.parametrize("shape", [(1, 1024, 1024), (8, 4096, 1024), (13, 100, 36), (16, 32000, 256), (33, 1024, 4096),
+                                   (64, 1024, 1024), (64, 40, 8)])
+def test_gemm_few_rows(capi, shape):
+    """At most 64 rows against a row-major [K, N] matrix (one decoding step): the fp32 cluster kernel that streams the
+    matrix with 8 CTAs per 32-column strip.  Ragged M, N and K, row pitches wider than the rows, bias + ReLU + alpha,
+    accumulation into C; fp32 accuracy and the same bits on every run."""
+    M, N, K = shape
+    rng = np.random.default_rng(M * 7 + N + K)
+    lda, ldb, ldc = K + 4, N + 8, N + 12
+    A = torch.zeros(M, lda, device="cuda"); A[:, :K] = dev(rng.standard_normal((M, K)).astype(np.float32))
+    W = torch.zeros(K, ldb, device="cuda"); W[:, :N] = dev(rng.standard_normal((K, N)).astype(np.float32))
+    bias = dev(rng.standard_normal(N).astype(np.float32))
+    product = A[:, :K].double() @ W[:, :N].double()
+    capi.check(capi.lib().onn_gemm_set_mode(0))
+
+    out = torch.full((M, ldc), 7.0, device="cuda")
+    capi.gemm(A, W, out, M, N, K, lda, ldb, ldc, 0, 1)
+    assert_close(host(out[:, :N]), host(product), 1e-5, "plain")
+    assert float((out[:, N:] - 7.0).abs().max()) == 0.0, "columns past N must stay untouched"
+    again = torch.full((M, ldc), 7.0, device="cuda")
+    capi.gemm(A, W, again, M, N, K, lda, ldb, ldc, 0, 1)
+    assert torch.equal(out, again), "the reduction over K must not depend on timing"
+
+    capi.gemm(A, W, out, M, N, K, lda, ldb, ldc, 0, 1, bias=bias, relu=True, alpha=0.5)
+    assert_close(host(out[:, :N]), host(torch.relu(0.5 * product + bias.double())), 1e-5, "bias + ReLU + alpha")
+
+    before = out.clone()
+    capi.gemm(A, W, out, M, N, K, lda, ldb, ldc, 0, 1, flags=capi.ACCUMULATE)
+    assert_close(host(out[:, :N]), host(before[:, :N].double() + product), 1e-5, "accumulate")
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
 @pytest.mark.parametrize("a_major,b_major", [(0, 1), (0, 0), (1, 1)])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (300, 520, 136), (64, 48, 1056), (1000, 72, 40),
                                    (1000, 520, 136), (1024, 512, 200)])   # the last two reach the two-CTA kernel

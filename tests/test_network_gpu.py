@@ -172,14 +172,18 @@ def test_greedy_decode(libs, gemm):
     t.set_parameters(params)
     decoded = t.greedy_decode(source, start_id=2, end_id=end_id)
     cached = t.greedy_decode(source, start_id=2, end_id=end_id, cached=True)     # one position per step, keys and values cached
-    cached_again = t.greedy_decode(source, start_id=2, end_id=end_id, cached=True)
+    cached_again = t.greedy_decode(source, start_id=2, end_id=end_id, cached=True)   # captures one graph per position
+    cached_replayed = t.greedy_decode(source, start_id=2, end_id=end_id, cached=True)  # replays them
+    cached_free = t.greedy_decode(source, start_id=2, end_id=-1, cached=True)       # another END id: the graphs are rebuilt
     t.close()
     capi.check(capi.lib().onn_gemm_set_mode(0))
     assert decoded.shape == expected.shape and (decoded[:, 0] == 2).all()
     assert np.array_equal(cached, cached_again), "the caches must start clean"
+    assert np.array_equal(cached, cached_replayed), "graph replay must give the eager loop's tokens"
     if gemm == "simt":
         assert np.array_equal(decoded, expected)
         assert np.array_equal(cached, expected)
+        assert np.array_equal(cached_free, free_run)
         return
     for decoded in (decoded, cached):
       for b in range(decoded.shape[0]):
