@@ -318,6 +318,23 @@ def ce2d(probabilities, targets):
     return float(stats[0]), probabilities
 
 
+def decode_attention(q, k_cache, v_cache, key_is_pad, length, H):
+    """One query row per sample against the first `length` cached keys and values.  q [B, E]; caches [B, S_cache, E];
+    key_is_pad uint8 [B, S_cache] or None.  Returns the context [B, E]."""
+    B, S_cache, E = k_cache.shape
+    out = torch.empty(B, E, device="cuda")
+    check(lib().onn_decode_attention(ptr(q), ptr(k_cache), ptr(v_cache), ptr(key_is_pad), ptr(out), i64(B), i64(S_cache), i64(length),
+                                     i64(E), i64(H), stream_ptr()), "onn_decode_attention")
+    return out
+
+
+def greedy_next_token_rows(probabilities, ids, finished, write_position, end_id):
+    """probabilities [B, V]; ids float [B, S] (column write_position receives the arg-max of unfinished rows); finished int32 [B]."""
+    B, V = probabilities.shape
+    check(lib().onn_greedy_next_token_rows(ptr(probabilities), ptr(ids), ptr(finished), i64(B), i64(ids.shape[1]), i64(V),
+                                           i64(write_position), int(end_id), stream_ptr()), "onn_greedy_next_token_rows")
+
+
 def grad_sqnorm(g):
     out = torch.empty(1, device="cuda")
     ws = _empty(lib().onn_grad_sqnorm_workspace_floats(i64(g.numel())))

@@ -2,10 +2,11 @@
 //
 // One decoding step of the transformer multiplies [batch, 1, E] activations by every weight matrix of the decoder: the
 // product is a weight stream, bound by HBM, and a 128-row tensor-core tile would give it to N/256 CTAs.  Here the weight
-// matrix is cut into strips of 32 columns and each strip into 8 ranges of K; the 8 CTAs of a strip form a thread-block
-// cluster, each streams its [K/8, 32] slab through a cp.async ring (the M rows of A with it), keeps a [MB, 32] partial
-// tile in registers, and the cluster adds the 8 partial tiles through distributed shared memory in a fixed order --
-// no workspace, no atomics, the same bits on every run.  A 1024 x 1024 matrix is read by 256 CTAs.
+// matrix is cut into strips of 32 columns and, while that gives fewer than two CTAs per SM, each strip into 2, 4 or 8
+// ranges of K; the CTAs of a strip form a thread-block cluster, each streams its slab through a deep cp.async ring (the
+// M rows of A with it), keeps a [MB, 32] partial tile in registers, and the cluster adds the partial tiles through
+// distributed shared memory in a fixed order -- no workspace, no atomics, the same bits on every run.  A 1024 x 1024
+// matrix is read by 256 CTAs, each with ~50 KB of loads in flight.
 #include <cooperative_groups.h>
 
 #include <cstdlib>
@@ -20,8 +21,10 @@ namespace onn
 {
 namespace skinny
 {
-constexpr int BN = 32, BK = 32, THREADS = 128, STAGES = 3, SPLITS = 8;
+constexpr int BN = 32, BK = 32, THREADS = 128;
 constexpr int A_PITCH = BK + 4;              // floats; keeps 16-byte alignment of every row
+// ring depth by rows per thread: about 50 KB of shared memory per CTA in every variant
+__host__ __device__ constexpr int stages_for(int rm) { return rm == 1 ? 8 : (rm == 2 ? 6 : 4); }
 
 struct Params
 {
@@ -41,19 +44,20 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool val
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
-// RM rows per thread: the CTA holds MB = 16 * RM rows of A
-template <int RM>
-__global__ void __cluster_dims__(1, SPLITS, 1) __launch_bounds__(THREADS)
+template <int RM> struct Stage { float w[BK][BN]; float a[16 * RM][A_PITCH]; };
+
+// RM rows per thread: the CTA holds MB = 16 * RM rows of A.  SPLITS CTAs (a cluster along y) share a strip.
+template <int RM, int SPLITS>
+__global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(const Params p)
 {
-    constexpr int MB = 16 * RM;
-    struct Stage { float w[BK][BN]; float a[MB][A_PITCH]; };
-    __shared__ __align__(16) Stage stages[STAGES];
+    constexpr int MB = 16 * RM, STAGES = stages_for(RM);
+    using Stage = skinny::Stage<RM>;
+    extern __shared__ __align__(16) unsigned char ring[];
+    Stage* stages = reinterpret_cast<Stage*>(ring);
     static_assert(sizeof(Stage) * STAGES >= sizeof(float) * MB * BN, "the partial tile reuses the ring");
-    static_assert(sizeof(Stage) * STAGES <= 48 * 1024, "static shared memory");
 
-    cg::cluster_group cluster = cg::this_cluster();
-    const int rank = (int)cluster.block_rank();
+    const int rank = SPLITS > 1 ? (int)blockIdx.y : 0;      // the cluster spans the whole y extent of the grid
     const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;
     const long long n0 = (long long)blockIdx.x * BN;
     const long long k_begin = rank * p.k_chunk;
@@ -121,16 +125,39 @@ gemm_skinny_kernel(const Params p)
         }
     }
     cp_async_wait<0>();
-    __syncthreads();                                     // the ring is free: it now holds this CTA's partial tile
     pdl_launch_dependents();
 
+    if constexpr(SPLITS == 1)
+    {
+#pragma unroll
+        for(int i = 0; i < RM; i++)
+        {
+            const int row = ty * RM + i;
+            if(row >= p.M) continue;
+#pragma unroll
+            for(int j = 0; j < 4; j++)
+            {
+                const long long n = n0 + tx * 4 + j;
+                if(n >= p.N) continue;
+                float value = p.alpha * acc[i][j];
+                if(p.bias) value += p.bias[n];
+                if(p.relu) value = fmaxf(value, 0.f);
+                float* dst = p.C + row * p.ldc + n;
+                *dst = p.accumulate ? *dst + value : value;
+            }
+        }
+    }
+    else
+    {
+    cg::cluster_group cluster = cg::this_cluster();
+    __syncthreads();                                     // the ring is free: it now holds this CTA's partial tile
     float (*partial)[BN] = reinterpret_cast<float (*)[BN]>(&stages[0]);
 #pragma unroll
     for(int i = 0; i < RM; i++)
         *reinterpret_cast<float4*>(&partial[ty * RM + i][tx * 4]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
     cluster.sync();
 
-    // CTA `rank` adds rows [rank * MB/8, (rank + 1) * MB/8) of the 8 partial tiles, always in the order 0..7
+    // CTA `rank` adds rows [rank * MB/SPLITS, (rank + 1) * MB/SPLITS) of the partial tiles, always in the order 0..SPLITS-1
     constexpr int ROWS = MB / SPLITS;
     for(int o = tid; o < ROWS * BN; o += THREADS)
     {
@@ -153,6 +180,7 @@ gemm_skinny_kernel(const Params p)
         }
     }
     cluster.sync();                                      // nobody leaves while its tile is still being read
+    }
 }
 }  // namespace skinny
 
@@ -168,22 +196,66 @@ bool gemm_skinny_takes(const onn_gemm_args& g)
     return g.M <= 16 || g.N * g.K <= (8LL << 20);
 }
 
+namespace skinny
+{
+template <int RM, int SPLITS>
+int launch(const Params& p, cudaStream_t stream)
+{
+    constexpr size_t shared = sizeof(Stage<RM>) * stages_for(RM);
+    static bool configured = false;                      // per instantiation; the attribute belongs to the function
+    if(!configured)
+    {
+        if(cudaFuncSetAttribute(gemm_skinny_kernel<RM, SPLITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
+            return ONN_ERR_CUDA;
+        configured = true;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)((p.N + BN - 1) / BN), SPLITS, 1);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attributes[1].id = cudaLaunchAttributeClusterDimension;
+    attributes[1].val.clusterDim.x = 1;
+    attributes[1].val.clusterDim.y = SPLITS;
+    attributes[1].val.clusterDim.z = 1;
+    config.attrs = attributes;
+    config.numAttrs = SPLITS > 1 ? 2 : 1;
+    if(cudaLaunchKernelEx(&config, gemm_skinny_kernel<RM, SPLITS>, p) != cudaSuccess) return ONN_ERR_CUDA;
+    count_launch();
+    return ONN_OK;
+}
+
+template <int RM>
+int launch_rows(const Params& p, int splits, cudaStream_t stream)
+{
+    switch(splits)
+    {
+        case 1: return launch<RM, 1>(p, stream);
+        case 2: return launch<RM, 2>(p, stream);
+        case 4: return launch<RM, 4>(p, stream);
+        default: return launch<RM, 8>(p, stream);
+    }
+}
+}  // namespace skinny
+
 int gemm_skinny_launch(const onn_gemm_args& g, cudaStream_t stream)
 {
     using namespace skinny;
+    // split K while the strips alone give fewer than two CTAs per SM and a CTA keeps at least two steps
+    const long long strips = (g.N + BN - 1) / BN;
+    int splits = 1;
+    while(splits < 8 && strips * splits < 296 && g.K / (splits * 2) >= 2 * BK) splits *= 2;
     Params p;
     p.A = g.A; p.W = g.B; p.bias = g.bias; p.C = g.C;
     p.M = g.M; p.N = g.N; p.K = g.K; p.lda = g.lda; p.ldb = g.ldb; p.ldc = g.ldc;
-    p.k_chunk = ((g.K + SPLITS - 1) / SPLITS + BK - 1) / BK * BK;
+    p.k_chunk = ((g.K + splits - 1) / splits + BK - 1) / BK * BK;
     p.alpha = g.alpha; p.relu = g.relu ? 1 : 0; p.accumulate = (g.flags & ONN_ACCUMULATE) ? 1 : 0;
-    const dim3 grid((unsigned)((g.N + BN - 1) / BN), SPLITS, 1);
-    cudaError_t status;
-    if(g.M <= 16) status = launch_overlapped(gemm_skinny_kernel<1>, grid, dim3(THREADS), 0, stream, p);
-    else if(g.M <= 32) status = launch_overlapped(gemm_skinny_kernel<2>, grid, dim3(THREADS), 0, stream, p);
-    else status = launch_overlapped(gemm_skinny_kernel<4>, grid, dim3(THREADS), 0, stream, p);
-    if(status != cudaSuccess) return ONN_ERR_CUDA;
-    count_launch();
-    return ONN_OK;
+    if(g.M <= 16) return launch_rows<1>(p, splits, stream);
+    if(g.M <= 32) return launch_rows<2>(p, splits, stream);
+    return launch_rows<4>(p, splits, stream);
 }
 
 }  // namespace onn

@@ -690,18 +690,36 @@ extern "C" int onn_softmax_rows(float* Y, int64_t rows, int64_t cols, void* stre
 
 // Greedy decoding step: per sample the arg-max (first index on ties) of one distribution, written as a float id into
 // the sample's id row unless the sample already produced END; finished[b] is set on END.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 greedy_next_token_kernel(const float* __restrict__ probabilities, long long sample_stride, float* __restrict__ ids, long long ids_stride,
                          int write_position, int* __restrict__ finished, int V, int end_id)
 {
-    __shared__ float best_value[256];
-    __shared__ int best_index[256];
+    __shared__ float best_value[1024];
+    __shared__ int best_index[1024];
     const int b = blockIdx.x;
     const float* row = probabilities + (long long)b * sample_stride;
     float value = -INFINITY;
     int index = 0x7fffffff;
-    for(int k = threadIdx.x; k < V; k += blockDim.x)
-        if(row[k] > value) { value = row[k]; index = k; }        // strided scan keeps the smallest index of each thread's maximum
+    // each thread walks its indices upwards and keeps the first of its maxima
+    if((((uintptr_t)row) & 15) == 0)
+    {
+        const int quads = V >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+        for(int k4 = threadIdx.x; k4 < quads; k4 += blockDim.x)
+        {
+            const float4 x = row4[k4];
+            if(x.x > value) { value = x.x; index = 4 * k4; }
+            if(x.y > value) { value = x.y; index = 4 * k4 + 1; }
+            if(x.z > value) { value = x.z; index = 4 * k4 + 2; }
+            if(x.w > value) { value = x.w; index = 4 * k4 + 3; }
+        }
+        for(int k = 4 * quads + threadIdx.x; k < V; k += blockDim.x)
+            if(row[k] > value) { value = row[k]; index = k; }
+    }
+    else
+        for(int k = threadIdx.x; k < V; k += blockDim.x)
+            if(row[k] > value) { value = row[k]; index = k; }
     best_value[threadIdx.x] = value;
     best_index[threadIdx.x] = index;
     __syncthreads();
@@ -727,11 +745,14 @@ greedy_next_token_kernel(const float* __restrict__ probabilities, long long samp
     }
 }
 
+// 256 threads for a short distribution, 1024 for a vocabulary
+static unsigned greedy_threads(int64_t V) { return V >= 4096 ? 1024u : 256u; }
+
 extern "C" int onn_greedy_next_token(const float* probabilities, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
                                      int64_t position, int end_id, void* stream)
 {
     ONN_CHECK_ARG(probabilities && ids && finished && B > 0 && S > 1 && V > 0 && position >= 0 && position + 1 < S && V < (1LL << 31));
-    greedy_next_token_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(probabilities + position * V, S * V, ids, S, (int)position + 1,
+    greedy_next_token_kernel<<<(unsigned)B, greedy_threads(V), 0, (cudaStream_t)stream>>>(probabilities + position * V, S * V, ids, S, (int)position + 1,
                                                                              finished, (int)V, end_id);
     count_launch();
     return launch_status();
@@ -741,7 +762,7 @@ extern "C" int onn_greedy_next_token_rows(const float* probabilities, float* ids
                                           int64_t write_position, int end_id, void* stream)
 {
     ONN_CHECK_ARG(probabilities && ids && finished && B > 0 && S > 1 && V > 0 && write_position > 0 && write_position < S && V < (1LL << 31));
-    greedy_next_token_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(probabilities, V, ids, S, (int)write_position, finished, (int)V, end_id);
+    greedy_next_token_kernel<<<(unsigned)B, greedy_threads(V), 0, (cudaStream_t)stream>>>(probabilities, V, ids, S, (int)write_position, finished, (int)V, end_id);
     count_launch();
     return launch_status();
 }
@@ -795,11 +816,123 @@ decode_attention_kernel(const float* __restrict__ q, const float* __restrict__ k
     }
 }
 
+// The same for head sizes that are a multiple of 4 (every configuration of the transformer): one CTA of 256 threads per
+// (sample, head).  Scores: 8 lanes share a key and read its row as float4 (32 keys per pass, rows read once, coalesced);
+// softmax over the scores in shared memory; output: hd/4 threads share a value row, 256/(hd/4) groups of them walk the
+// keys side by side, and their partial sums are added in a fixed order.
+__global__ void __launch_bounds__(256)
+decode_attention_block_kernel(const float* __restrict__ q, const float* __restrict__ k_cache, const float* __restrict__ v_cache,
+                              const uint8_t* __restrict__ key_is_pad, float* __restrict__ out,
+                              int H, int S_cache, int length, int E, float scale)
+{
+    extern __shared__ __align__(16) float shared[];            // q[hd] | partial[1024] | reduce[16] | scores[S_cache]
+    const int hd = E / H, chunks = hd >> 2;
+    float* q_shared = shared;
+    float* partial = q_shared + hd;
+    float* reduce = partial + 1024;
+    float* scores = reduce + 16;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    const long long cache_row0 = (long long)b * S_cache;
+    for(int d = tid; d < hd; d += 256) q_shared[d] = q[(long long)b * E + h * hd + d];
+    __syncthreads();
+
+    // scores
+    const int sub = tid & 7, slot = tid >> 3;
+    float thread_max = -INFINITY;
+    for(int j0 = 0; j0 < length; j0 += 32)
+    {
+        const int j = j0 + slot;
+        float dot = 0.f;
+        if(j < length)
+        {
+            const float4* k_row = reinterpret_cast<const float4*>(k_cache + (cache_row0 + j) * E + h * hd);
+            for(int c = sub; c < chunks; c += 8)
+            {
+                const float4 kv = k_row[c];
+                const float4 qv = *reinterpret_cast<const float4*>(q_shared + 4 * c);
+                dot = fmaf(qv.x, kv.x, dot); dot = fmaf(qv.y, kv.y, dot); dot = fmaf(qv.z, kv.z, dot); dot = fmaf(qv.w, kv.w, dot);
+            }
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        if(j < length)
+        {
+            float s = dot * scale;
+            if(key_is_pad && key_is_pad[cache_row0 + j]) s = -1e9f;        // overwrite, as the training path
+            if(sub == 0) scores[j] = s;
+            thread_max = fmaxf(thread_max, s);
+        }
+    }
+    thread_max = warp_max(thread_max);
+    if(lane == 0) reduce[warp] = thread_max;
+    __syncthreads();
+    float row_max = reduce[0];
+#pragma unroll
+    for(int w = 1; w < 8; w++) row_max = fmaxf(row_max, reduce[w]);
+
+    float thread_sum = 0.f;
+    for(int j = tid; j < length; j += 256)
+    {
+        const float e = __expf(scores[j] - row_max);
+        scores[j] = e;
+        thread_sum += e;
+    }
+    thread_sum = warp_sum(thread_sum);
+    if(lane == 0) reduce[8 + warp] = thread_sum;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for(int w = 0; w < 8; w++) total += reduce[8 + w];
+    const float inv = total > 0.f ? 1.0f / total : 0.f;
+
+    // weighted sum of the value rows
+    const int groups = 256 / chunks;
+    if(tid < groups * chunks)
+    {
+        const int group = tid / chunks, c = tid % chunks;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for(int j = group; j < length; j += groups)
+        {
+            const float p = scores[j];
+            const float4 v = reinterpret_cast<const float4*>(v_cache + (cache_row0 + j) * E + h * hd)[c];
+            acc.x = fmaf(p, v.x, acc.x); acc.y = fmaf(p, v.y, acc.y); acc.z = fmaf(p, v.z, acc.z); acc.w = fmaf(p, v.w, acc.w);
+        }
+        *reinterpret_cast<float4*>(partial + group * hd + 4 * c) = acc;
+    }
+    __syncthreads();
+    for(int d = tid; d < hd; d += 256)
+    {
+        float sum = 0.f;
+        for(int g = 0; g < groups; g++) sum += partial[g * hd + d];
+        out[(long long)b * E + h * hd + d] = sum * inv;
+    }
+}
+
 extern "C" int onn_decode_attention(const float* q, const float* k_cache, const float* v_cache, const uint8_t* key_is_pad, float* out,
                                     int64_t B, int64_t S_cache, int64_t length, int64_t E, int64_t H, void* stream)
 {
     ONN_CHECK_ARG(q && k_cache && v_cache && out && B > 0 && H > 0 && E > 0 && E % H == 0 && length > 0 && length <= S_cache);
     const int hd = (int)(E / H);
+    const bool aligned = ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0;
+    if(hd % 4 == 0 && hd <= 256 && aligned && B * H < (1LL << 31))
+    {
+        const size_t shared = (size_t)(hd + 1024 + 16 + S_cache) * sizeof(float);
+        if(shared > 200 * 1024) return ONN_ERR_UNSUPPORTED;
+        static size_t configured = 48 * 1024;
+        if(shared > configured)
+        {
+            if(cudaFuncSetAttribute(decode_attention_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
+                return ONN_ERR_CUDA;
+            configured = shared;
+        }
+        decode_attention_block_kernel<<<(unsigned)(B * H), 256, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, out, (int)H,
+                                                                                                 (int)S_cache, (int)length, (int)E,
+                                                                                                 1.0f / sqrtf((float)hd));
+        count_launch();
+        return launch_status();
+    }
     const size_t shared = 4 * (size_t)(hd + S_cache) * sizeof(float);
     if(shared > 200 * 1024) return ONN_ERR_UNSUPPORTED;
     static size_t configured = 48 * 1024;

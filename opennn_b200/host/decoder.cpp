@@ -132,13 +132,24 @@ const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index po
         }
         else if(Normalization3d* norm = dynamic_cast<Normalization3d*>(layer))
         {
-            // statistics are not kept: inference only
-            check_onn(onn_layernorm_fwd(input_of(i, 0), nullptr, norm->gammas_device.data, norm->betas_device.data, out, nullptr, query.data,
+            // statistics are not kept: inference only.  An Addition<3> that only this layer reads is summed inside the kernel
+            const type* x = nullptr;
+            const type* addend = nullptr;
+            const Index source = input_indices[i][0];
+            if(source >= 0 && forward_propagation->layers[size_t(source)]->fused_into_consumer)
+            {
+                x = input_of(size_t(source), 0);
+                addend = input_of(size_t(source), 1);
+            }
+            else
+                x = input_of(i, 0);
+            check_onn(onn_layernorm_fwd(x, addend, norm->gammas_device.data, norm->betas_device.data, out, nullptr, query.data,
                                         query.data + B, nullptr, B, norm->embedding_dimension, EPSILON, 0, stream()), "IncrementalDecoder: normalization");
         }
         else if(dynamic_cast<Addition3d*>(layer))
         {
-            check_onn(onn_add(input_of(i, 0), input_of(i, 1), out, outputs[i]->size(), 0, stream()), "IncrementalDecoder: addition");
+            if(!forward_propagation->layers[i]->fused_into_consumer)
+                check_onn(onn_add(input_of(i, 0), input_of(i, 1), out, outputs[i]->size(), 0, stream()), "IncrementalDecoder: addition");
         }
         else
             throw std::runtime_error("IncrementalDecoder: layer type " + layer->get_name() + " is not handled");

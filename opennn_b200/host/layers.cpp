@@ -41,6 +41,9 @@ void TensorCuda::resize(Index new_count)
     check_cuda(cudaMalloc(reinterpret_cast<void**>(&data), size_t(new_count) * sizeof(type)), "TensorCuda::resize");
     count = new_count;
     check_cuda(cudaMemset(data, 0, size_t(count) * sizeof(type)), "TensorCuda::resize memset");
+    // the fill runs on the legacy default stream and may return before it has run; the compute stream is non-blocking
+    // and does not wait for it, so a kernel launched right after could see its output wiped
+    check_cuda(cudaStreamSynchronize(nullptr), "TensorCuda::resize synchronize");
 }
 
 void TensorCuda::fill(type value)

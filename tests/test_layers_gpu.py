@@ -241,6 +241,58 @@ def test_adam_and_norm(capi):
         assert not host(g).any(), "zero_grad must clear the gradient"
 
 
+@pytest.mark.parametrize("B,S_cache,length,E,H", [(3, 256, 256, 1024, 16), (2, 40, 17, 64, 8), (5, 9, 1, 32, 8), (2, 12, 12, 12, 2),
+                                                  (1, 300, 299, 512, 2)])
+def test_decode_attention(capi, B, S_cache, length, E, H):
+    """Attention of one query row over cached keys and values against an fp64 evaluation: padded keys take the score
+    -1e9 (a row of nothing but padding becomes uniform), slots past `length` are never read (they hold NaN here).
+    Head sizes 64, 8, 4, 6 (not a multiple of 4: the one-warp kernel) and 256."""
+    rng = np.random.default_rng(B * 100 + E)
+    hd = E // H
+    q = dev(rng.standard_normal((B, E)).astype(np.float32))
+    k = dev(rng.standard_normal((B, S_cache, E)).astype(np.float32))
+    v = dev(rng.standard_normal((B, S_cache, E)).astype(np.float32))
+    k[:, length:] = float("nan"); v[:, length:] = float("nan")
+    pad = torch.zeros(B, S_cache, dtype=torch.uint8, device="cuda")
+    pad[0, length // 2:] = 1
+    if B > 1:
+        pad[1, :] = 1
+    out = capi.decode_attention(q, k, v, pad, length, H)
+    qh = q.double().view(B, H, 1, hd)
+    kh = k[:, :length].double().view(B, length, H, hd).permute(0, 2, 1, 3)
+    vh = v[:, :length].double().view(B, length, H, hd).permute(0, 2, 1, 3)
+    scores = (qh @ kh.transpose(-1, -2)) / np.sqrt(hd)
+    scores = torch.where(pad[:, None, None, :length].bool(), torch.full_like(scores, -1e9), scores)
+    expected = (torch.softmax(scores, dim=-1) @ vh).reshape(B, E)
+    assert_close(host(out), host(expected), 2e-5, "context")
+    assert torch.equal(out, capi.decode_attention(q, k, v, pad, length, H)), "same bits on every run"
+    assert_close(host(capi.decode_attention(q, k, v, None, length, H)),
+                 host((torch.softmax((qh @ kh.transpose(-1, -2)) / np.sqrt(hd), dim=-1) @ vh).reshape(B, E)), 2e-5, "no padding flags")
+
+
+@pytest.mark.parametrize("V", [37, 4096, 32000, 32003])
+def test_greedy_next_token_rows(capi, V):
+    """Arg-max per row with the first index on ties, END marks a row finished, finished rows are left alone."""
+    rng = np.random.default_rng(V)
+    B, S = 6, 5
+    p = rng.random((B, V)).astype(np.float32) * 0.5
+    winners = [V - 1, 0, V // 2, 3, 7, V - 2]
+    for b, w in enumerate(winners):
+        p[b, w] = 0.9
+    p[2, V // 2 + 5:V // 2 + 9] = 0.9                     # ties behind the winner: the first index wins
+    if V > 2000:
+        p[3, 3 + 1024] = 0.9                              # a tie held by another thread of the scan
+    ids = torch.zeros(B, S, device="cuda")
+    finished = torch.zeros(B, dtype=torch.int32, device="cuda")
+    finished[4] = 1
+    view = dev(p) if V % 4 == 0 else dev(np.concatenate([np.zeros((1, 1), np.float32), p.reshape(1, -1)], axis=1)).view(-1)[1:].view(B, V)
+    capi.greedy_next_token_rows(view, ids, finished, 2, end_id=V - 2)
+    got = host(ids)[:, 2]
+    assert got.tolist() == [V - 1, 0, V // 2, 3, 0, V - 2]
+    assert host(finished).tolist() == [0, 0, 0, 0, 1, 1]
+    assert not host(ids)[:, [0, 1, 3, 4]].any()
+
+
 @pytest.mark.parametrize("shape", [(1, 1024, 1024), (8, 4096, 1024), (13, 100, 36), (16, 32000, 256), (33, 1024, 4096),
                                    (64, 1024, 1024), (64, 40, 8)])
 def test_gemm_few_rows(capi, shape):
