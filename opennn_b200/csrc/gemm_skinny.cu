@@ -2,11 +2,14 @@
 //
 // One decoding step of the transformer multiplies [batch, 1, E] activations by every weight matrix of the decoder: the
 // product is a weight stream, bound by HBM, and a 128-row tensor-core tile would give it to N/256 CTAs.  Here the weight
-// matrix is cut into strips of 32 columns and, while that gives fewer than two CTAs per SM, each strip into 2, 4 or 8
-// ranges of K; the CTAs of a strip form a thread-block cluster, each streams its slab through a deep cp.async ring (the
-// M rows of A with it), keeps a [MB, 32] partial tile in registers, and the cluster adds the partial tiles through
-// distributed shared memory in a fixed order -- no workspace, no atomics, the same bits on every run.  A 1024 x 1024
-// matrix is read by 256 CTAs, each with ~50 KB of loads in flight.
+// matrix is cut into strips of 128 columns (64 for more than 16 rows, 32 for a narrow matrix) and, while the strips
+// alone leave SMs idle, each strip into 2, 4 or 8 ranges of K; the CTAs of a strip form a thread-block cluster.  Each
+// CTA streams its slab through a deep cp.async ring (the M rows of A with it); a thread keeps an 8 x 4 block of the
+// tile in registers for its share of the K rows of every ring slot; the K shares inside the CTA, then the CTAs of the
+// cluster (through distributed shared memory), are added in a fixed order -- no workspace, no atomics, the same bits
+// on every run.  Measured on a B200 inside a CUDA graph (weights not in L2): 8 x 1024 x 1024 in 5.1 us, 8 x 1024 x 4096
+// in 8.3 us, 8 x 4096 x 1024 in 10.5 us, against 1.5 us for an empty node; 64 rows take 11, 19 and 34 us (CUDA-core
+// arithmetic).  The tensor-core kernel keeps vocabulary-sized matrices: its 1 KB TMA rows read DRAM three times faster.
 #include <cooperative_groups.h>
 
 #include <cstdlib>
@@ -21,10 +24,8 @@ namespace onn
 {
 namespace skinny
 {
-constexpr int BN = 32, BK = 32, THREADS = 128;
+constexpr int BK = 32, THREADS = 256;
 constexpr int A_PITCH = BK + 4;              // floats; keeps 16-byte alignment of every row
-// ring depth by rows per thread: about 50 KB of shared memory per CTA in every variant
-__host__ __device__ constexpr int stages_for(int rm) { return rm == 1 ? 8 : (rm == 2 ? 6 : 4); }
 
 struct Params
 {
@@ -44,21 +45,28 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool val
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
-template <int RM> struct Stage { float w[BK][BN]; float a[16 * RM][A_PITCH]; };
+// One ring slot: BK rows of the strip and the same K range of the MB rows of A.
+template <int MB, int BN> struct Stage { float w[BK][BN]; float a[MB][A_PITCH]; };
+// ring depth: about 54 KB (narrow strips) or 110 KB (wide strips) of shared memory per CTA
+template <int MB, int BN> __host__ __device__ constexpr int stages_for() { return (BN == 32 ? 54 : 110) * 1024 / (int)sizeof(Stage<MB, BN>); }
 
-// RM rows per thread: the CTA holds MB = 16 * RM rows of A.  SPLITS CTAs (a cluster along y) share a strip.
-template <int RM, int SPLITS>
+// The CTA computes an [MB, BN] tile over its K range.  A thread owns 8 rows x 4 columns of it (so a float4 of the strip
+// read from shared memory feeds 32 FMAs); the 256 threads are BN/4 across, MB/8 down and KS = 8192/(MB*BN) deep: the
+// BK rows of a ring slot are dealt to the KS slices, whose tiles are added in a fixed order at the end.
+// SPLITS CTAs (a cluster along y) share a strip.
+template <int MB, int BN, int SPLITS>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(const Params p)
 {
-    constexpr int MB = 16 * RM, STAGES = stages_for(RM);
-    using Stage = skinny::Stage<RM>;
+    constexpr int STAGES = stages_for<MB, BN>(), TX = BN / 4, TY = MB / 8, KS = THREADS / (TX * TY), KPS = BK / KS;
+    static_assert(TX * TY * KS == THREADS && KPS * KS == BK && KPS >= 1 && STAGES >= 3, "tile shape");
+    using Stage = skinny::Stage<MB, BN>;
     extern __shared__ __align__(16) unsigned char ring[];
     Stage* stages = reinterpret_cast<Stage*>(ring);
-    static_assert(sizeof(Stage) * STAGES >= sizeof(float) * MB * BN, "the partial tile reuses the ring");
+    static_assert(sizeof(Stage) * STAGES >= sizeof(float) * (KS + 1) * MB * BN, "the partial tiles reuse the ring");
 
     const int rank = SPLITS > 1 ? (int)blockIdx.y : 0;      // the cluster spans the whole y extent of the grid
-    const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;
+    const int tid = threadIdx.x, tx = tid % TX, ty = (tid / TX) % TY, ks = tid / (TX * TY);
     const long long n0 = (long long)blockIdx.x * BN;
     const long long k_begin = rank * p.k_chunk;
     const long long k_end = p.K < k_begin + p.k_chunk ? p.K : k_begin + p.k_chunk;
@@ -71,24 +79,25 @@ gemm_skinny_kernel(const Params p)
         Stage& s = stages[step % STAGES];
         const long long k0 = k_begin + (long long)step * BK;
 #pragma unroll
-        for(int i = 0; i < 2; i++)                       // W: BK rows of 8 float4
+        for(int i = 0; i < BK * TX / THREADS; i++)       // W: BK rows of TX float4; a warp covers whole rows where it can
         {
-            const int e = tid + i * THREADS, row = e >> 3, c4 = e & 7;
+            const int e = tid + i * THREADS, row = e / TX, c4 = e % TX;
             const long long gk = k0 + row, gn = n0 + c4 * 4;
             const bool valid = gk < k_end && gn < p.N;
             cp_async_16(&s.w[row][c4 * 4], valid ? p.W + gk * p.ldb + gn : p.W, valid);
         }
 #pragma unroll
-        for(int i = 0; i < RM; i++)                      // A: MB rows of 8 float4
+        for(int i = 0; i < (MB * 8 + THREADS - 1) / THREADS; i++)     // A: MB rows of 8 float4
         {
             const int e = tid + i * THREADS, m = e >> 3, k4 = e & 7;
+            if(MB * 8 % THREADS != 0 && e >= MB * 8) break;
             const long long gk = k0 + k4 * 4;
             const bool valid = m < p.M && gk < k_end;
             cp_async_16(&s.a[m][k4 * 4], valid ? p.A + m * p.lda + gk : p.A, valid);
         }
     };
 
-    float acc[RM][4] = {};
+    float acc[8][4] = {};
 
     for(int s = 0; s < STAGES - 1; s++)
     {
@@ -102,73 +111,61 @@ gemm_skinny_kernel(const Params p)
         if(step + STAGES - 1 < steps) load_stage(step + STAGES - 1);
         cp_async_commit();
         const Stage& s = stages[step % STAGES];
-#pragma unroll
-        for(int kk = 0; kk < BK; kk += 4)
+        if constexpr(KPS % 4 == 0)
         {
-            float4 a[RM];
+            // four K rows at a time: the rows of A come as float4 (one shared-memory wavefront per row, broadcast)
 #pragma unroll
-            for(int i = 0; i < RM; i++) a[i] = *reinterpret_cast<const float4*>(&s.a[ty * RM + i][kk]);
-#pragma unroll
-            for(int j = 0; j < 4; j++)
+            for(int j = 0; j < KPS; j += 4)
             {
-                const float4 w = *reinterpret_cast<const float4*>(&s.w[kk + j][tx * 4]);
+                const int k = ks * KPS + j;
+                float4 w[4];
 #pragma unroll
-                for(int i = 0; i < RM; i++)
+                for(int q = 0; q < 4; q++) w[q] = *reinterpret_cast<const float4*>(&s.w[k + q][tx * 4]);
+#pragma unroll
+                for(int r = 0; r < 8; r++)
                 {
-                    const float av = j == 0 ? a[i].x : (j == 1 ? a[i].y : (j == 2 ? a[i].z : a[i].w));
-                    acc[i][0] = fmaf(av, w.x, acc[i][0]);
-                    acc[i][1] = fmaf(av, w.y, acc[i][1]);
-                    acc[i][2] = fmaf(av, w.z, acc[i][2]);
-                    acc[i][3] = fmaf(av, w.w, acc[i][3]);
+                    const float4 a = *reinterpret_cast<const float4*>(&s.a[ty * 8 + r][k]);
+                    acc[r][0] = fmaf(a.x, w[0].x, acc[r][0]); acc[r][1] = fmaf(a.x, w[0].y, acc[r][1]);
+                    acc[r][2] = fmaf(a.x, w[0].z, acc[r][2]); acc[r][3] = fmaf(a.x, w[0].w, acc[r][3]);
+                    acc[r][0] = fmaf(a.y, w[1].x, acc[r][0]); acc[r][1] = fmaf(a.y, w[1].y, acc[r][1]);
+                    acc[r][2] = fmaf(a.y, w[1].z, acc[r][2]); acc[r][3] = fmaf(a.y, w[1].w, acc[r][3]);
+                    acc[r][0] = fmaf(a.z, w[2].x, acc[r][0]); acc[r][1] = fmaf(a.z, w[2].y, acc[r][1]);
+                    acc[r][2] = fmaf(a.z, w[2].z, acc[r][2]); acc[r][3] = fmaf(a.z, w[2].w, acc[r][3]);
+                    acc[r][0] = fmaf(a.w, w[3].x, acc[r][0]); acc[r][1] = fmaf(a.w, w[3].y, acc[r][1]);
+                    acc[r][2] = fmaf(a.w, w[3].z, acc[r][2]); acc[r][3] = fmaf(a.w, w[3].w, acc[r][3]);
+                }
+            }
+        }
+        else
+        {
+#pragma unroll
+            for(int j = 0; j < KPS; j++)
+            {
+                const int k = ks * KPS + j;
+                const float4 w = *reinterpret_cast<const float4*>(&s.w[k][tx * 4]);
+#pragma unroll
+                for(int r = 0; r < 8; r++)
+                {
+                    const float a = s.a[ty * 8 + r][k];
+                    acc[r][0] = fmaf(a, w.x, acc[r][0]); acc[r][1] = fmaf(a, w.y, acc[r][1]);
+                    acc[r][2] = fmaf(a, w.z, acc[r][2]); acc[r][3] = fmaf(a, w.w, acc[r][3]);
                 }
             }
         }
     }
     cp_async_wait<0>();
     pdl_launch_dependents();
+    __syncthreads();                                     // the ring is free: it now holds the tiles of the KS slices
 
-    if constexpr(SPLITS == 1)
-    {
+    float (*slices)[MB][BN] = reinterpret_cast<float (*)[MB][BN]>(ring);           // [KS] tiles, then the CTA's sum
+    float (*partial)[BN] = reinterpret_cast<float (*)[BN]>(ring + sizeof(float) * KS * MB * BN);
 #pragma unroll
-        for(int i = 0; i < RM; i++)
-        {
-            const int row = ty * RM + i;
-            if(row >= p.M) continue;
-#pragma unroll
-            for(int j = 0; j < 4; j++)
-            {
-                const long long n = n0 + tx * 4 + j;
-                if(n >= p.N) continue;
-                float value = p.alpha * acc[i][j];
-                if(p.bias) value += p.bias[n];
-                if(p.relu) value = fmaxf(value, 0.f);
-                float* dst = p.C + row * p.ldc + n;
-                *dst = p.accumulate ? *dst + value : value;
-            }
-        }
-    }
-    else
-    {
-    cg::cluster_group cluster = cg::this_cluster();
-    __syncthreads();                                     // the ring is free: it now holds this CTA's partial tile
-    float (*partial)[BN] = reinterpret_cast<float (*)[BN]>(&stages[0]);
-#pragma unroll
-    for(int i = 0; i < RM; i++)
-        *reinterpret_cast<float4*>(&partial[ty * RM + i][tx * 4]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-    cluster.sync();
+    for(int r = 0; r < 8; r++)
+        *reinterpret_cast<float4*>(&slices[ks][ty * 8 + r][tx * 4]) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+    __syncthreads();
 
-    // CTA `rank` adds rows [rank * MB/SPLITS, (rank + 1) * MB/SPLITS) of the partial tiles, always in the order 0..SPLITS-1
-    constexpr int ROWS = MB / SPLITS;
-    for(int o = tid; o < ROWS * BN; o += THREADS)
+    auto finish = [&](int row, int col, float sum)
     {
-        const int row = rank * ROWS + o / BN, col = o % BN;
-        float sum = 0.f;
-#pragma unroll
-        for(int q = 0; q < SPLITS; q++)
-        {
-            const float (*remote)[BN] = reinterpret_cast<const float (*)[BN]>(cluster.map_shared_rank(&stages[0], q));
-            sum += remote[row][col];
-        }
         const long long n = n0 + col;
         if(row < p.M && n < p.N)
         {
@@ -178,34 +175,50 @@ gemm_skinny_kernel(const Params p)
             float* dst = p.C + row * p.ldc + n;
             *dst = p.accumulate ? *dst + value : value;
         }
+    };
+
+    // the CTA's tile: slices added in the order 0..KS-1
+    for(int o = tid; o < MB * BN; o += THREADS)
+    {
+        const int row = o / BN, col = o % BN;
+        float sum = 0.f;
+#pragma unroll
+        for(int q = 0; q < KS; q++) sum += slices[q][row][col];
+        if constexpr(SPLITS == 1) finish(row, col, sum);
+        else partial[row][col] = sum;
     }
-    cluster.sync();                                      // nobody leaves while its tile is still being read
+
+    if constexpr(SPLITS > 1)
+    {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        // CTA `rank` adds its 1/SPLITS of the tile's elements over the cluster, always in the order 0..SPLITS-1
+        constexpr int SHARE = MB * BN / SPLITS;
+        static_assert(SHARE * SPLITS == MB * BN, "the tile divides among the cluster");
+        for(int o = tid; o < SHARE; o += THREADS)
+        {
+            const int element = rank * SHARE + o, row = element / BN, col = element % BN;
+            float sum = 0.f;
+#pragma unroll
+            for(int q = 0; q < SPLITS; q++)
+            {
+                const float (*remote)[BN] = reinterpret_cast<const float (*)[BN]>(cluster.map_shared_rank(&partial[0][0], q));
+                sum += remote[row][col];
+            }
+            finish(row, col, sum);
+        }
+        cluster.sync();                                  // nobody leaves while its tile is still being read
     }
 }
-}  // namespace skinny
 
-bool gemm_skinny_takes(const onn_gemm_args& g)
-{
-    static const bool enabled = []{ const char* e = std::getenv("ONN_B200_GEMM_SKINNY"); return !(e && e[0] == '0'); }();
-    if(!enabled || g.M > 64 || g.a_major != 0 || g.b_major != 1) return false;
-    if(g.batch_inner != 1 || g.batch_outer != 1 || g.k_parts > 1 || g.split_k > 1) return false;
-    if(g.relu_mask || g.relu_bits || g.relu_bits_out || g.colsum_out) return false;
-    if((g.K & 3) || (g.N & 3) || (g.lda & 3) || (g.ldb & 3)) return false;
-    if(((uintptr_t)g.A & 15) || ((uintptr_t)g.B & 15)) return false;
-    // CUDA-core arithmetic: past ~1 GFLOP the tensor-core kernel wins even with most of its tile rows empty
-    return g.M <= 16 || g.N * g.K <= (8LL << 20);
-}
-
-namespace skinny
-{
-template <int RM, int SPLITS>
+template <int MB, int BN, int SPLITS>
 int launch(const Params& p, cudaStream_t stream)
 {
-    constexpr size_t shared = sizeof(Stage<RM>) * stages_for(RM);
+    constexpr size_t shared = sizeof(Stage<MB, BN>) * stages_for<MB, BN>();
     static bool configured = false;                      // per instantiation; the attribute belongs to the function
     if(!configured)
     {
-        if(cudaFuncSetAttribute(gemm_skinny_kernel<RM, SPLITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
+        if(cudaFuncSetAttribute(gemm_skinny_kernel<MB, BN, SPLITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
             return ONN_ERR_CUDA;
         configured = true;
     }
@@ -223,39 +236,64 @@ int launch(const Params& p, cudaStream_t stream)
     attributes[1].val.clusterDim.z = 1;
     config.attrs = attributes;
     config.numAttrs = SPLITS > 1 ? 2 : 1;
-    if(cudaLaunchKernelEx(&config, gemm_skinny_kernel<RM, SPLITS>, p) != cudaSuccess) return ONN_ERR_CUDA;
+    if(cudaLaunchKernelEx(&config, gemm_skinny_kernel<MB, BN, SPLITS>, p) != cudaSuccess) return ONN_ERR_CUDA;
     count_launch();
     return ONN_OK;
 }
 
-template <int RM>
-int launch_rows(const Params& p, int splits, cudaStream_t stream)
+template <int MB, int BN>
+int launch_splits(const Params& p, int splits, cudaStream_t stream)
 {
     switch(splits)
     {
-        case 1: return launch<RM, 1>(p, stream);
-        case 2: return launch<RM, 2>(p, stream);
-        case 4: return launch<RM, 4>(p, stream);
-        default: return launch<RM, 8>(p, stream);
+        case 1: return launch<MB, BN, 1>(p, stream);
+        case 2: return launch<MB, BN, 2>(p, stream);
+        case 4: return launch<MB, BN, 4>(p, stream);
+        default: return launch<MB, BN, 8>(p, stream);
     }
 }
+
+inline int launch_shape(const Params& p, int bn, int splits, cudaStream_t stream)
+{
+    if(bn == 128) return p.M <= 8 ? launch_splits<8, 128>(p, splits, stream) : launch_splits<16, 128>(p, splits, stream);
+    if(bn == 64) return p.M <= 32 ? launch_splits<32, 64>(p, splits, stream) : launch_splits<64, 64>(p, splits, stream);
+    if(p.M <= 8) return launch_splits<8, 32>(p, splits, stream);
+    if(p.M <= 16) return launch_splits<16, 32>(p, splits, stream);
+    if(p.M <= 32) return launch_splits<32, 32>(p, splits, stream);
+    return launch_splits<64, 32>(p, splits, stream);
+}
 }  // namespace skinny
+
+bool gemm_skinny_takes(const onn_gemm_args& g)
+{
+    static const bool enabled = []{ const char* e = std::getenv("ONN_B200_GEMM_SKINNY"); return !(e && e[0] == '0'); }();
+    if(!enabled || g.M > 64 || g.a_major != 0 || g.b_major != 1) return false;
+    if(g.batch_inner != 1 || g.batch_outer != 1 || g.k_parts > 1 || g.split_k > 1) return false;
+    if(g.relu_mask || g.relu_bits || g.relu_bits_out || g.colsum_out) return false;
+    if((g.K & 3) || (g.N & 3) || (g.lda & 3) || (g.ldb & 3)) return false;
+    if(((uintptr_t)g.A & 15) || ((uintptr_t)g.B & 15)) return false;
+    // 32-column strips read 128 bytes per matrix row: fine while the matrix is a few MB, well below the DRAM rate of
+    // the tensor-core kernel's 1 KB TMA rows on a vocabulary-sized one (measured: 1.5 against 4.5 TB/s on 1024 x 32000)
+    return g.N * g.K <= (8LL << 20);
+}
 
 int gemm_skinny_launch(const onn_gemm_args& g, cudaStream_t stream)
 {
     using namespace skinny;
-    // split K while the strips alone give fewer than two CTAs per SM and a CTA keeps at least two steps
-    const long long strips = (g.N + BN - 1) / BN;
+    // Strips of 128 columns (512 contiguous bytes of every matrix row per request) for up to 16 rows of A, of 64 columns
+    // beyond (the arithmetic of 64 rows wants two CTAs per SM), of 32 for a narrow matrix; K is split while the strips
+    // alone leave SMs idle and a CTA keeps at least two steps, up to a cluster of 8 (16 measured no faster).
+    const int bn = g.N < 512 ? 32 : (g.M > 16 ? 64 : 128);
+    const long long strips = (g.N + bn - 1) / bn;
+    const long long enough = bn == 128 ? 128 : 256;
     int splits = 1;
-    while(splits < 8 && strips * splits < 296 && g.K / (splits * 2) >= 2 * BK) splits *= 2;
+    while(splits < 8 && strips * splits < enough && g.K / (splits * 2) >= 2 * BK) splits *= 2;
     Params p;
     p.A = g.A; p.W = g.B; p.bias = g.bias; p.C = g.C;
     p.M = g.M; p.N = g.N; p.K = g.K; p.lda = g.lda; p.ldb = g.ldb; p.ldc = g.ldc;
     p.k_chunk = ((g.K + splits - 1) / splits + BK - 1) / BK * BK;
     p.alpha = g.alpha; p.relu = g.relu ? 1 : 0; p.accumulate = (g.flags & ONN_ACCUMULATE) ? 1 : 0;
-    if(g.M <= 16) return launch_rows<1>(p, splits, stream);
-    if(g.M <= 32) return launch_rows<2>(p, splits, stream);
-    return launch_rows<4>(p, splits, stream);
+    return launch_shape(p, bn, splits, stream);
 }
 
 }  // namespace onn

@@ -294,7 +294,7 @@ def test_greedy_next_token_rows(capi, V):
 
 
 @pytest.mark.parametrize("shape", [(1, 1024, 1024), (8, 4096, 1024), (13, 100, 36), (16, 32000, 256), (33, 1024, 4096),
-                                   (64, 1024, 1024), (64, 40, 8)])
+                                   (64, 1024, 1024), (64, 40, 8), (20, 2048, 512), (30, 200, 72), (5, 64, 4096)])
 def test_gemm_few_rows(capi, shape):
     """At most 64 rows against a row-major [K, N] matrix (one decoding step): the fp32 cluster kernel that streams the
     matrix with 8 CTAs per 32-column strip.  Ragged M, N and K, row pitches wider than the rows, bias + ReLU + alpha,
