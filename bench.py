@@ -265,6 +265,31 @@ def time_row_kernels(capi, torch, w):
     return {"kernel": "layernorm_fwd/bwd, ce3d_fwd_bwd, adam", "kernels": out}
 
 
+def time_greedy_decode(trainer, torch, w, rows, tokens):
+    """Greedy decoding of `rows` source sequences with cached keys and values, `tokens` target positions each (the
+    caller of the same layers on the inference side): one eager call, one that captures a graph per position, then timed
+    replays.  Random parameters, no END token, so every row runs to the full length."""
+    import time
+    import numpy as np
+    t = trainer.Trainer(trainer.TRANSFORMER, w["S_in"], tokens, w["V_in"], w["V_out"], w["E"], w["H"], w["F"], w["L"], rows)
+    rng = np.random.default_rng(0)
+    t.set_parameters((0.02 * rng.standard_normal(t.parameters_number)).astype(np.float32))
+    source = rng.integers(1, w["V_in"], size=(rows, w["S_in"])).astype(np.float32)
+    reference = t.greedy_decode(source, end_id=-1, cached=True)
+    t.greedy_decode(source, end_id=-1, cached=True)
+    best = float("inf")
+    same = True
+    for _ in range(2):
+        torch.cuda.synchronize()
+        start = time.perf_counter()
+        out = t.greedy_decode(source, end_id=-1, cached=True)
+        best = min(best, time.perf_counter() - start)
+        same = same and bool((out == reference).all())
+    t.close()
+    return {"decode": "greedy, cached keys and values, one CUDA graph per position", "rows": rows, "tokens_per_row": tokens - 1,
+            "seconds": best, "tokens_per_s": rows * (tokens - 1) / best, "replay_matches_eager": same}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -303,6 +328,10 @@ def run_ours(args):
         return
     if args.profile_kernel == "attention":
         emit(dict(time_attention_core(capi, torch, w), profiling_only=True))
+        return
+    if args.profile_kernel == "decode":
+        rows = args.profile_batch or 8
+        emit(dict(time_greedy_decode(trainer, torch, w, rows, args.decode_tokens or w["S_dec"]), profiling_only=True))
         return
     if args.profile_batch:
         w = dict(w, global_batch=args.profile_batch, name=w["name"] + f" (profiling batch {args.profile_batch})")
@@ -427,10 +456,12 @@ def main():
     parser.add_argument("--micro-batch", type=int, default=0, help="samples per micro-batch (default: the workload's own)")
     parser.add_argument("--workload", default="config5", choices=["config5", "config2"],
                         help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network")
-    parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention", "rowwise"],
+    parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention", "rowwise", "decode"],
                         help="profiling aid: launch only the dominant GEMM (FFN-up shape) four times on buffers larger than L2, "
                              "or only one attention layer (forward and backward, 32 samples) twice, or only the HBM-bound kernels "
-                             "(LayerNorm forward / backward, fused softmax-cross-entropy, Adam) at the benchmark's sizes")
+                             "(LayerNorm forward / backward, fused softmax-cross-entropy, Adam) at the benchmark's sizes; decode: greedy decoding "
+                             "with cached keys and values of --profile-batch rows (default 8) over --decode-tokens positions")
+    parser.add_argument("--decode-tokens", type=int, default=0, help="target positions for --profile-kernel decode (default: the workload's)")
     args = parser.parse_args()
     # Libraries (NCCL prints its version) write to file descriptor 1: keep it for the ONE JSON line by
     # pointing fd 1 at stderr while the benchmark runs and printing the line to the saved descriptor.
