@@ -413,6 +413,43 @@ def run_ours(args):
     if status != 0:
         raise SystemExit("a tcgen05 GEMM gave up on a bounded wait: the numbers are void")
 
+    # Data-parallel runs: what the gradient exchange costs.  (a) the all-reduce of the whole gradient arena on its own,
+    # through the library's communicator, as bus bandwidth 2(n-1)/n * bytes / time; (b) the same local batches stepped
+    # without any exchange: the difference to the data-parallel step is the time the exchange is NOT hidden behind
+    # back-propagation (replicas diverge from here on, which no longer matters: nothing is measured after it).
+    allreduce = None
+    if world > 1:
+        import ctypes
+        arena = torch.zeros(t.parameters_number, device="cuda")
+        torch_stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def exchange(_):
+            capi.check(capi.lib().onn_dp_allreduce(comm, capi.ptr(arena), ctypes.c_int64(arena.numel()), torch_stream), "onn_dp_allreduce")
+            capi.check(capi.lib().onn_dp_wait(comm, torch_stream), "onn_dp_wait")
+
+        def timed_on_current(fn, repeats):
+            barrier()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(repeats):
+                fn(i)
+            stop.record()
+            barrier()
+            elapsed = torch.tensor([start.elapsed_time(stop)], device="cuda")
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+            return float(elapsed.item()) * 1e-3 / repeats
+
+        exchange(0)
+        exchange_seconds = timed_on_current(exchange, 5)
+        t.set_dp(None, 1)
+        device_step(0)
+        local_seconds = timed(device_step, args.steps) / args.steps
+        arena_bytes = 4 * t.parameters_number
+        allreduce = {"bytes": arena_bytes, "alone_ms": 1e3 * exchange_seconds,
+                     "bus_gbs": 2 * (world - 1) / world * arena_bytes / exchange_seconds / 1e9,
+                     "step_ms_without_exchange": 1e3 * local_seconds,
+                     "exposed_ms_per_step": 1e3 * (seconds / args.steps - local_seconds)}
+
     if rank == 0:
         roofline = time_dominant_kernel(capi, torch, w, peaks)
         cpu = None
@@ -435,7 +472,11 @@ def run_ours(args):
                     "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4 * (4 * (local_batch // micro) + 2) * world,
                     "last_loss": last_stats[0][0] if last_stats[0] else None},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            # decoder tokens are the metric's unit; the encoder side of every sample is computed as well
+            "encoder_plus_decoder_tokens_per_s": (w["global_batch"] * (w["S_dec"] + w["S_in"])) * args.steps / seconds,
         }
+        if allreduce:
+            line["allreduce"] = allreduce
         emit(line)
 
     t.close()
