@@ -1,4 +1,5 @@
-// fp32 GEMM for a handful of rows: C[M,N] = alpha * A[M,K] W[K,N] (+ bias)(ReLU), M <= 64.
+// GEMM for a handful of rows: C[M,N] = alpha * A[M,K] W[K,N] (+ bias)(ReLU), M <= 64.  fp32 arithmetic up to 16 rows (and
+// for a matrix narrower than 512 columns), tf32 mma with fp32 accumulation for 17 to 64 rows.
 //
 // One decoding step of the transformer multiplies [batch, 1, E] activations by every weight matrix of the decoder: the
 // product is a weight stream, bound by HBM, and a 128-row tensor-core tile would give it to N/256 CTAs.  Here the weight
@@ -8,8 +9,9 @@
 // tile in registers for its share of the K rows of every ring slot; the K shares inside the CTA, then the CTAs of the
 // cluster (through distributed shared memory), are added in a fixed order -- no workspace, no atomics, the same bits
 // on every run.  Measured on a B200 inside a CUDA graph (weights not in L2): 8 x 1024 x 1024 in 5.1 us, 8 x 1024 x 4096
-// in 8.3 us, 8 x 4096 x 1024 in 10.5 us, against 1.5 us for an empty node; 64 rows take 11, 19 and 34 us (CUDA-core
-// arithmetic).  The tensor-core kernel keeps vocabulary-sized matrices: its 1 KB TMA rows read DRAM three times faster.
+// in 8.3 us, 8 x 4096 x 1024 in 10.5 us, against 1.5 us for an empty node; 64 rows take 7.8, 12 and 17.7 us with the mma
+// variant below (11, 19 and 34 us on CUDA cores).  The tcgen05 kernel keeps vocabulary-sized matrices: its 1 KB TMA
+// rows read DRAM three times faster.
 #include <cooperative_groups.h>
 
 #include <cstdlib>
@@ -211,19 +213,178 @@ gemm_skinny_kernel(const Params p)
     }
 }
 
-template <int MB, int BN, int SPLITS>
-int launch(const Params& p, cudaStream_t stream)
+// ---------------------------------------------------------------------------------------------------------------
+// 17 to 64 rows: the same weight stream, but the arithmetic (64 x K x N FMAs) no longer hides behind it on CUDA cores.
+// This variant keeps the ring, the strips (64 columns) and the cluster reduction and does the products with
+// mma.sync m16n8k8 on tf32 operands rounded to nearest from the fp32 values in shared memory (fp32 accumulation), as
+// the tensor-core path of the large GEMMs does.  8 warps: MB/32 down (two 16-row tiles each), the rest across.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int MMA_BN = 64, MMA_W_PITCH = MMA_BN + 8;     // pitch 72: the four K rows a fragment load touches fall in distinct banks
+template <int MB> struct MmaStage { float w[BK][MMA_W_PITCH]; float a[MB][A_PITCH]; };
+template <int MB> __host__ __device__ constexpr int mma_stages() { return 110 * 1024 / (int)sizeof(MmaStage<MB>); }
+
+__device__ __forceinline__ uint32_t to_tf32(float x)
 {
-    constexpr size_t shared = sizeof(Stage<MB, BN>) * stages_for<MB, BN>();
-    static bool configured = false;                      // per instantiation; the attribute belongs to the function
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int MB, int SPLITS>
+__global__ void __launch_bounds__(THREADS)
+gemm_skinny_mma_kernel(const Params p)
+{
+    constexpr int BN = MMA_BN, STAGES = mma_stages<MB>(), WM = MB / 32, WN = 8 / WM, NT = BN / (8 * WN);
+    static_assert(WM >= 1 && WM * 32 == MB && NT >= 1 && STAGES >= 3, "tile shape");
+    using Stage = MmaStage<MB>;
+    extern __shared__ __align__(16) unsigned char ring[];
+    Stage* stages = reinterpret_cast<Stage*>(ring);
+    static_assert(sizeof(Stage) * STAGES >= sizeof(float) * MB * BN, "the partial tile reuses the ring");
+
+    const int rank = SPLITS > 1 ? (int)blockIdx.y : 0;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int warp_m = warp % WM, warp_n = warp / WM;
+    const long long n0 = (long long)blockIdx.x * BN;
+    const long long k_begin = rank * p.k_chunk;
+    const long long k_end = p.K < k_begin + p.k_chunk ? p.K : k_begin + p.k_chunk;
+    const int steps = k_end > k_begin ? (int)((k_end - k_begin + BK - 1) / BK) : 0;
+
+    pdl_wait();
+
+    auto load_stage = [&](int step)
+    {
+        Stage& s = stages[step % STAGES];
+        const long long k0 = k_begin + (long long)step * BK;
+#pragma unroll
+        for(int i = 0; i < BK * (BN / 4) / THREADS; i++)
+        {
+            const int e = tid + i * THREADS, row = e / (BN / 4), c4 = e % (BN / 4);
+            const long long gk = k0 + row, gn = n0 + c4 * 4;
+            const bool valid = gk < k_end && gn < p.N;
+            cp_async_16(&s.w[row][c4 * 4], valid ? p.W + gk * p.ldb + gn : p.W, valid);
+        }
+#pragma unroll
+        for(int i = 0; i < MB * 8 / THREADS; i++)
+        {
+            const int e = tid + i * THREADS, m = e >> 3, k4 = e & 7;
+            const long long gk = k0 + k4 * 4;
+            const bool valid = m < p.M && gk < k_end;
+            cp_async_16(&s.a[m][k4 * 4], valid ? p.A + m * p.lda + gk : p.A, valid);
+        }
+    };
+
+    float acc[2][NT][4] = {};
+
+    for(int s = 0; s < STAGES - 1; s++)
+    {
+        if(s < steps) load_stage(s);
+        cp_async_commit();
+    }
+    for(int step = 0; step < steps; step++)
+    {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        if(step + STAGES - 1 < steps) load_stage(step + STAGES - 1);
+        cp_async_commit();
+        const Stage& s = stages[step % STAGES];
+#pragma unroll
+        for(int k8 = 0; k8 < BK; k8 += 8)
+        {
+            uint32_t a[2][4], b[NT][2];
+#pragma unroll
+            for(int mt = 0; mt < 2; mt++)
+            {
+                const int row = warp_m * 32 + mt * 16 + g;
+                a[mt][0] = to_tf32(s.a[row][k8 + t]);
+                a[mt][1] = to_tf32(s.a[row + 8][k8 + t]);
+                a[mt][2] = to_tf32(s.a[row][k8 + t + 4]);
+                a[mt][3] = to_tf32(s.a[row + 8][k8 + t + 4]);
+            }
+#pragma unroll
+            for(int nt = 0; nt < NT; nt++)
+            {
+                const int col = (warp_n * NT + nt) * 8 + g;
+                b[nt][0] = to_tf32(s.w[k8 + t][col]);
+                b[nt][1] = to_tf32(s.w[k8 + t + 4][col]);
+            }
+#pragma unroll
+            for(int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for(int nt = 0; nt < NT; nt++) mma_tf32(acc[mt][nt], a[mt], b[nt]);
+        }
+    }
+    cp_async_wait<0>();
+    pdl_launch_dependents();
+    __syncthreads();                                     // the ring is free: it now holds this CTA's tile
+
+    float (*partial)[BN] = reinterpret_cast<float (*)[BN]>(ring);
+#pragma unroll
+    for(int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for(int nt = 0; nt < NT; nt++)
+        {
+            const int row = warp_m * 32 + mt * 16 + g, col = (warp_n * NT + nt) * 8 + 2 * t;
+            *reinterpret_cast<float2*>(&partial[row][col]) = make_float2(acc[mt][nt][0], acc[mt][nt][1]);
+            *reinterpret_cast<float2*>(&partial[row + 8][col]) = make_float2(acc[mt][nt][2], acc[mt][nt][3]);
+        }
+
+    auto finish = [&](int row, int col, float sum)
+    {
+        const long long n = n0 + col;
+        if(row < p.M && n < p.N)
+        {
+            float value = p.alpha * sum;
+            if(p.bias) value += p.bias[n];
+            if(p.relu) value = fmaxf(value, 0.f);
+            float* dst = p.C + row * p.ldc + n;
+            *dst = p.accumulate ? *dst + value : value;
+        }
+    };
+
+    if constexpr(SPLITS == 1)
+    {
+        __syncthreads();
+        for(int o = tid; o < MB * BN; o += THREADS) finish(o / BN, o % BN, partial[o / BN][o % BN]);
+    }
+    else
+    {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        constexpr int SHARE = MB * BN / SPLITS;
+        for(int o = tid; o < SHARE; o += THREADS)
+        {
+            const int element = rank * SHARE + o, row = element / BN, col = element % BN;
+            float sum = 0.f;
+#pragma unroll
+            for(int q = 0; q < SPLITS; q++)
+            {
+                const float (*remote)[BN] = reinterpret_cast<const float (*)[BN]>(cluster.map_shared_rank(&partial[0][0], q));
+                sum += remote[row][col];
+            }
+            finish(row, col, sum);
+        }
+        cluster.sync();                                  // nobody leaves while its tile is still being read
+    }
+}
+
+// Launch with the cluster along y (and programmatic dependent launch, as every kernel of the step).
+template <typename Kernel>
+int launch_kernel(Kernel kernel, bool& configured, size_t shared, int bn, int splits, const Params& p, cudaStream_t stream)
+{
     if(!configured)
     {
-        if(cudaFuncSetAttribute(gemm_skinny_kernel<MB, BN, SPLITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
-            return ONN_ERR_CUDA;
+        if(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess) return ONN_ERR_CUDA;
         configured = true;
     }
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)((p.N + BN - 1) / BN), SPLITS, 1);
+    config.gridDim = dim3((unsigned)((p.N + bn - 1) / bn), splits, 1);
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = shared;
     config.stream = stream;
@@ -232,13 +393,39 @@ int launch(const Params& p, cudaStream_t stream)
     attributes[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     attributes[1].id = cudaLaunchAttributeClusterDimension;
     attributes[1].val.clusterDim.x = 1;
-    attributes[1].val.clusterDim.y = SPLITS;
+    attributes[1].val.clusterDim.y = splits;
     attributes[1].val.clusterDim.z = 1;
     config.attrs = attributes;
-    config.numAttrs = SPLITS > 1 ? 2 : 1;
-    if(cudaLaunchKernelEx(&config, gemm_skinny_kernel<MB, BN, SPLITS>, p) != cudaSuccess) return ONN_ERR_CUDA;
+    config.numAttrs = splits > 1 ? 2 : 1;
+    if(cudaLaunchKernelEx(&config, kernel, p) != cudaSuccess) return ONN_ERR_CUDA;
     count_launch();
     return ONN_OK;
+}
+
+template <int MB, int SPLITS>
+int launch_mma(const Params& p, cudaStream_t stream)
+{
+    static bool configured = false;                      // per instantiation; the attribute belongs to the function
+    return launch_kernel(gemm_skinny_mma_kernel<MB, SPLITS>, configured, sizeof(MmaStage<MB>) * mma_stages<MB>(), MMA_BN, SPLITS, p, stream);
+}
+
+template <int MB>
+int launch_mma_splits(const Params& p, int splits, cudaStream_t stream)
+{
+    switch(splits)
+    {
+        case 1: return launch_mma<MB, 1>(p, stream);
+        case 2: return launch_mma<MB, 2>(p, stream);
+        case 4: return launch_mma<MB, 4>(p, stream);
+        default: return launch_mma<MB, 8>(p, stream);
+    }
+}
+
+template <int MB, int BN, int SPLITS>
+int launch(const Params& p, cudaStream_t stream)
+{
+    static bool configured = false;                      // per instantiation; the attribute belongs to the function
+    return launch_kernel(gemm_skinny_kernel<MB, BN, SPLITS>, configured, sizeof(Stage<MB, BN>) * stages_for<MB, BN>(), BN, SPLITS, p, stream);
 }
 
 template <int MB, int BN>
@@ -256,7 +443,7 @@ int launch_splits(const Params& p, int splits, cudaStream_t stream)
 inline int launch_shape(const Params& p, int bn, int splits, cudaStream_t stream)
 {
     if(bn == 128) return p.M <= 8 ? launch_splits<8, 128>(p, splits, stream) : launch_splits<16, 128>(p, splits, stream);
-    if(bn == 64) return p.M <= 32 ? launch_splits<32, 64>(p, splits, stream) : launch_splits<64, 64>(p, splits, stream);
+    if(bn == 64) return p.M <= 32 ? launch_mma_splits<32>(p, splits, stream) : launch_mma_splits<64>(p, splits, stream);
     if(p.M <= 8) return launch_splits<8, 32>(p, splits, stream);
     if(p.M <= 16) return launch_splits<16, 32>(p, splits, stream);
     if(p.M <= 32) return launch_splits<32, 32>(p, splits, stream);
