@@ -99,3 +99,26 @@ def test_classifier_training_steps(libs, name, gemm):
     assert np.abs(after - g["params_out"]).max() <= 2.2 * 1e-3 * steps
     assert capi.lib().onn_gemm_device_status() == 0
     c.close()
+
+
+def test_classifier_at_transformer_sizes(libs):
+    """The classifier at the layer sizes of the benchmark network (64 x 256 tokens, E 1024, 16 heads, hidden 4096), where
+    the CPU oracle is out of reach: loss and gradients of a freshly initialised network are finite, repeated steps on one batch bring the loss down, and the probabilities of every sample sum to one."""
+    capi, trainer = libs
+    capi.check(capi.lib().onn_gemm_set_mode(0))
+    B, S, V, E, H, hidden, classes = 64, 256, 32000, 1024, 16, 4096, 8
+    rng = np.random.default_rng(3)
+    ids = O.synthetic_ids(rng, B, S, V, 64, S)
+    targets = np.eye(classes, dtype=np.float32)[rng.integers(0, classes, B)]
+    ids_d, targets_d = torch.from_numpy(ids).cuda(), torch.from_numpy(targets).cuda()
+    c = trainer.TextClassifier(V, S, E, H, [hidden], classes, B)
+    probabilities = c.forward(ids_d)
+    assert np.abs(probabilities.sum(axis=1) - 1).max() <= 1e-5
+    first, norm = c.step_device(ids_d, targets_d, update=False)
+    assert np.isfinite(first) and np.isfinite(norm) and norm > 0
+    assert first > 0
+    assert np.isfinite(c.get_gradients()).all()
+    losses = [c.step_device(ids_d, targets_d, update=True)[0] for _ in range(12)]
+    assert losses[-1] < losses[0], losses
+    assert capi.lib().onn_gemm_device_status() == 0
+    c.close()
