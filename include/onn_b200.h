@@ -229,6 +229,12 @@ int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y, uint
  * dX_colsum (optional, [in]): the column sums of dX (after the mask) are ADDED to it -- that is the
  * bias gradient of the layer that produced X, which may then pass db = NULL in its own call.
  * db may be NULL (bias gradient not wanted here). */
+/* Several Linear Dense forward passes over the same input: Y[i] = X W[i] + b[i], i < count <= 4, row pitch ldy[i] >= out
+ * (the query, key and value projections of a self-attention layer on one decoding position, whose key and value rows
+ * go straight into their cache slots).  One launch when rows <= 64 and the few-rows kernel takes the shape, else one
+ * product after the other.  b may be NULL (no biases). */
+int onn_dense_fwd_shared_input(const float* X, const float* const* W, const float* const* b, float* const* Y,
+                               const int64_t* ldy, int count, int64_t rows, int64_t in, int64_t out, void* stream);
 int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
                   float* dW, float* db, float* dX, const float* dX_relu_mask, const uint32_t* dX_relu_bits,
                   float* dX_colsum,
@@ -351,10 +357,12 @@ int onn_greedy_next_token_rows(const float* probabilities, float* ids, int* fini
 
 /* Attention of ONE query row per sample against keys and values kept from earlier decoding steps (no counterpart in
  * the reference, whose decoding loop recomputes every position for every token): q [B, E] (projected), k_cache and
- * v_cache [B, S_cache, E] of which the first `length` rows are valid, key_is_pad [B, S_cache] bytes or NULL (a set flag
- * overwrites the score with -1e9 as in onn_mha_fwd), out [B, E] = concatenated head outputs before the output
- * projection.  Scale 1/sqrt(E/H).  fp32 throughout. */
-int onn_decode_attention(const float* q, const float* k_cache, const float* v_cache, const uint8_t* key_is_pad, float* out,
+ * v_cache [B, S_cache, E] of which the first `length` rows are valid, key_is_pad bytes or NULL: the flag of key j of
+ * sample b is key_is_pad[b * pad_stride_sample + j * pad_stride_key] ([B, S_cache]: strides S_cache and 1; one row of B
+ * flags per position, as a producing kernel writes them: strides 1 and B); a set flag overwrites the score with -1e9 as
+ * in onn_mha_fwd.  out [B, E] = concatenated head outputs before the output projection.  Scale 1/sqrt(E/H).  fp32. */
+int onn_decode_attention(const float* q, const float* k_cache, const float* v_cache, const uint8_t* key_is_pad,
+                         int64_t pad_stride_sample, int64_t pad_stride_key, float* out,
                          int64_t B, int64_t S_cache, int64_t length, int64_t E, int64_t H, void* stream);
 /* flags[r] = 1 where every feature of row r has |x| <= 1e-7: the key-padding rule of MultiHeadAttention
  * (opennn/multihead_attention_layer.cpp:574-603) for a caller that keeps its own key cache. */

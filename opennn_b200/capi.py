@@ -57,7 +57,7 @@ EXPORTS = [
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
     "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_pooling3d_fwd", "onn_pooling3d_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
-    "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
+    "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_dense_fwd_shared_input", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
     "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam",
     "onn_dp_unique_id", "onn_dp_init", "onn_dp_allreduce", "onn_dp_wait", "onn_dp_finalize",
 ]
@@ -318,13 +318,27 @@ def ce2d(probabilities, targets):
     return float(stats[0]), probabilities
 
 
-def decode_attention(q, k_cache, v_cache, key_is_pad, length, H):
+def dense_fwd_shared_input(x, weights, biases, outputs, pitches):
+    """outputs[i][:, :out] = x @ weights[i] + biases[i]; outputs are preallocated, row pitch pitches[i] floats."""
+    count = len(weights)
+    rows, features = x.shape
+    out = weights[0].shape[1]
+    W = (C.c_void_p * count)(*[w.data_ptr() for w in weights])
+    b = (C.c_void_p * count)(*[v.data_ptr() for v in biases]) if biases is not None else None
+    Y = (C.c_void_p * count)(*[y.data_ptr() for y in outputs])
+    ld = (C.c_int64 * count)(*pitches)
+    check(lib().onn_dense_fwd_shared_input(ptr(x), W, b, Y, ld, count, i64(rows), i64(features), i64(out), stream_ptr()),
+          "onn_dense_fwd_shared_input")
+
+
+def decode_attention(q, k_cache, v_cache, key_is_pad, length, H, position_major=False):
     """One query row per sample against the first `length` cached keys and values.  q [B, E]; caches [B, S_cache, E];
-    key_is_pad uint8 [B, S_cache] or None.  Returns the context [B, E]."""
+    key_is_pad uint8 [B, S_cache] (or [S_cache, B] with position_major) or None.  Returns the context [B, E]."""
     B, S_cache, E = k_cache.shape
     out = torch.empty(B, E, device="cuda")
-    check(lib().onn_decode_attention(ptr(q), ptr(k_cache), ptr(v_cache), ptr(key_is_pad), ptr(out), i64(B), i64(S_cache), i64(length),
-                                     i64(E), i64(H), stream_ptr()), "onn_decode_attention")
+    strides = (1, B) if position_major else (S_cache, 1)
+    check(lib().onn_decode_attention(ptr(q), ptr(k_cache), ptr(v_cache), ptr(key_is_pad), i64(strides[0]), i64(strides[1]), ptr(out),
+                                     i64(B), i64(S_cache), i64(length), i64(E), i64(H), stream_ptr()), "onn_decode_attention")
     return out
 
 

@@ -20,6 +20,8 @@ int gemm_tc_bounded_wait_selftest(int* gave_up_host);
 // 8 x N/32 CTAs, cluster reduction over K.  ONN_B200_GEMM_SKINNY=0 turns it off.
 bool gemm_skinny_takes(const onn_gemm_args& g);
 int gemm_skinny_launch(const onn_gemm_args& g, cudaStream_t stream);
+// `count` (at most 4) products that differ in B, bias, C and ldc only, each accepted by gemm_skinny_takes: one launch.
+int gemm_skinny_launch_shared_input(const onn_gemm_args* gs, int count, cudaStream_t stream);
 
 // Front end used by the layer code (same as onn_gemm).
 int gemm(const onn_gemm_args& g, cudaStream_t stream);

@@ -29,13 +29,17 @@ namespace skinny
 constexpr int BK = 32, THREADS = 256;
 constexpr int A_PITCH = BK + 4;              // floats; keeps 16-byte alignment of every row
 
+constexpr int MAX_PROBLEMS = 4;      // products that share A, N, K and the epilogue options in one launch (grid z)
+
 struct Params
 {
-    const float* A; const float* W; const float* bias; float* C;
-    long long M, N, K, lda, ldb, ldc;
+    const float* A;
+    const float* Ws[MAX_PROBLEMS]; const float* biases[MAX_PROBLEMS]; float* Cs[MAX_PROBLEMS]; long long ldcs[MAX_PROBLEMS];
+    long long M, N, K, lda, ldb;
     long long k_chunk;                       // K range of one CTA, a multiple of BK
     float alpha;
     int relu, accumulate;
+    int problems;                            // grid z
 };
 
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid)
@@ -68,6 +72,10 @@ gemm_skinny_kernel(const Params p)
     static_assert(sizeof(Stage) * STAGES >= sizeof(float) * (KS + 1) * MB * BN, "the partial tiles reuse the ring");
 
     const int rank = SPLITS > 1 ? (int)blockIdx.y : 0;      // the cluster spans the whole y extent of the grid
+    const float* const W = p.Ws[blockIdx.z];
+    const float* const bias = p.biases[blockIdx.z];
+    float* const C = p.Cs[blockIdx.z];
+    const long long ldc = p.ldcs[blockIdx.z];
     const int tid = threadIdx.x, tx = tid % TX, ty = (tid / TX) % TY, ks = tid / (TX * TY);
     const long long n0 = (long long)blockIdx.x * BN;
     const long long k_begin = rank * p.k_chunk;
@@ -86,7 +94,7 @@ gemm_skinny_kernel(const Params p)
             const int e = tid + i * THREADS, row = e / TX, c4 = e % TX;
             const long long gk = k0 + row, gn = n0 + c4 * 4;
             const bool valid = gk < k_end && gn < p.N;
-            cp_async_16(&s.w[row][c4 * 4], valid ? p.W + gk * p.ldb + gn : p.W, valid);
+            cp_async_16(&s.w[row][c4 * 4], valid ? W + gk * p.ldb + gn : W, valid);
         }
 #pragma unroll
         for(int i = 0; i < (MB * 8 + THREADS - 1) / THREADS; i++)     // A: MB rows of 8 float4
@@ -172,9 +180,9 @@ gemm_skinny_kernel(const Params p)
         if(row < p.M && n < p.N)
         {
             float value = p.alpha * sum;
-            if(p.bias) value += p.bias[n];
+            if(bias) value += bias[n];
             if(p.relu) value = fmaxf(value, 0.f);
-            float* dst = p.C + row * p.ldc + n;
+            float* dst = C + row * ldc + n;
             *dst = p.accumulate ? *dst + value : value;
         }
     };
@@ -249,6 +257,10 @@ gemm_skinny_mma_kernel(const Params p)
     static_assert(sizeof(Stage) * STAGES >= sizeof(float) * MB * BN, "the partial tile reuses the ring");
 
     const int rank = SPLITS > 1 ? (int)blockIdx.y : 0;
+    const float* const W = p.Ws[blockIdx.z];
+    const float* const bias = p.biases[blockIdx.z];
+    float* const C = p.Cs[blockIdx.z];
+    const long long ldc = p.ldcs[blockIdx.z];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int warp_m = warp % WM, warp_n = warp / WM;
     const long long n0 = (long long)blockIdx.x * BN;
@@ -268,7 +280,7 @@ gemm_skinny_mma_kernel(const Params p)
             const int e = tid + i * THREADS, row = e / (BN / 4), c4 = e % (BN / 4);
             const long long gk = k0 + row, gn = n0 + c4 * 4;
             const bool valid = gk < k_end && gn < p.N;
-            cp_async_16(&s.w[row][c4 * 4], valid ? p.W + gk * p.ldb + gn : p.W, valid);
+            cp_async_16(&s.w[row][c4 * 4], valid ? W + gk * p.ldb + gn : W, valid);
         }
 #pragma unroll
         for(int i = 0; i < MB * 8 / THREADS; i++)
@@ -341,9 +353,9 @@ gemm_skinny_mma_kernel(const Params p)
         if(row < p.M && n < p.N)
         {
             float value = p.alpha * sum;
-            if(p.bias) value += p.bias[n];
+            if(bias) value += bias[n];
             if(p.relu) value = fmaxf(value, 0.f);
-            float* dst = p.C + row * p.ldc + n;
+            float* dst = C + row * ldc + n;
             *dst = p.accumulate ? *dst + value : value;
         }
     };
@@ -384,7 +396,7 @@ int launch_kernel(Kernel kernel, bool& configured, size_t shared, int bn, int sp
         configured = true;
     }
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)((p.N + bn - 1) / bn), splits, 1);
+    config.gridDim = dim3((unsigned)((p.N + bn - 1) / bn), splits, (unsigned)p.problems);
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = shared;
     config.stream = stream;
@@ -464,23 +476,33 @@ bool gemm_skinny_takes(const onn_gemm_args& g)
     return g.N * g.K <= (8LL << 20);
 }
 
-int gemm_skinny_launch(const onn_gemm_args& g, cudaStream_t stream)
+int gemm_skinny_launch_shared_input(const onn_gemm_args* gs, int count, cudaStream_t stream)
 {
     using namespace skinny;
+    if(count < 1 || count > MAX_PROBLEMS) return ONN_ERR_INVALID_ARGUMENT;
+    const onn_gemm_args& g = gs[0];
     // Strips of 128 columns (512 contiguous bytes of every matrix row per request) for up to 16 rows of A, of 64 columns
-    // beyond (the arithmetic of 64 rows wants two CTAs per SM), of 32 for a narrow matrix; K is split while the strips
-    // alone leave SMs idle and a CTA keeps at least two steps, up to a cluster of 8 (16 measured no faster).
+    // beyond (tf32 mma tiles), of 32 for a narrow matrix; K is split while the strips alone leave SMs idle and a CTA
+    // keeps at least two steps, up to a cluster of 8 (16 measured no faster).
     const int bn = g.N < 512 ? 32 : (g.M > 16 ? 64 : 128);
-    const long long strips = (g.N + bn - 1) / bn;
+    const long long strips = (g.N + bn - 1) / bn * count;
     const long long enough = bn == 128 ? 128 : 256;
     int splits = 1;
     while(splits < 8 && strips * splits < enough && g.K / (splits * 2) >= 2 * BK) splits *= 2;
-    Params p;
-    p.A = g.A; p.W = g.B; p.bias = g.bias; p.C = g.C;
-    p.M = g.M; p.N = g.N; p.K = g.K; p.lda = g.lda; p.ldb = g.ldb; p.ldc = g.ldc;
+    Params p = {};
+    p.A = g.A;
+    for(int i = 0; i < MAX_PROBLEMS; i++)
+    {
+        const onn_gemm_args& gi = gs[i < count ? i : 0];
+        p.Ws[i] = gi.B; p.biases[i] = gi.bias; p.Cs[i] = gi.C; p.ldcs[i] = gi.ldc;
+    }
+    p.M = g.M; p.N = g.N; p.K = g.K; p.lda = g.lda; p.ldb = g.ldb;
     p.k_chunk = ((g.K + splits - 1) / splits + BK - 1) / BK * BK;
     p.alpha = g.alpha; p.relu = g.relu ? 1 : 0; p.accumulate = (g.flags & ONN_ACCUMULATE) ? 1 : 0;
+    p.problems = count;
     return launch_shape(p, bn, splits, stream);
 }
+
+int gemm_skinny_launch(const onn_gemm_args& g, cudaStream_t stream) { return gemm_skinny_launch_shared_input(&g, 1, stream); }
 
 }  // namespace onn

@@ -99,6 +99,25 @@ extern "C" int onn_dense_fwd(const float* X, const float* W, const float* b, flo
     return ONN_OK;
 }
 
+extern "C" int onn_dense_fwd_shared_input(const float* X, const float* const* W, const float* const* b, float* const* Y,
+                                          const int64_t* ldy, int count, int64_t rows, int64_t in, int64_t out, void* stream)
+{
+    ONN_CHECK_ARG(X && W && Y && ldy && count >= 1 && count <= 4 && rows > 0 && in > 0 && out > 0);
+    cudaStream_t s = (cudaStream_t)stream;
+    onn_gemm_args g[4];
+    bool one_launch = gemm_mode() == 0;
+    for(int i = 0; i < count; i++)
+    {
+        ONN_CHECK_ARG(W[i] && Y[i] && ldy[i] >= out);
+        g[i] = plain_gemm(X, 0, in, W[i], 1, out, Y[i], ldy[i], rows, out, in);
+        g[i].bias = b ? b[i] : nullptr;
+        one_launch = one_launch && gemm_skinny_takes(g[i]);
+    }
+    if(one_launch) return gemm_skinny_launch_shared_input(g, count, s);
+    for(int i = 0; i < count; i++) ONN_TRY(gemm(g[i], s));
+    return ONN_OK;
+}
+
 extern "C" int onn_dense_bwd(const float* X, const float* W, const float* Y, float* dY,
                              float* dW, float* db, float* dX, const float* dX_relu_mask, const uint32_t* dX_relu_bits,
                              float* dX_colsum,

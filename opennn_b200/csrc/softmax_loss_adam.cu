@@ -771,8 +771,8 @@ extern "C" int onn_greedy_next_token_rows(const float* probabilities, float* ids
 // warp.  Lanes own keys for the scores (each a full dot product over the head) and head features for the output.
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache, const float* __restrict__ v_cache,
-                        const uint8_t* __restrict__ key_is_pad, float* __restrict__ out,
-                        int B, int H, int S_cache, int length, int E, float scale)
+                        const uint8_t* __restrict__ key_is_pad, long long pad_stride_sample, long long pad_stride_key,
+                        float* __restrict__ out, int B, int H, int S_cache, int length, int E, float scale)
 {
     extern __shared__ float shared[];                          // per warp: hd query values, then `length` scores
     const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
@@ -793,7 +793,7 @@ decode_attention_kernel(const float* __restrict__ q, const float* __restrict__ k
         float dot = 0.f;
         for(int d = 0; d < hd; d++) dot = fmaf(q_shared[d], k_row[d], dot);
         float s = dot * scale;
-        if(key_is_pad && key_is_pad[(long long)b * S_cache + j]) s = -1e9f;     // overwrite, as the training path
+        if(key_is_pad && key_is_pad[b * pad_stride_sample + j * pad_stride_key]) s = -1e9f;     // overwrite, as the training path
         scores[j] = s;
         row_max = fmaxf(row_max, s);
     }
@@ -822,8 +822,8 @@ decode_attention_kernel(const float* __restrict__ q, const float* __restrict__ k
 // keys side by side, and their partial sums are added in a fixed order.
 __global__ void __launch_bounds__(256)
 decode_attention_block_kernel(const float* __restrict__ q, const float* __restrict__ k_cache, const float* __restrict__ v_cache,
-                              const uint8_t* __restrict__ key_is_pad, float* __restrict__ out,
-                              int H, int S_cache, int length, int E, float scale)
+                              const uint8_t* __restrict__ key_is_pad, long long pad_stride_sample, long long pad_stride_key,
+                              float* __restrict__ out, int H, int S_cache, int length, int E, float scale)
 {
     extern __shared__ __align__(16) float shared[];            // q[hd] | partial[1024] | reduce[16] | scores[S_cache]
     const int hd = E / H, chunks = hd >> 2;
@@ -860,7 +860,7 @@ decode_attention_block_kernel(const float* __restrict__ q, const float* __restri
         if(j < length)
         {
             float s = dot * scale;
-            if(key_is_pad && key_is_pad[cache_row0 + j]) s = -1e9f;        // overwrite, as the training path
+            if(key_is_pad && key_is_pad[b * pad_stride_sample + j * pad_stride_key]) s = -1e9f;        // overwrite, as the training path
             if(sub == 0) scores[j] = s;
             thread_max = fmaxf(thread_max, s);
         }
@@ -910,7 +910,8 @@ decode_attention_block_kernel(const float* __restrict__ q, const float* __restri
     }
 }
 
-extern "C" int onn_decode_attention(const float* q, const float* k_cache, const float* v_cache, const uint8_t* key_is_pad, float* out,
+extern "C" int onn_decode_attention(const float* q, const float* k_cache, const float* v_cache, const uint8_t* key_is_pad,
+                                    int64_t pad_stride_sample, int64_t pad_stride_key, float* out,
                                     int64_t B, int64_t S_cache, int64_t length, int64_t E, int64_t H, void* stream)
 {
     ONN_CHECK_ARG(q && k_cache && v_cache && out && B > 0 && H > 0 && E > 0 && E % H == 0 && length > 0 && length <= S_cache);
@@ -927,7 +928,8 @@ extern "C" int onn_decode_attention(const float* q, const float* k_cache, const 
                 return ONN_ERR_CUDA;
             configured = shared;
         }
-        decode_attention_block_kernel<<<(unsigned)(B * H), 256, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, out, (int)H,
+        decode_attention_block_kernel<<<(unsigned)(B * H), 256, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, pad_stride_sample,
+                                                                                                 pad_stride_key, out, (int)H,
                                                                                                  (int)S_cache, (int)length, (int)E,
                                                                                                  1.0f / sqrtf((float)hd));
         count_launch();
@@ -942,7 +944,8 @@ extern "C" int onn_decode_attention(const float* q, const float* k_cache, const 
         configured = shared;
     }
     const long long items = B * H;
-    decode_attention_kernel<<<(unsigned)((items + 3) / 4), 128, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, out, (int)B, (int)H,
+    decode_attention_kernel<<<(unsigned)((items + 3) / 4), 128, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, pad_stride_sample, pad_stride_key,
+                                                                                             out, (int)B, (int)H,
                                                                                              (int)S_cache, (int)length, (int)E,
                                                                                              1.0f / sqrtf((float)hd));
     count_launch();

@@ -70,6 +70,23 @@ const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index po
     const Index B = batch_size;
     const type* last = nullptr;
 
+    // Padding flags of this position's keys, one row of B bytes per position in each self-attention cache.  Where the
+    // layer's input comes from an Embedding or a Normalization3d, that kernel writes the flags as it writes the rows
+    // (the training path takes them from the same place); any other producer is scanned by the attention branch below.
+    vector<uint8_t*> flags_from_producer(layers.size(), nullptr);
+    vector<char> flags_are_written(layers.size(), 0);
+    for(size_t i = 0; i < layers.size(); i++)
+    {
+        const MultiHeadAttention* attention = dynamic_cast<const MultiHeadAttention*>(layers[i].get());
+        if(!attention || !decoder_side[i] || attention->is_cross_attention()) continue;
+        const Index producer = input_indices[i][0];
+        if(producer < 0 || flags_from_producer[size_t(producer)]) continue;
+        const string& kind = layers[size_t(producer)]->get_name();
+        if(kind != "Embedding" && kind != "Normalization3d") continue;
+        flags_from_producer[size_t(producer)] = reinterpret_cast<uint8_t*>(caches[i]->key_is_pad.data) + position * B;
+        flags_are_written[i] = 1;
+    }
+
     // the current position's ids, one per sample, contiguous
     check_cuda(cudaMemcpy2DAsync(step_ids.data, sizeof(type), ids + position, size_t(ids_stride) * sizeof(type), sizeof(type), size_t(B),
                                  cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream())), "IncrementalDecoder: ids");
@@ -92,7 +109,7 @@ const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index po
             if(!embedding->positional_encoding_device.data) embedding->copy_positional_encoding_device();
             const Index E = embedding->embedding_dimension;
             check_onn(onn_embedding_fwd(step_ids.data, embedding->weights_device.data, embedding->positional_encoding_device.data + position * E, out,
-                                        nullptr, B, 1, E, embedding->vocabulary_size, embedding->scale_embedding,
+                                        flags_from_producer[i], B, 1, E, embedding->vocabulary_size, embedding->scale_embedding,
                                         embedding->add_positional_encoding, 0, stream()), "IncrementalDecoder: embedding");
         }
         else if(MultiHeadAttention* attention = dynamic_cast<MultiHeadAttention*>(layer))
@@ -101,26 +118,27 @@ const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index po
             const type* x = input_of(i, 0);
             AttentionCache& cache = *caches[i];
             Index length = cache.capacity;                              // cross-attention: the whole encoder output
-            check_onn(onn_dense_fwd(x, attention->query_weights_device.data, attention->query_biases_device.data, query.data, nullptr,
-                                    B, E, E, ONN_ACT_LINEAR, 0, stream()), "IncrementalDecoder: query");
-            if(!attention->cross_attention)
+            if(attention->cross_attention)
+                check_onn(onn_dense_fwd(x, attention->query_weights_device.data, attention->query_biases_device.data, query.data, nullptr,
+                                        B, E, E, ONN_ACT_LINEAR, 0, stream()), "IncrementalDecoder: query");
+            else
             {
-                // this position's key and value rows go to slot `position` of the cache (row pitch capacity * E per sample)
-                onn_gemm_args g = {};
-                g.A = x; g.M = B; g.N = E; g.K = E; g.lda = E; g.ldb = E; g.ldc = cache.capacity * E;
-                g.a_major = 0; g.b_major = 1; g.batch_inner = 1; g.batch_outer = 1; g.alpha = 1.0f;
-                g.B = attention->key_weights_device.data; g.bias = attention->key_biases_device.data; g.C = cache.keys.data + position * E;
-                check_onn(onn_gemm(&g, stream()), "IncrementalDecoder: key row");
-                g.B = attention->value_weights_device.data; g.bias = attention->value_biases_device.data; g.C = cache.values.data + position * E;
-                check_onn(onn_gemm(&g, stream()), "IncrementalDecoder: value row");
+                // query, and this position's key and value rows straight into slot `position` of the caches (row pitch
+                // capacity * E per sample): three products over the same input, one launch
+                const float* weights[3] = {attention->query_weights_device.data, attention->key_weights_device.data, attention->value_weights_device.data};
+                const float* biases[3] = {attention->query_biases_device.data, attention->key_biases_device.data, attention->value_biases_device.data};
+                float* results[3] = {query.data, cache.keys.data + position * E, cache.values.data + position * E};
+                const int64_t pitches[3] = {E, cache.capacity * E, cache.capacity * E};
+                check_onn(onn_dense_fwd_shared_input(x, weights, biases, results, pitches, 3, B, E, E, stream()), "IncrementalDecoder: projections");
                 // padding flag of the new key: the layer's input row is all zero (a PAD token behind a finished sequence)
-                uint8_t* flags = reinterpret_cast<uint8_t*>(cache.key_is_pad.data);
-                check_onn(onn_rows_are_zero(x, reinterpret_cast<uint8_t*>(context.data), B, E, stream()), "IncrementalDecoder: padding");
-                check_cuda(cudaMemcpy2DAsync(flags + position, size_t(cache.capacity), context.data, 1, 1, size_t(B), cudaMemcpyDeviceToDevice,
-                                             static_cast<cudaStream_t>(stream())), "IncrementalDecoder: padding flag");
+                if(!flags_are_written[i])
+                    check_onn(onn_rows_are_zero(x, reinterpret_cast<uint8_t*>(cache.key_is_pad.data) + position * B, B, E, stream()),
+                              "IncrementalDecoder: padding");
                 length = position + 1;
             }
+            // flags: [B, capacity] for the encoder output, one row of B per position for the self-attention cache
             check_onn(onn_decode_attention(query.data, cache.keys.data, cache.values.data, reinterpret_cast<const uint8_t*>(cache.key_is_pad.data),
+                                           attention->cross_attention ? cache.capacity : 1, attention->cross_attention ? 1 : B,
                                            context.data, B, cache.capacity, length, E, H, stream()), "IncrementalDecoder: attention");
             check_onn(onn_dense_fwd(context.data, attention->projection_weights_device.data, attention->projection_biases_device.data, out, nullptr,
                                     B, E, E, ONN_ACT_LINEAR, 0, stream()), "IncrementalDecoder: output projection");
@@ -144,7 +162,7 @@ const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index po
             else
                 x = input_of(i, 0);
             check_onn(onn_layernorm_fwd(x, addend, norm->gammas_device.data, norm->betas_device.data, out, nullptr, query.data,
-                                        query.data + B, nullptr, B, norm->embedding_dimension, EPSILON, 0, stream()), "IncrementalDecoder: normalization");
+                                        query.data + B, flags_from_producer[i], B, norm->embedding_dimension, EPSILON, 0, stream()), "IncrementalDecoder: normalization");
         }
         else if(dynamic_cast<Addition3d*>(layer))
         {

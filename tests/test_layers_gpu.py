@@ -241,6 +241,26 @@ def test_adam_and_norm(capi):
         assert not host(g).any(), "zero_grad must clear the gradient"
 
 
+@pytest.mark.parametrize("rows,features,out", [(8, 1024, 1024), (40, 256, 512), (3, 36, 20), (100, 64, 64)])
+def test_dense_fwd_shared_input(capi, gemm_mode, rows, features, out):
+    """Three Linear projections of one input in one call, two of them written into rows of a wider buffer (cache
+    slots), against an fp64 product and against the three separate Dense forward passes (to rounding: the split of K
+    may differ between one and three products per launch).  100 rows: one product after the other on the large-GEMM
+    path.  Columns of the wider buffers past `out` stay untouched."""
+    rng = np.random.default_rng(rows + out)
+    x = dev(rng.standard_normal((rows, features)).astype(np.float32))
+    weights = [dev((0.1 * rng.standard_normal((features, out))).astype(np.float32)) for _ in range(3)]
+    biases = [dev(rng.standard_normal(out).astype(np.float32)) for _ in range(3)]
+    pitches = [out, 5 * out, 3 * out + 4]
+    outputs = [torch.full((rows, p), 7.0, device="cuda") for p in pitches]
+    capi.dense_fwd_shared_input(x, weights, biases, outputs, pitches)
+    for w, b, y in zip(weights, biases, outputs):
+        separate = capi.dense_fwd(x, w, b, "Linear")
+        assert_close(host(y[:, :out]), host(x.double() @ w.double() + b.double()), TOL, "product")
+        assert_close(host(y[:, :out]), host(separate), 1e-5 if rows <= 16 or gemm_mode == "simt" else TOL, "against the separate pass")
+        assert y.shape[1] == out or float((y[:, out:] - 7.0).abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("B,S_cache,length,E,H", [(3, 256, 256, 1024, 16), (2, 40, 17, 64, 8), (5, 9, 1, 32, 8), (2, 12, 12, 12, 2),
                                                   (1, 300, 299, 512, 2)])
 def test_decode_attention(capi, B, S_cache, length, E, H):
@@ -266,6 +286,7 @@ def test_decode_attention(capi, B, S_cache, length, E, H):
     expected = (torch.softmax(scores, dim=-1) @ vh).reshape(B, E)
     assert_close(host(out), host(expected), 2e-5, "context")
     assert torch.equal(out, capi.decode_attention(q, k, v, pad, length, H)), "same bits on every run"
+    assert torch.equal(out, capi.decode_attention(q, k, v, pad.t().contiguous(), length, H, position_major=True)), "flags stored per position"
     assert_close(host(capi.decode_attention(q, k, v, None, length, H)),
                  host((torch.softmax((qh @ kh.transpose(-1, -2)) / np.sqrt(hd), dim=-1) @ vh).reshape(B, E)), 2e-5, "no padding flags")
 
