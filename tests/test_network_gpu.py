@@ -316,3 +316,34 @@ def test_full_size_network(libs, name):
     assert l2_err <= 2e-2
     assert capi.lib().onn_gemm_device_status() == 0
     t.close()
+
+
+def test_samples_of_nothing_but_padding(libs):
+    """Edge of the padding rules on the whole network: one sample whose source sequence is all PAD (its cross-attention
+    sees only masked keys: every score is -1e9 and the weights become uniform), one whose target side is all PAD (no
+    active token: it adds nothing to the loss and its output gradient is zero), one with an out-of-range target id.
+    fp32 GEMMs against the restated reference arithmetic: loss, accuracy and the whole gradient."""
+    capi, trainer = libs
+    capi.check(capi.lib().onn_gemm_set_mode(1))
+    name = "tiny_encdec_odd"
+    mode, B, S_in, S_dec, V_in, V_out, E, H, F, L, steps, seed, lo, hi = CONFIGS[name]
+    net, params, external, targets = network_inputs(name)
+    external = {k: v.copy() for k, v in external.items()}
+    targets = targets.copy()
+    external[-2][0, :] = 0
+    external[-1][1, :] = 0
+    targets[1, :] = 0
+    targets[2, 0] = V_out + 5
+    dec, enc, tgt = device_batch(external, targets)
+    t = make_trainer(trainer, name)
+    t.set_parameters(params)
+    error, accuracy, active, _ = t.step_device(dec, enc, tgt, update=False)
+    probabilities = net.forward(params, external)
+    expected_error, expected_accuracy, expected_active = O.ce3d_error(probabilities, targets)
+    assert active == expected_active == int(((targets > 0) & (targets < V_out)).sum())
+    assert abs(error - expected_error) <= 1e-5 * abs(expected_error)
+    assert abs(accuracy - expected_accuracy) <= 1e-6
+    expected = net.backward(params, O.ce3d_output_gradients(probabilities, targets))
+    assert_close(t.get_gradients(), expected, 1e-4, "gradient")
+    assert capi.lib().onn_gemm_device_status() == 0
+    t.close()
