@@ -355,6 +355,12 @@ int onn_greedy_next_token(const float* probabilities, float* ids, int* finished,
 int onn_greedy_next_token_rows(const float* probabilities, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
                                int64_t write_position, int end_id, void* stream);
 
+/* The same step from LOGITS [B, V] (a Dense "Softmax" layer run with ONN_DEFER_SOFTMAX): softmax and arg-max in one
+ * kernel.  The probabilities are formed exactly as onn_softmax_rows forms them, compared and not stored, so the token is
+ * the one onn_softmax_rows + onn_greedy_next_token_rows give; `logits` is left unchanged. */
+int onn_greedy_next_token_logits(const float* logits, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
+                                 int64_t write_position, int end_id, void* stream);
+
 /* Attention of ONE query row per sample against keys and values kept from earlier decoding steps (no counterpart in
  * the reference, whose decoding loop recomputes every position for every token): q [B, E] (projected), k_cache and
  * v_cache [B, S_cache, E] of which the first `length` rows are valid, key_is_pad bytes or NULL: the flag of key j of

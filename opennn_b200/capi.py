@@ -57,7 +57,7 @@ EXPORTS = [
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
     "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_pooling3d_fwd", "onn_pooling3d_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
-    "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_dense_fwd_shared_input", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
+    "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_dense_fwd_shared_input", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_greedy_next_token_logits", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
     "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam",
     "onn_dp_unique_id", "onn_dp_init", "onn_dp_allreduce", "onn_dp_wait", "onn_dp_finalize",
 ]
@@ -347,6 +347,13 @@ def greedy_next_token_rows(probabilities, ids, finished, write_position, end_id)
     B, V = probabilities.shape
     check(lib().onn_greedy_next_token_rows(ptr(probabilities), ptr(ids), ptr(finished), i64(B), i64(ids.shape[1]), i64(V),
                                            i64(write_position), int(end_id), stream_ptr()), "onn_greedy_next_token_rows")
+
+
+def greedy_next_token_logits(logits, ids, finished, write_position, end_id):
+    """As greedy_next_token_rows, from logits [B, V]: softmax and arg-max fused."""
+    B, V = logits.shape
+    check(lib().onn_greedy_next_token_logits(ptr(logits), ptr(ids), ptr(finished), i64(B), i64(ids.shape[1]), i64(V),
+                                             i64(write_position), int(end_id), stream_ptr()), "onn_greedy_next_token_logits")
 
 
 def grad_sqnorm(g):

@@ -745,6 +745,73 @@ greedy_next_token_kernel(const float* __restrict__ probabilities, long long samp
     }
 }
 
+// Softmax and greedy step in one kernel for a row of logits: the probabilities are formed exactly as
+// softmax_rows_kernel forms them (same statistics, same expression) but only compared, never stored; first index on ties.
+__global__ void __launch_bounds__(kLossThreads)
+softmax_greedy_kernel(const float* __restrict__ logits, int V, float* __restrict__ ids, long long ids_stride, int write_position,
+                      int* __restrict__ finished, int end_id)
+{
+    __shared__ float scratch_f[16];
+    __shared__ int scratch_i[8];
+    __shared__ float best_value[kLossThreads];
+    __shared__ int best_index[kLossThreads];
+    const int b = blockIdx.x;
+    const float* row = logits + (long long)b * V;
+    const RowStats st = row_statistics(row, V, scratch_f, scratch_i);
+    const float inv = st.sum > 0.f ? 1.0f / st.sum : 0.f;
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    if((V & 3) == 0 && aligned16(row))
+        for(int i = threadIdx.x * 4; i < V; i += kLossThreads * 4)
+        {
+            const float4 x = ld4(row + i);
+            const float p0 = __expf(x.x - st.max) * inv, p1 = __expf(x.y - st.max) * inv;
+            const float p2 = __expf(x.z - st.max) * inv, p3 = __expf(x.w - st.max) * inv;
+            if(p0 > value) { value = p0; index = i; }
+            if(p1 > value) { value = p1; index = i + 1; }
+            if(p2 > value) { value = p2; index = i + 2; }
+            if(p3 > value) { value = p3; index = i + 3; }
+        }
+    else
+        for(int i = threadIdx.x; i < V; i += kLossThreads)
+        {
+            const float p = __expf(row[i] - st.max) * inv;
+            if(p > value) { value = p; index = i; }
+        }
+    best_value[threadIdx.x] = value;
+    best_index[threadIdx.x] = index;
+    __syncthreads();
+    for(int step = kLossThreads / 2; step > 0; step >>= 1)
+    {
+        if(threadIdx.x < step)
+        {
+            const float other = best_value[threadIdx.x + step];
+            const int other_index = best_index[threadIdx.x + step];
+            if(other > best_value[threadIdx.x] || (other == best_value[threadIdx.x] && other_index < best_index[threadIdx.x]))
+            {
+                best_value[threadIdx.x] = other;
+                best_index[threadIdx.x] = other_index;
+            }
+        }
+        __syncthreads();
+    }
+    if(threadIdx.x == 0 && !finished[b])
+    {
+        const int token = best_index[0] == 0x7fffffff ? 0 : best_index[0];
+        ids[(long long)b * ids_stride + write_position] = (float)token;
+        if(token == end_id) finished[b] = 1;
+    }
+}
+
+extern "C" int onn_greedy_next_token_logits(const float* logits, float* ids, int* finished, int64_t B, int64_t S, int64_t V,
+                                            int64_t write_position, int end_id, void* stream)
+{
+    ONN_CHECK_ARG(logits && ids && finished && B > 0 && S > 1 && V > 0 && write_position > 0 && write_position < S && V < (1LL << 31));
+    softmax_greedy_kernel<<<(unsigned)B, kLossThreads, 0, (cudaStream_t)stream>>>(logits, (int)V, ids, S, (int)write_position, finished, end_id);
+    count_launch();
+    return launch_status();
+}
+
 // 256 threads for a short distribution, 1024 for a vocabulary
 static unsigned greedy_threads(int64_t V) { return V >= 4096 ? 1024u : 256u; }
 

@@ -63,12 +63,13 @@ void IncrementalDecoder::start()
     }
 }
 
-const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index position)
+const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index position, bool output_logits)
 {
     const vector<unique_ptr<Layer>>& layers = network->get_layers();
     const vector<vector<Index>>& input_indices = network->get_layer_input_indices();
     const Index B = batch_size;
     const type* last = nullptr;
+    last_output_is_logits = false;
 
     // Padding flags of this position's keys, one row of B bytes per position in each self-attention cache.  Where the
     // layer's input comes from an Embedding or a Normalization3d, that kernel writes the flags as it writes the rows
@@ -145,8 +146,11 @@ const type* IncrementalDecoder::step(const type* ids, Index ids_stride, Index po
         }
         else if(Dense3d* dense = dynamic_cast<Dense3d*>(layer))
         {
+            const bool defer = output_logits && i + 1 == layers.size() && dense->get_activation_code() == ONN_ACT_SOFTMAX;
+            last_output_is_logits = defer;
             check_onn(onn_dense_fwd(input_of(i, 0), dense->weights_device.data, dense->biases_device.data, out, nullptr, B, dense->inputs_number,
-                                    dense->neurons_number, dense->get_activation_code(), 0, stream()), "IncrementalDecoder: dense");
+                                    dense->neurons_number, dense->get_activation_code(), defer ? ONN_DEFER_SOFTMAX : 0, stream()),
+                      "IncrementalDecoder: dense");
         }
         else if(Normalization3d* norm = dynamic_cast<Normalization3d*>(layer))
         {

@@ -524,9 +524,14 @@ extern "C" int onn_trainer_greedy_decode(onn_trainer* t, const float* encoder_id
 static void decode_position(onn_trainer* t, Index i, int end_id)
 {
     const Index B = t->micro_batch, S_dec = t->decoder_sequence_length;
-    const type* probabilities = t->decoder->step(t->decode_ids.data, S_dec, i - 1);
-    check_onn(onn_greedy_next_token_rows(probabilities, t->decode_ids.data, reinterpret_cast<int*>(t->decode_finished.data), B, S_dec,
-                                         t->vocabulary_size, i, end_id, t->stream), "greedy step");
+    // the output layer leaves logits where it can: softmax and arg-max are one kernel then
+    const type* distribution = t->decoder->step(t->decode_ids.data, S_dec, i - 1, true);
+    if(t->decoder->output_is_logits())
+        check_onn(onn_greedy_next_token_logits(distribution, t->decode_ids.data, reinterpret_cast<int*>(t->decode_finished.data), B, S_dec,
+                                               t->vocabulary_size, i, end_id, t->stream), "greedy step");
+    else
+        check_onn(onn_greedy_next_token_rows(distribution, t->decode_ids.data, reinterpret_cast<int*>(t->decode_finished.data), B, S_dec,
+                                             t->vocabulary_size, i, end_id, t->stream), "greedy step");
 }
 
 // Replays position i from its graph, capturing it first if need be.  Returns false (nothing has run) if graphs cannot be used.

@@ -691,10 +691,14 @@ public:
     void start();
     // Feeds the decoder ids of `position` (device, one float per sample at ids[b * ids_stride + position]) through the
     // decoder side and returns the device pointer of the last layer's output for that position: [batch, vocabulary].
-    const type* step(const type* ids, Index ids_stride, Index position);
+    // output_logits: if the last layer is a Dense "Softmax", leave its logits (the caller fuses the softmax into what
+    // it does next); true is returned through output_is_logits() for that step
+    const type* step(const type* ids, Index ids_stride, Index position, bool output_logits = false);
+    bool output_is_logits() const { return last_output_is_logits; }
 
 private:
     struct AttentionCache { TensorCuda keys, values, key_is_pad; Index capacity = 0; };
+    bool last_output_is_logits = false;
 
     NeuralNetwork* network = nullptr;
     ForwardPropagationCuda* forward_propagation = nullptr;

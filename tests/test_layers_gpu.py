@@ -241,6 +241,29 @@ def test_adam_and_norm(capi):
         assert not host(g).any(), "zero_grad must clear the gradient"
 
 
+@pytest.mark.parametrize("V", [37, 4096, 32000])
+def test_greedy_next_token_from_logits(capi, V):
+    """Softmax and arg-max in one kernel give the token of the two separate kernels, on rows with exact ties, with
+    logits so close that their probabilities round to the same float, and with a finished row."""
+    rng = np.random.default_rng(V + 1)
+    B, S = 7, 4
+    x = rng.standard_normal((B, V)).astype(np.float32)
+    x[1, 5] = x[1, V - 3] = 9.0                               # exact tie: the first index
+    x[2, V // 2] = 8.0; x[2, 3] = np.nextafter(np.float32(8.0), np.float32(0))      # one ulp below, earlier in the row
+    x[3] = 0.0                                                # a flat row
+    x[4, V - 1] = 30.0                                        # saturated
+    logits = dev(x)
+    ids_a, ids_b = torch.zeros(B, S, device="cuda"), torch.zeros(B, S, device="cuda")
+    fin_a = torch.zeros(B, dtype=torch.int32, device="cuda"); fin_a[6] = 1
+    fin_b = fin_a.clone()
+    capi.greedy_next_token_logits(logits, ids_a, fin_a, 1, end_id=V - 1)
+    assert np.array_equal(host(logits), x), "the logits stay as they were"
+    probabilities = capi.softmax_rows(logits.clone())
+    capi.greedy_next_token_rows(probabilities, ids_b, fin_b, 1, end_id=V - 1)
+    assert torch.equal(ids_a, ids_b) and torch.equal(fin_a, fin_b)
+    assert host(ids_a)[1, 1] == 5 and host(ids_a)[3, 1] == 0 and host(ids_a)[4, 1] == V - 1 and host(fin_a)[4] == 1
+
+
 @pytest.mark.parametrize("rows,features,out", [(8, 1024, 1024), (40, 256, 512), (3, 36, 20), (100, 64, 64)])
 def test_dense_fwd_shared_input(capi, gemm_mode, rows, features, out):
     """Three Linear projections of one input in one call, two of them written into rows of a wider buffer (cache
