@@ -49,6 +49,12 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool val
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(d), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Cluster barrier with a relaxed arrive: it orders nothing (the default release would first wait for this thread's
+// global stores of C to be performed), it only keeps every CTA resident until all have read each other's tiles.
+__device__ __forceinline__ void cluster_exit_barrier()
+{
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
 // One ring slot: BK rows of the strip and the same K range of the MB rows of A.
@@ -217,7 +223,7 @@ gemm_skinny_kernel(const Params p)
             }
             finish(row, col, sum);
         }
-        cluster.sync();                                  // nobody leaves while its tile is still being read
+        cluster_exit_barrier();                          // nobody leaves while its tile is still being read
     }
 }
 
@@ -382,7 +388,7 @@ gemm_skinny_mma_kernel(const Params p)
             }
             finish(row, col, sum);
         }
-        cluster.sync();                                  // nobody leaves while its tile is still being read
+        cluster_exit_barrier();                          // nobody leaves while its tile is still being read
     }
 }
 
