@@ -290,6 +290,32 @@ def time_greedy_decode(trainer, torch, w, rows, tokens):
             "seconds": best, "tokens_per_s": rows * (tokens - 1) / best, "replay_matches_eager": same}
 
 
+def time_classifier_step(trainer, torch, w, rows, steps):
+    """Training step of the text-classification network (Embedding -> self-attention -> max pooling -> Dense<2> head,
+    CrossEntropyError2d, Adam) at the benchmark's layer sizes, `rows` samples per step, ids resident on the device."""
+    import numpy as np
+    classes = 8
+    c = trainer.TextClassifier(w["V_in"], w["S_in"], w["E"], w["H"], [w["F"]], classes, rows)
+    rng = np.random.default_rng(1)
+    ids = torch.from_numpy(rng.integers(1, w["V_in"], size=(rows, w["S_in"])).astype(np.float32)).cuda()
+    targets = torch.from_numpy(np.eye(classes, dtype=np.float32)[rng.integers(0, classes, rows)]).cuda()
+    for _ in range(3):
+        c.step_device(ids, targets, update=True)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        error, _ = c.step_device(ids, targets, update=True)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    parameters = c.parameters_number
+    c.close()
+    return {"classifier": "TextClassificationNetwork, one attention layer, hidden %d, %d classes" % (w["F"], classes), "rows": rows,
+            "sequence": w["S_in"], "parameters": parameters, "ms_per_step": ms, "tokens_per_s": rows * w["S_in"] / (1e-3 * ms),
+            "last_error": error}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -328,6 +354,9 @@ def run_ours(args):
         return
     if args.profile_kernel == "attention":
         emit(dict(time_attention_core(capi, torch, w), profiling_only=True))
+        return
+    if args.profile_kernel == "classifier":
+        emit(dict(time_classifier_step(trainer, torch, w, args.profile_batch or 64, max(args.steps, 5)), profiling_only=True))
         return
     if args.profile_kernel == "decode":
         rows = args.profile_batch or 8
@@ -497,11 +526,12 @@ def main():
     parser.add_argument("--micro-batch", type=int, default=0, help="samples per micro-batch (default: the workload's own)")
     parser.add_argument("--workload", default="config5", choices=["config5", "config2"],
                         help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network")
-    parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention", "rowwise", "decode"],
+    parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention", "rowwise", "decode", "classifier"],
                         help="profiling aid: launch only the dominant GEMM (FFN-up shape) four times on buffers larger than L2, "
                              "or only one attention layer (forward and backward, 32 samples) twice, or only the HBM-bound kernels "
                              "(LayerNorm forward / backward, fused softmax-cross-entropy, Adam) at the benchmark's sizes; decode: greedy decoding "
-                             "with cached keys and values of --profile-batch rows (default 8) over --decode-tokens positions")
+                             "with cached keys and values of --profile-batch rows (default 8) over --decode-tokens positions; classifier: "
+                             "training steps of the text-classification network at the benchmark's layer sizes")
     parser.add_argument("--decode-tokens", type=int, default=0, help="target positions for --profile-kernel decode (default: the workload's)")
     args = parser.parse_args()
     # Libraries (NCCL prints its version) write to file descriptor 1: keep it for the ONE JSON line by
