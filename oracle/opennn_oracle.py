@@ -138,6 +138,10 @@ def dense_forward(x, weights, biases, activation):
         return np.maximum(combos, F32(0)), (combos > 0).astype(F32)
     if activation == "Softmax":
         return softmax_last(combos), None
+    if activation == "Sigmoid":
+        # opennn/layer.h:196-204: y = 1 / (1 + exp(-x)), derivative y (1 - y)
+        y = (F32(1) / (F32(1) + np.exp(-combos).astype(F32))).astype(F32)
+        return y, (y * (F32(1) - y)).astype(F32)
     raise ValueError(activation)
 
 
@@ -285,6 +289,23 @@ def ce2d_output_gradients(probabilities, targets):
     """opennn/cross_entropy_error.cpp:114-134: (y - t) / samples -- the softmax Jacobian is folded in, the Softmax
     Dense layer passes it on unchanged (dense_layer.h:834-840)."""
     return ((probabilities - targets) / F32(probabilities.shape[0])).astype(F32)
+
+
+def ce2d_binary_error(outputs, targets):
+    """opennn/cross_entropy_error.cpp:36-55 (one output): y clipped to [eps, 1 - eps];
+    -sum(t log y + (1 - t) log(1 - y)) / samples; NaN or infinity becomes 10."""
+    samples = outputs.shape[0]
+    y = np.minimum(np.maximum(outputs, EPSILON), F32(1) - EPSILON).astype(F32)
+    terms = (targets * np.log(y) + (F32(1) - targets) * np.log(F32(1) - y)).astype(F32)
+    error = F32(terms.sum(dtype=F32) / F32(-samples))
+    return error if np.isfinite(error) else F32(10)
+
+
+def ce2d_binary_output_gradients(outputs, targets):
+    """opennn/cross_entropy_error.cpp:90-110: (-t / (y + eps) + (1 - t) / (1 - y + eps)) / samples; the Sigmoid layer
+    behind it multiplies by y (1 - y)."""
+    samples = F32(outputs.shape[0])
+    return ((-targets / (outputs + EPSILON) + (F32(1) - targets) / (F32(1) - outputs + EPSILON)) / samples).astype(F32)
 
 
 # --------------------------------------------------------------------------------------
@@ -488,8 +509,12 @@ class Network:
     def train_step_2d(self, arena, m, v, iteration, ids, targets, lr=1e-3):
         """The same loop body with CrossEntropyError2d on a classifier: targets are one-hot rows [B, classes]."""
         probabilities = self.forward(arena, {-1: ids})
-        error = ce2d_error(probabilities, targets)
-        gradient = self.backward(arena, ce2d_output_gradients(probabilities, targets))
+        if probabilities.shape[-1] == 1:                     # one output: the binary form of the loss
+            error = ce2d_binary_error(probabilities, targets)
+            gradient = self.backward(arena, ce2d_binary_output_gradients(probabilities, targets))
+        else:
+            error = ce2d_error(probabilities, targets)
+            gradient = self.backward(arena, ce2d_output_gradients(probabilities, targets))
         iteration += 1
         adam_update(arena, gradient, m, v, iteration, lr=lr)
         return error, gradient, iteration
@@ -517,7 +542,7 @@ def _encoder_block(net, S, E, H, F, source):
 
 def build_text_classifier(V, S, E, H, hidden, classes):
     """opennn/standard_networks.cpp:575-615: Embedding (scaled, with positions) -> self-attention -> max pooling over
-    the sequence -> Dense<2> ReLU layers -> Dense<2> Softmax (Sigmoid for a single output, not restated here)."""
+    the sequence -> Dense<2> ReLU layers -> Dense<2> Softmax, or Sigmoid for a single output."""
     net = Network()
     net.add("Embedding", [-1], V=V, S=S, E=E)
     net.add("MultiHeadAttention", Sq=S, Sk=S, E=E, H=H, causal=False)
@@ -526,7 +551,7 @@ def build_text_classifier(V, S, E, H, hidden, classes):
     for size in hidden:
         net.add("Dense2d", **{"in": width, "out": size, "activation": "RectifiedLinear"})
         width = size
-    net.add("Dense2d", **{"in": width, "out": classes, "activation": "Softmax"})
+    net.add("Dense2d", **{"in": width, "out": classes, "activation": "Softmax" if classes > 1 else "Sigmoid"})
     return net.compile()
 
 

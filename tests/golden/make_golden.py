@@ -222,6 +222,7 @@ CLASSIFIER_CASES = {
     # name: B, S, V, E, H, hidden, classes, steps
     "classifier_tiny": (6, 12, 50, 16, 2, 24, 3, 3),
     "classifier_head64": (8, 72, 200, 128, 2, 256, 5, 3),
+    "classifier_binary": (6, 12, 50, 16, 2, 24, 1, 3),        # one output: Sigmoid + the binary cross-entropy
 }
 
 
@@ -232,8 +233,8 @@ def classifier_inputs(name):
     net = O.build_text_classifier(V, S, E, H, [hidden], classes)
     params = net.default_parameters(rng)
     ids = O.synthetic_ids(rng, B, S, V, max(2, S // 3), S)
-    labels = rng.integers(0, classes, B)
-    targets = np.eye(classes, dtype=F32)[labels]
+    labels = rng.integers(0, max(classes, 2), B)
+    targets = np.eye(classes, dtype=F32)[labels] if classes > 1 else labels.astype(F32).reshape(B, 1)
     return net, params, ids, targets
 
 

@@ -110,7 +110,7 @@ def test_network_training_steps(name):
     assert_close(arena, g["params_out_sample"], 1e-4, "parameters after Adam")
 
 
-@pytest.mark.parametrize("name", ["classifier_tiny", "classifier_head64"])
+@pytest.mark.parametrize("name", ["classifier_tiny", "classifier_head64", "classifier_binary"])
 def test_text_classifier_training_steps(name):
     """Embedding -> attention -> max pooling -> Dense<2> head with the 2-D cross-entropy, against the reference's
     probabilities, first gradient, loss history and parameters after three Adam steps."""
