@@ -49,6 +49,7 @@ extern "C" {
 #define ONN_ACT_LINEAR   0
 #define ONN_ACT_RELU     1
 #define ONN_ACT_SOFTMAX  2
+#define ONN_ACT_SIGMOID  3   /* "Sigmoid" / "Logistic": y = 1 / (1 + exp(-x)) (opennn/layer.h:196-204) */
 
 const char* onn_status_string(int status);
 int onn_version(void);
@@ -217,9 +218,9 @@ int onn_dense_fwd(const float* X, const float* W, const float* b, float* Y, uint
                   uint32_t flags, void* stream);
 
 /* Backward replaces cudnnActivationBackward + 3 GEMMs (opennn/dense_layer.h:1235-1374);
- * CPU semantics dense_layer.h:816-866:  delta = dY * act'(Y) (ReLU: Y > 0; Linear and
+ * CPU semantics dense_layer.h:816-866:  delta = dY * act'(Y) (ReLU: Y > 0; Sigmoid: Y (1 - Y); Linear and
  * Softmax: delta = dY), dW = X^T delta, db = column sums of delta, dX = delta W^T.
- * dY is overwritten with delta for ReLU (as the reference does in place) unless
+ * dY is overwritten with delta for ReLU and Sigmoid (as the reference does in place) unless
  * ONN_DELTA_READY says it already holds delta.  dX may be NULL (ONN_ACCUMULATE adds into it).
  * dW and db are ACCUMULATED into (the gradient arena is zeroed once per step).
  * dX_relu_mask (optional, [rows, in]): dX is multiplied by (mask > 0), i.e. the ReLU
@@ -343,6 +344,15 @@ int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_co
  * stats (device, 2 floats) receives {error, rows}; row_scratch is [rows] floats. */
 int onn_ce2d_fwd_bwd(float* probabilities, const float* targets, float* stats, float* row_scratch,
                      int64_t rows, int64_t classes, void* stream);
+/* The same loss with ONE output per sample (a Dense<2> "Sigmoid" head): opennn/cross_entropy_error.cpp:36-55 and 90-110.
+ * error = -sum(t log y' + (1 - t) log(1 - y')) / rows with y' = y clipped to [eps, 1 - eps] (NaN or infinity -> 10);
+ * outputs [rows] are overwritten with the gradient g = (-t / (y + eps) + (1 - t) / (1 - y + eps)) / rows, which the
+ * Sigmoid layer's onn_dense_bwd multiplies by y (1 - y) -- but y is gone once g sits in its place.  A caller whose
+ * output buffer doubles as the gradient buffer passes fold_sigmoid != 0: outputs then receive delta = g * (y (1 - y))
+ * and that layer's onn_dense_bwd takes ONN_DELTA_READY.  stats (device, 2 floats) receives {error, rows};
+ * row_scratch [rows]. */
+int onn_ce2d_binary_fwd_bwd(float* outputs, const float* targets, float* stats, float* row_scratch, int64_t rows,
+                            int fold_sigmoid, void* stream);
 
 /* Greedy decoding step (the body of the loop at opennn/standard_networks.cpp:1016-1034, which reads the distribution
  * back to the host and scans it there): for each of B samples the arg-max -- first index on ties -- of

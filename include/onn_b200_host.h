@@ -105,10 +105,11 @@ void* onn_trainer_stream(onn_trainer* trainer);
 /* -------------------------------------------------------------------------------------
  * Text classification (opennn/standard_networks.cpp:575-615, TextClassificationNetwork): Embedding (scaled, with
  * positions) -> self-attention -> max Pooling3d over the sequence -> Dense<2> "RectifiedLinear" layers ->
- * Dense<2> "Softmax", trained with CrossEntropyError2d (opennn/cross_entropy_error.cpp:58-77, 114-134) and Adam
+ * Dense<2> "Softmax" (one class: Dense<2> "Sigmoid"), trained with CrossEntropyError2d
+ * (opennn/cross_entropy_error.cpp:58-77, 114-134; one class: the binary form, :36-55, 90-110) and Adam
  * (lr 1e-3, betas 0.9 / 0.999, clip norm 1, iteration 1).  One GPU, one batch per step of exactly `batch` samples.
  * ids [batch, sequence_length] (token ids as floats, 0 = padding) and targets [batch, classes] (one-hot) are DEVICE
- * pointers.  statistics (host, 2 floats, optional) receives {error, gradient norm}.  classes >= 2.
+ * pointers (one class: targets [batch, 1] holding 0 or 1).  statistics (host, 2 floats, optional) receives {error, gradient norm}.
  * ------------------------------------------------------------------------------------- */
 typedef struct onn_classifier onn_classifier;
 const char* onn_classifier_last_error(void);

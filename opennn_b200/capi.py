@@ -57,7 +57,7 @@ EXPORTS = [
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
     "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_pooling3d_fwd", "onn_pooling3d_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
-    "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_dense_fwd_shared_input", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_greedy_next_token_logits", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
+    "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_ce2d_binary_fwd_bwd", "onn_dense_fwd_shared_input", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_greedy_next_token_logits", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
     "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam",
     "onn_dp_unique_id", "onn_dp_init", "onn_dp_allreduce", "onn_dp_wait", "onn_dp_finalize",
 ]
@@ -316,6 +316,16 @@ def ce2d(probabilities, targets):
     check(lib().onn_ce2d_fwd_bwd(ptr(probabilities), ptr(targets), ptr(stats), ptr(scratch), i64(rows), i64(classes), stream_ptr()),
           "onn_ce2d_fwd_bwd")
     return float(stats[0]), probabilities
+
+
+def ce2d_binary(outputs, targets, fold_sigmoid=False):
+    """CrossEntropyError2d with one output per sample.  Returns (error, gradient or Sigmoid delta); `outputs` is consumed."""
+    rows = outputs.numel()
+    stats = torch.empty(2, device="cuda")
+    scratch = torch.empty(rows, device="cuda")
+    check(lib().onn_ce2d_binary_fwd_bwd(ptr(outputs), ptr(targets), ptr(stats), ptr(scratch), i64(rows), int(fold_sigmoid), stream_ptr()),
+          "onn_ce2d_binary_fwd_bwd")
+    return float(stats[0]), outputs
 
 
 def dense_fwd_shared_input(x, weights, biases, outputs, pitches):

@@ -16,6 +16,8 @@ int launch_attention_softmax(float* scores, const uint8_t* key_is_pad, long long
 int launch_attention_softmax_bwd(const float* P, float* dP, long long rows, int Sk, cudaStream_t s);
 int launch_colsum_accumulate(const float* D, long long rows, long long cols, long long ld, float* out, cudaStream_t s);
 int launch_relu_delta(float* dY, const float* Y, long long n, cudaStream_t s);
+int launch_sigmoid(float* Y, long long n, cudaStream_t s);
+int launch_sigmoid_delta(float* dY, const float* Y, long long n, cudaStream_t s);
 
 #define ONN_TRY(expr) do { const int status_ = (expr); if(status_ != ONN_OK) return status_; } while(0)
 
@@ -86,7 +88,7 @@ extern "C" int onn_dense_fwd(const float* X, const float* W, const float* b, flo
                              uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(X && W && Y && rows > 0 && in > 0 && out > 0);
-    ONN_CHECK_ARG(activation == ONN_ACT_LINEAR || activation == ONN_ACT_RELU || activation == ONN_ACT_SOFTMAX);
+    ONN_CHECK_ARG(activation == ONN_ACT_LINEAR || activation == ONN_ACT_RELU || activation == ONN_ACT_SOFTMAX || activation == ONN_ACT_SIGMOID);
     ONN_CHECK_ARG(!relu_bits || activation == ONN_ACT_RELU);
     cudaStream_t s = (cudaStream_t)stream;
     onn_gemm_args g = plain_gemm(X, 0, in, W, 1, out, Y, out, rows, out, in);
@@ -96,6 +98,7 @@ extern "C" int onn_dense_fwd(const float* X, const float* W, const float* b, flo
     g.relu_bits_ld = onn_relu_bits_words_per_row(out);
     ONN_TRY(gemm(g, s));
     if(activation == ONN_ACT_SOFTMAX && !(flags & ONN_DEFER_SOFTMAX)) ONN_TRY(onn_softmax_rows(Y, rows, out, stream));
+    if(activation == ONN_ACT_SIGMOID) ONN_TRY(launch_sigmoid(Y, rows * out, s));
     return ONN_OK;
 }
 
@@ -125,12 +128,13 @@ extern "C" int onn_dense_bwd(const float* X, const float* W, const float* Y, flo
                              uint32_t flags, void* stream)
 {
     ONN_CHECK_ARG(X && W && dY && dW && rows > 0 && in > 0 && out > 0);
-    ONN_CHECK_ARG(activation == ONN_ACT_LINEAR || activation == ONN_ACT_RELU || activation == ONN_ACT_SOFTMAX);
-    ONN_CHECK_ARG(activation != ONN_ACT_RELU || Y);
+    ONN_CHECK_ARG(activation == ONN_ACT_LINEAR || activation == ONN_ACT_RELU || activation == ONN_ACT_SOFTMAX || activation == ONN_ACT_SIGMOID);
+    ONN_CHECK_ARG((activation != ONN_ACT_RELU && activation != ONN_ACT_SIGMOID) || Y);
     cudaStream_t s = (cudaStream_t)stream;
 
     // delta = dY * act'(Y); ReLU rewrites dY in place, as the reference does
     if(activation == ONN_ACT_RELU && !(flags & ONN_DELTA_READY)) ONN_TRY(launch_relu_delta(dY, Y, rows * out, s));
+    if(activation == ONN_ACT_SIGMOID && !(flags & ONN_DELTA_READY)) ONN_TRY(launch_sigmoid_delta(dY, Y, rows * out, s));
     const float* delta = dY;
 
     ONN_TRY(weight_gradients(X, delta, dW, db, rows, in, out, s));

@@ -669,6 +669,36 @@ int launch_colsum_accumulate(const float* D, long long rows, long long cols, lon
     return launch_status();
 }
 
+// Sigmoid activation (opennn/layer.h:196-204) in place, and its delta dY * y (1 - y) in place on dY.
+__global__ void sigmoid_kernel(float* __restrict__ Y, long long n)
+{
+    for(long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        Y[i] = 1.0f / (1.0f + expf(-Y[i]));
+}
+
+__global__ void sigmoid_delta_kernel(float* __restrict__ dY, const float* __restrict__ Y, long long n)
+{
+    for(long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    {
+        const float y = Y[i];
+        dY[i] = dY[i] * (y * (1.0f - y));
+    }
+}
+
+int launch_sigmoid(float* Y, long long n, cudaStream_t s)
+{
+    sigmoid_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(Y, n);
+    count_launch();
+    return launch_status();
+}
+
+int launch_sigmoid_delta(float* dY, const float* Y, long long n, cudaStream_t s)
+{
+    sigmoid_delta_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(dY, Y, n);
+    count_launch();
+    return launch_status();
+}
+
 int launch_relu_delta(float* dY, const float* Y, long long n, cudaStream_t s)
 {
     relu_delta_kernel<<<grid_for((n + 3) / 4, 256, 8), 256, 0, s>>>(dY, Y, n);
@@ -1056,6 +1086,49 @@ __global__ void ce2d_finish_kernel(const float* __restrict__ row_terms, long lon
     for(long long i = threadIdx.x; i < rows; i += blockDim.x) mine += row_terms[i];
     const float total = block_sum(mine, scratch);
     if(threadIdx.x == 0) { stats[0] = total / (float)(-rows); stats[1] = (float)rows; }
+}
+
+// CrossEntropyError2d with one output: per sample the error term and, in place, the output gradient.
+__global__ void ce2d_binary_kernel(float* __restrict__ outputs, const float* __restrict__ targets, float* __restrict__ row_terms, long long rows,
+                                   int fold_sigmoid)
+{
+    const float eps = 1.1920929e-07f, inv_rows = 1.0f / (float)rows;
+    for(long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += (long long)gridDim.x * blockDim.x)
+    {
+        const float y = outputs[i], t = targets[i];
+        const float clipped = fminf(fmaxf(y, eps), 1.0f - eps);
+        row_terms[i] = t * logf(clipped) + (1.0f - t) * logf(1.0f - clipped);
+        const float gradient = (-t / (y + eps) + (1.0f - t) / (1.0f - y + eps)) * inv_rows;
+        outputs[i] = fold_sigmoid ? gradient * (y * (1.0f - y)) : gradient;
+    }
+}
+
+__global__ void ce2d_binary_finish_kernel(const float* __restrict__ row_terms, long long rows, float* __restrict__ stats)
+{
+    __shared__ float scratch[32];
+    float mine = 0.f;
+    for(long long i = threadIdx.x; i < rows; i += blockDim.x) mine += row_terms[i];
+    const float total = block_sum(mine, scratch);
+    if(threadIdx.x == 0)
+    {
+        float error = total / (float)(-rows);
+        if(isnan(error) || isinf(error)) error = 10.0f;          // opennn/cross_entropy_error.cpp:53-54
+        stats[0] = error;
+        stats[1] = (float)rows;
+    }
+}
+
+extern "C" int onn_ce2d_binary_fwd_bwd(float* outputs, const float* targets, float* stats, float* row_scratch, int64_t rows,
+                                       int fold_sigmoid, void* stream)
+{
+    ONN_CHECK_ARG(outputs && targets && stats && row_scratch && rows > 0);
+    cudaStream_t s = (cudaStream_t)stream;
+    ce2d_binary_kernel<<<grid_for(rows, 256, 8), 256, 0, s>>>(outputs, targets, row_scratch, rows, fold_sigmoid);
+    count_launch();
+    if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    ce2d_binary_finish_kernel<<<1, 1024, 0, s>>>(row_scratch, rows, stats);
+    count_launch();
+    return launch_status();
 }
 
 extern "C" int onn_ce2d_fwd_bwd(float* probabilities, const float* targets, float* stats, float* row_scratch,

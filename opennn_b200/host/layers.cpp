@@ -398,6 +398,7 @@ int Dense3d::get_activation_code() const
     if(activation_function == "Linear") return ONN_ACT_LINEAR;
     if(activation_function == "RectifiedLinear") return ONN_ACT_RELU;
     if(activation_function == "Softmax") return ONN_ACT_SOFTMAX;
+    if(activation_function == "Sigmoid" || activation_function == "Logistic") return ONN_ACT_SIGMOID;   // layer.h:129-136
     throw std::runtime_error("Unknown activation: " + activation_function);
 }
 

@@ -181,7 +181,7 @@ Transformer::Transformer(Index input_sequence_length, Index decoder_sequence_len
 TextClassificationNetwork::TextClassificationNetwork(Index vocabulary_size, Index sequence_length, Index embedding_dimension, Index heads_number,
                                                      const vector<Index>& complexity_dimensions, Index classes)
 {
-    if(classes < 2) throw std::runtime_error("TextClassificationNetwork: the single-output (Sigmoid) variant is not implemented on this path.");
+    if(classes < 1) throw std::runtime_error("TextClassificationNetwork: at least one output.");
     auto embedding = std::make_unique<Embedding>(Shape{vocabulary_size, sequence_length}, embedding_dimension, "embedding_layer");
     embedding->set_scale_embedding(true);
     embedding->set_add_positional_encoding(true);
@@ -195,7 +195,7 @@ TextClassificationNetwork::TextClassificationNetwork(Index vocabulary_size, Inde
                   {get_layers_number() - 1});
         width = complexity_dimensions[i];
     }
-    add_layer(Dense3d::make_rank2(width, classes, "Softmax", "classification_layer"), {get_layers_number() - 1});
+    add_layer(Dense3d::make_rank2(width, classes, classes > 1 ? "Softmax" : "Sigmoid", "classification_layer"), {get_layers_number() - 1});
     compile();
     set_parameters_random();
 }

@@ -149,10 +149,21 @@ void CrossEntropyError2d::back_propagate(const TensorViewCuda& targets, ForwardP
     const TensorViewCuda outputs = forward_propagation.layers[size_t(last)]->outputs;
     const Index classes = outputs.shape.back();
     const Index samples = outputs.size() / classes;
-    if(classes < 2) throw std::runtime_error("CrossEntropyError2d: the binary (one output) variant is not implemented on this path.");
     if(targets.size() != samples * classes) throw std::runtime_error("CrossEntropyError2d: targets must be [samples, classes]");
-    check_onn(onn_ce2d_fwd_bwd(outputs.data, targets.data, statistics, row_scratch, samples, classes, stream()),
-              "CrossEntropyError2d::back_propagate");
+    if(classes == 1)
+    {
+        // binary form: the output buffer doubles as the gradient buffer, so the kernel leaves the Sigmoid layer's delta
+        auto* dense_back = dynamic_cast<Dense3dBackPropagationCuda*>(back_propagation.layers[size_t(last)].get());
+        const Dense3d* dense = dynamic_cast<const Dense3d*>(layers[size_t(last)].get());
+        if(!dense_back || !dense || dense->get_activation_code() != ONN_ACT_SIGMOID)
+            throw std::runtime_error("CrossEntropyError2d: one output needs a Dense \"Sigmoid\" output layer on this path.");
+        dense_back->delta_is_ready = true;
+        check_onn(onn_ce2d_binary_fwd_bwd(outputs.data, targets.data, statistics, row_scratch, samples, 1, stream()),
+                  "CrossEntropyError2d::back_propagate");
+    }
+    else
+        check_onn(onn_ce2d_fwd_bwd(outputs.data, targets.data, statistics, row_scratch, samples, classes, stream()),
+                  "CrossEntropyError2d::back_propagate");
     back_propagation.layers[size_t(last)]->output_gradients[0] = outputs;
     for(Index i = last; i >= first; i--)
         layers[size_t(i)]->back_propagate(forward_propagation.layers[size_t(i)], back_propagation.layers[size_t(i)]);

@@ -46,6 +46,26 @@ def test_cross_entropy_2d_kernel(libs):
         assert_close(gradient.cpu().numpy(), O.ce2d_output_gradients(probabilities, targets), 1e-6, "gradient")
 
 
+def test_binary_cross_entropy_2d_kernel(libs):
+    """onn_ce2d_binary_fwd_bwd against the restated CPU formulas, with outputs of exactly 0 and 1 (clipped in the error,
+    not in the gradient), plain and with the Sigmoid derivative folded in."""
+    capi, _ = libs
+    rng = np.random.default_rng(9)
+    for rows in (6, 1000):
+        y = (1.0 / (1.0 + np.exp(-2.0 * rng.standard_normal((rows, 1))))).astype(np.float32)
+        t = rng.integers(0, 2, (rows, 1)).astype(np.float32)
+        y[0], t[0] = 0.0, 0.0
+        y[1], t[1] = 1.0, 1.0
+        y[2], t[2] = 1.0, 0.0
+        expected_error = O.ce2d_binary_error(y, t)
+        expected_gradient = O.ce2d_binary_output_gradients(y, t)
+        error, gradient = capi.ce2d_binary(torch.from_numpy(y.copy()).cuda(), torch.from_numpy(t).cuda())
+        assert abs(error - expected_error) <= 1e-5 * abs(expected_error), (rows, error, expected_error)
+        assert_close(gradient.cpu().numpy(), expected_gradient, 1e-6, "gradient")
+        _, delta = capi.ce2d_binary(torch.from_numpy(y.copy()).cuda(), torch.from_numpy(t).cuda(), fold_sigmoid=True)
+        assert_close(delta.cpu().numpy(), expected_gradient * (y * (1 - y)), 1e-6, "delta")
+
+
 def test_classifier_structure(libs):
     _, trainer = libs
     B, S, V, E, H, hidden, classes, _ = CLASSIFIER_CASES["classifier_tiny"]
@@ -96,7 +116,7 @@ def test_classifier_training_steps(libs, name, gemm):
     # changes; on a network this small those few parameters show in the norm
     print(f"[{name}/{gemm}] parameters after {steps} Adam steps: l2-rel {l2_err:.2e}")
     assert l2_err <= (TOL if gemm == "simt" else 1e-2), f"parameters after Adam: l2-rel {l2_err:.2e}"
-    assert np.abs(after - g["params_out"]).max() <= 2.2 * 1e-3 * steps
+    assert np.abs(after - g["params_out"]).max() <= 2.2 * 1e-3 * steps      # classifier_binary: one Sigmoid output, binary loss
     assert capi.lib().onn_gemm_device_status() == 0
     c.close()
 
