@@ -20,7 +20,7 @@ ACCUMULATE = 2
 DEFER_SOFTMAX = 8
 DELTA_READY = 16
 ACT_LINEAR, ACT_RELU, ACT_SOFTMAX = 0, 1, 2
-ACTIVATIONS = {"Linear": ACT_LINEAR, "RectifiedLinear": ACT_RELU, "Softmax": ACT_SOFTMAX}
+ACTIVATIONS = {"Linear": ACT_LINEAR, "RectifiedLinear": ACT_RELU, "Softmax": ACT_SOFTMAX, "Sigmoid": 3, "Logistic": 3}
 
 
 class OnnError(RuntimeError):

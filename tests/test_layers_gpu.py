@@ -264,6 +264,30 @@ def test_greedy_next_token_from_logits(capi, V):
     assert host(ids_a)[1, 1] == 5 and host(ids_a)[3, 1] == 0 and host(ids_a)[4, 1] == V - 1 and host(fin_a)[4] == 1
 
 
+@pytest.mark.parametrize("rows,features,out", [(6, 24, 1), (100, 64, 12), (300, 256, 128)])
+def test_dense_sigmoid(capi, gemm_mode, rows, features, out):
+    """Dense "Sigmoid" forward and backward against an fp64 evaluation: y = 1 / (1 + exp(-(x W + b))),
+    delta = dY y (1 - y) written over dY, dW = X^T delta, db = column sums, dX = delta W^T."""
+    rng = np.random.default_rng(rows + out)
+    x = dev(rng.standard_normal((rows, features)).astype(np.float32))
+    w = dev((0.2 * rng.standard_normal((features, out))).astype(np.float32))
+    b = dev(rng.standard_normal(out).astype(np.float32))
+    d_y = dev(rng.standard_normal((rows, out)).astype(np.float32))
+    def close(a, e, what):
+        # tf32 products: a single element may sit a little above 1e-3 of the largest; the L2 error may not
+        max_err, l2_err = errors(host(a), host(e))
+        assert l2_err <= TOL and max_err <= (2 * TOL if gemm_mode == "auto" else TOL), f"{what}: max {max_err:.2e}, l2 {l2_err:.2e}"
+
+    y = capi.dense_fwd(x, w, b, "Sigmoid")
+    expected_y = torch.sigmoid(x.double() @ w.double() + b.double())
+    close(y, expected_y, "y")
+    dx, dw, db = capi.dense_bwd(x, w, y, d_y.clone(), "Sigmoid")
+    delta = d_y.double() * expected_y * (1 - expected_y)
+    close(dw, x.double().t() @ delta, "dW")
+    close(db, delta.sum(dim=0), "db")
+    close(dx, delta @ w.double().t(), "dX")
+
+
 @pytest.mark.parametrize("rows,features,out", [(8, 1024, 1024), (40, 256, 512), (3, 36, 20), (100, 64, 64)])
 def test_dense_fwd_shared_input(capi, gemm_mode, rows, features, out):
     """Three Linear projections of one input in one call, two of them written into rows of a wider buffer (cache
