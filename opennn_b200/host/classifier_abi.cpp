@@ -2,6 +2,7 @@
 // TextClassificationNetwork (opennn/standard_networks.cpp:575-615) with CrossEntropyError2d and Adam and runs the body
 // of the training loop (opennn/adaptive_moment_estimation.cpp:697-718) one optimiser step at a time on one GPU.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/onn_b200_host.h"
@@ -25,8 +26,17 @@ struct onn_classifier
     bool gradients_dirty = false;
     type* pinned = nullptr;              // {error, samples, square norm}
 
+    // CUDA-graph replay of forward pass + loss + back-propagation from the second step on: ids and targets are copied
+    // into fixed buffers first, so the captured kernels always read the same addresses (ONN_B200_GRAPHS=0 turns it off)
+    TensorCuda staged_ids, staged_targets;
+    cudaGraphExec_t step_graph = nullptr;
+    uint64_t graph_launches = 0;
+    bool graphs_enabled = true;
+    Index eager_steps = 0;
+
     ~onn_classifier()
     {
+        if(step_graph) cudaGraphExecDestroy(step_graph);
         if(pinned) cudaFreeHost(pinned);
         if(stream) cudaStreamDestroy(stream);
     }
@@ -70,6 +80,9 @@ extern "C" int onn_classifier_create(onn_classifier** out, int64_t vocabulary_si
         c->optimization.set(c->network->get_parameters_number());
         c->statistics.resize(8);
         c->row_scratch.resize(batch);
+        c->staged_ids.resize(batch * sequence_length);
+        c->staged_targets.resize(batch * classes);
+        if(const char* e = std::getenv("ONN_B200_GRAPHS")) c->graphs_enabled = e[0] != '0';
         check_cuda(cudaMallocHost(reinterpret_cast<void**>(&c->pinned), 4 * sizeof(type)), "pinned statistics");
         check_cuda(cudaStreamSynchronize(c->stream), "synchronize");
         *out = c.release();
@@ -156,10 +169,44 @@ extern "C" int onn_classifier_step_device(onn_classifier* c, const float* ids, c
         Device::instance().set_compute_stream(c->stream);
         if(c->gradients_dirty) c->back.gradients.fill(0);
         c->gradients_dirty = true;
-        const vector<TensorViewCuda> inputs = {TensorViewCuda(const_cast<float*>(ids), {c->batch, c->sequence_length})};
-        c->network->forward_propagate(inputs, *c->forward, true);
-        c->loss->back_propagate(TensorViewCuda(const_cast<float*>(targets), {c->batch, c->classes}), *c->forward, c->back,
-                                c->statistics.data, c->row_scratch.data);
+        check_cuda(cudaMemcpyAsync(c->staged_ids.data, ids, size_t(c->batch * c->sequence_length) * sizeof(type), cudaMemcpyDeviceToDevice, c->stream), "ids");
+        check_cuda(cudaMemcpyAsync(c->staged_targets.data, targets, size_t(c->batch * c->classes) * sizeof(type), cudaMemcpyDeviceToDevice, c->stream), "targets");
+        auto propagate = [&]
+        {
+            const vector<TensorViewCuda> inputs = {TensorViewCuda(c->staged_ids.data, {c->batch, c->sequence_length})};
+            c->network->forward_propagate(inputs, *c->forward, true);
+            c->loss->back_propagate(TensorViewCuda(c->staged_targets.data, {c->batch, c->classes}), *c->forward, c->back,
+                                    c->statistics.data, c->row_scratch.data);
+        };
+        bool replayed = false;
+        if(c->graphs_enabled && c->eager_steps > 0)            // the first step runs eagerly: it configures every kernel
+        {
+            if(!c->step_graph)
+            {
+                const uint64_t launches_before = onn_launch_count();
+                cudaGraph_t captured = nullptr;
+                bool ok = cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+                if(ok)
+                {
+                    try { propagate(); }
+                    catch(...) { ok = false; }
+                    ok = (cudaStreamEndCapture(c->stream, &captured) == cudaSuccess) && ok && captured != nullptr;
+                }
+                if(ok) ok = cudaGraphInstantiate(&c->step_graph, captured, 0) == cudaSuccess;
+                if(captured) cudaGraphDestroy(captured);
+                c->graph_launches = onn_launch_count() - launches_before;
+                onn_launch_count_add(0 - c->graph_launches);      // counted at capture, launched below
+                if(!ok) { cudaGetLastError(); c->step_graph = nullptr; c->graphs_enabled = false; }
+            }
+            if(c->step_graph)
+            {
+                check_cuda(cudaGraphLaunch(c->step_graph, c->stream), "step graph launch");
+                onn_launch_count_add(c->graph_launches);
+                replayed = true;
+            }
+        }
+        if(!replayed) propagate();
+        c->eager_steps++;
         if(statistics)
             check_cuda(cudaMemcpyAsync(c->pinned, c->statistics.data, 2 * sizeof(type), cudaMemcpyDeviceToHost, c->stream), "statistics");
         if(update)
