@@ -12,12 +12,18 @@ Launched by torchrun for N > 1 (one rank per GPU).  Rank 0 prints ONE JSON line.
   e2e       the same step through the host-buffer entry point: pinned host ids are copied to
             the device inside the timed region and the loss statistics are read back each step.
   roofline  the dominant kernel (tcgen05 tf32 GEMM at the FFN shape of this workload), timed
-            alone with CUDA events, against the measured dense tensor peak.
+            alone with CUDA events, against a TF32 tensor peak MEASURED in this run the way
+            MEASURED_PEAKS.json measured bf16 (a library GEMM at 8192^3 as a peak probe: best of
+            10 = burst, back to back for 4 s = sustained); the other GEMM layouts of the step
+            (input gradient, weight gradient, vocabulary projection) and the HBM-bound kernels
+            (LayerNorm, cross-entropy, Adam; against the measured copy bandwidth) beside it.
   cpu_baseline  the unmodified reference CPU library (oracle/_ref) on the box's host cores,
             on a bounded sample of the same workload (N = 1 only).
 
 --impl reference times that CPU library alone (the reference has no multi-GPU path and its
 own CUDA path needs cuDNN + its build system, which this benchmark does not run).
+--workload config3 | config4 print a profiling line for BASELINE.json's configs 3 and 4
+(tokens/s of the training step on one GPU, and the reference CPU library at full size).
 
 Data are synthetic: token ids uniform in [1, 32000), row lengths ~U[64, 256], right-padded
 with id 0, seed 3; parameters are the reference's default random initialisation.
@@ -43,6 +49,12 @@ WORKLOAD = dict(name="config5_large_encdec", S_in=256, S_dec=256, V_in=32000, V_
 # reachable with --workload config2, which prints a profiling line (step time with and without CUDA-graph replay)
 SMALL_WORKLOAD = dict(name="config2_small_encdec", S_in=32, S_dec=32, V_in=1000, V_out=1000, E=64, H=4, F=128, L=1,
                       global_batch=32, micro_batch=32, seed=3, min_len=8, max_len=32)
+# reference configs 3 (mid encoder-decoder) and 4 (long-sequence decoder-only stack, no padding): profiling lines
+MID_WORKLOAD = dict(name="config3_mid_encdec", S_in=128, S_dec=128, V_in=8000, V_out=8000, E=512, H=8, F=2048, L=6,
+                    global_batch=64, micro_batch=64, seed=1, min_len=32, max_len=128)
+LONG_WORKLOAD = dict(name="config4_long_decoder_only", decoder_only=True, S_in=0, S_dec=1024, V_in=0, V_out=8000, E=512, H=8, F=2048, L=2,
+                     global_batch=16, micro_batch=16, seed=2, min_len=1024, max_len=1024)
+CPU_SAMPLE_BATCH = 8          # samples of the 512-sample config-5 step the reference CPU library is timed on
 METRIC = "train tokens/s (fwd+bwd+Adam)"
 UNIT = "tokens/s"
 
@@ -61,6 +73,8 @@ def synthetic_batch(rng, batch, w):
     import numpy as np
 
     def ids(S, V):
+        if S == 0:
+            return None
         x = rng.integers(1, V, size=(batch, S)).astype(np.float32)
         lengths = rng.integers(w["min_len"], w["max_len"] + 1, size=batch)
         x[np.arange(S)[None, :] >= lengths[:, None]] = 0
@@ -80,11 +94,21 @@ def time_reference_cpu(w, batch, steps):
     cores = os.cpu_count() or 1
     rng = np.random.default_rng(w["seed"])
     enc, dec, tgt = synthetic_batch(rng, batch, w)
-    spec = dict(mode="transformer", B=batch, S_in=w["S_in"], S_dec=w["S_dec"], V_in=w["V_in"], V_out=w["V_out"], E=w["E"],
-                H=w["H"], F=w["F"], L=w["L"], steps=steps, lr=1e-3, dump=0, random_parameters=1)
-    _, seconds = ref_runner.run(spec, {"enc_ids": enc, "dec_ids": dec, "targets": tgt}, [], threads=cores)
+    spec = dict(mode="decoder" if w.get("decoder_only") else "transformer", B=batch, S_in=w["S_in"], S_dec=w["S_dec"], V_in=w["V_in"],
+                V_out=w["V_out"], E=w["E"], H=w["H"], F=w["F"], L=w["L"], steps=steps, lr=1e-3, dump=0, random_parameters=1)
+    tensors = {"dec_ids": dec, "targets": tgt}
+    if enc is not None:
+        tensors["enc_ids"] = enc
+    _, seconds = ref_runner.run(spec, tensors, [], threads=cores)
     best = min(seconds[1:]) if len(seconds) > 1 else seconds[0]
     return batch * w["S_dec"] / best, cores, seconds
+
+
+def workload_config(w, world, micro):
+    """The `config` object of the result line: the workload both arms run (the reference arm a bounded sample of it)."""
+    return {"workload": w["name"], "global_batch": w["global_batch"], "seq_len": w["S_dec"], "parallelism": f"dp{world}",
+            "micro_batch": micro, "layers": "6+6", "d_model": w["E"], "heads": w["H"], "ffn": w["F"], "vocab": w["V_out"],
+            "l2": "per-step working set (tens of GB of activations) far exceeds the 126 MB L2; batches rotate"}
 
 
 def run_reference(args):
@@ -96,7 +120,7 @@ def run_reference(args):
     if not ref_runner.available():
         emit({"impl": "reference", "unavailable": "oracle/_ref/onn_ref_harness is not built (make -C oracle)"})
         return
-    sample_batch = 2
+    sample_batch = CPU_SAMPLE_BATCH
     steps = max(2, min(args.steps + min(args.warmup, 1), 3))
     start = time.time()
     value, cores, seconds = time_reference_cpu(w, sample_batch, steps)
@@ -104,7 +128,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(seconds) - 1,
         "warmup": 1, "ms_per_step": 1e3 * min(seconds[1:]), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["name"], "global_batch": w["global_batch"], "seq_len": w["S_dec"], "parallelism": "cpu"},
+        "config": workload_config(w, args.gpus, min(w["micro_batch"], w["global_batch"] // max(args.gpus, 1))),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
                          "sample": f"batch {sample_batch} of the {w['global_batch']}-sample step (same S, E, H, F, V, L), "
                                    f"best of {len(seconds) - 1} steps after 1 warm-up, OpenMP/Eigen on {cores} threads, -O2"},
@@ -158,26 +182,95 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def time_dominant_kernel(capi, torch, w, peaks, copies=4, launches=24, with_cublas=True):
-    """The tcgen05 GEMM at the FFN-up shape of one micro-batch (M = 64*256 tokens, K = 1024,
-    N = 4096), launched back to back on fresh buffers larger than L2, timed with CUDA events."""
-    M, K, N = w["micro_batch"] * w["S_dec"], w["E"], w["F"]
-    # copies x (64 + 16 + 256) MiB of operands and outputs: every launch misses L2
-    A = [torch.randn(M, K, device="cuda") for _ in range(copies)]
-    B = [torch.randn(K, N, device="cuda") * 0.05 for _ in range(copies)]
-    Cm = [torch.empty(M, N, device="cuda") for _ in range(copies)]
-    bias = torch.zeros(N, device="cuda")
-    for i in range(copies):                      # warm-up
-        capi.gemm(A[i], B[i], Cm[i], M, N, K, K, N, N, 0, 1, bias=bias, relu=True)
+def measure_tf32_peak(torch, sustained_seconds=4.0):
+    """Dense TF32 tensor peak of this GPU, measured the way MEASURED_PEAKS.json measured bf16: a library GEMM
+    (torch.matmul with TF32 operands allowed) at 8192^3, best of 10 launches (burst) and back to back for
+    `sustained_seconds` (sustained, under the power cap).  A peak probe only: no product path calls it."""
+    n = 8192
+    a, b = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")
+    c = torch.empty(n, n, device="cuda")
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    flops = 2.0 * n ** 3
+    for _ in range(3):
+        torch.matmul(a, b, out=c)
+    torch.cuda.synchronize()
+    best = float("inf")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(10):
+        start.record()
+        torch.matmul(a, b, out=c)
+        stop.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(stop) * 1e-3)
+    sustained = None
+    if sustained_seconds > 0:
+        launches = max(10, int(sustained_seconds / best))
+        start.record()
+        for _ in range(launches):
+            torch.matmul(a, b, out=c)
+        stop.record()
+        torch.cuda.synchronize()
+        sustained = flops * launches / (start.elapsed_time(stop) * 1e-3) / 1e12
+    torch.backends.cuda.matmul.allow_tf32 = previous
+    return {"tf32_tflops": flops / best / 1e12, "tf32_tflops_sustained": sustained,
+            "how": "torch.matmul fp32 with TF32 operands allowed, 8192^3: best of 10 (burst) and back to back for %.0f s (sustained)" % sustained_seconds}
+
+
+def weight_gradient_splits(M, N, K):
+    """The reduction split the Dense layer picks for dW = X^T D (M = in, N = out, K = rows): the count, up to 16, whose
+    last wave of 256 x 256 tiles on 74 CTA pairs is fullest, each extra split charged 0.4 % for its pass of reduce-adds
+    (choose_split_k in opennn_b200/csrc/layers.cu; restated here so that the timed launch is the layer's own)."""
+    tiles, units = ((M + 255) // 256) * ((N + 255) // 256), 74
+    if tiles >= 4 * units or K < 1024:
+        return 1
+    best, best_score = 1, 0.0
+    for s in range(1, min(K // 512, 16) + 1):
+        work = tiles * s
+        waves = (work + units - 1) // units
+        score = work / (waves * units) - 0.004 * s
+        if score > best_score + 1e-9:
+            best, best_score = s, score
+    return best
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch, from ncu captures of `bench.py --profile-kernel ...`
+# (--set full --clock-control none, one kernel, two launches); the summaries of those captures are committed.
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    "gemm_tc2_kernel<0,1> M16384 N4096 K1024": {"read": 110.0e6, "write": 218.9e6, "algorithmic": 84e6 + 268e6},
+}
+
+
+def time_gemm(capi, torch, M, N, K, a_major, b_major, copies, launches, split_k=0, bias=False, relu=False):
+    """One GEMM shape of the step through onn_gemm, launched back to back on `copies` operand sets that together exceed
+    L2, timed with CUDA events.  Majors as the layers use them: (0,1) Y = X W, (0,0) dX = D W^T, (1,1) dW = X^T D."""
+    A = [torch.randn((M, K) if a_major == 0 else (K, M), device="cuda") for _ in range(copies)]
+    B = [torch.randn((K, N) if b_major == 1 else (N, K), device="cuda") * 0.05 for _ in range(copies)]
+    Cm = [torch.zeros(M, N, device="cuda") for _ in range(copies)]
+    lda, ldb = (K if a_major == 0 else M), (N if b_major == 1 else K)
+    bias_t = torch.zeros(N, device="cuda") if bias else None
+
+    def launch(i):
+        capi.gemm(A[i], B[i], Cm[i], M, N, K, lda, ldb, N, a_major, b_major, bias=bias_t, relu=relu, split_k=split_k)
+    for i in range(copies):
+        launch(i)
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for i in range(launches):
-        j = i % copies
-        capi.gemm(A[j], B[j], Cm[j], M, N, K, K, N, N, 0, 1, bias=bias, relu=True)
+        launch(i % copies)
     stop.record()
     torch.cuda.synchronize()
     seconds = start.elapsed_time(stop) * 1e-3 / launches
+    return seconds, A, B, Cm
+
+
+def time_dominant_kernel(capi, torch, w, peaks, copies=4, launches=24, with_cublas=True, tf32=None, other_layouts=True):
+    """The tcgen05 GEMM at the FFN-up shape of one micro-batch (M = 64*256 tokens, K = 1024,
+    N = 4096), launched back to back on fresh buffers larger than L2, timed with CUDA events."""
+    M, K, N = w["micro_batch"] * w["S_dec"], w["E"], w["F"]
+    # copies x (64 + 16 + 256) MiB of operands and outputs: every launch misses L2
+    seconds, A, B, Cm = time_gemm(capi, torch, M, N, K, 0, 1, copies, launches, bias=True, relu=True)
     flops = 2.0 * M * N * K
     achieved = flops / seconds / 1e12
 
@@ -188,6 +281,7 @@ def time_dominant_kernel(capi, torch, w, peaks, copies=4, launches=24, with_cubl
         for i in range(copies):
             torch.matmul(A[i], B[i], out=Cm[i])
         torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for i in range(launches):
             j = i % copies
@@ -196,15 +290,38 @@ def time_dominant_kernel(capi, torch, w, peaks, copies=4, launches=24, with_cubl
         torch.cuda.synchronize()
         cublas_tf32 = flops / (start.elapsed_time(stop) * 1e-3 / launches) / 1e12
         torch.backends.cuda.matmul.allow_tf32 = False
+    del A, B, Cm
 
-    return {"bound": "tensor", "kernel": "gemm_tc2_kernel<0,1> (Dense forward with bias + ReLU, two-CTA tcgen05, tf32 operands, fp32 accumulate)",
-            "shape": {"M": M, "N": N, "K": K}, "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-            "frac": achieved / peaks["tflops"], "frac_of_tf32_rate": achieved / (0.5 * peaks["tflops"]), "peak_source": "dense bf16 burst, " + peaks["source"] +
-            "; tf32 operands have half the bf16 rate, so 0.5 is this kernel's ceiling on this scale",
-            "us_per_launch": seconds * 1e6, "cublas_tf32_same_shape_tflops": cublas_tf32,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised in
-            # profiles/gemm_tc2_ffn_up_M16384_N4096_K1024_ncu.md (algorithmic bytes: 84 MB in + 268 MB out)
-            "traffic": 328.9e6}
+    # the kernel computes with tf32 operands, so its roofline is the TF32 tensor peak measured in this run (burst: the
+    # kernel is timed alone); the fraction of the bf16 burst peak of MEASURED_PEAKS.json stays beside it
+    if tf32:
+        peak, peak_source = tf32["tf32_tflops"], "dense TF32 burst, measured in this run (" + tf32["how"] + ")"
+    else:
+        peak, peak_source = 0.5 * peaks["tflops"], "half the dense bf16 burst peak (" + peaks["source"] + "): no TF32 probe in this run"
+    traffic = NCU_DRAM_BYTES_PER_LAUNCH["gemm_tc2_kernel<0,1> M16384 N4096 K1024"]
+    line = {"bound": "tensor", "kernel": "gemm_tc2_kernel<0,1> (Dense forward with bias + ReLU, two-CTA tcgen05, tf32 operands, fp32 accumulate)",
+            "shape": {"M": M, "N": N, "K": K}, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak, "frac_of_bf16_burst": achieved / peaks["tflops"], "bf16_burst_tflops": peaks["tflops"],
+            "peak_source": peak_source, "us_per_launch": seconds * 1e6, "cublas_tf32_same_shape_tflops": cublas_tf32,
+            "traffic": (traffic["read"] + traffic["write"]) if (M, N, K) == (16384, 4096, 1024) else None,
+            "algorithmic_bytes": 4.0 * (M * K + K * N + M * N)}
+    if tf32:
+        line["tf32_peak"] = tf32
+    if other_layouts:
+        V = w["V_out"]
+        shapes = [("input_gradient dX = D W^T, gemm_tc2_kernel<0,0>", M, K, N, 0, 0, 0),          # FFN-up layer: [M, F] x [E, F]^T
+                  ("weight_gradient dW = X^T D, gemm_tc2_kernel<1,1>, split-K", K, N, M, 1, 1, weight_gradient_splits(K, N, M)),
+                  ("ffn_down forward Y = X W, gemm_tc2_kernel<0,1>", M, K, N, 0, 1, 0),             # [M, F] x [F, E]
+                  ("vocabulary_projection Y = X W, gemm_tc2_kernel<0,1>", M, V, K, 0, 1, 0)]
+        layouts = {}
+        for name, m, n, k, a_major, b_major, splits in shapes:
+            sec, a, b, c = time_gemm(capi, torch, m, n, k, a_major, b_major, 2 if n >= 8192 else copies, 12, split_k=splits)
+            del a, b, c
+            tflops = 2.0 * m * n * k / sec / 1e12
+            layouts[name] = {"shape": {"M": m, "N": n, "K": k}, "split_k": splits, "us_per_launch": sec * 1e6, "achieved": tflops,
+                             "frac": tflops / peak, "frac_of_bf16_burst": tflops / peaks["tflops"]}
+        line["other_layouts"] = layouts
+    return line
 
 
 def time_attention_core(capi, torch, w):
@@ -230,21 +347,27 @@ def time_attention_core(capi, torch, w):
             "mha_fwd_us": start.elapsed_time(middle) * 1e3, "mha_bwd_us": middle.elapsed_time(stop) * 1e3}
 
 
-def time_row_kernels(capi, torch, w):
+def time_row_kernels(capi, torch, w, peaks=None, repeats=3):
     """The HBM-bound kernels of the step at the sizes of one micro-batch (and the whole parameter arena for Adam),
-    each launched twice on tensors larger than L2, timed with CUDA events."""
+    on tensors larger than L2 with every row active, timed with CUDA events (one warm-up launch, then the best of
+    `repeats` single launches); with `peaks`, each as a fraction of the measured copy bandwidth."""
     rows, E, V = w["micro_batch"] * w["S_dec"], w["E"], w["V_out"]
     out = {}
 
     def timed(name, fn, algorithmic_bytes):
         fn()
         torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        fn()
-        stop.record()
-        torch.cuda.synchronize()
-        out[name] = {"us": start.elapsed_time(stop) * 1e3, "algorithmic_MB": algorithmic_bytes / 1e6}
+        best = float("inf")
+        for _ in range(repeats):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            stop.record()
+            torch.cuda.synchronize()
+            best = min(best, start.elapsed_time(stop) * 1e-3)
+        out[name] = {"us": best * 1e6, "algorithmic_MB": algorithmic_bytes / 1e6, "achieved_gbs": algorithmic_bytes / best / 1e9}
+        if peaks:
+            out[name]["frac"] = algorithmic_bytes / best / 1e9 / peaks["hbm_gbs"]
 
     x, r, dy = (torch.randn(rows, E, device="cuda") for _ in range(3))
     gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
@@ -256,13 +379,15 @@ def time_row_kernels(capi, torch, w):
     logits = torch.randn(rows, V, device="cuda")
     targets = torch.randint(1, V, (rows,), device="cuda").float()
     timed("ce3d_fwd_bwd", lambda: capi.ce3d(logits, targets), 8 * rows * V)
+    timed("ce3d_fwd_bwd_two_sweeps", lambda: capi.ce3d(logits, targets, flags=32), 8 * rows * V)
     del logits
     n = 274_700_000                                   # the parameter count of config 5, rounded
     p, m, v, g = (torch.zeros(n, device="cuda") for _ in range(4))
     g.fill_(1e-3)
     sq = capi.grad_sqnorm(g)
     timed("adam", lambda: capi.adam(p, m, v, g, 2, sqnorm=sq, zero_grad=False), 32 * n)
-    return {"kernel": "layernorm_fwd/bwd, ce3d_fwd_bwd, adam", "kernels": out}
+    return {"kernel": "layernorm_fwd/bwd, ce3d_fwd_bwd, adam", "bound": "hbm", "peak_gbs": peaks["hbm_gbs"] if peaks else None,
+            "peak_source": ("copy bandwidth, " + peaks["source"]) if peaks else None, "kernels": out}
 
 
 def time_greedy_decode(trainer, torch, w, rows, tokens):
@@ -340,17 +465,17 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    if args.workload == "config2":
-        w = SMALL_WORKLOAD
+    if args.workload != "config5":
+        w = {"config2": SMALL_WORKLOAD, "config3": MID_WORKLOAD, "config4": LONG_WORKLOAD}[args.workload]
     if args.micro_batch:
         w = dict(w, micro_batch=args.micro_batch)
     peaks = measured_peaks()
     if args.profile_kernel == "gemm":
         # small stand-alone case for an ncu capture of the dominant kernel: 2 warm-up + 2 timed launches, 0.7 GB on the device
-        emit(dict(time_dominant_kernel(capi, torch, w, peaks, copies=2, launches=2, with_cublas=False), profiling_only=True))
+        emit(dict(time_dominant_kernel(capi, torch, w, peaks, copies=2, launches=2, with_cublas=False, other_layouts=False), profiling_only=True))
         return
     if args.profile_kernel == "rowwise":
-        emit(dict(time_row_kernels(capi, torch, w), profiling_only=True))
+        emit(dict(time_row_kernels(capi, torch, w, peaks, repeats=1), profiling_only=True))
         return
     if args.profile_kernel == "attention":
         emit(dict(time_attention_core(capi, torch, w), profiling_only=True))
@@ -366,7 +491,8 @@ def run_ours(args):
         w = dict(w, global_batch=args.profile_batch, name=w["name"] + f" (profiling batch {args.profile_batch})")
     local_batch = w["global_batch"] // world
     micro = min(w["micro_batch"], local_batch)
-    t = trainer.Trainer(trainer.TRANSFORMER, w["S_in"], w["S_dec"], w["V_in"], w["V_out"], w["E"], w["H"], w["F"], w["L"], micro)
+    kind = trainer.DECODER_ONLY if w.get("decoder_only") else trainer.TRANSFORMER
+    t = trainer.Trainer(kind, w["S_in"], w["S_dec"], w["V_in"], w["V_out"], w["E"], w["H"], w["F"], w["L"], micro)
     if world > 1:
         # host-side check first: every rank present, same parameter arena and micro-batch on all of them
         comm = trainer.dp_init_from_torch(signature={"parameters": t.parameters_number, "micro_batch": micro, "workload": w["name"]})
@@ -378,9 +504,10 @@ def run_ours(args):
     host_batches, device_batches = [], []
     for _ in range(pool):
         enc, dec, tgt = synthetic_batch(rng, w["global_batch"], w)
-        pinned = [torch.from_numpy(np.ascontiguousarray(x)).pin_memory() for x in trainer.shard_batch((dec, enc, tgt), rank, world)]
+        pinned = [None if x is None else torch.from_numpy(np.ascontiguousarray(x)).pin_memory()
+                  for x in trainer.shard_batch((dec, enc, tgt), rank, world)]
         host_batches.append(pinned)
-        device_batches.append([x.cuda() for x in pinned])
+        device_batches.append([None if x is None else x.cuda() for x in pinned])
 
     def barrier():
         if world > 1:
@@ -426,12 +553,25 @@ def run_ours(args):
     clocks = sampler.stop() if sampler else None
 
     if args.profile_batch or args.workload != "config5":
-        line = {"profiling_only": True, "workload": w["name"], "ms_per_step": 1e3 * seconds / args.steps, "gpu_launches": int(launches)}
+        line = {"profiling_only": True, "workload": w["name"], "ms_per_step": 1e3 * seconds / args.steps, "gpu_launches": int(launches),
+                "tokens_per_s": tokens_per_step * args.steps / seconds, "steps": args.steps, "clocks": clocks,
+                "config": {k: w[k] for k in ("S_in", "S_dec", "V_out", "E", "H", "F", "L", "global_batch", "micro_batch")}}
         if args.workload != "config5":
             # the same steps launched kernel by kernel, to show what the graph replay of the micro-batch saves
             t.set_graph_capture(False)
             device_step(0)
             line["ms_per_step_without_graphs"] = 1e3 * timed(device_step, args.steps) / args.steps
+            status = capi.lib().onn_gemm_device_status()
+            if status != 0:
+                raise SystemExit("a kernel gave up on a bounded wait: the numbers are void")
+            if rank == 0 and args.workload in ("config3", "config4") and not args.no_cpu_baseline:
+                # the reference CPU library on the same configuration at full size (second of two steps)
+                from oracle import ref_runner
+                if ref_runner.available():
+                    value, cores, step_seconds = time_reference_cpu(w, w["global_batch"], 2)
+                    line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cores, "kind": "reference", "seconds_per_step": step_seconds,
+                                            "sample": "the whole configuration, second of 2 steps, unmodified reference CPU library, "
+                                                      f"OpenMP/Eigen on {cores} threads, -O2"}
         if rank == 0:
             emit(line)
         t.close()
@@ -468,37 +608,44 @@ def run_ours(args):
             dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
             return float(elapsed.item()) * 1e-3 / repeats
 
+        sharded = os.environ.get("ONN_B200_DP_SHARDED", "1") != "0"
         exchange(0)
         exchange_seconds = timed_on_current(exchange, 5)
         t.set_dp(None, 1)
         device_step(0)
         local_seconds = timed(device_step, args.steps) / args.steps
         arena_bytes = 4 * t.parameters_number
-        allreduce = {"bytes": arena_bytes, "alone_ms": 1e3 * exchange_seconds,
+        allreduce = {"update": "sharded: reduce-scatter by buckets, Adam on 1/world of the arena, all-gather" if sharded else
+                               "all-reduce by buckets, the whole update on every rank",
+                     "carve_sms": int(os.environ.get("ONN_B200_DP_CARVE_SMS", "0") or 0),
+                     "bytes": arena_bytes, "alone_ms": 1e3 * exchange_seconds,
                      "bus_gbs": 2 * (world - 1) / world * arena_bytes / exchange_seconds / 1e9,
                      "step_ms_without_exchange": 1e3 * local_seconds,
                      "exposed_ms_per_step": 1e3 * (seconds / args.steps - local_seconds)}
 
     if rank == 0:
-        roofline = time_dominant_kernel(capi, torch, w, peaks)
+        t.close()                                     # the stand-alone kernel timings below want the trainer's memory
+        # the kernel figures belong to the one-GPU line; data-parallel lines keep the dominant kernel and a burst probe only
+        tf32 = measure_tf32_peak(torch, sustained_seconds=4.0 if world == 1 else 0.0)
+        roofline = time_dominant_kernel(capi, torch, w, peaks, tf32=tf32, other_layouts=world == 1)
+        if world == 1:
+            roofline["hbm_kernels"] = time_row_kernels(capi, torch, w, peaks)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             from oracle import ref_runner
             if ref_runner.available():
-                value, cores, step_seconds = time_reference_cpu(w, 2, 2)
+                value, cores, step_seconds = time_reference_cpu(w, CPU_SAMPLE_BATCH, 2)
                 cpu = {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
-                       "sample": f"batch 2 of the {w['global_batch']}-sample step (same S, E, H, F, V, L), second of 2 steps, "
+                       "sample": f"batch {CPU_SAMPLE_BATCH} of the {w['global_batch']}-sample step (same S, E, H, F, V, L), second of 2 steps, "
                                  f"unmodified reference CPU library, OpenMP/Eigen on {cores} threads, -O2"}
         ids_bytes = 4 * w["global_batch"] * (2 * w["S_dec"] + w["S_in"])
         line = {
             "metric": METRIC, "value": tokens_per_step * args.steps / seconds, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": 1e3 * seconds / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "tf32 operands, f32 accumulate/storage", "data": "synthetic",
-            "config": {"workload": w["name"], "global_batch": w["global_batch"], "seq_len": w["S_dec"], "parallelism": f"dp{world}",
-                       "micro_batch": micro, "layers": "6+6", "d_model": w["E"], "heads": w["H"], "ffn": w["F"], "vocab": w["V_out"],
-                       "l2": "per-step working set (tens of GB of activations) far exceeds the 126 MB L2; batches rotate"},
+            "config": workload_config(w, world, micro),
             "e2e": {"value": tokens_per_step * args.steps / e2e_seconds, "unit": UNIT, "ms_per_step": 1e3 * e2e_seconds / args.steps,
-                    "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4 * (4 * (local_batch // micro) + 2) * world,
+                    "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4 * (4 * (local_batch // micro) + 3) * world,
                     "last_loss": last_stats[0][0] if last_stats[0] else None},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             # decoder tokens are the metric's unit; the encoder side of every sample is computed as well
@@ -524,8 +671,9 @@ def main():
                         help="profiling aid: run the device-resident loop only, on a global batch of this many samples "
                              "(the line it prints is not a benchmark result)")
     parser.add_argument("--micro-batch", type=int, default=0, help="samples per micro-batch (default: the workload's own)")
-    parser.add_argument("--workload", default="config5", choices=["config5", "config2"],
-                        help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network")
+    parser.add_argument("--workload", default="config5", choices=["config5", "config2", "config3", "config4"],
+                        help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network, config3 / config4 "
+                             "one for the mid encoder-decoder and the long-sequence decoder-only stack (with the reference CPU library beside it)")
     parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention", "rowwise", "decode", "classifier"],
                         help="profiling aid: launch only the dominant GEMM (FFN-up shape) four times on buffers larger than L2, "
                              "or only one attention layer (forward and backward, 32 samples) twice, or only the HBM-bound kernels "

@@ -44,6 +44,7 @@ extern "C" {
 #define ONN_ACCUMULATE          2u     /* add into the destination instead of overwriting */
 #define ONN_DEFER_SOFTMAX       8u     /* Dense "Softmax": leave logits; the loss kernel fuses the softmax */
 #define ONN_DELTA_READY        16u     /* Dense backward: dY already holds dY * act'(Y) */
+#define ONN_CE_TWO_SWEEPS      32u     /* onn_ce3d_fwd_bwd: keep to the kernel that sweeps each row twice through global memory */
 
 /* activations of Dense<3> used by the transformer (opennn/standard_networks.cpp:745,753,890) */
 #define ONN_ACT_LINEAR   0
@@ -110,9 +111,21 @@ int onn_gemm(const onn_gemm_args* args, void* stream);
  * CUDA-core fp32 kernel, 2 = require tcgen05 (ONN_ERR_UNSUPPORTED if it cannot run).
  * The environment variable ONN_B200_GEMM=simt|tc sets the initial value. */
 int onn_gemm_set_mode(int mode);
-/* 0, or ONN_ERR_DEVICE_TIMEOUT if a tcgen05 GEMM gave up on a bounded barrier wait since
- * the last call (the status word is read back and cleared; synchronises the device). */
+/* 0, or ONN_ERR_DEVICE_TIMEOUT if a kernel of this library (tcgen05 GEMM, fused attention, staged cross-entropy)
+ * gave up on a bounded barrier wait since the last call.  The status words are read back and cleared; the call
+ * synchronises the whole device first, so it sees every kernel launched before it on any stream. */
 int onn_gemm_device_status(void);
+/* The same information in stream order and without a host synchronisation: enqueues on `stream` a one-thread kernel
+ * that writes the OR of the status words to device_word[0] (0 = no wait has run out).  It sees the kernels that
+ * precede it on `stream`; nothing is cleared (onn_gemm_device_status clears).  A caller copies the word to pinned
+ * memory with its other read-backs, or hands it to onn_adam_guarded so that a step whose kernels gave up does not
+ * reach the parameters.  No counterpart in the reference. */
+int onn_device_status_gather(uint32_t* device_word, void* stream);
+/* How many SMs the persistent kernels (tcgen05 GEMMs, fused attention, staged cross-entropy: one CTA or CTA pair per
+ * SM holding most of its shared memory) occupy from the next launch on: 0 or >= 148 = all of them (the default).
+ * A data-parallel caller lowers it while NCCL reduces a gradient bucket, so that NCCL's CTAs find free SMs instead of
+ * waiting for a kernel boundary.  Takes effect in stream order (it is read when a kernel is launched). */
+int onn_set_sm_limit(int sms);
 /* Failure-detection self-test (no counterpart in the reference): runs a one-thread kernel that waits, with a
  * 1 ms limit, on a barrier nothing ever signals.  *gave_up receives 1 when the wait ran out as it must; the
  * kernel returns normally, the context stays usable, and the next onn_gemm_device_status() reports
@@ -329,6 +342,9 @@ const float* onn_mha_attention_weights(const float* fwd_workspace,
  * Softmax Dense layer leaves them).  probabilities_out (optional) receives p.
  * stats (device, 4 floats) receives {sum of -log terms, #correct, #active(local), 0};
  * row_scratch is [2*rows] floats.
+ * Rows of 4096 to 55296 logits (a multiple of 4, 16-byte aligned, no probabilities_out) are staged in shared
+ * memory by a persistent kernel, so each logit crosses HBM once in and once out; other shapes, and calls with
+ * ONN_CE_TWO_SWEEPS in flags, take one CTA per row that sweeps the row twice (the second sweep mostly from L2).
  * ------------------------------------------------------------------------------------- */
 int onn_ce3d_count_active(const float* targets, int64_t rows, int64_t V, float* counts, void* stream);
 int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float* active_count,
@@ -401,20 +417,44 @@ int onn_grad_sqnorm(const float* g, int64_t n, float* sqnorm, float* workspace, 
 int onn_adam(float* p, float* m, float* v, float* g, int64_t n,
              float lr, float beta1, float beta2, float eps, float bc1, float bc2,
              float clip_norm, const float* sqnorm, float grad_scale, int zero_grad, void* stream);
+/* onn_adam that leaves p, m, v and g untouched when skip_if_nonzero[0] != 0 (device word, see
+ * onn_device_status_gather; NULL = plain onn_adam). */
+int onn_adam_guarded(float* p, float* m, float* v, float* g, int64_t n,
+                     float lr, float beta1, float beta2, float eps, float bc1, float bc2,
+                     float clip_norm, const float* sqnorm, float grad_scale, int zero_grad,
+                     const uint32_t* skip_if_nonzero, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Data-parallel gradient exchange (no counterpart in the reference, which is single-GPU):
- * NCCL all-reduce (sum) of contiguous fp32 buffers on a dedicated communication stream.
+ * NCCL collectives (sum) on contiguous fp32 buffers on a dedicated communication stream.
  * One process per GPU.  The 128-byte unique id is created on rank 0 with onn_dp_unique_id
  * and handed to the other ranks by the caller (any out-of-band channel).
+ * ncclCommInitRank has no time limit: check on the host that every rank is present before
+ * calling onn_dp_init (the Python binding does, with a bounded rendezvous).
  * ------------------------------------------------------------------------------------- */
 typedef struct onn_dp_comm onn_dp_comm;
 int onn_dp_unique_id(void* host_id128);
 int onn_dp_init(onn_dp_comm** comm, const void* host_id128, int world, int rank);
+/* The same with a cap on the CTAs (SMs) NCCL's kernels may use; 0 = NCCL's own choice. */
+int onn_dp_init_config(onn_dp_comm** comm, const void* host_id128, int world, int rank, int max_ctas);
+int onn_dp_world(const onn_dp_comm* comm);
+int onn_dp_rank(const onn_dp_comm* comm);
 /* Enqueue all-reduce(sum) of buf[0..n) in place on the comm stream after `after_stream`'s
  * current work; onn_dp_wait makes `stream` wait for everything enqueued so far. */
 int onn_dp_allreduce(onn_dp_comm* comm, float* buf, int64_t n, void* after_stream);
+/* Reduce-scatter: send holds world * recv_count floats; recv receives the sum over ranks of this rank's
+ * recv_count-float part.  All-gather: every rank contributes send_count floats, recv receives world * send_count
+ * (rank r's part at r * send_count; send may lie inside recv at that place).  Ordered like onn_dp_allreduce. */
+int onn_dp_reduce_scatter(onn_dp_comm* comm, const float* send, float* recv, int64_t recv_count, void* after_stream);
+int onn_dp_all_gather(onn_dp_comm* comm, const float* send, float* recv, int64_t send_count, void* after_stream);
+/* Zero buf[0..n) on the comm stream after the collectives enqueued so far (a gradient bucket that has been
+ * reduced is cleared for the next step off the compute stream). */
+int onn_dp_zero(onn_dp_comm* comm, float* buf, int64_t n);
 int onn_dp_wait(onn_dp_comm* comm, void* stream);
+/* After a failure between collectives on this rank (an exception half-way through a step) the ranks no longer
+ * agree on which collective comes next: mark the communicator, and every later call returns ONN_ERR_NCCL instead
+ * of joining a collective the peers are not in.  A failed NCCL call marks it by itself. */
+int onn_dp_mark_failed(onn_dp_comm* comm);
 int onn_dp_finalize(onn_dp_comm* comm);
 
 #ifdef __cplusplus

@@ -54,8 +54,19 @@ int onn_trainer_set_learning_rate(onn_trainer* trainer, float learning_rate);
 int onn_trainer_set_iteration(onn_trainer* trainer, int64_t iteration);
 
 /* Data parallelism: every rank holds a full replica and calls step with its shard of the
- * batch; gradients and the active-token count are summed across ranks (onn_dp_*). */
+ * batch; gradients and the active-token count are summed across ranks (onn_dp_*).
+ * A step that updates reduce-scatters the gradient arena bucket by bucket from inside back-propagation, runs the
+ * norm, clip and Adam on this rank's 1/world of every bucket (the moments exist for that share only) and all-gathers
+ * the updated parameters; a step with update = 0 all-reduces, so that every rank can read the whole gradient.
+ * onn_trainer_set_dp_options, BEFORE onn_trainer_set_dp: sharded_update = 0 keeps the all-reduce and the whole update
+ * on every rank (ONN_B200_DP_SHARDED=0 does the same); carve_sms > 0 makes the persistent kernels of the carve_launches
+ * launches that follow a bucket (rounded up to a layer) leave that many SMs free for NCCL's kernels
+ * (ONN_B200_DP_CARVE_SMS, ONN_B200_DP_CARVE_LAUNCHES; see onn_set_sm_limit); bucket_floats > 0 sets the size of a
+ * gradient bucket (default 16 Mi floats = 64 MiB, ONN_B200_DP_BUCKET_FLOATS).
+ * world = 1 (comm NULL) returns the trainer to single-GPU steps; moments are not carried over between the two modes.
+ * An exception in the middle of a data-parallel step marks the communicator failed (onn_dp_mark_failed). */
 int onn_trainer_set_dp(onn_trainer* trainer, onn_dp_comm* comm, int world);
+int onn_trainer_set_dp_options(onn_trainer* trainer, int sharded_update, int carve_sms, int carve_launches, int64_t bucket_floats);
 
 /* CUDA-graph replay of the micro-batch (forward, loss, back-propagation), on by default (ONN_B200_GRAPHS=0 or
  * enabled = 0 turns it off).  The first step runs eagerly; after that every micro-batch index is captured once
@@ -64,7 +75,10 @@ int onn_trainer_set_dp(onn_trainer* trainer, onn_dp_comm* comm, int world);
  * hands gradient buckets to the all-reduce as it goes, always runs eagerly.  Results do not change. */
 int onn_trainer_set_graph_capture(onn_trainer* trainer, int enabled);
 
-/* One optimiser step on a batch of `batch` samples (a multiple of micro_batch).
+/* One optimiser step on a batch of `batch` samples (a multiple of micro_batch, at most 64 micro-batches).
+ * After back-propagation the step gathers the bounded-wait status words of its kernels in stream order
+ * (onn_device_status_gather); the update does not run if one is set, and the call that next synchronises (a step with
+ * statistics, onn_trainer_synchronize) or the next step returns ONN_ERR_DEVICE_TIMEOUT.
  * ids and targets are floats holding integers, [batch, sequence]; encoder_ids is NULL for
  * the decoder-only network.  update = 0 stops after back-propagation (gradients stay in the
  * arena for onn_trainer_get_gradients; the next step starts by zeroing them).
@@ -127,6 +141,13 @@ int onn_classifier_set_learning_rate(onn_classifier* classifier, float learning_
 int onn_classifier_forward(onn_classifier* classifier, const float* ids, float* host_probabilities);
 /* forward pass, loss, back-propagation and (update != 0) the Adam update */
 int onn_classifier_step_device(onn_classifier* classifier, const float* ids, const float* targets, int update, float* statistics);
+/* Output of one layer after the last forward pass (for parity checks), and its size in floats. */
+int onn_classifier_get_layer_output(onn_classifier* classifier, int layer, float* host_output, int64_t count);
+int64_t onn_classifier_layer_output_size(const onn_classifier* classifier, int layer);
+/* Data-parallel training: every rank steps its own `batch` samples; the gradient arena and {error, samples} are
+ * summed over the ranks after back-propagation (onn_dp_allreduce) and the update divides by the rank count, since the
+ * loss is a mean over samples.  onn_classifier_get_gradients then returns the sum over ranks.  world = 1: off. */
+int onn_classifier_set_dp(onn_classifier* classifier, onn_dp_comm* comm, int world);
 
 #ifdef __cplusplus
 }

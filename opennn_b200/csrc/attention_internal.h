@@ -21,4 +21,5 @@ int attention_bwd_fused_launch(const float* k, const float* v, const float* weig
                                float* d_scores, float* d_q, float* d_bias_q, long long B, long long Sq, long long Sk, long long E, long long H,
                                float scale, cudaStream_t stream);
 int attention_tc_read_status();
+const unsigned int* attention_tc_status_word();      // device address on the current device
 }

@@ -671,14 +671,9 @@ template <bool BACKWARD>
 static int launch_attention_core(const CUtensorMap& a, const CUtensorMap& b1, const CUtensorMap& b2, const CUtensorMap& w, const CUtensorMap& o,
                                  const CUtensorMap& in, const AttnParams& p, cudaStream_t stream)
 {
-    static bool configured = false;
-    if(!configured)
-    {
-        if(cudaFuncSetAttribute(attention_core_kernel<kAttnHeadSize, BACKWARD>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess)
-            return ONN_ERR_CUDA;
-        configured = true;
-    }
-    const int grid = (int)(p.items < kSmCount ? p.items : kSmCount);
+    static PerDeviceBytes configured;                        // per instantiation and per device
+    if(!ensure_dynamic_smem(attention_core_kernel<kAttnHeadSize, BACKWARD>, configured, kAttnSmem)) return ONN_ERR_CUDA;
+    const int grid = (int)(p.items < sm_limit() ? p.items : sm_limit());
     const cudaError_t launched = launch_overlapped(attention_core_kernel<kAttnHeadSize, BACKWARD>, dim3(grid), dim3(kAttnThreads), kAttnSmem, stream, a, b1, b2, w, o, in, p);
     count_launch();
     return launched == cudaSuccess ? launch_status() : ONN_ERR_CUDA;
@@ -728,6 +723,8 @@ int attention_bwd_fused_launch(const float* k, const float* v, const float* weig
     if(!ok) return ONN_ERR_UNSUPPORTED;
     return launch_attention_core<true>(map_do, map_v, map_k, map_ds, map_dq, map_w, p, stream);
 }
+
+const unsigned int* attention_tc_status_word() { return tc::status_word_address(); }
 
 int attention_tc_read_status()
 {

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include <cstdlib>
+#include <mutex>
 #include <utility>
 
 #include "../../include/onn_b200.h"
@@ -15,11 +16,34 @@ namespace onn
 
 constexpr int kSmCount = 148;   // B200: 2 dies x 74 SMs; grids are sized in multiples of this
 
+// How many SMs the persistent kernels (one CTA or CTA pair per SM, most of the SM's shared memory each) may occupy;
+// kSmCount unless a caller has asked for fewer with onn_set_sm_limit, e.g. to leave SMs to NCCL's kernels while a
+// gradient bucket is being reduced.  Read on the host at launch time, so it takes effect in stream order.
+int sm_limit();
+
 #define ONN_CHECK_ARG(cond) do { if(!(cond)) return ONN_ERR_INVALID_ARGUMENT; } while(0)
 
 inline int launch_status()
 {
     return cudaGetLastError() == cudaSuccess ? ONN_OK : ONN_ERR_CUDA;
+}
+
+// A function attribute (the dynamic shared memory a kernel may use) belongs to the CURRENT device's copy of the
+// function, so it is set once per device, before the first launch there that needs it.  One PerDeviceBytes per kernel.
+constexpr int kMaxDevices = 64;
+struct PerDeviceBytes { std::mutex lock; size_t bytes[kMaxDevices]; };
+
+template <typename Kernel>
+inline bool ensure_dynamic_smem(Kernel kernel, PerDeviceBytes& state, size_t wanted)
+{
+    int device = 0;
+    if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return false;
+    std::lock_guard<std::mutex> guard(state.lock);
+    if(wanted <= state.bytes[device]) return true;
+    if(wanted > 48 * 1024 &&
+       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wanted) != cudaSuccess) return false;
+    state.bytes[device] = wanted;
+    return true;
 }
 
 inline int grid_for(long long work_items, int items_per_block, int blocks_per_sm)

@@ -3,11 +3,13 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "gemm_internal.h"
 #include "attention_internal.h"
 #include "launch_counter.h"
+#include "rowwise_internal.h"
 
 namespace onn
 {
@@ -23,8 +25,17 @@ static int initial_mode()
 }
 
 static std::atomic<int> g_mode{initial_mode()};
+static std::atomic<int> g_sm_limit{kSmCount};
+
+int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
 
 int gemm_mode() { return g_mode.load(std::memory_order_relaxed); }
+
+// ORs the status words of the kernels with bounded waits into one word, in stream order.
+__global__ void status_gather_kernel(const unsigned int* a, const unsigned int* b, const unsigned int* c, unsigned int* out)
+{
+    out[0] = a[0] | b[0] | c[0];
+}
 
 int gemm(const onn_gemm_args& g, cudaStream_t stream)
 {
@@ -87,11 +98,43 @@ extern "C" int onn_gemm_set_mode(int mode)
     return ONN_OK;
 }
 
+extern "C" int onn_set_sm_limit(int sms)
+{
+    ONN_CHECK_ARG(sms >= 0);
+    g_sm_limit.store(sms == 0 || sms > kSmCount ? kSmCount : (sms < 2 ? 2 : sms), std::memory_order_relaxed);
+    return ONN_OK;
+}
+
 extern "C" int onn_gemm_device_status(void)
 {
     const int gemm_status = gemm_tc_read_status();
     const int attention_status = attention_tc_read_status();
-    return gemm_status != ONN_OK ? gemm_status : attention_status;
+    const int loss_status = ce3d_staged_read_status();
+    return gemm_status != ONN_OK ? gemm_status : attention_status != ONN_OK ? attention_status : loss_status;
+}
+
+extern "C" int onn_device_status_gather(uint32_t* device_word, void* stream)
+{
+    ONN_CHECK_ARG(device_word);
+    // the three addresses belong to the current device; looked up per device, once
+    static std::mutex lock;
+    static const unsigned int* words[kMaxDevices][3] = {};
+    int device = 0;
+    if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return ONN_ERR_CUDA;
+    const unsigned int* a; const unsigned int* b; const unsigned int* c;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        if(!words[device][0])
+        {
+            const unsigned int* found[3] = { gemm_tc_status_word(), attention_tc_status_word(), ce3d_staged_status_word() };
+            if(!found[0] || !found[1] || !found[2]) return ONN_ERR_CUDA;
+            for(int i = 0; i < 3; i++) words[device][i] = found[i];
+        }
+        a = words[device][0]; b = words[device][1]; c = words[device][2];
+    }
+    status_gather_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(a, b, c, device_word);
+    count_launch();
+    return launch_status();
 }
 
 extern "C" int onn_selftest_bounded_wait(int* gave_up)

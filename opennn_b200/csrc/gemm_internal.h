@@ -14,6 +14,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream);
 // k_parts > 1: true when the two-CTA kernel can run the product in one launch (else the front end adds up P launches).
 bool gemm_tc_takes_parts(const onn_gemm_args& g);
 int gemm_tc_read_status();
+const unsigned int* gemm_tc_status_word();           // device address on the current device
 int gemm_tc_bounded_wait_selftest(int* gave_up_host);
 
 // fp32 CUDA-core kernel for M <= 64 rows against a [K, N] row-major matrix (one decoding step): streams the matrix with

@@ -394,13 +394,9 @@ gemm_skinny_mma_kernel(const Params p)
 
 // Launch with the cluster along y (and programmatic dependent launch, as every kernel of the step).
 template <typename Kernel>
-int launch_kernel(Kernel kernel, bool& configured, size_t shared, int bn, int splits, const Params& p, cudaStream_t stream)
+int launch_kernel(Kernel kernel, PerDeviceBytes& configured, size_t shared, int bn, int splits, const Params& p, cudaStream_t stream)
 {
-    if(!configured)
-    {
-        if(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess) return ONN_ERR_CUDA;
-        configured = true;
-    }
+    if(!ensure_dynamic_smem(kernel, configured, shared)) return ONN_ERR_CUDA;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)((p.N + bn - 1) / bn), splits, (unsigned)p.problems);
     config.blockDim = dim3(THREADS);
@@ -423,7 +419,7 @@ int launch_kernel(Kernel kernel, bool& configured, size_t shared, int bn, int sp
 template <int MB, int SPLITS>
 int launch_mma(const Params& p, cudaStream_t stream)
 {
-    static bool configured = false;                      // per instantiation; the attribute belongs to the function
+    static PerDeviceBytes configured;                    // per instantiation and device; the attribute belongs to the function
     return launch_kernel(gemm_skinny_mma_kernel<MB, SPLITS>, configured, sizeof(MmaStage<MB>) * mma_stages<MB>(), MMA_BN, SPLITS, p, stream);
 }
 
@@ -442,7 +438,7 @@ int launch_mma_splits(const Params& p, int splits, cudaStream_t stream)
 template <int MB, int BN, int SPLITS>
 int launch(const Params& p, cudaStream_t stream)
 {
-    static bool configured = false;                      // per instantiation; the attribute belongs to the function
+    static PerDeviceBytes configured;                    // per instantiation and device; the attribute belongs to the function
     return launch_kernel(gemm_skinny_kernel<MB, BN, SPLITS>, configured, sizeof(Stage<MB, BN>) * stages_for<MB, BN>(), BN, SPLITS, p, stream);
 }
 

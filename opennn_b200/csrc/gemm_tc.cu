@@ -89,6 +89,7 @@ struct Params
     unsigned long long tail_token;                         // this launch's value of "zeroed" in tail_flags
     unsigned long long* tail_flags;                        // [tail tile][8 epilogue warps of a pair]
     unsigned int* tail_visits;                             // same shape: adders that have seen the token (0, 1, back to 0)
+    int sm_cap;                                            // host side: SMs this launch may occupy (read once per launch: the plan and the grid must agree)
 };
 
 // Instruction descriptor: D = fp32, A = B = tf32, M = 128, N = BN, majors as given.
@@ -596,6 +597,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint64_t* acc_empty_bar = bars + 2 * STAGES2 + 2;         // [2]        used in the leader only
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // [r] = 1 + the number of stage fills the producer of CTA r has started, published to both CTAs when it stops (0 = not yet)
+    volatile uint32_t* fills_started = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -607,6 +610,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for(int s = 0; s < STAGES2; s++) { mbar_init(smem_u32(full_bar + s), 1); mbar_init(smem_u32(empty_bar + s), 1); }
         for(int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full_bar + a), 1); mbar_init(smem_u32(acc_empty_bar + a), 2 * kEpilogueWarps); }
         *abort_flag = 0;
+        fills_started[0] = 0; fills_started[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if(warp == 1)
@@ -628,7 +632,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // ---------------- TMA producer (one per CTA: own A rows, own half of B) ----------------
         if(lane == 0)
         {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, fills = 0;
             bool ok = true;
             for(long long w = pair; ok && w < p.total_work; w += pairs)
             {
@@ -650,14 +654,50 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     else tma2_load_4d(a_dst, &map_a, bar, k0, m0, part, 0);
                     if(B_MN) tma2_load_5d(b_dst, &map_b, bar, 0, k0, n0 / 32, part, 0);
                     else tma2_load_4d(b_dst, &map_b, bar, k0, n0, part, 0);
+                    fills++;
                     if(++stage == STAGES2) { stage = 0; phase ^= 1; }
                 }
             }
+            // Both producers say how many stage fills they started (two stores per kernel).  After a wait has run out
+            // that is what lets the pair drain its copies: a fill's bytes of BOTH CTAs complete on the leader's barrier,
+            // so a barrier phase only one of them started would never complete and nobody could tell when its copy had
+            // landed.  The CTA that is behind therefore starts the fills the other one started (same stages, the
+            // first tile's coordinates: the data no longer matters), the leader arms them, and then waits -- bounded --
+            // until the last phase started on every stage is complete.  Only then do the CTAs go on to the cluster
+            // barrier that precedes the release of tensor memory and the exit.
+            fills_started[rank] = fills + 1;
+            asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(map_to_cta(smem_u32(const_cast<uint32_t*>(fills_started) + rank), rank ^ 1u)), "r"(fills + 1) : "memory");
+            asm volatile("fence.acq_rel.cluster;" ::: "memory");
             if(*abort_flag)
             {
-                // give copies that are still in flight time to land before this CTA's shared memory goes away
+                uint32_t theirs = 0;
                 const unsigned long long start = clock64();
-                while(clock64() - start < 200000ull) { }
+                // the partner stops at the latest one wait limit after this CTA did
+                while((theirs = fills_started[rank ^ 1u]) == 0 && clock64() - start < 2 * kWaitCycles) { }
+                const uint32_t target = theirs > fills + 1 ? theirs - 1 : fills;
+                while(fills < target)
+                {
+                    const uint32_t a_dst = smem_u32(smem + (size_t)stage * STAGE2_BYTES), b_dst = a_dst + A_STAGE_BYTES;
+                    const uint32_t bar = map_to_cta(smem_u32(full_bar + stage), 0);
+                    if(leader) mbar_arrive_expect_tx(smem_u32(full_bar + stage), 2 * STAGE2_BYTES);
+                    if(A_MN) tma2_load_5d(a_dst, &map_a, bar, 0, 0, (int)rank * 4, 0, 0);
+                    else tma2_load_4d(a_dst, &map_a, bar, 0, (int)rank * 128, 0, 0);
+                    if(B_MN) tma2_load_5d(b_dst, &map_b, bar, 0, 0, (int)rank * 4, 0, 0);
+                    else tma2_load_4d(b_dst, &map_b, bar, 0, (int)rank * 128, 0, 0);
+                    fills++;
+                    if(++stage == STAGES2) { stage = 0; phase ^= 1; }
+                }
+                if(leader)
+                {
+                    // fill n uses stage n % STAGES2 in phase (n / STAGES2) & 1: wait for the last fill of every stage
+                    for(uint32_t back = 1; back <= (uint32_t)STAGES2 && back <= fills; back++)
+                    {
+                        const uint32_t n = fills - back;
+                        const unsigned long long since = clock64();
+                        while(!mbar_try_wait(smem_u32(full_bar + n % STAGES2), (n / STAGES2) & 1u))
+                            if(clock64() - since > kWaitCycles) break;
+                    }
+                }
             }
         }
     }
@@ -836,14 +876,9 @@ template <int BN, int STAGES, int A_MN, int B_MN>
 static int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const Params& p, cudaStream_t stream)
 {
     constexpr int smem = STAGES * (A_STAGE_BYTES + BN * BK * 4) + EPI_BYTES + 1024 + 256;
-    static bool configured = false;
-    if(!configured)
-    {
-        if(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            return ONN_ERR_CUDA;
-        configured = true;
-    }
-    const long long cap = (long long)kSmCount * (BN == 64 ? 2 : 1);
+    static PerDeviceBytes configured;                        // per instantiation and per device
+    if(!ensure_dynamic_smem(gemm_tc_kernel<BN, STAGES, A_MN, B_MN>, configured, smem)) return ONN_ERR_CUDA;
+    const long long cap = (long long)p.sm_cap * (BN == 64 ? 2 : 1);
     const int grid = (int)(p.total_work < cap ? p.total_work : cap);
     const cudaError_t launched = launch_overlapped(gemm_tc_kernel<BN, STAGES, A_MN, B_MN>, dim3(grid), dim3(kThreads), smem, stream, map_a, map_b, map_c, p);
     count_launch();
@@ -863,14 +898,9 @@ template <int A_MN, int B_MN>
 static int launch_pair_variant(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const Params& p, cudaStream_t stream)
 {
     constexpr int smem = STAGES2 * STAGE2_BYTES + EPI_BYTES + 1024 + 256;
-    static bool configured = false;
-    if(!configured)
-    {
-        if(cudaFuncSetAttribute(gemm_tc2_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            return ONN_ERR_CUDA;
-        configured = true;
-    }
-    const long long pairs_cap = kSmCount / 2;
+    static PerDeviceBytes configured;                        // per instantiation and per device
+    if(!ensure_dynamic_smem(gemm_tc2_kernel<A_MN, B_MN>, configured, smem)) return ONN_ERR_CUDA;
+    const long long pairs_cap = p.sm_cap / 2;
     const long long pairs = p.total_work < pairs_cap ? p.total_work : pairs_cap;
     const cudaError_t launched = launch_overlapped(gemm_tc2_kernel<A_MN, B_MN>, dim3((unsigned)(2 * pairs)), dim3(kThreads), smem, stream, map_a, map_b, map_c, p);
     count_launch();
@@ -889,7 +919,6 @@ static __device__ unsigned int g_tail_visits[kTailFlagSets * kTailFlagsPerSet];
 
 static int tail_flags_for_current_device(unsigned long long** flags, unsigned int** visits)
 {
-    constexpr int kMaxDevices = 64;
     static std::mutex mutex;
     static unsigned long long* resolved_flags[kMaxDevices] = {};
     static unsigned int* resolved_visits[kMaxDevices] = {};
@@ -953,6 +982,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.relu_bits_out = g.relu_bits_out; p.relu_bits = g.relu_bits; p.relu_bits_ld = g.relu_bits_ld;
     p.colsum = g.colsum_out; p.colsum_stride_inner = g.colsum_stride_inner;
     p.tail_tiles = 0; p.tail_token = 0; p.tail_flags = nullptr; p.tail_visits = nullptr;
+    p.sm_cap = sm_limit();
     p.relu = g.relu; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
     p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
     p.a_batch_inner_on = g.batch_inner > 1 && g.a_stride_inner != 0; p.a_batch_outer_on = g.batch_outer > 1 && g.a_stride_outer != 0;
@@ -986,7 +1016,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
         p.total_work = (long long)p.m_blocks * p.n_blocks * splits;
         // a last wave that is at most half full is split in two along the reduction (linear epilogues only)
         static const bool tail_split_enabled = []{ const char* e = std::getenv("ONN_B200_GEMM_TAIL_SPLIT"); return !(e && e[0] == '0'); }();
-        const long long tiles = (long long)p.m_blocks * p.n_blocks, pairs_cap = kSmCount / 2, tail = tiles % pairs_cap;
+        const long long tiles = (long long)p.m_blocks * p.n_blocks, pairs_cap = p.sm_cap / 2, tail = tiles % pairs_cap;
         if(tail_split_enabled && splits == 1 && tiles > pairs_cap && tail > 0 && 2 * tail <= pairs_cap && k_blocks >= 16 &&
            !g.relu && !g.relu_mask && !g.relu_bits && !g.relu_bits_out)
         {
@@ -1040,6 +1070,8 @@ int gemm_tc_bounded_wait_selftest(int* gave_up_host)
     if(cudaMemcpy(gave_up_host, flag, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ONN_ERR_CUDA;
     return ONN_OK;
 }
+
+const unsigned int* gemm_tc_status_word() { return tc::status_word_address(); }
 
 int gemm_tc_read_status()
 {

@@ -44,7 +44,7 @@ static int choose_split_k(long long M, long long N, long long K)
     const bool pair = M >= 512 && N >= 256 && M % 32 == 0 && N % 32 == 0;
     const long long bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
     const long long tiles = pair ? ((M + 255) / 256) * ((N + 255) / 256) : ((M + 127) / 128) * ((N + bn - 1) / bn);
-    const long long units = pair ? kSmCount / 2 : kSmCount;
+    const long long units = pair ? sm_limit() / 2 : sm_limit();
     if(tiles >= 4 * units || K < 1024) return 1;
     // pick the split count whose last wave is fullest; every extra split costs one more pass of
     // reduce-adds over the output, so ties go to the smaller count

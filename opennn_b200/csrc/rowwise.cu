@@ -540,13 +540,10 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
     if(fast)
     {
         const size_t smem = (size_t)kRowWarps * sets * E * sizeof(float);   // 64 KiB (96 KiB with the dx sums) at E = 1024
-        static bool configured = false;                          // once: attribute calls do not belong inside a stream capture
-        if(smem > 48 * 1024 && !configured)
-        {
-            cudaFuncSetAttribute(layernorm_bwd_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-            cudaFuncSetAttribute(layernorm_bwd_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-            configured = true;
-        }
+        // once per device: attribute calls do not belong inside a stream capture, so the first (eager) call sets both
+        static PerDeviceBytes configured_plain, configured_sums;
+        if(smem > 48 * 1024 && !(ensure_dynamic_smem(layernorm_bwd_kernel<8, false>, configured_plain, 64 * 1024) &&
+                                 ensure_dynamic_smem(layernorm_bwd_kernel<8, true>, configured_sums, 96 * 1024))) return ONN_ERR_CUDA;
         switch(vec_count(E))
         {
             case 1: ONN_LN_BWD(1); break;
@@ -561,12 +558,8 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
         if(smem > 48 * 1024)
         {
             if(smem > 200 * 1024) return ONN_ERR_UNSUPPORTED;
-            static size_t configured_bytes = 0;
-            if(smem > configured_bytes)
-            {
-                cudaFuncSetAttribute(layernorm_bwd_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                configured_bytes = smem;
-            }
+            static PerDeviceBytes configured;
+            if(!ensure_dynamic_smem(layernorm_bwd_generic_kernel, configured, smem)) return ONN_ERR_CUDA;
         }
         layernorm_bwd_generic_kernel<<<grid, kRowThreads, smem, s>>>(dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, rows, (int)E);
     }
@@ -606,7 +599,6 @@ static __device__ __align__(256) float g_layernorm_bwd_static_partials[2 * kSmCo
 
 namespace
 {
-constexpr int kMaxDevices = 64;
 std::mutex g_static_partials_mutex;
 float* g_static_partials_address[kMaxDevices] = {};    // device address of the array above, per device
 

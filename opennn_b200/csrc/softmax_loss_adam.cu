@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "launch_counter.h"
+#include "rowwise_internal.h"
 
 namespace onn
 {
@@ -546,8 +547,11 @@ __global__ void sqnorm_finish_kernel(const float* __restrict__ partials, int cou
 __global__ void __launch_bounds__(256)
 adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ g,
             long long n, float lr, float beta1, float beta2, float eps,
-            float bc1, float bc2, float clip_norm, const float* __restrict__ sqnorm, float grad_scale, int zero_grad)
+            float bc1, float bc2, float clip_norm, const float* __restrict__ sqnorm, float grad_scale, int zero_grad,
+            const unsigned int* __restrict__ skip_if_nonzero)
 {
+    // a step whose kernels gave up on a bounded wait holds an incomplete gradient: leave p, m, v and g as they are
+    if(skip_if_nonzero && skip_if_nonzero[0] != 0u) return;
     float scale = grad_scale;
     if(sqnorm && clip_norm > 0.f)
     {
@@ -1018,13 +1022,8 @@ extern "C" int onn_decode_attention(const float* q, const float* k_cache, const 
     {
         const size_t shared = (size_t)(hd + 1024 + 16 + S_cache) * sizeof(float);
         if(shared > 200 * 1024) return ONN_ERR_UNSUPPORTED;
-        static size_t configured = 48 * 1024;
-        if(shared > configured)
-        {
-            if(cudaFuncSetAttribute(decode_attention_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
-                return ONN_ERR_CUDA;
-            configured = shared;
-        }
+        static PerDeviceBytes configured;
+        if(!ensure_dynamic_smem(decode_attention_block_kernel, configured, shared)) return ONN_ERR_CUDA;
         decode_attention_block_kernel<<<(unsigned)(B * H), 256, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, pad_stride_sample,
                                                                                                  pad_stride_key, out, (int)H,
                                                                                                  (int)S_cache, (int)length, (int)E,
@@ -1034,12 +1033,8 @@ extern "C" int onn_decode_attention(const float* q, const float* k_cache, const 
     }
     const size_t shared = 4 * (size_t)(hd + S_cache) * sizeof(float);
     if(shared > 200 * 1024) return ONN_ERR_UNSUPPORTED;
-    static size_t configured = 48 * 1024;
-    if(shared > configured)
-    {
-        if(cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess) return ONN_ERR_CUDA;
-        configured = shared;
-    }
+    static PerDeviceBytes configured;
+    if(!ensure_dynamic_smem(decode_attention_kernel, configured, shared)) return ONN_ERR_CUDA;
     const long long items = B * H;
     decode_attention_kernel<<<(unsigned)((items + 3) / 4), 128, shared, (cudaStream_t)stream>>>(q, k_cache, v_cache, key_is_pad, pad_stride_sample, pad_stride_key,
                                                                                              out, (int)B, (int)H,
@@ -1159,10 +1154,18 @@ extern "C" int onn_ce3d_fwd_bwd(float* logits, const float* targets, const float
     ONN_CHECK_ARG(logits && targets && active_count && stats && row_scratch);
     ONN_CHECK_ARG(rows > 0 && V > 1 && rows < (1LL << 31) && V < (1LL << 31));
     cudaStream_t s = (cudaStream_t)stream;
-    ce3d_fwd_bwd_kernel<<<(unsigned)rows, kLossThreads, 0, s>>>(logits, targets, active_count, probabilities_out, row_scratch,
-                                                                 rows, (int)V, inputs_are_probabilities);
-    count_launch();
-    if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    if(!(flags & ONN_CE_TWO_SWEEPS) && ce3d_staged_takes(logits, probabilities_out, rows, V))
+    {
+        // long rows: staged in shared memory, each logit crosses HBM once in and once out
+        if(ce3d_staged_launch(logits, targets, active_count, row_scratch, rows, (int)V, inputs_are_probabilities, s) != ONN_OK) return ONN_ERR_CUDA;
+    }
+    else
+    {
+        ce3d_fwd_bwd_kernel<<<(unsigned)rows, kLossThreads, 0, s>>>(logits, targets, active_count, probabilities_out, row_scratch,
+                                                                     rows, (int)V, inputs_are_probabilities);
+        count_launch();
+        if(launch_status() != ONN_OK) return ONN_ERR_CUDA;
+    }
     ce3d_finish_kernel<<<1, 1024, 0, s>>>(row_scratch, targets, rows, V, stats);
     count_launch();
     return launch_status();
@@ -1187,14 +1190,22 @@ extern "C" int onn_grad_sqnorm(const float* g, int64_t n, float* sqnorm, float* 
     return launch_status();
 }
 
-extern "C" int onn_adam(float* p, float* m, float* v, float* g, int64_t n,
-                        float lr, float beta1, float beta2, float eps, float bc1, float bc2,
-                        float clip_norm, const float* sqnorm, float grad_scale, int zero_grad, void* stream)
+extern "C" int onn_adam_guarded(float* p, float* m, float* v, float* g, int64_t n,
+                                float lr, float beta1, float beta2, float eps, float bc1, float bc2,
+                                float clip_norm, const float* sqnorm, float grad_scale, int zero_grad,
+                                const uint32_t* skip_if_nonzero, void* stream)
 {
     ONN_CHECK_ARG(p && m && v && g && n > 0 && bc1 != 0.f && bc2 != 0.f);
     const int grid = grid_for((n + 3) / 4, 256, 8);
     adam_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p, m, v, g, n, lr, beta1, beta2, eps,
-                                                        bc1, bc2, clip_norm, sqnorm, grad_scale, zero_grad);
+                                                        bc1, bc2, clip_norm, sqnorm, grad_scale, zero_grad, skip_if_nonzero);
     count_launch();
     return launch_status();
+}
+
+extern "C" int onn_adam(float* p, float* m, float* v, float* g, int64_t n,
+                        float lr, float beta1, float beta2, float eps, float bc1, float bc2,
+                        float clip_norm, const float* sqnorm, float grad_scale, int zero_grad, void* stream)
+{
+    return onn_adam_guarded(p, m, v, g, n, lr, beta1, beta2, eps, bc1, bc2, clip_norm, sqnorm, grad_scale, zero_grad, nullptr, stream);
 }

@@ -222,8 +222,12 @@ inline bool make_wide_map(CUtensorMap* map, const float* base, long long mn, lon
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The status word belongs to the translation unit that includes this header (internal linkage), so the host functions
+// that name it have internal linkage too: an `inline` function with external linkage would be merged across translation
+// units by the linker and then read one unit's word for all of them.
+
 // Reads and clears this translation unit's device status word (synchronises the device).
-inline int read_and_clear_status(unsigned int* status)
+static inline int read_and_clear_status(unsigned int* status)
 {
     unsigned int zero = 0;
     *status = 0;
@@ -231,6 +235,15 @@ inline int read_and_clear_status(unsigned int* status)
     if(cudaMemcpyFromSymbol(status, g_status, sizeof(*status)) != cudaSuccess) return -1;
     if(*status != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
     return 0;
+}
+
+// Device address of this translation unit's status word on the current device (nullptr on failure), for kernels
+// that look at it in stream order.
+static inline const unsigned int* status_word_address()
+{
+    unsigned int* address = nullptr;
+    if(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_status) != cudaSuccess) return nullptr;
+    return address;
 }
 
 }  // namespace tc

@@ -24,7 +24,13 @@ struct onn_classifier
     Index batch = 0, sequence_length = 0, classes = 0;
     cudaStream_t stream = nullptr;
     bool gradients_dirty = false;
-    type* pinned = nullptr;              // {error, samples, square norm}
+    type* pinned = nullptr;              // {error, samples, square norm, bounded-wait status (as bits)}
+
+    // data-parallel training: every rank steps its own `batch` samples; the gradient arena and the error are summed
+    // over ranks after back-propagation and divided by the number of ranks (the loss is a mean over the samples)
+    onn_dp_comm* comm = nullptr;
+    int world = 1;
+    TensorCuda status_word;              // OR of the kernels' bounded-wait status words, in stream order
 
     // CUDA-graph replay of forward pass + loss + back-propagation from the second step on: ids and targets are copied
     // into fixed buffers first, so the captured kernels always read the same addresses (ONN_B200_GRAPHS=0 turns it off)
@@ -46,7 +52,11 @@ template <typename F>
 static int guarded(F&& body)
 {
     try { body(); return ONN_OK; }
-    catch(const std::exception& e) { g_classifier_error = e.what(); return ONN_ERR_CUDA; }
+    catch(const std::exception& e)
+    {
+        g_classifier_error = e.what();
+        return std::strstr(e.what(), "bounded device-side wait") ? ONN_ERR_DEVICE_TIMEOUT : ONN_ERR_CUDA;
+    }
     catch(...) { g_classifier_error = "unknown exception"; return ONN_ERR_CUDA; }
 }
 
@@ -79,6 +89,8 @@ extern "C" int onn_classifier_create(onn_classifier** out, int64_t vocabulary_si
         c->back.set(batch, c->network.get(), c->forward.get());
         c->optimization.set(c->network->get_parameters_number());
         c->statistics.resize(8);
+        c->status_word.resize(8);
+        c->adam.set_skip_word(reinterpret_cast<const uint32_t*>(c->status_word.data));
         c->row_scratch.resize(batch);
         c->staged_ids.resize(batch * sequence_length);
         c->staged_targets.resize(batch * classes);
@@ -137,6 +149,32 @@ extern "C" int onn_classifier_get_gradients(onn_classifier* c, float* host_gradi
         check_cuda(cudaMemcpy(host_gradients, c->back.gradients.data, size_t(c->back.gradients.size()) * sizeof(type), cudaMemcpyDeviceToHost),
                    "get_gradients");
     });
+}
+
+extern "C" int onn_classifier_get_layer_output(onn_classifier* c, int layer, float* host_output, int64_t count)
+{
+    if(!c || !host_output || layer < 0 || layer >= int(c->network->get_layers_number())) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        const TensorViewCuda outputs = c->forward->layers[size_t(layer)]->outputs;
+        if(count > outputs.size()) throw std::runtime_error("get_layer_output: count exceeds the layer's output size");
+        check_cuda(cudaStreamSynchronize(c->stream), "synchronize");
+        check_cuda(cudaMemcpy(host_output, outputs.data, size_t(count) * sizeof(type), cudaMemcpyDeviceToHost), "get_layer_output");
+    });
+}
+
+extern "C" int64_t onn_classifier_layer_output_size(const onn_classifier* c, int layer)
+{
+    if(!c || layer < 0 || layer >= int(c->network->get_layers_number())) return 0;
+    return c->forward->layers[size_t(layer)]->outputs.size();
+}
+
+extern "C" int onn_classifier_set_dp(onn_classifier* c, onn_dp_comm* comm, int world)
+{
+    if(!c || world < 1 || (world > 1 && !comm)) return ONN_ERR_INVALID_ARGUMENT;
+    c->comm = world > 1 ? comm : nullptr;
+    c->world = world;
+    return ONN_OK;
 }
 
 extern "C" int onn_classifier_set_learning_rate(onn_classifier* c, float learning_rate)
@@ -207,11 +245,20 @@ extern "C" int onn_classifier_step_device(onn_classifier* c, const float* ids, c
         }
         if(!replayed) propagate();
         c->eager_steps++;
+        check_onn(onn_device_status_gather(reinterpret_cast<uint32_t*>(c->status_word.data), c->stream), "device status");
+        if(c->comm)
+        {
+            // sum over ranks of the gradient arena and of {error, samples}; the update below divides by the rank count
+            check_onn(onn_dp_allreduce(c->comm, c->back.gradients.data, c->back.gradients.size(), c->stream), "gradient all-reduce");
+            check_onn(onn_dp_allreduce(c->comm, c->statistics.data, 2, c->stream), "statistics all-reduce");
+            check_onn(onn_dp_wait(c->comm, c->stream), "gradient wait");
+        }
         if(statistics)
             check_cuda(cudaMemcpyAsync(c->pinned, c->statistics.data, 2 * sizeof(type), cudaMemcpyDeviceToHost, c->stream), "statistics");
+        const type gradient_scale = type(1) / type(c->world);
         if(update)
         {
-            c->adam.update_parameters(c->network.get(), c->back.gradients, c->optimization);
+            c->adam.update_parameters(c->network.get(), c->back.gradients, c->optimization, gradient_scale);
             c->gradients_dirty = false;                      // the update kernel zeroes the arena for the next step
         }
         else if(statistics)
@@ -220,9 +267,18 @@ extern "C" int onn_classifier_step_device(onn_classifier* c, const float* ids, c
         if(statistics)
         {
             check_cuda(cudaMemcpyAsync(c->pinned + 2, c->optimization.square_norm.data, sizeof(type), cudaMemcpyDeviceToHost, c->stream), "norm");
+            check_cuda(cudaMemcpyAsync(c->pinned + 3, c->status_word.data, sizeof(type), cudaMemcpyDeviceToHost, c->stream), "status");
             check_cuda(cudaStreamSynchronize(c->stream), "synchronize");
-            statistics[0] = c->pinned[0];
-            statistics[1] = std::sqrt(c->pinned[2]);
+            uint32_t status_bits;
+            std::memcpy(&status_bits, c->pinned + 3, sizeof(status_bits));
+            if(status_bits != 0)
+            {
+                onn_gemm_device_status();                    // reads and clears the words
+                if(c->comm) onn_dp_mark_failed(c->comm);
+                throw std::runtime_error("a kernel gave up on a bounded device-side wait; the step's update was skipped");
+            }
+            statistics[0] = c->pinned[0] / type(c->world);
+            statistics[1] = std::sqrt(c->pinned[2]) / type(c->world);
             if(std::isnan(statistics[0])) throw std::runtime_error("Error is NAN.");
         }
     });

@@ -16,6 +16,15 @@ using namespace opennn_b200;
 
 static thread_local string g_last_error;
 
+// An error that keeps its status code across the C boundary (anything else becomes ONN_ERR_CUDA).
+struct StatusError : std::runtime_error
+{
+    StatusError(int status, const string& what) : std::runtime_error(what), status(status) {}
+    int status;
+};
+
+constexpr Index kMaxMicroBatches = 64;    // statistics slots of one step (BackPropagationCuda::statistics)
+
 struct onn_trainer
 {
     unique_ptr<NeuralNetwork> network;
@@ -32,10 +41,33 @@ struct onn_trainer
     bool gradients_dirty = false;
 
     onn_dp_comm* comm = nullptr;
-    int world = 1;
+    int world = 1, rank = 0;
     vector<Index> layer_offsets;          // start of each layer's slice in the gradient arena
     Index pending_high = 0;               // end of the slice not yet handed to the all-reduce
     Index bucket_floats = 16 << 20;       // 64 MiB buckets: large enough for NVLink bandwidth, small enough to overlap
+
+    // Sharded update (data-parallel steps that update): the arena, rounded up to a multiple of 4 * world floats, is cut
+    // into buckets of shard_bucket floats on a fixed grid; each bucket is reduce-scattered as soon as back-propagation
+    // has finished every gradient in it, rank r receiving the r-th part of each bucket into own_gradient (bucket k's
+    // part at k * shard_bucket / world).  The norm is taken over the own parts and summed over ranks, clip + Adam run
+    // on the own parts only (moments own_m, own_v: 1 / world of the arena), and an all-gather per bucket brings the
+    // updated parameters back to every replica.
+    bool sharded_update = true;           // ONN_B200_DP_SHARDED=0: all-reduce + the whole update on every rank
+    Index shard_bucket = 0, shard_total = 0, own_size = 0;
+    Index pending_bucket = -1;            // highest bucket not yet handed to the reduce-scatter
+    bool sharded_step = false;            // this step reduce-scatters (set per step: update and world > 1)
+    TensorCuda own_gradient, own_m, own_v;
+
+    // SMs left to NCCL while a bucket is in flight: the persistent kernels of the next carve_launches launches (rounded
+    // up to a layer) occupy 148 - carve_sms SMs, so NCCL's CTAs start at once instead of at a kernel boundary
+    int carve_sms = 0, carve_launches = 4;
+    bool narrowed = false;
+    uint64_t narrowed_at = 0;
+
+    // failure detection in stream order: OR of the kernels' bounded-wait status words, gathered after back-propagation,
+    // guards the update and is copied to pinned memory with every step
+    TensorCuda status_word;
+    volatile uint32_t* pinned_status = nullptr;
 
     TensorCuda staged_decoder, staged_encoder, staged_targets;
 
@@ -78,6 +110,7 @@ struct onn_trainer
         }
         if(copy_stream) cudaStreamDestroy(copy_stream);
         if(pinned_scalars) cudaFreeHost(pinned_scalars);
+        if(pinned_status) cudaFreeHost(const_cast<uint32_t*>(pinned_status));
         if(stream) cudaStreamDestroy(stream);
     }
 };
@@ -86,8 +119,25 @@ template <typename F>
 static int guarded(F&& body)
 {
     try { body(); return ONN_OK; }
+    catch(const StatusError& e) { g_last_error = e.what(); return e.status; }
     catch(const std::exception& e) { g_last_error = e.what(); return ONN_ERR_CUDA; }
     catch(...) { g_last_error = "unknown exception"; return ONN_ERR_CUDA; }
+}
+
+static int environment_int(const char* name, int fallback)
+{
+    const char* e = std::getenv(name);
+    return e && *e ? std::atoi(e) : fallback;
+}
+
+// Throws if a kernel of a step already run gave up on a bounded wait (the guarded update of that step did not run).
+static void check_device_status(onn_trainer* t)
+{
+    if(!t->pinned_status || *t->pinned_status == 0) return;
+    *t->pinned_status = 0;
+    onn_gemm_device_status();                                   // reads and clears the words (synchronises the device)
+    if(t->comm) onn_dp_mark_failed(t->comm);                    // this replica skipped an update the others made
+    throw StatusError(ONN_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded device-side wait; the step's update was skipped");
 }
 
 extern "C" const char* onn_trainer_last_error(void) { return g_last_error.c_str(); }
@@ -128,6 +178,16 @@ extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
         t->optimization = std::make_unique<ADAMOptimizationDataCuda>(t->adam.get());
         if(const char* e = std::getenv("ONN_B200_GRAPHS")) t->graphs_enabled = e[0] != '0';
         check_cuda(cudaMallocHost(reinterpret_cast<void**>(&t->pinned_scalars), 8 * sizeof(type)), "pinned scalars");
+        uint32_t* pinned_status = nullptr;
+        check_cuda(cudaMallocHost(reinterpret_cast<void**>(&pinned_status), 8 * sizeof(uint32_t)), "pinned status");
+        *pinned_status = 0;
+        t->pinned_status = pinned_status;
+        t->status_word.resize(8);
+        t->adam->set_skip_word(reinterpret_cast<const uint32_t*>(t->status_word.data));
+        t->sharded_update = environment_int("ONN_B200_DP_SHARDED", 1) != 0;
+        t->carve_sms = environment_int("ONN_B200_DP_CARVE_SMS", 0);
+        t->carve_launches = environment_int("ONN_B200_DP_CARVE_LAUNCHES", 4);
+        t->bucket_floats = std::max(1024, environment_int("ONN_B200_DP_BUCKET_FLOATS", 16 << 20));
 
         Index offset = 0;
         for(const unique_ptr<Layer>& layer : t->network->get_layers())
@@ -206,24 +266,138 @@ extern "C" int onn_trainer_set_iteration(onn_trainer* t, int64_t iteration)
 
 extern "C" int onn_trainer_set_dp(onn_trainer* t, onn_dp_comm* comm, int world)
 {
-    if(!t || world < 1) return ONN_ERR_INVALID_ARGUMENT;
-    t->comm = world > 1 ? comm : nullptr;
-    t->world = world;
+    if(!t || world < 1 || (world > 1 && !comm)) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        t->comm = world > 1 ? comm : nullptr;
+        t->world = world;
+        t->rank = t->comm ? onn_dp_rank(comm) : 0;
+        if(t->comm && onn_dp_world(comm) != world) throw std::runtime_error("set_dp: the communicator has another number of ranks");
+        t->shard_total = 0;
+        const Index parameters_number = t->network->get_parameters_number();
+        if(!t->comm || !t->sharded_update)
+        {
+            // the whole update on this rank: it needs moments for the whole arena
+            if(t->optimization->gradient_exponential_decay.size() == 0)
+            {
+                t->optimization->gradient_exponential_decay.resize(parameters_number);
+                t->optimization->square_gradient_exponential_decay.resize(parameters_number);
+            }
+            t->own_gradient.free(); t->own_m.free(); t->own_v.free();
+            return;
+        }
+        const Index unit = 4 * Index(world);                    // every rank's part of every bucket starts 16-byte aligned
+        const Index parameters = t->network->get_parameters_number();
+        const Index total = (parameters + unit - 1) / unit * unit;
+        if(total > t->back->neural_network.gradients.capacity || total > t->network->get_parameters_device().capacity)
+            throw std::runtime_error("set_dp: too many ranks for the sharded update (the arenas are padded to 1024 floats)");
+        t->shard_total = total;
+        t->shard_bucket = std::max<Index>(unit, t->bucket_floats / unit * unit);
+        t->own_size = total / world;
+        t->own_gradient.resize(t->own_size);
+        t->own_m.resize(t->own_size);
+        t->own_v.resize(t->own_size);
+        // moments live for the own parts only: 1 / world of the arena each
+        t->optimization->gradient_exponential_decay.free();
+        t->optimization->square_gradient_exponential_decay.free();
+        check_cuda(cudaStreamSynchronize(t->stream), "set_dp");
+    });
+}
+
+extern "C" int onn_trainer_set_dp_options(onn_trainer* t, int sharded_update, int carve_sms, int carve_launches, int64_t bucket_floats)
+{
+    if(!t || carve_sms < 0 || carve_launches < 0 || bucket_floats < 0) return ONN_ERR_INVALID_ARGUMENT;
+    if(t->comm) { g_last_error = "set_dp_options: call before onn_trainer_set_dp"; return ONN_ERR_INVALID_ARGUMENT; }
+    t->sharded_update = sharded_update != 0;
+    t->carve_sms = carve_sms;
+    t->carve_launches = carve_launches;
+    if(bucket_floats > 0) t->bucket_floats = bucket_floats;
     return ONN_OK;
 }
 
-// Called after layer `layer` has back-propagated: every gradient slice from this layer's
-// offset up is final on the compute stream.  Hands full buckets to the all-reduce.
+static void narrow_for_exchange(onn_trainer* t)
+{
+    if(t->carve_sms <= 0) return;
+    check_onn(onn_set_sm_limit(148 - t->carve_sms), "sm limit");
+    t->narrowed = true;
+    t->narrowed_at = onn_launch_count();
+}
+
+static void widen_after_exchange(onn_trainer* t, bool now)
+{
+    if(!t->narrowed) return;
+    if(!now && onn_launch_count() - t->narrowed_at < uint64_t(t->carve_launches)) return;
+    onn_set_sm_limit(0);
+    t->narrowed = false;
+}
+
+// Bucket k of the fixed grid: reduce-scatter into the own parts, then clear it for the next step off the compute stream.
+static void reduce_scatter_bucket(onn_trainer* t, Index k)
+{
+    const Index low = k * t->shard_bucket;
+    const Index size = std::min(t->shard_bucket, t->shard_total - low);
+    type* gradients = t->back->neural_network.gradients.data;
+    check_onn(onn_dp_reduce_scatter(t->comm, gradients + low, t->own_gradient.data + low / t->world, size / t->world, t->stream),
+              "gradient reduce-scatter");
+    check_onn(onn_dp_zero(t->comm, gradients + low, size), "gradient bucket clear");
+}
+
+// Called after layer `layer` has back-propagated: every gradient slice from this layer's offset up is final on the
+// compute stream.  Hands what is complete to the exchange: whole buckets of the fixed grid (sharded update) or the
+// layers gathered so far once they make up a bucket (all-reduce).  layer < 0: everything that is left.
 static void gradient_ready(void* context, Index layer)
 {
     onn_trainer* t = static_cast<onn_trainer*>(context);
-    const Index low = t->layer_offsets[size_t(layer)];
-    if(t->pending_high - low >= t->bucket_floats || (layer == 0 && t->pending_high > low))
+    const Index low = layer <= 0 ? 0 : t->layer_offsets[size_t(layer)];
+    bool issued = false;
+    if(t->sharded_step)
     {
+        for(; t->pending_bucket >= 0 && t->pending_bucket * t->shard_bucket >= low; t->pending_bucket--)
+        {
+            if(!issued) narrow_for_exchange(t);
+            issued = true;
+            reduce_scatter_bucket(t, t->pending_bucket);
+        }
+    }
+    else if(t->pending_high - low >= t->bucket_floats || (layer <= 0 && t->pending_high > low))
+    {
+        narrow_for_exchange(t);
+        issued = true;
         check_onn(onn_dp_allreduce(t->comm, t->back->neural_network.gradients.data + low, t->pending_high - low, t->stream),
                   "gradient all-reduce");
         t->pending_high = low;
     }
+    if(!issued) widen_after_exchange(t, false);
+}
+
+// Clip + Adam on this rank's parts of the reduced gradient, then the updated parameters back to every replica.
+static void sharded_update(onn_trainer* t)
+{
+    check_onn(onn_dp_wait(t->comm, t->stream), "gradient wait");
+    type* square_norm = t->optimization->square_norm.data;
+    check_onn(onn_grad_sqnorm(t->own_gradient.data, t->own_size, square_norm, t->optimization->norm_workspace.data, t->stream), "gradient norm");
+    check_onn(onn_dp_allreduce(t->comm, square_norm, 1, t->stream), "gradient norm all-reduce");
+    check_onn(onn_dp_wait(t->comm, t->stream), "gradient norm wait");
+
+    type bias_correction_1, bias_correction_2;
+    t->adam->advance(*t->optimization, bias_correction_1, bias_correction_2);
+    type* parameters = t->network->get_parameters_device().data;
+    const uint32_t* skip = reinterpret_cast<const uint32_t*>(t->status_word.data);
+    const Index buckets = (t->shard_total + t->shard_bucket - 1) / t->shard_bucket;
+    for(Index k = 0; k < buckets; k++)
+    {
+        const Index low = k * t->shard_bucket;
+        const Index part = std::min(t->shard_bucket, t->shard_total - low) / t->world;
+        type* own_parameters = parameters + low + t->rank * part;
+        const Index own = low / t->world;
+        check_onn(onn_adam_guarded(own_parameters, t->own_m.data + own, t->own_v.data + own, t->own_gradient.data + own, part,
+                                   t->adam->get_learning_rate(), t->adam->get_beta_1(), t->adam->get_beta_2(), EPSILON,
+                                   bias_correction_1, bias_correction_2, t->adam->get_gradient_clip_norm(), square_norm, type(1), 0, skip,
+                                   t->stream), "sharded Adam");
+        // the all-gather of this bucket waits for this bucket's update only and overlaps the next bucket's
+        check_onn(onn_dp_all_gather(t->comm, own_parameters, parameters + low, part, t->stream), "parameter all-gather");
+    }
+    check_onn(onn_dp_wait(t->comm, t->stream), "parameter wait");
 }
 
 // Replays (capturing it first if need be) the forward pass, loss and back-propagation of micro-batch number `chunk`.
@@ -294,12 +468,44 @@ static bool replay_micro_batch(onn_trainer* t, const BatchCuda& source, Index ch
     return true;
 }
 
+// Whatever ends the step, the hook that hands gradients to the exchange does not outlive it and the SM limit is lifted.
+struct ExchangeScope
+{
+    explicit ExchangeScope(onn_trainer* t) : t(t) {}
+    ~ExchangeScope()
+    {
+        t->loss->gradient_ready_hook = nullptr;
+        widen_after_exchange(t, true);
+    }
+    onn_trainer* t;
+};
+
+static void run_step_body(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,
+                          Index batch, bool update, float* statistics);
+
 static void run_step(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,
                      Index batch, bool update, float* statistics)
 {
     if(batch <= 0 || batch % t->micro_batch != 0) throw std::runtime_error("step: batch must be a positive multiple of micro_batch");
+    if(batch / t->micro_batch > kMaxMicroBatches) throw std::runtime_error("step: at most 64 micro-batches per step (batch / micro_batch)");
     if(!decoder_ids || !targets || (!t->decoder_only && !encoder_ids)) throw std::runtime_error("step: missing ids or targets");
+    check_device_status(t);
+    try { run_step_body(t, decoder_ids, encoder_ids, targets, batch, update, statistics); }
+    catch(...)
+    {
+        // a step that ends half-way has joined some of its collectives and not others: the ranks no longer agree on
+        // which one comes next, so this rank must not enqueue another
+        if(t->comm) onn_dp_mark_failed(t->comm);
+        throw;
+    }
+}
+
+static void run_step_body(onn_trainer* t, const float* decoder_ids, const float* encoder_ids, const float* targets,
+                          Index batch, bool update, float* statistics)
+{
     Device::instance().set_compute_stream(t->stream);
+    ExchangeScope scope(t);
+    t->sharded_step = t->comm && update && t->shard_total > 0;
     const Index S_dec = t->decoder_sequence_length, S_in = t->input_sequence_length;
     TensorCuda& gradients = t->back->neural_network.gradients;
 
@@ -336,34 +542,49 @@ static void run_step(onn_trainer* t, const float* decoder_ids, const float* enco
         if(hands_out_gradients)
         {
             t->pending_high = gradients.size();
+            t->pending_bucket = t->sharded_step ? (t->shard_total - 1) / t->shard_bucket : -1;
             t->loss->gradient_ready_hook = gradient_ready;
             t->loss->gradient_ready_context = t;
         }
         t->loss->back_propagate(micro, *t->forward, *t->back, chunk > 0);
+        if(hands_out_gradients) gradient_ready(t, -1);           // whatever the layer walk left (it ends at the first trainable layer)
         t->loss->gradient_ready_hook = nullptr;
+        widen_after_exchange(t, true);
     }
     t->eager_steps++;
 
-    if(t->comm)
-    {
-        check_onn(onn_dp_allreduce(t->comm, t->back->statistics.data, 4 * t->back->statistics_slot, t->stream), "statistics all-reduce");
-        check_onn(onn_dp_wait(t->comm, t->stream), "gradient wait");
-    }
+    // OR of the bounded-wait status words of everything this step has run: guards the update, read with the statistics
+    uint32_t* status_word = reinterpret_cast<uint32_t*>(t->status_word.data);
+    check_onn(onn_device_status_gather(status_word, t->stream), "device status");
 
-    if(update)
+    if(t->comm)
+        check_onn(onn_dp_allreduce(t->comm, t->back->statistics.data, 4 * t->back->statistics_slot, t->stream), "statistics all-reduce");
+
+    if(t->sharded_step)
     {
-        t->adam->update_parameters(*t->back, *t->optimization);
-        t->gradients_dirty = false;                              // the update kernel zeroes the arena for the next step
+        sharded_update(t);
+        t->gradients_dirty = false;                              // every bucket was cleared after its reduce-scatter
     }
-    else if(statistics)
-        check_onn(onn_grad_sqnorm(gradients.data, gradients.size(), t->optimization->square_norm.data, t->optimization->norm_workspace.data,
-                                  t->stream), "gradient norm");
+    else
+    {
+        if(t->comm) check_onn(onn_dp_wait(t->comm, t->stream), "gradient wait");
+        if(update)
+        {
+            t->adam->update_parameters(*t->back, *t->optimization);
+            t->gradients_dirty = false;                          // the update kernel zeroes the arena for the next step
+        }
+        else if(statistics)
+            check_onn(onn_grad_sqnorm(gradients.data, gradients.size(), t->optimization->square_norm.data, t->optimization->norm_workspace.data,
+                                      t->stream), "gradient norm");
+    }
+    check_cuda(cudaMemcpyAsync(const_cast<uint32_t*>(t->pinned_status), status_word, sizeof(uint32_t), cudaMemcpyDeviceToHost, t->stream), "status readback");
 
     if(statistics)
     {
         check_cuda(cudaMemcpyAsync(t->pinned_scalars, t->optimization->square_norm.data, sizeof(type), cudaMemcpyDeviceToHost, t->stream), "norm readback");
         check_cuda(cudaMemcpyAsync(t->pinned_scalars + 1, t->back->active_count.data, sizeof(type), cudaMemcpyDeviceToHost, t->stream), "count readback");
         t->loss->read_error(*t->back, 0);                        // synchronises the stream
+        check_device_status(t);
         // statistics slots were summed over ranks; so is the active count in pinned_scalars[1]
         double loss_sum = 0, correct = 0;
         for(Index k = 0; k < t->back->statistics_slot; k++)
@@ -643,7 +864,7 @@ extern "C" int onn_trainer_get_layer_output(onn_trainer* t, int layer, float* ho
 extern "C" int onn_trainer_synchronize(onn_trainer* t)
 {
     if(!t) return ONN_ERR_INVALID_ARGUMENT;
-    return guarded([&] { check_cuda(cudaStreamSynchronize(t->stream), "synchronize"); });
+    return guarded([&] { check_cuda(cudaStreamSynchronize(t->stream), "synchronize"); check_device_status(t); });
 }
 
 extern "C" void* onn_trainer_stream(onn_trainer* t) { return t ? t->stream : nullptr; }

@@ -38,9 +38,10 @@ void TensorCuda::resize(Index new_count)
 {
     free();
     if(new_count <= 0) return;
-    check_cuda(cudaMalloc(reinterpret_cast<void**>(&data), size_t(new_count) * sizeof(type)), "TensorCuda::resize");
+    capacity = (new_count + 1023) & ~Index(1023);
+    check_cuda(cudaMalloc(reinterpret_cast<void**>(&data), size_t(capacity) * sizeof(type)), "TensorCuda::resize");
     count = new_count;
-    check_cuda(cudaMemset(data, 0, size_t(count) * sizeof(type)), "TensorCuda::resize memset");
+    check_cuda(cudaMemset(data, 0, size_t(capacity) * sizeof(type)), "TensorCuda::resize memset");
     // the fill runs on the legacy default stream and may return before it has run; the compute stream is non-blocking
     // and does not wait for it, so a kernel launched right after could see its output wiped
     check_cuda(cudaStreamSynchronize(nullptr), "TensorCuda::resize synchronize");
@@ -58,6 +59,7 @@ void TensorCuda::free()
     if(data) cudaFree(data);
     data = nullptr;
     count = 0;
+    capacity = 0;
 }
 
 static Index padded(Index count) { return (count + 7) & ~Index(7); }    // EIGEN_MAX_ALIGN_BYTES / sizeof(float) = 8

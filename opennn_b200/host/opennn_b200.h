@@ -55,6 +55,8 @@ struct TensorCuda
 {
     type* data = nullptr;
     Index count = 0;
+    Index capacity = 0;               // floats allocated: count rounded up to 1024, the slack zero-filled, so that a
+                                      // collective may round an arena up to a multiple of 4 * ranks floats
 
     TensorCuda() {}
     ~TensorCuda() { free(); }
@@ -665,10 +667,19 @@ public:
     // the same update on any network and gradient arena (used with CrossEntropyError2d)
     void update_parameters(NeuralNetwork* network, TensorCuda& gradients, ADAMOptimizationDataCuda& optimization_data,
                            type gradient_scale = 1) const;
+    // iteration++ and the two bias corrections of that iteration (adaptive_moment_estimation.cpp:449-454)
+    void advance(ADAMOptimizationDataCuda& optimization_data, type& bias_correction_1, type& bias_correction_2) const;
+    type get_beta_1() const { return beta_1; }
+    type get_beta_2() const { return beta_2; }
+    type get_gradient_clip_norm() const { return gradient_clip_norm; }
+    // device word (or nullptr): when it is not zero the update kernel leaves parameters, moments and gradient alone
+    // (onn_adam_guarded): a step whose kernels gave up on a bounded wait must not reach the parameters
+    void set_skip_word(const uint32_t* word) { skip_if_nonzero = word; }
 
 private:
     CrossEntropyError3d* loss = nullptr;
     type learning_rate = type(0.001), beta_1 = type(0.9), beta_2 = type(0.999), gradient_clip_norm = type(1.0);   // .h:86-92
+    const uint32_t* skip_if_nonzero = nullptr;
 };
 
 

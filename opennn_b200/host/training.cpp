@@ -203,19 +203,25 @@ void AdaptiveMomentEstimation::update_parameters(BackPropagationCuda& back_propa
 void AdaptiveMomentEstimation::update_parameters(NeuralNetwork* network, TensorCuda& gradients, ADAMOptimizationDataCuda& optimization_data,
                                                  type gradient_scale) const
 {
-    optimization_data.iteration++;
-    const type iteration = type(optimization_data.iteration);
-    const type bias_correction_1 = type(1) - std::pow(beta_1, iteration);
-    const type bias_correction_2 = type(1) - std::pow(beta_2, iteration);
+    type bias_correction_1, bias_correction_2;
+    advance(optimization_data, bias_correction_1, bias_correction_2);
 
     const Index n = network->get_parameters_number();
     check_onn(onn_grad_sqnorm(gradients.data, n, optimization_data.square_norm.data, optimization_data.norm_workspace.data, stream()),
               "AdaptiveMomentEstimation: gradient norm");
-    check_onn(onn_adam(network->get_parameters_device().data, optimization_data.gradient_exponential_decay.data,
-                       optimization_data.square_gradient_exponential_decay.data, gradients.data, n,
-                       learning_rate, beta_1, beta_2, EPSILON, bias_correction_1, bias_correction_2,
-                       gradient_clip_norm, optimization_data.square_norm.data, gradient_scale, 1, stream()),
+    check_onn(onn_adam_guarded(network->get_parameters_device().data, optimization_data.gradient_exponential_decay.data,
+                               optimization_data.square_gradient_exponential_decay.data, gradients.data, n,
+                               learning_rate, beta_1, beta_2, EPSILON, bias_correction_1, bias_correction_2,
+                               gradient_clip_norm, optimization_data.square_norm.data, gradient_scale, 1, skip_if_nonzero, stream()),
               "AdaptiveMomentEstimation::update_parameters");
+}
+
+void AdaptiveMomentEstimation::advance(ADAMOptimizationDataCuda& optimization_data, type& bias_correction_1, type& bias_correction_2) const
+{
+    optimization_data.iteration++;
+    const type iteration = type(optimization_data.iteration);
+    bias_correction_1 = type(1) - std::pow(beta_1, iteration);
+    bias_correction_2 = type(1) - std::pow(beta_2, iteration);
 }
 
 }  // namespace opennn_b200

@@ -23,11 +23,12 @@ HOST_EXPORTS = [
     "onn_trainer_layers_number", "onn_trainer_layer_info", "onn_trainer_set_parameters", "onn_trainer_get_parameters",
     "onn_trainer_get_gradients", "onn_trainer_set_learning_rate", "onn_trainer_set_iteration", "onn_trainer_set_dp",
     "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_step_host_i32", "onn_trainer_forward", "onn_trainer_get_layer_output",
-    "onn_trainer_synchronize", "onn_trainer_stream", "onn_trainer_set_graph_capture",
+    "onn_trainer_synchronize", "onn_trainer_stream", "onn_trainer_set_graph_capture", "onn_trainer_set_dp_options",
     "onn_trainer_greedy_decode", "onn_trainer_greedy_decode_cached",
     "onn_classifier_last_error", "onn_classifier_create", "onn_classifier_destroy", "onn_classifier_parameters_number",
     "onn_classifier_layers_number", "onn_classifier_layer_info", "onn_classifier_set_parameters", "onn_classifier_get_parameters",
     "onn_classifier_get_gradients", "onn_classifier_set_learning_rate", "onn_classifier_forward", "onn_classifier_step_device",
+    "onn_classifier_get_layer_output", "onn_classifier_layer_output_size", "onn_classifier_set_dp",
 ]
 
 _host = None
@@ -46,6 +47,7 @@ def host_lib():
         L.onn_trainer_stream.restype = C.c_void_p
         L.onn_classifier_last_error.restype = C.c_char_p
         L.onn_classifier_parameters_number.restype = C.c_int64
+        L.onn_classifier_layer_output_size.restype = C.c_int64
         L.onn_classifier_destroy.restype = None
         _host = L
     return _host
@@ -113,6 +115,14 @@ class Trainer:
 
     def set_dp(self, comm_handle, world):
         _check(host_lib().onn_trainer_set_dp(self._handle, comm_handle, int(world)), "set_dp")
+
+    def set_dp_options(self, sharded_update=True, carve_sms=0, carve_launches=4, bucket_floats=0):
+        """Before set_dp.  sharded_update: reduce-scatter the gradient buckets, clip + Adam on this rank's 1/world of
+        the arena, all-gather the parameters (False: all-reduce and the whole update on every rank).  carve_sms: SMs
+        the persistent kernels leave free for NCCL during the carve_launches launches that follow a bucket.
+        bucket_floats: size of a gradient bucket (0 = the default, 64 MiB)."""
+        _check(host_lib().onn_trainer_set_dp_options(self._handle, int(bool(sharded_update)), int(carve_sms), int(carve_launches),
+                                                     C.c_int64(int(bucket_floats))), "set_dp_options")
 
     def step_device(self, dec_ids, enc_ids, targets, update=True, want_statistics=True):
         """dec_ids / enc_ids / targets: torch CUDA float tensors [batch, S].  Returns
@@ -234,6 +244,17 @@ class TextClassifier:
     def set_learning_rate(self, lr):
         self._check(host_lib().onn_classifier_set_learning_rate(self._handle, C.c_float(lr)), "set_learning_rate")
 
+    def set_dp(self, comm_handle, world):
+        """Data-parallel training: every rank steps its own `batch` samples; gradients and the error are averaged
+        over the ranks before the update (get_gradients then returns the SUM over ranks)."""
+        self._check(host_lib().onn_classifier_set_dp(self._handle, comm_handle, int(world)), "set_dp")
+
+    def layer_output(self, i):
+        """Output of layer i after the last forward pass, as a flat float32 array."""
+        a = np.empty(int(host_lib().onn_classifier_layer_output_size(self._handle, int(i))), dtype=np.float32)
+        self._check(host_lib().onn_classifier_get_layer_output(self._handle, int(i), _f32_ptr(a), C.c_int64(a.size)), "get_layer_output")
+        return a
+
     def forward(self, ids):
         """ids: torch CUDA float tensor [batch, S].  Returns the class probabilities [batch, classes] (numpy)."""
         assert tuple(ids.shape) == (self.batch, self.S)
@@ -263,6 +284,24 @@ def shard_batch(arrays, rank, world):
         share = a.shape[0] // world
         shards.append(a[rank * share:(rank + 1) * share])
     return shards
+
+
+def shard_layout(parameters, world, bucket_floats=16 << 20):
+    """The partition the sharded data-parallel update works on (the trainer's C++ side computes the same): the arena
+    is rounded up to a multiple of 4 * world floats (`total`) and cut on a fixed grid into buckets of `bucket` floats
+    (itself a multiple of 4 * world); rank r owns the r-th of `world` equal parts of every bucket, so every part
+    starts on a 16-byte boundary.  Returns (total, bucket, [(low, part)] per bucket): rank r's share of a bucket is
+    arena[low + r * part : low + (r + 1) * part], kept compactly at own[low // world : low // world + part]."""
+    unit = 4 * world
+    total = (parameters + unit - 1) // unit * unit
+    bucket = max(unit, bucket_floats // unit * unit)
+    parts = []
+    low = 0
+    while low < total:
+        size = min(bucket, total - low)
+        parts.append((low, size // world))
+        low += size
+    return total, bucket, parts
 
 
 class DpRendezvousError(RuntimeError):
@@ -296,17 +335,19 @@ def dp_check_replicas(signature, timeout_s=60.0):
     return published[0]
 
 
-def dp_init_from_torch(signature=None, timeout_s=60.0):
+def dp_init_from_torch(signature=None, timeout_s=60.0, max_ctas=None):
     """Creates the NCCL communicator of libonn_b200 for the ranks of an initialised
-    torch.distributed process group (the 128-byte unique id travels through it).  With a `signature`
-    the ranks first check on the host that all of them are present and hold the same replica
-    (dp_check_replicas), so a missing rank or a mismatched parameter arena ends the job with an
-    error instead of a hang inside ncclCommInitRank or a corrupted all-reduce."""
+    torch.distributed process group (the 128-byte unique id travels through it).  The ranks first check
+    on the host that all of them are present and hold the same replica (dp_check_replicas on `signature`;
+    without one, on the number of ranks alone), so a missing rank or a mismatched parameter arena ends the
+    job with an error instead of a wait without limit inside ncclCommInitRank or a corrupted all-reduce.
+    max_ctas caps the SMs NCCL's kernels may use (default: ONN_B200_DP_MAX_CTAS, else NCCL's own choice)."""
     import torch
     import torch.distributed as dist
     world, rank = dist.get_world_size(), dist.get_rank()
-    if signature is not None:
-        dp_check_replicas(signature, timeout_s)
+    dp_check_replicas(signature if signature is not None else {"world": world}, timeout_s)
+    if max_ctas is None:
+        max_ctas = int(os.environ.get("ONN_B200_DP_MAX_CTAS", "0") or 0)
     uid = (C.c_char * 128)()
     if rank == 0:
         capi.check(capi.lib().onn_dp_unique_id(uid), "onn_dp_unique_id")
@@ -314,5 +355,5 @@ def dp_init_from_torch(signature=None, timeout_s=60.0):
     dist.broadcast_object_list(payload, src=0)
     uid_buffer = (C.c_char * 128).from_buffer_copy(payload[0])
     comm = C.c_void_p()
-    capi.check(capi.lib().onn_dp_init(C.byref(comm), uid_buffer, int(world), int(rank)), "onn_dp_init")
+    capi.check(capi.lib().onn_dp_init_config(C.byref(comm), uid_buffer, int(world), int(rank), int(max_ctas)), "onn_dp_init_config")
     return comm

@@ -349,13 +349,15 @@ def ce3d_output_gradients(probabilities, targets, active_count=None):
 # Adam
 # --------------------------------------------------------------------------------------
 
-def adam_update(parameters, gradient, m, v, iteration, lr=1e-3, beta_1=0.9, beta_2=0.999, clip_norm=1.0):
+def adam_update(parameters, gradient, m, v, iteration, lr=1e-3, beta_1=0.9, beta_2=0.999, clip_norm=1.0, norm=None):
     """opennn/adaptive_moment_estimation.cpp:444-473.  `iteration` is the value AFTER the
-    increment (the loop starts at 1, so the first step passes 2).  Updates in place."""
+    increment (the loop starts at 1, so the first step passes 2).  Updates in place.
+    `norm`: the gradient norm to clip by when `gradient` is only a part of the whole gradient (a
+    data-parallel rank that updates its share of the arena clips by the norm of the whole)."""
     lr, beta_1, beta_2, clip_norm = F32(lr), F32(beta_1), F32(beta_2), F32(clip_norm)
     bc1 = F32(1) - F32(np.power(beta_1, F32(iteration)))
     bc2 = F32(1) - F32(np.power(beta_2, F32(iteration)))
-    norm = F32(np.sqrt(np.sum(gradient.astype(np.float64) ** 2)))
+    norm = F32(np.sqrt(np.sum(gradient.astype(np.float64) ** 2))) if norm is None else F32(norm)
     g = gradient
     if clip_norm > 0 and norm > clip_norm:
         g = (gradient * (clip_norm / norm)).astype(F32)

@@ -2,8 +2,11 @@
 onn_classifier_* driver) against the outputs of the reference recorded in tests/golden/classifier_*.npz.
 
 fp32 GEMMs ("simt"): 1e-3 on everything (measured: ~1e-6).  Tensor cores ("auto", tf32 operands): probabilities and loss
-to 1e-3; parameters after Adam to 1e-2 in L2 and to Adam's step bound element-wise; the gradient's L2 error is bounded by 3e-2 because a tf32-sized change of an attention output can move the
-arg-max of the sequence pooling, or flip a ReLU, for a feature whose two candidates are within rounding distance.
+to 1e-3; the gradient to 1e-3 against the oracle run with the DEVICE's discrete choices -- the arg-max positions of the
+sequence pooling and the ReLU masks: a tf32-sized change of an attention output can move the arg-max, or flip a ReLU, for
+a feature whose two candidates are within rounding distance, which changes that feature's gradient by 100 % at any
+precision.  The test bounds how many choices differ and how close the candidates were; the raw difference to the
+reference is printed and bounded loosely.  Parameters after Adam: 1e-2 in L2 and Adam's step bound element-wise.
 """
 
 import numpy as np
@@ -66,6 +69,36 @@ def test_binary_cross_entropy_2d_kernel(libs):
         assert_close(delta.cpu().numpy(), expected_gradient * (y * (1 - y)), 1e-6, "delta")
 
 
+def choice_aligned_gradient(c, net, params, ids, targets, batch, sequence):
+    """Oracle forward in fp32; the pooling layer's arg-max positions and the ReLU masks replaced by the device's; oracle
+    back-propagation.  Returns (gradient, choices that differ, choices in all)."""
+    probabilities = net.forward(params, {-1: ids})
+    differ = total = 0
+    for i, layer in enumerate(net.layers):
+        if layer["kind"] == "Pooling3d" and layer["method"] == "MaxPooling":
+            attention = net.outputs[i - 1]                                       # [B, S, E], fp32
+            on_device = c.layer_output(i - 1).reshape(attention.shape)
+            positions = np.argmax(on_device, axis=1)                             # first maximum, as the kernel
+            moved = positions != net.saved[i]
+            ours = np.take_along_axis(attention, positions[:, None, :], axis=1)[:, 0, :]
+            theirs = np.take_along_axis(attention, net.saved[i][:, None, :], axis=1)[:, 0, :]
+            # another position may win only where the fp32 values of the two were within rounding distance
+            assert np.abs(ours - theirs)[moved].max(initial=0.0) <= 2e-3 * np.abs(attention).max()
+            differ += int(moved.sum())
+            total += moved.size
+            net.saved[i] = positions
+        if layer["kind"] == "Dense2d" and layer["activation"] == "RectifiedLinear":
+            mask = (c.layer_output(i) > 0).astype(np.float32).reshape(net.saved[i].shape)
+            flipped = mask != net.saved[i]
+            assert np.abs(net.outputs[i][flipped]).max(initial=0.0) <= 2e-3 * np.abs(net.outputs[i]).max()
+            differ += int(flipped.sum())
+            total += flipped.size
+            net.saved[i] = mask
+    if probabilities.shape[-1] == 1:
+        return net.backward(params, O.ce2d_binary_output_gradients(probabilities, targets)), differ, total
+    return net.backward(params, O.ce2d_output_gradients(probabilities, targets)), differ, total
+
+
 def test_classifier_structure(libs):
     _, trainer = libs
     B, S, V, E, H, hidden, classes, _ = CLASSIFIER_CASES["classifier_tiny"]
@@ -88,7 +121,7 @@ def test_classifier_training_steps(libs, name, gemm):
     capi.check(capi.lib().onn_gemm_set_mode(1 if gemm == "simt" else 0))
     g = golden(name)
     B, S, V, E, H, hidden, classes, steps = CLASSIFIER_CASES[name]
-    _, params, ids, targets = classifier_inputs(name)
+    net, params, ids, targets = classifier_inputs(name)
     ids_d, targets_d = torch.from_numpy(ids).cuda(), torch.from_numpy(targets).cuda()
     c = trainer.TextClassifier(V, S, E, H, [hidden], classes, B)
     c.set_parameters(params)
@@ -104,7 +137,13 @@ def test_classifier_training_steps(libs, name, gemm):
     if gemm == "simt":
         assert max_err <= TOL and l2_err <= TOL
     else:
-        assert l2_err <= 3e-2
+        aligned, differ, total = choice_aligned_gradient(c, net, params, ids, targets, B, S)
+        aligned_max, aligned_l2 = errors(gradient, aligned)
+        print(f"[{name}/{gemm}] pooling positions and ReLU masks that differ: {differ}/{total}; gradient against the oracle with "
+              f"the device's choices: max {aligned_max:.2e} l2 {aligned_l2:.2e}")
+        assert differ <= max(2, 2e-3 * total), f"{differ} of {total} discrete choices differ"
+        assert aligned_max <= TOL and aligned_l2 <= TOL
+        assert l2_err <= 3e-2, "raw gradient difference beyond what moved arg-max positions and ReLU flips explain"
 
     for step in range(steps):
         error, _ = c.step_device(ids_d, targets_d, update=True)

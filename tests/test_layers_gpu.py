@@ -190,6 +190,9 @@ def test_mha(capi, gemm_mode, name):
     # 1e-3, which is why the per-view bound is on the L2 error and the whole arena is judged on both
     device_arena = np.concatenate([host(grads["d" + key]).ravel() for key in ref])
     reference_arena = np.concatenate([value.ravel() for value in ref.values()])
+    arena_max, arena_l2 = errors(device_arena, reference_arena)
+    if arena_max > TOL:
+        print(f"\n[{name}/{gemm_mode}] parameter gradients: largest element error {arena_max:.2e} (l2 {arena_l2:.2e})")
     assert_close(device_arena, reference_arena, TOL if gemm_mode == "simt" else 2 * TOL, "parameter gradients")
     for key, value in ref.items():
         _, l2 = errors(host(grads["d" + key]), value, floor=floor)
@@ -218,6 +221,61 @@ def test_ce3d_all_masked(capi):
     targets = torch.zeros(2, 3, device="cuda")
     error, accuracy, grad, _ = capi.ce3d(logits, targets)
     assert error == 0.0 and accuracy == 0.0 and not host(grad).any()
+
+
+@pytest.mark.parametrize("rows,V", [(5, 4096), (301, 4100), (200, 8000), (333, 32000), (40, 55296), (9, 55300)])
+def test_ce3d_long_rows(capi, rows, V):
+    """Rows of 4096 logits and more are staged in shared memory by the persistent kernel (ring of 8 KiB chunks: V = 4100
+    ends in a 4-float chunk, 55296 fills the ring exactly, 55300 is past it and falls back to the two-sweep kernel).
+    Against the restated reference arithmetic and against the two-sweep kernel on the same inputs: padding targets,
+    targets past the vocabulary, a row with two equal maxima (the first one counts), logits and probabilities as input."""
+    from oracle import opennn_oracle as O
+    ONN_CE_TWO_SWEEPS = 32
+    rng = np.random.default_rng(rows * 131 + V)
+    logits = (3.0 * rng.standard_normal((1, rows, V))).astype(np.float32)
+    targets = rng.integers(1, V, size=(1, rows)).astype(np.float32)
+    targets[0, ::5] = 0                                   # padding
+    targets[0, 3] = V + 7                                 # past the vocabulary: inactive
+    if rows > 8:
+        top = float(logits[0, 6].max()) + 1.0             # two equal maxima far apart: arg-max is the first
+        logits[0, 6, V - 3] = top
+        logits[0, 6, 17] = top
+        targets[0, 6] = 17
+        targets[0, 7] = float(V - 1)                      # the very last logit of a row
+    shifted = logits - logits.max(axis=-1, keepdims=True)
+    p = np.exp(shifted, dtype=np.float32)
+    p = (p / p.sum(axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    expected_error, expected_accuracy, count = O.ce3d_error(p, targets)
+    expected_gradient = O.ce3d_output_gradients(p, targets)
+
+    error, accuracy, gradient, _ = capi.ce3d(dev(logits), dev(targets))
+    error2, accuracy2, gradient2, _ = capi.ce3d(dev(logits), dev(targets), flags=ONN_CE_TWO_SWEEPS)
+    assert abs(error - expected_error) <= 1e-5 * abs(expected_error)
+    assert abs(accuracy - expected_accuracy) <= 1e-6 and accuracy == accuracy2
+    assert abs(error - error2) <= 1e-6 * abs(error2)
+    assert_close(host(gradient), expected_gradient, 1e-5, "dlogits")
+    assert_close(host(gradient), host(gradient2), 1e-5, "dlogits, staged against two sweeps")
+    inactive = ~((targets[0] > 0) & (targets[0] < V))
+    assert not host(gradient)[0, inactive].any()
+
+    error3, accuracy3, gradient3, _ = capi.ce3d(dev(p), dev(targets), inputs_are_probabilities=True)
+    assert abs(error3 - expected_error) <= 1e-6 * abs(expected_error) and accuracy3 == accuracy
+    assert_close(host(gradient3), expected_gradient, 1e-6, "dlogits from probabilities")
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 1_000_003])
+def test_add(capi, n):
+    """Addition<3> on its own (opennn/addition_layer.h:65-76, y = a + b): bit for bit the fp32 sum, for sizes that are
+    not a multiple of the vector width and for operands that start off a 16-byte boundary (the scalar path)."""
+    rng = np.random.default_rng(n)
+    a, b = rng.standard_normal(n + 1).astype(np.float32), rng.standard_normal(n + 1).astype(np.float32)
+    for offset in (0, 1):
+        a_d, b_d = dev(a)[offset:offset + n], dev(b)[offset:offset + n]
+        out = capi.add(a_d, b_d)
+        assert np.array_equal(host(out), a[offset:offset + n] + b[offset:offset + n])
+    out = capi.add(dev(a)[:n], dev(a)[:n])                      # both operands the same buffer
+    assert np.array_equal(host(out), a[:n] + a[:n])
 
 
 def test_adam_and_norm(capi):
@@ -487,6 +545,8 @@ def test_mha_head64(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
     def check(device, reference, what, floor=0.0):
         max_err, l2_err = errors(device, reference, floor)
         assert np.all(np.isfinite(device)), what
+        if max_err > TOL:
+            print(f"\n[mha_head64 B{B} H{H} Sq{Sq} Sk{Sk} causal{int(causal)} cross{int(cross)}] {what}: largest element error {max_err:.2e} (l2 {l2_err:.2e})")
         assert l2_err <= TOL and max_err <= (TOL if gemm_mode == "simt" else 2 * TOL), f"{what}: max-rel {max_err:.3e}, l2-rel {l2_err:.3e}"
 
     check(host(weights), saved["weights"], "attention weights")

@@ -110,6 +110,25 @@ def test_network_training_steps(name):
     assert_close(arena, g["params_out_sample"], 1e-4, "parameters after Adam")
 
 
+@pytest.mark.parametrize("name", sorted(LARGE))
+def test_full_size_network_first_step(name):
+    """The restatement at the full size of configs 3, 4 and a batch-8 slice of config 5 against what the reference
+    left in the fixtures: first-step loss and accuracy, per-view gradient norms, every 4099th gradient element.  The
+    GPU parity tests judge whole gradient arenas at these sizes with this restatement, so it is pinned here first.
+    Two fp32 evaluations with different summation orders (Eigen there, BLAS here) already put a few ReLU
+    pre-activations on opposite sides of zero at this size, which shows as 4e-4 to 6e-4 in the sampled gradient
+    (2e-4 bounds the small networks); loss, accuracy and the per-view norms are not sensitive to it."""
+    g = golden(name)
+    net, params, external, targets = network_inputs(name)
+    probabilities = net.forward(params, external)
+    error, accuracy, _ = O.ce3d_error(probabilities, targets)
+    assert abs(error - g["loss"][0]) <= 1e-5 * abs(g["loss"][0])
+    assert abs(accuracy - g["loss"][1]) <= 1e-6
+    gradient = net.backward(params, O.ce3d_output_gradients(probabilities, targets))
+    assert_close(gradient[::int(g["sample_stride"])], g["grad_sample"], 1e-3, "gradient samples")
+    assert_close(view_norms(net, gradient), g["grad_view_norms"], 2e-4, "per-view gradient norms")
+
+
 @pytest.mark.parametrize("name", ["classifier_tiny", "classifier_head64", "classifier_binary"])
 def test_text_classifier_training_steps(name):
     """Embedding -> attention -> max pooling -> Dense<2> head with the 2-D cross-entropy, against the reference's
