@@ -106,10 +106,10 @@ typedef struct onn_gemm_args
 
 int onn_gemm(const onn_gemm_args* args, void* stream);
 
-/* Which implementation the next onn_gemm calls use: 0 = automatic (tcgen05 whenever the
- * operands meet the TMA alignment rules: 16-byte aligned bases and pitches), 1 = force the
- * CUDA-core fp32 kernel, 2 = require tcgen05 (ONN_ERR_UNSUPPORTED if it cannot run).
- * The environment variable ONN_B200_GEMM=simt|tc sets the initial value. */
+/* Test hook.  onn_gemm runs on the tcgen05 kernels whenever the operands meet the TMA alignment rules (16-byte aligned
+ * bases and pitches); operands that do not are served by a CUDA-core fp32 kernel.  A test can pin the next onn_gemm
+ * calls to one of the two to cross-check them against each other: 0 = the rule above (the only setting a product
+ * path uses), 1 = the CUDA-core fp32 kernel for everything, 2 = tcgen05 or ONN_ERR_UNSUPPORTED. */
 int onn_gemm_set_mode(int mode);
 /* 0, or ONN_ERR_DEVICE_TIMEOUT if a kernel of this library (tcgen05 GEMM, fused attention, staged cross-entropy)
  * gave up on a bounded barrier wait since the last call.  The status words are read back and cleared; the call
@@ -342,8 +342,8 @@ const float* onn_mha_attention_weights(const float* fwd_workspace,
  * Softmax Dense layer leaves them).  probabilities_out (optional) receives p.
  * stats (device, 4 floats) receives {sum of -log terms, #correct, #active(local), 0};
  * row_scratch is [2*rows] floats.
- * Rows of 4096 to 55296 logits (a multiple of 4, 16-byte aligned, no probabilities_out) are staged in shared
- * memory by a persistent kernel, so each logit crosses HBM once in and once out; other shapes, and calls with
+ * Rows of 4096 to 35712 logits (a multiple of 4, 16-byte aligned, no probabilities_out) are held in registers by a
+ * persistent kernel that is fed through shared memory, so each logit crosses HBM once in and once out; other shapes, and calls with
  * ONN_CE_TWO_SWEEPS in flags, take one CTA per row that sweeps the row twice (the second sweep mostly from L2).
  * ------------------------------------------------------------------------------------- */
 int onn_ce3d_count_active(const float* targets, int64_t rows, int64_t V, float* counts, void* stream);

@@ -16,15 +16,9 @@ namespace onn
 
 std::atomic<uint64_t> g_launch_count{0};
 
-static int initial_mode()
-{
-    const char* env = std::getenv("ONN_B200_GEMM");
-    if(env && std::strcmp(env, "simt") == 0) return 1;
-    if(env && std::strcmp(env, "tc") == 0) return 2;
-    return 0;
-}
-
-static std::atomic<int> g_mode{initial_mode()};
+// 0 unless a test has asked for one kernel family (onn_gemm_set_mode): the tensor-core kernel runs wherever the operands
+// meet the TMA alignment rules, the CUDA-core kernel takes the rest
+static std::atomic<int> g_mode{0};
 static std::atomic<int> g_sm_limit{kSmCount};
 
 int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
@@ -32,9 +26,9 @@ int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
 int gemm_mode() { return g_mode.load(std::memory_order_relaxed); }
 
 // ORs the status words of the kernels with bounded waits into one word, in stream order.
-__global__ void status_gather_kernel(const unsigned int* a, const unsigned int* b, const unsigned int* c, unsigned int* out)
+__global__ void status_gather_kernel(const unsigned int* a, const unsigned int* b, const unsigned int* c, const unsigned int* d, unsigned int* out)
 {
-    out[0] = a[0] | b[0] | c[0];
+    out[0] = a[0] | b[0] | c[0] | d[0];
 }
 
 int gemm(const onn_gemm_args& g, cudaStream_t stream)
@@ -110,7 +104,8 @@ extern "C" int onn_gemm_device_status(void)
     const int gemm_status = gemm_tc_read_status();
     const int attention_status = attention_tc_read_status();
     const int loss_status = ce3d_staged_read_status();
-    return gemm_status != ONN_OK ? gemm_status : attention_status != ONN_OK ? attention_status : loss_status;
+    const int long_status = attention_long_read_status();
+    return gemm_status != ONN_OK ? gemm_status : attention_status != ONN_OK ? attention_status : loss_status != ONN_OK ? loss_status : long_status;
 }
 
 extern "C" int onn_device_status_gather(uint32_t* device_word, void* stream)
@@ -118,21 +113,21 @@ extern "C" int onn_device_status_gather(uint32_t* device_word, void* stream)
     ONN_CHECK_ARG(device_word);
     // the three addresses belong to the current device; looked up per device, once
     static std::mutex lock;
-    static const unsigned int* words[kMaxDevices][3] = {};
+    static const unsigned int* words[kMaxDevices][4] = {};
     int device = 0;
     if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return ONN_ERR_CUDA;
-    const unsigned int* a; const unsigned int* b; const unsigned int* c;
+    const unsigned int* a; const unsigned int* b; const unsigned int* c; const unsigned int* d;
     {
         std::lock_guard<std::mutex> guard(lock);
         if(!words[device][0])
         {
-            const unsigned int* found[3] = { gemm_tc_status_word(), attention_tc_status_word(), ce3d_staged_status_word() };
-            if(!found[0] || !found[1] || !found[2]) return ONN_ERR_CUDA;
-            for(int i = 0; i < 3; i++) words[device][i] = found[i];
+            const unsigned int* found[4] = { gemm_tc_status_word(), attention_tc_status_word(), ce3d_staged_status_word(), attention_long_status_word() };
+            if(!found[0] || !found[1] || !found[2] || !found[3]) return ONN_ERR_CUDA;
+            for(int i = 0; i < 4; i++) words[device][i] = found[i];
         }
-        a = words[device][0]; b = words[device][1]; c = words[device][2];
+        a = words[device][0]; b = words[device][1]; c = words[device][2]; d = words[device][3];
     }
-    status_gather_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(a, b, c, device_word);
+    status_gather_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(a, b, c, d, device_word);
     count_launch();
     return launch_status();
 }

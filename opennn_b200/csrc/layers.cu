@@ -261,12 +261,17 @@ extern "C" int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_param
         g.bias = params->bv;
         ONN_TRY(gemm(g, s));
     }
-    // attention core: one fused kernel where the shapes allow (head size 64, source length <= 256), else
-    // scores GEMM -> mask + softmax -> context GEMM
+    // attention core: one fused kernel where the shapes allow (head size 64; source lengths above 256 are walked in
+    // key tiles), else scores GEMM -> mask + softmax -> context GEMM
     static const bool fused_enabled = []{ const char* e = std::getenv("ONN_B200_ATTENTION_FUSED"); return !(e && e[0] == '0'); }();
+    const bool aligned = host_aligned16(q) && host_aligned16(k) && host_aligned16(v) && host_aligned16(p) && host_aligned16(ctx);
     if(fused_enabled && gemm_mode() != 1 && attention_fwd_fused_supported(q, k, v, p, ctx, B, Sq, Sk, E, H))
     {
         ONN_TRY(attention_fwd_fused_launch(q, k, v, pad_flags, p, ctx, B, Sq, Sk, E, H, causal, scale, s));
+    }
+    else if(fused_enabled && gemm_mode() != 1 && aligned && attention_long_supported(B, Sq, Sk, E, H))
+    {
+        ONN_TRY(attention_long_fwd_launch(q, k, v, pad_flags, p, ctx, B, Sq, Sk, E, H, causal, scale, s));
     }
     else
     {
@@ -302,7 +307,6 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
                            int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H, int causal,
                            float* ws, uint32_t flags, void* stream)
 {
-    (void)causal;
     ONN_CHECK_ARG(Xq && Xs && params && fwd_ws && dY && grads && dXq && B > 0 && Sq > 0 && Sk > 0 && E > 0 && H > 0 && E % H == 0);
     const bool self_attention = Xs == Xq;
     ONN_CHECK_ARG(self_attention ? dXs == nullptr : dXs != nullptr);
@@ -334,9 +338,16 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
     }
     // dP, dS and dQ: one fused kernel where the shapes allow, else GEMM -> softmax backward -> GEMM
     static const bool fused_enabled = []{ const char* e = std::getenv("ONN_B200_ATTENTION_FUSED"); return !(e && e[0] == '0'); }();
+    const bool aligned = host_aligned16(k) && host_aligned16(v) && host_aligned16(p) && host_aligned16(ctx) && host_aligned16(dctx) &&
+                         host_aligned16(dp) && host_aligned16(dq);
     if(fused_enabled && gemm_mode() != 1 && attention_bwd_fused_supported(k, v, p, ctx, dctx, dp, dq, B, Sq, Sk, E, H))
     {
         ONN_TRY(attention_bwd_fused_launch(k, v, p, ctx, dctx, dp, dq, grads->dbq, B, Sq, Sk, E, H, scale, s));
+    }
+    else if(fused_enabled && gemm_mode() != 1 && aligned && attention_long_supported(B, Sq, Sk, E, H))
+    {
+        // with a causal mask the weights of whole key tiles above the diagonal are zero: the kernel skips them
+        ONN_TRY(attention_long_bwd_launch(k, v, p, ctx, dctx, dp, dq, grads->dbq, B, Sq, Sk, E, H, causal, scale, s));
     }
     else
     {

@@ -6,7 +6,7 @@
 
 namespace onn
 {
-// Takes rows of at least 4096 and at most 55296 logits, a multiple of 4, 16-byte aligned, no separate probabilities output.
+// Takes rows of at least 4096 and at most 35712 logits, a multiple of 4, 16-byte aligned, no separate probabilities output.
 bool ce3d_staged_takes(const float* logits, const float* probabilities_out, long long rows, long long V);
 // In place: logits (or probabilities) -> (p - onehot) / active; row_scratch as the two-sweep kernel leaves it.
 int ce3d_staged_launch(float* logits, const float* targets, const float* active_count, float* row_scratch,

@@ -58,3 +58,17 @@ def test_trainer_refuses_without_gpu(built):
         assert "no CUDA device" in str(error)
     else:
         raise AssertionError("creating a trainer without a GPU must fail")
+
+
+def test_reference_side_binding_compiles():
+    """oracle/binding_check.cpp defines Normalization3d's two ...Cuda overrides (opennn/layer.h:348-358) with calls into
+    the C ABI and is compiled against the reference's own headers.  Needs the OpenNN checkout (OPENNN_REFERENCE, or a
+    directory named "reference" beside this repository); skipped where there is none."""
+    import shutil
+    import subprocess
+    import pytest
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    reference = os.environ.get("OPENNN_REFERENCE", os.path.join(os.path.dirname(root), "reference"))
+    if not os.path.isdir(os.path.join(reference, "opennn")) or shutil.which("make") is None:
+        pytest.skip("no OpenNN checkout here")
+    subprocess.run(["make", "-C", os.path.join(root, "oracle"), f"REF={reference}", "binding-check"], check=True, capture_output=True)

@@ -223,10 +223,11 @@ def test_ce3d_all_masked(capi):
     assert error == 0.0 and accuracy == 0.0 and not host(grad).any()
 
 
-@pytest.mark.parametrize("rows,V", [(5, 4096), (301, 4100), (200, 8000), (333, 32000), (40, 55296), (9, 55300)])
+@pytest.mark.parametrize("rows,V", [(5, 4096), (301, 4100), (200, 8000), (333, 32000), (40, 35712), (9, 35716), (7, 51584)])
 def test_ce3d_long_rows(capi, rows, V):
-    """Rows of 4096 logits and more are staged in shared memory by the persistent kernel (ring of 8 KiB chunks: V = 4100
-    ends in a 4-float chunk, 55296 fills the ring exactly, 55300 is past it and falls back to the two-sweep kernel).
+    """Rows of 4096 to 35712 logits are held in registers by the persistent kernel, fed through a ring of 3968-float
+    chunks in shared memory (V = 4100 ends in a 132-float chunk, 8000 takes the 3-chunk instantiation, 35712 is nine full
+    chunks; 35716 and 51584 are past it and fall back to the two-sweep kernel).
     Against the restated reference arithmetic and against the two-sweep kernel on the same inputs: padding targets,
     targets past the vocabulary, a row with two equal maxima (the first one counts), logits and probabilities as input."""
     from oracle import opennn_oracle as O
@@ -515,10 +516,16 @@ def test_gemm_layouts(capi, gemm_mode, a_major, b_major, shape):
 
 @pytest.mark.parametrize("B,H,Sq,Sk,causal,cross", [(2, 2, 256, 256, True, False), (2, 2, 256, 256, False, True),
                                                       (1, 3, 200, 136, False, True), (3, 1, 40, 72, False, True),
-                                                      (2, 2, 72, 72, True, False)])
+                                                      (2, 2, 72, 72, True, False),
+                                                      # source lengths above 256: the kernels that walk the keys in tiles of 256
+                                                      (2, 2, 300, 300, True, False), (1, 2, 130, 520, False, True),
+                                                      (3, 1, 72, 260, False, True), (1, 2, 1024, 1024, True, False),
+                                                      (2, 1, 512, 512, False, False), (2, 1, 384, 768, False, True)])
 def test_mha_head64(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
-    """MultiHeadAttention at head size 64, the shapes the fused attention-core kernel serves (whole and ragged
-    query tiles, source lengths up to 256, causal and key-padding masks), forward and backward against the oracle."""
+    """MultiHeadAttention at head size 64, the shapes the fused attention-core kernels serve (whole and ragged
+    query tiles; source lengths up to 256 in one accumulator row, longer ones in key tiles of 256 with whole tiles
+    above the causal diagonal skipped and a last tile of 4 keys; causal and key-padding masks), forward and backward
+    against the oracle."""
     from oracle import opennn_oracle as O
     E = 64 * H
     rng = np.random.default_rng(B * 1000 + Sq + Sk)
