@@ -279,6 +279,40 @@ def test_add(capi, n):
     assert np.array_equal(host(out), a[:n] + a[:n])
 
 
+@pytest.mark.parametrize("sms", [140, 132, 74, 3])
+def test_sm_limit_keeps_results(capi, sms):
+    """onn_set_sm_limit makes the persistent kernels (tcgen05 GEMMs with their split tail wave and split-K, the fused
+    attention core, the staged cross-entropy) occupy fewer SMs, e.g. to leave some to NCCL; the results stay the same
+    up to the order of the split sums."""
+    from oracle import opennn_oracle as O
+    rng = np.random.default_rng(sms)
+    M, N, K = 4864, 1024, 512                           # 76 tile pairs: a split tail wave on 74 pairs, none on fewer
+    a, b = dev(rng.standard_normal((M, K))), dev(0.05 * rng.standard_normal((K, N)))
+    x = dev(rng.standard_normal((2, 256, 128)))
+    p = {n: dev(rng.uniform(-0.1, 0.1, (128, 128))) for n in ("Wq", "Wk", "Wv", "Wo")}
+    p.update({n: dev(0.05 * rng.standard_normal(128)) for n in ("bq", "bk", "bv", "bo")})
+    logits = (3.0 * rng.standard_normal((1, 300, 8000))).astype(np.float32)
+    targets = rng.integers(1, 8000, size=(1, 300)).astype(np.float32)
+
+    def run():
+        c, dw = torch.zeros(M, N, device="cuda"), torch.zeros(K, N, device="cuda")
+        capi.gemm(a, b, c, M, N, K, K, N, N, 0, 1)
+        capi.gemm(a, c, dw, K, N, M, K, N, N, 1, 1, split_k=4)               # dW = A^T C, reduction split four ways
+        y, ws = capi.mha_fwd(x, x, p, 2, True)
+        _, _, gradient, _ = capi.ce3d(dev(logits), dev(targets))
+        return [host(t) for t in (c, dw, y, gradient)]
+
+    reference = run()
+    capi.check(capi.lib().onn_set_sm_limit(sms))
+    try:
+        limited = run()
+    finally:
+        capi.check(capi.lib().onn_set_sm_limit(0))
+    for got, expected, what in zip(limited, reference, ("product", "split-K product", "attention output", "loss gradient")):
+        assert_close(got, expected, 1e-4, what)                 # split sums are added in another order
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
 def test_adam_and_norm(capi):
     from oracle import opennn_oracle as O
     rng = np.random.default_rng(7)
