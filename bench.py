@@ -111,6 +111,29 @@ def workload_config(w, world, micro):
             "l2": "per-step working set (tens of GB of activations) far exceeds the 126 MB L2; batches rotate"}
 
 
+def time_reference_gpu_path(w, batch, steps):
+    """The reference's OWN CUDA path (cuBLAS SGEMM + cuDNN + opennn/kernel.cu, the loop body of train_cuda) on the
+    same configuration and synthetic batch: the existing GPU implementation, for comparison only.  Needs the binary
+    `make -C oracle cuda` builds; returns None without it."""
+    import numpy as np
+    from oracle import ref_runner
+    if not ref_runner.cuda_available():
+        return None
+    rng = np.random.default_rng(w["seed"])
+    enc, dec, tgt = synthetic_batch(rng, batch, w)
+    spec = dict(mode="decoder_cuda" if w.get("decoder_only") else "transformer_cuda", B=batch, S_in=w["S_in"], S_dec=w["S_dec"], V_in=w["V_in"],
+                V_out=w["V_out"], E=w["E"], H=w["H"], F=w["F"], L=w["L"], steps=steps, lr=1e-3, random_parameters=1)
+    tensors = {"dec_ids": dec, "targets": tgt}
+    if enc is not None:
+        tensors["enc_ids"] = enc
+    out, seconds = ref_runner.run(spec, tensors, ["loss"], cuda=True)
+    timed = seconds[2:] if len(seconds) > 3 else seconds[1:]
+    best = min(timed)
+    return {"what": "reference's own CUDA path (cuBLAS SGEMM, cuDNN, opennn/kernel.cu), fp32, one GPU, same configuration and batch",
+            "ms_per_step": 1e3 * best, "tokens_per_s": batch * w["S_dec"] / best, "steps_timed": len(timed),
+            "loss_first_last": [float(out["loss"][0]), float(out["loss"][-2])] if "loss" in out else None}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -590,6 +613,11 @@ def run_ours(args):
             status = capi.lib().onn_gemm_device_status()
             if status != 0:
                 raise SystemExit("a kernel gave up on a bounded wait: the numbers are void")
+            if rank == 0 and args.workload in ("config3", "config4"):
+                t.close()
+                gpu_reference = time_reference_gpu_path(w, w["global_batch"], 8)
+                if gpu_reference:
+                    line["reference_gpu_path"] = gpu_reference
             if rank == 0 and args.workload in ("config3", "config4") and not args.no_cpu_baseline:
                 # the reference CPU library on the same configuration at full size (second of two steps)
                 from oracle import ref_runner

@@ -16,6 +16,12 @@
 //                the loop body of adaptive_moment_estimation.cpp:249-284
 //   decoder      decoder-only stack assembled with add_layer the way Transformer::set
 //                assembles its decoder, minus cross-attention
+//   transformer_cuda / decoder_cuda   (only in the binary built with the reference's CUDA path,
+//                `make -C oracle cuda`): the same networks through the reference's OWN GPU path,
+//                the loop body of AdaptiveMomentEstimation::train_cuda
+//                (adaptive_moment_estimation.cpp:697-721): cuBLAS SGEMM + cuDNN + opennn/kernel.cu.
+//                Timed per step with a device synchronisation on both sides; it is the
+//                "existing GPU implementation" the new path is compared with, nothing more.
 //
 // Token ids and targets are floats holding integers, as in the reference (dataset.h:525-558).
 
@@ -437,6 +443,105 @@ void run_network(bool decoder_only)
 
 
 
+#ifdef OPENNN_CUDA
+
+// The reference's own CUDA training step on a batch made by hand (BatchCuda needs a Dataset only to size itself:
+// dataset.cpp:4397-4460; its members are public).
+void run_network_cuda(bool decoder_only)
+{
+    const Index B = spec_index("B");
+    const Index S_in = spec_index("S_in");
+    const Index S_dec = spec_index("S_dec");
+    const Index V_in = spec_index("V_in");
+    const Index V_out = spec_index("V_out");
+    const Index E = spec_index("E");
+    const Index H = spec_index("H");
+    const Index F = spec_index("F");
+    const Index L = spec_index("L");
+    const Index steps = spec_index("steps", 1);
+
+    unique_ptr<NeuralNetwork> network;
+    if(decoder_only)
+    {
+        network = make_unique<NeuralNetwork>();
+        build_decoder_only(*network, S_dec, V_out, E, H, F, L);
+    }
+    else
+        network = make_unique<Transformer>(S_in, S_dec, V_in, V_out, E, H, F, L);
+
+    VectorR& parameters = network->get_parameters();
+    if(spec_index("random_parameters") == 0)
+    {
+        const vector<type> parameters_in = read_bin("params", parameters.size());
+        memcpy(parameters.data(), parameters_in.data(), parameters_in.size() * sizeof(type));
+    }
+
+    CrossEntropyError3d loss(network.get(), nullptr);
+    loss.set_regularization_method("None");
+
+    BatchCuda batch;
+    batch.samples_number = B;
+    const vector<type> targets = read_bin("targets", B * S_dec);
+    const vector<type> decoder_ids = read_bin("dec_ids", B * S_dec);
+    if(!decoder_only)
+    {
+        const vector<type> encoder_ids = read_bin("enc_ids", B * S_in);
+        batch.input_shape = {B, S_in};
+        batch.num_input_features = S_in;
+        batch.inputs_device.resize({B, S_in});
+        CHECK_CUDA(cudaMemcpy(batch.inputs_device.data, encoder_ids.data(), encoder_ids.size() * sizeof(type), cudaMemcpyHostToDevice));
+        batch.decoder_shape = {B, S_dec};
+        batch.num_decoder_features = S_dec;
+        batch.decoder_device.resize({B, S_dec});
+        CHECK_CUDA(cudaMemcpy(batch.decoder_device.data, decoder_ids.data(), decoder_ids.size() * sizeof(type), cudaMemcpyHostToDevice));
+    }
+    else
+    {
+        batch.input_shape = {B, S_dec};
+        batch.num_input_features = S_dec;
+        batch.inputs_device.resize({B, S_dec});
+        CHECK_CUDA(cudaMemcpy(batch.inputs_device.data, decoder_ids.data(), decoder_ids.size() * sizeof(type), cudaMemcpyHostToDevice));
+    }
+    batch.target_shape = {B, S_dec};
+    batch.num_target_features = S_dec;
+    batch.targets_device.resize({B, S_dec});
+    CHECK_CUDA(cudaMemcpy(batch.targets_device.data, targets.data(), targets.size() * sizeof(type), cudaMemcpyHostToDevice));
+
+    ForwardPropagationCuda forward(B, network.get());
+    network->copy_parameters_device();
+    BackPropagationCuda back(B, &loss);
+
+    AdaptiveMomentEstimation adam(&loss);
+    adam.set_learning_rate(type(spec_double("lr", 1e-3)));
+    ADAMOptimizationDataCuda optimization_data(&adam);
+    optimization_data.iteration = 1;
+
+    vector<type> history;
+    vector<double> step_seconds;
+    for(Index step = 0; step < steps; step++)
+    {
+        CHECK_CUDA(cudaDeviceSynchronize());
+        const double start = now_seconds();
+
+        back.neural_network.gradients.fill(0.0f);
+        network->forward_propagate(batch.get_inputs_device(), forward, true);
+        loss.back_propagate(batch, forward, back);
+        adam.update_parameters(back, optimization_data);
+
+        CHECK_CUDA(cudaDeviceSynchronize());
+        step_seconds.push_back(now_seconds() - start);
+        history.push_back(back.error);
+        history.push_back(back.accuracy(0));
+    }
+
+    write_bin("loss", history.data(), history.size());
+    ofstream timing(dir_path + "/timing.txt");
+    for(const double seconds : step_seconds) timing << seconds << "\n";
+}
+
+#endif
+
+
 // Text classifier (Embedding -> MultiHeadAttention -> Pooling3d -> Dense<2>... -> Softmax) with CrossEntropyError2d.
 
 void run_classifier()
@@ -533,6 +638,10 @@ int main(int argc, char** argv)
         else if(mode == "ce3d") run_ce3d();
         else if(mode == "transformer") run_network(false);
         else if(mode == "decoder") run_network(true);
+#ifdef OPENNN_CUDA
+        else if(mode == "transformer_cuda") run_network_cuda(false);
+        else if(mode == "decoder_cuda") run_network_cuda(true);
+#endif
         else if(mode == "classifier") run_classifier();
         else throw runtime_error("unknown mode " + mode);
     }

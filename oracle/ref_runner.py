@@ -17,17 +17,25 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 HARNESS = os.path.join(HERE, "_ref", "onn_ref_harness")
+# the same harness built against the reference's own CUDA path (`make -C oracle cuda`): modes transformer_cuda / decoder_cuda
+HARNESS_CUDA = os.path.join(HERE, "_ref_cuda", "onn_ref_harness_cuda")
 
 
 def available() -> bool:
     return os.path.isfile(HARNESS) and os.access(HARNESS, os.X_OK)
 
 
-def run(spec: dict, tensors: dict, outputs: list[str], threads: int | None = None, keep: bool = False):
+def cuda_available() -> bool:
+    return os.path.isfile(HARNESS_CUDA) and os.access(HARNESS_CUDA, os.X_OK)
+
+
+def run(spec: dict, tensors: dict, outputs: list[str], threads: int | None = None, keep: bool = False, cuda: bool = False):
     """Write spec + tensors to a scratch dir, run the harness, read back `outputs`.
-    Returns (dict name -> flat float32 array, list of per-step seconds)."""
-    if not available():
-        raise RuntimeError("reference harness not built: make -C oracle")
+    Returns (dict name -> flat float32 array, list of per-step seconds).
+    cuda: run the binary built with the reference's CUDA path (its *_cuda modes)."""
+    binary = HARNESS_CUDA if cuda else HARNESS
+    if not (cuda_available() if cuda else available()):
+        raise RuntimeError("reference harness not built: make -C oracle" + (" cuda" if cuda else ""))
     scratch = tempfile.mkdtemp(prefix="onn_ref_")
     try:
         spec = dict(spec)
@@ -41,7 +49,7 @@ def run(spec: dict, tensors: dict, outputs: list[str], threads: int | None = Non
         env = dict(os.environ)
         if threads is not None:
             env["OMP_NUM_THREADS"] = str(threads)
-        subprocess.run([HARNESS, scratch], check=True, env=env)
+        subprocess.run([binary, scratch], check=True, env=env)
         result = {}
         for name in outputs:
             path = os.path.join(scratch, name + ".bin")
