@@ -111,6 +111,14 @@ int onn_gemm(const onn_gemm_args* args, void* stream);
  * calls to one of the two to cross-check them against each other: 0 = the rule above (the only setting a product
  * path uses), 1 = the CUDA-core fp32 kernel for everything, 2 = tcgen05 or ONN_ERR_UNSUPPORTED. */
 int onn_gemm_set_mode(int mode);
+/* Key and value gradients of onn_mha_bwd: 0 (the default) = two batched GEMMs over the stored weights P and the score
+ * gradient dS, as the reference computes them (opennn/multihead_attention_layer.cpp:843-887); 1 = where the fused
+ * attention kernels serve the layer (head size 64, at most 256 keys), one kernel that forms P and dS again on the SM
+ * from Q, K, V, dO and the per-row softmax statistics the forward pass left in its workspace, so that dS is never
+ * written and P is not read a third time.  Measured on B200 the second is not faster yet (same results within tf32
+ * rounding), which is why it is not the default; the environment variable ONN_B200_ATTENTION_KV_GRAD=1 selects it
+ * for a whole process.  A forward/backward pair must run under one setting.  Returns the previous setting. */
+int onn_mha_set_kv_grad_by_recomputation(int enabled);
 /* 0, or ONN_ERR_DEVICE_TIMEOUT if a kernel of this library (tcgen05 GEMM, fused attention, staged cross-entropy)
  * gave up on a bounded barrier wait since the last call.  The status words are read back and cleared; the call
  * synchronises the whole device first, so it sees every kernel launched before it on any stream. */

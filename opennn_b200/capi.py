@@ -52,7 +52,7 @@ class MhaGrads(C.Structure):
 
 
 EXPORTS = [
-    "onn_status_string", "onn_version", "onn_gemm", "onn_gemm_set_mode", "onn_gemm_device_status",
+    "onn_status_string", "onn_version", "onn_gemm", "onn_gemm_set_mode", "onn_mha_set_kv_grad_by_recomputation", "onn_gemm_device_status",
     "onn_launch_count", "onn_launch_count_add", "onn_selftest_bounded_wait", "onn_embedding_fwd", "onn_embedding_bwd", "onn_ids_to_float",
     "onn_layernorm_fwd", "onn_layernorm_bwd_workspace_floats", "onn_layernorm_bwd", "onn_layernorm_bwd_static", "onn_add",
     "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_pooling3d_fwd", "onn_pooling3d_bwd", "onn_softmax_rows",

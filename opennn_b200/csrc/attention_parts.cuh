@@ -34,6 +34,11 @@ struct AttnParams
     const float* d_context;                               // [B, Sq, E] its gradient
     float* d_bias_q;                                      // [E]: column sums of dQ are added here (may be null)
     long long E;
+    // hand-over to the key / value gradient kernel (attention_kv_grad.cu), all [B, H, Sq]; null = not wanted
+    float* row_max_out;                                   // forward: log2-domain maximum of every query row, masks applied
+    float* row_inv_out;                                   // forward: 1 / sum of the row's tf32-rounded exponentials
+    float* delta_out;                                     // backward: rowsum(dO * O)
+    int skip_score_gradient_store;                        // backward: dS stays on the SM (nobody reads it from HBM)
 };
 
 #define ONN_LIST8(M, v, o) M(v[(o)]), M(v[(o) + 1]), M(v[(o) + 2]), M(v[(o) + 3]), M(v[(o) + 4]), M(v[(o) + 5]), M(v[(o) + 6]), M(v[(o) + 7])

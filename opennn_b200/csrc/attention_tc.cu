@@ -236,6 +236,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 exchange[half * kQRows + r_local] = delta;
                 pair_barrier(quadrant);
                 delta += exchange[(half ^ 1) * kQRows + r_local];
+                if(p.delta_out && half == 0 && q_row < p.Sq) p.delta_out[((long long)it.b * p.H + it.h) * p.Sq + q_row] = delta;
 
                 // dS = P * (dP - delta), 32 columns at a time.  dP comes from tensor memory one block ahead of its use; the
                 // weights arrived in this warp's four ring blocks by TMA (requested while the previous item was still being
@@ -280,7 +281,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             }
                             fence_async_shared();
                             __syncwarp();
-                            if(lane == 0)
+                            if(lane == 0 && !p.skip_score_gradient_store)
                             {
                                 tma_store_4d(&map_p, buffer, block * 32, row0, it.h, it.b);
                                 bulk_commit();
@@ -462,6 +463,13 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 pair_barrier(quadrant);
                 total += exchange[(half ^ 1) * kQRows + r_local];
                 const float inv = total > 0.f ? 1.0f / total : 0.f;
+                if(p.row_max_out && half == 0 && q_row < p.Sq)
+                {
+                    // what the key / value gradient kernel needs to form this row's weights again without reading them
+                    const long long at = ((long long)it.b * p.H + it.h) * p.Sq + q_row;
+                    p.row_max_out[at] = row_max;
+                    p.row_inv_out[at] = inv;
+                }
 
                 // the attention weights leave from the registers while the context MMAs run
 #pragma unroll
@@ -561,7 +569,8 @@ static int launch_attention_core(const CUtensorMap& a, const CUtensorMap& b1, co
 }  // namespace tc
 
 int attention_fwd_fused_launch(const float* q, const float* k, const float* v, const unsigned char* key_is_pad,
-                               float* weights, float* context, long long B, long long Sq, long long Sk, long long E, long long H,
+                               float* weights, float* context, float* row_max_out, float* row_inv_out,
+                               long long B, long long Sq, long long Sk, long long E, long long H,
                                int causal, float scale, cudaStream_t stream)
 {
     using namespace tc;
@@ -569,6 +578,8 @@ int attention_fwd_fused_launch(const float* q, const float* k, const float* v, c
     AttnParams p = attention_params(B, Sq, Sk, E, H, scale);
     p.key_is_pad = key_is_pad;
     p.causal = causal;
+    p.row_max_out = row_max_out && row_inv_out ? row_max_out : nullptr;
+    p.row_inv_out = row_inv_out;
 
     CUtensorMap map_q, map_k, map_v, map_p, map_ctx;
     bool ok = make_map(&map_q, q, E, Sq, E, 1, 0, (int)B, Sq * E, 32, kQRows, false);
@@ -583,7 +594,8 @@ int attention_fwd_fused_launch(const float* q, const float* k, const float* v, c
 // dS = P * (dP - rowsum(P * dP)) with dP = dO V^T, written to d_scores ([B, H, Sq, Sk]); dQ = scale * dS K written to
 // d_q ([B, Sq, E]); the column sums of dQ are added to d_bias_q ([E], may be null).
 int attention_bwd_fused_launch(const float* k, const float* v, const float* weights, const float* context, const float* d_context,
-                               float* d_scores, float* d_q, float* d_bias_q, long long B, long long Sq, long long Sk, long long E, long long H,
+                               float* d_scores, float* d_q, float* d_bias_q, float* delta_out, int store_score_gradient,
+                               long long B, long long Sq, long long Sk, long long E, long long H,
                                float scale, cudaStream_t stream)
 {
     using namespace tc;
@@ -592,6 +604,8 @@ int attention_bwd_fused_launch(const float* k, const float* v, const float* weig
     p.context = context;
     p.d_context = d_context;
     p.d_bias_q = d_bias_q;
+    p.delta_out = delta_out;
+    p.skip_score_gradient_store = store_score_gradient ? 0 : 1;
 
     CUtensorMap map_do, map_v, map_k, map_ds, map_dq, map_w;
     bool ok = make_map(&map_do, d_context, E, Sq, E, 1, 0, (int)B, Sq * E, 32, kQRows, false);

@@ -26,9 +26,10 @@ int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
 int gemm_mode() { return g_mode.load(std::memory_order_relaxed); }
 
 // ORs the status words of the kernels with bounded waits into one word, in stream order.
-__global__ void status_gather_kernel(const unsigned int* a, const unsigned int* b, const unsigned int* c, const unsigned int* d, unsigned int* out)
+__global__ void status_gather_kernel(const unsigned int* a, const unsigned int* b, const unsigned int* c, const unsigned int* d,
+                                     const unsigned int* e, unsigned int* out)
 {
-    out[0] = a[0] | b[0] | c[0] | d[0];
+    out[0] = a[0] | b[0] | c[0] | d[0] | e[0];
 }
 
 int gemm(const onn_gemm_args& g, cudaStream_t stream)
@@ -105,7 +106,9 @@ extern "C" int onn_gemm_device_status(void)
     const int attention_status = attention_tc_read_status();
     const int loss_status = ce3d_staged_read_status();
     const int long_status = attention_long_read_status();
-    return gemm_status != ONN_OK ? gemm_status : attention_status != ONN_OK ? attention_status : loss_status != ONN_OK ? loss_status : long_status;
+    const int kv_status = attention_kv_grad_read_status();
+    return gemm_status != ONN_OK ? gemm_status : attention_status != ONN_OK ? attention_status : loss_status != ONN_OK ? loss_status :
+           long_status != ONN_OK ? long_status : kv_status;
 }
 
 extern "C" int onn_device_status_gather(uint32_t* device_word, void* stream)
@@ -113,21 +116,22 @@ extern "C" int onn_device_status_gather(uint32_t* device_word, void* stream)
     ONN_CHECK_ARG(device_word);
     // the three addresses belong to the current device; looked up per device, once
     static std::mutex lock;
-    static const unsigned int* words[kMaxDevices][4] = {};
+    static const unsigned int* words[kMaxDevices][5] = {};
     int device = 0;
     if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return ONN_ERR_CUDA;
-    const unsigned int* a; const unsigned int* b; const unsigned int* c; const unsigned int* d;
+    const unsigned int* w[5];
     {
         std::lock_guard<std::mutex> guard(lock);
         if(!words[device][0])
         {
-            const unsigned int* found[4] = { gemm_tc_status_word(), attention_tc_status_word(), ce3d_staged_status_word(), attention_long_status_word() };
-            if(!found[0] || !found[1] || !found[2] || !found[3]) return ONN_ERR_CUDA;
-            for(int i = 0; i < 4; i++) words[device][i] = found[i];
+            const unsigned int* found[5] = { gemm_tc_status_word(), attention_tc_status_word(), ce3d_staged_status_word(),
+                                             attention_long_status_word(), attention_kv_grad_status_word() };
+            for(int i = 0; i < 5; i++) if(!found[i]) return ONN_ERR_CUDA;
+            for(int i = 0; i < 5; i++) words[device][i] = found[i];
         }
-        a = words[device][0]; b = words[device][1]; c = words[device][2]; d = words[device][3];
+        for(int i = 0; i < 5; i++) w[i] = words[device][i];
     }
-    status_gather_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(a, b, c, d, device_word);
+    status_gather_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(w[0], w[1], w[2], w[3], w[4], device_word);
     count_launch();
     return launch_status();
 }

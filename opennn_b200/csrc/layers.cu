@@ -1,6 +1,7 @@
 // Layer-level entry points built from the GEMM primitive and the row kernels:
 // Dense<3> forward/backward and MultiHeadAttention forward/backward.
 #include <math.h>
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -158,9 +159,12 @@ extern "C" int onn_dense_bwd(const float* X, const float* W, const float* Y, flo
 
 namespace
 {
+// how onn_mha_bwd forms dK and dV: 0 = batched GEMMs over P and dS, 1 = the recomputation kernel where it applies
+std::atomic<int> g_kv_grad_by_recomputation{ []{ const char* e = std::getenv("ONN_B200_ATTENTION_KV_GRAD"); return (e && e[0] == '1') ? 1 : 0; }() };
+
 struct MhaForwardLayout
 {
-    size_t q, k, v, p, ctx, pad, total;
+    size_t q, k, v, p, ctx, pad, row_max, row_inv, total;
     MhaForwardLayout(int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H)
     {
         size_t at = 0;
@@ -171,13 +175,16 @@ struct MhaForwardLayout
         p = take((size_t)B * H * Sq * Sk);
         ctx = take((size_t)B * Sq * E);
         pad = take(((size_t)B * Sk + 3) / 4);
+        // per query row, for the key / value gradient kernel: the maximum and 1 / sum the softmax of that row used
+        row_max = take((size_t)B * H * Sq);
+        row_inv = take((size_t)B * H * Sq);
         total = at;
     }
 };
 
 struct MhaBackwardLayout
 {
-    size_t dctx, dp, dq, dk, dv, total;
+    size_t dctx, dp, dq, dk, dv, delta, total;
     MhaBackwardLayout(int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H)
     {
         size_t at = 0;
@@ -187,6 +194,7 @@ struct MhaBackwardLayout
         dq = take((size_t)B * Sq * E);
         dk = take((size_t)B * Sk * E);
         dv = take((size_t)B * Sk * E);
+        delta = take((size_t)B * H * Sq);                 // rowsum(dO * O), from the query-gradient kernel to the key / value one
         total = at;
     }
 };
@@ -206,6 +214,11 @@ void score_strides(onn_gemm_args& g, char which, long long H, long long Sq, long
     if(which == 'c') { g.c_stride_inner = Sq * Sk; g.c_stride_outer = H * Sq * Sk; }
 }
 }  // namespace
+
+extern "C" int onn_mha_set_kv_grad_by_recomputation(int enabled)
+{
+    return g_kv_grad_by_recomputation.exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed);
+}
 
 extern "C" size_t onn_mha_fwd_workspace_floats(int64_t B, int64_t Sq, int64_t Sk, int64_t E, int64_t H)
 {
@@ -267,7 +280,10 @@ extern "C" int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_param
     const bool aligned = host_aligned16(q) && host_aligned16(k) && host_aligned16(v) && host_aligned16(p) && host_aligned16(ctx);
     if(fused_enabled && gemm_mode() != 1 && attention_fwd_fused_supported(q, k, v, p, ctx, B, Sq, Sk, E, H))
     {
-        ONN_TRY(attention_fwd_fused_launch(q, k, v, pad_flags, p, ctx, B, Sq, Sk, E, H, causal, scale, s));
+        // back-propagation forms the weights again from Q, K and these per-row statistics, and needs the key flags for it
+        if(pad_flags != reinterpret_cast<const uint8_t*>(ws + L.pad) &&
+           cudaMemcpyAsync(ws + L.pad, pad_flags, (size_t)(B * Sk), cudaMemcpyDeviceToDevice, s) != cudaSuccess) return ONN_ERR_CUDA;
+        ONN_TRY(attention_fwd_fused_launch(q, k, v, pad_flags, p, ctx, ws + L.row_max, ws + L.row_inv, B, Sq, Sk, E, H, causal, scale, s));
     }
     else if(fused_enabled && gemm_mode() != 1 && aligned && attention_long_supported(B, Sq, Sk, E, H))
     {
@@ -328,21 +344,37 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         onn_gemm_args g = plain_gemm(dY, 0, E, Wo, 0, E, dctx, E, rows_q, E, E);
         ONN_TRY(gemm(g, s));
     }
-    // dV = P^T dO
+    // dP, dS and dQ: one fused kernel where the shapes allow, else GEMM -> softmax backward -> GEMM
+    static const bool fused_enabled = []{ const char* e = std::getenv("ONN_B200_ATTENTION_FUSED"); return !(e && e[0] == '0'); }();
+    const bool kv_kernel_enabled = g_kv_grad_by_recomputation.load(std::memory_order_relaxed) != 0;
+    // Where the forward pass ran on the single-tile fused kernel it left every query row's softmax statistics, and the
+    // key and value gradients come from ONE kernel that forms the weights again on the SM (no pass over P or dS, and
+    // dS is never written); elsewhere from two batched GEMMs over P and dS.  Back-propagation must therefore run with
+    // the kernels its forward pass ran with (the same GEMM mode and environment switches).
+    const bool kv_by_recomputation = fused_enabled && kv_kernel_enabled && gemm_mode() != 1 &&
+                                     attention_bwd_fused_supported(k, v, p, ctx, dctx, dp, dq, B, Sq, Sk, E, H) &&
+                                     attention_kv_grad_supported(q, k, v, dctx, dk, dv, B, Sq, Sk, E, H);
+    if(!kv_by_recomputation)
     {
+        // dV = P^T dO
         onn_gemm_args g = plain_gemm(p, 1, Sk, dctx, 1, E, dv, E, Sk, hd, Sq);
         g.batch_inner = (int)H; g.batch_outer = (int)B;
         score_strides(g, 'a', H, Sq, Sk); head_strides(g, 'b', Sq, E, hd); head_strides(g, 'c', Sk, E, hd);
         g.colsum_out = grads->dbv; g.colsum_stride_inner = hd;      // dbv = column sums of dV, taken in the epilogue
         ONN_TRY(gemm(g, s));
     }
-    // dP, dS and dQ: one fused kernel where the shapes allow, else GEMM -> softmax backward -> GEMM
-    static const bool fused_enabled = []{ const char* e = std::getenv("ONN_B200_ATTENTION_FUSED"); return !(e && e[0] == '0'); }();
     const bool aligned = host_aligned16(k) && host_aligned16(v) && host_aligned16(p) && host_aligned16(ctx) && host_aligned16(dctx) &&
                          host_aligned16(dp) && host_aligned16(dq);
-    if(fused_enabled && gemm_mode() != 1 && attention_bwd_fused_supported(k, v, p, ctx, dctx, dp, dq, B, Sq, Sk, E, H))
+    if(kv_by_recomputation)
     {
-        ONN_TRY(attention_bwd_fused_launch(k, v, p, ctx, dctx, dp, dq, grads->dbq, B, Sq, Sk, E, H, scale, s));
+        float* delta = ws + L.delta;
+        ONN_TRY(attention_bwd_fused_launch(k, v, p, ctx, dctx, dp, dq, grads->dbq, delta, 0, B, Sq, Sk, E, H, scale, s));
+        ONN_TRY(attention_kv_grad_launch(q, k, v, dctx, reinterpret_cast<const unsigned char*>(fwd_ws + F.pad), fwd_ws + F.row_max, fwd_ws + F.row_inv,
+                                         delta, dk, dv, grads->dbk, grads->dbv, B, Sq, Sk, E, H, causal, scale, s));
+    }
+    else if(fused_enabled && gemm_mode() != 1 && attention_bwd_fused_supported(k, v, p, ctx, dctx, dp, dq, B, Sq, Sk, E, H))
+    {
+        ONN_TRY(attention_bwd_fused_launch(k, v, p, ctx, dctx, dp, dq, grads->dbq, nullptr, 1, B, Sq, Sk, E, H, scale, s));
     }
     else if(fused_enabled && gemm_mode() != 1 && aligned && attention_long_supported(B, Sq, Sk, E, H))
     {
@@ -371,6 +403,7 @@ extern "C" int onn_mha_bwd(const float* Xq, const float* Xs, const onn_mha_param
         }
     }
     // dK = scale * dS^T Q
+    if(!kv_by_recomputation)
     {
         onn_gemm_args g = plain_gemm(dp, 1, Sk, q, 1, E, dk, E, Sk, hd, Sq);
         g.batch_inner = (int)H; g.batch_outer = (int)B;

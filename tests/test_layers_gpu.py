@@ -560,6 +560,25 @@ def test_mha_head64(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
     query tiles; source lengths up to 256 in one accumulator row, longer ones in key tiles of 256 with whole tiles
     above the causal diagonal skipped and a last tile of 4 keys; causal and key-padding masks), forward and backward
     against the oracle."""
+    mha_head64_case(capi, gemm_mode, B, H, Sq, Sk, causal, cross)
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,causal,cross", [(2, 2, 256, 256, True, False), (2, 2, 256, 256, False, True),
+                                                      (1, 3, 200, 136, False, True), (3, 1, 40, 72, False, True),
+                                                      (2, 2, 72, 72, True, False), (5, 16, 192, 192, True, False)])
+def test_mha_head64_kv_grad_by_recomputation(capi, B, H, Sq, Sk, causal, cross):
+    """The same layer with dK and dV from the kernel that forms the weights again on the SM (one key tile and two,
+    ragged tiles, an item of a single query step, more work items than SMs), against the oracle."""
+    previous = capi.lib().onn_mha_set_kv_grad_by_recomputation(1)
+    try:
+        launches = capi.lib().onn_launch_count()
+        mha_head64_case(capi, "auto", B, H, Sq, Sk, causal, cross)
+    finally:
+        capi.lib().onn_mha_set_kv_grad_by_recomputation(previous)
+    assert capi.lib().onn_launch_count() > launches
+
+
+def mha_head64_case(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
     from oracle import opennn_oracle as O
     E = 64 * H
     rng = np.random.default_rng(B * 1000 + Sq + Sk)
@@ -599,6 +618,9 @@ def test_mha_head64(capi, gemm_mode, B, H, Sq, Sk, causal, cross):
         check(host(dxs), dxs_e, "dxs")
     for name in ("dWq", "dWk", "dWv", "dWo", "dbq", "dbv", "dbo"):
         check(host(grads[name]), grads_e[name], name, floor=1e-6)
+    # the key bias gradient is zero in exact arithmetic (a softmax row does not change when every score of the row
+    # moves by the same amount), so it is compared on the scale of the query bias gradient
+    assert np.abs(host(grads["dbk"]) - grads_e["dbk"]).max() <= 2 * TOL * max(np.abs(grads_e["dbq"]).max(), 1e-3), "dbk"
     assert capi.lib().onn_gemm_device_status() == 0
 
 
