@@ -613,7 +613,7 @@ def run_ours(args):
             status = capi.lib().onn_gemm_device_status()
             if status != 0:
                 raise SystemExit("a kernel gave up on a bounded wait: the numbers are void")
-            if rank == 0 and args.workload in ("config3", "config4"):
+            if rank == 0 and args.workload in ("config3", "config4") and not args.no_cpu_baseline:
                 t.close()
                 gpu_reference = time_reference_gpu_path(w, w["global_batch"], 8)
                 if gpu_reference:

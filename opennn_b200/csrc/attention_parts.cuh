@@ -112,6 +112,11 @@ __device__ __forceinline__ AttnItem decode_item(const AttnParams& p, long long w
     // the query tiles of one head are neighbours, so the second one finds K and V in L2
     AttnItem it;
     it.q_tile = (int)(w % p.q_tiles); w /= p.q_tiles;
+    // With a causal mask over several key tiles a query tile's work grows with its index, and a CTA that strides through
+    // the items by the grid size would keep meeting the same few tile indices (148 and 8 query tiles: only t and t + 4).
+    // Rotating the tile order of each head by roughly the round in which the head is reached lets every CTA meet all of
+    // them; within a head it is still a permutation.
+    if(p.causal && p.key_tiles > 1) it.q_tile = (int)((it.q_tile + (w * p.q_tiles) / gridDim.x) % p.q_tiles);
     it.h = (int)(w % p.H);
     it.b = (int)(w / p.H);
     return it;
