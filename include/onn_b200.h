@@ -459,6 +459,14 @@ int onn_dp_all_gather(onn_dp_comm* comm, const float* send, float* recv, int64_t
  * reduced is cleared for the next step off the compute stream). */
 int onn_dp_zero(onn_dp_comm* comm, float* buf, int64_t n);
 int onn_dp_wait(onn_dp_comm* comm, void* stream);
+/* Finer-grained waits: onn_dp_mark records position `slot` (0 .. ONN_DP_MARKS - 1) on the comm stream after what has
+ * been enqueued so far; onn_dp_wait_mark makes `stream` wait for the work before that position only (the comm stream
+ * runs in order, so a later mark implies the earlier ones).  The trainer marks each parameter bucket's all-gather and
+ * lets the next step's forward pass wait layer by layer, so the gathers run under it.  A slot must have been marked
+ * before it is waited for; marking it again moves it. */
+#define ONN_DP_MARKS 64
+int onn_dp_mark(onn_dp_comm* comm, int slot);
+int onn_dp_wait_mark(onn_dp_comm* comm, int slot, void* stream);
 /* After a failure between collectives on this rank (an exception half-way through a step) the ranks no longer
  * agree on which collective comes next: mark the communicator, and every later call returns ONN_ERR_NCCL instead
  * of joining a collective the peers are not in.  A failed NCCL call marks it by itself. */

@@ -113,6 +113,13 @@ int onn_trainer_greedy_decode(onn_trainer* trainer, const float* encoder_ids, fl
 int onn_trainer_greedy_decode_cached(onn_trainer* trainer, const float* encoder_ids, float* decoded_ids, int start_id, int end_id);
 int onn_trainer_get_layer_output(onn_trainer* trainer, int layer, float* host_output, int64_t count);
 int onn_trainer_synchronize(onn_trainer* trainer);
+/* After a data-parallel step with the sharded update the all-gathers that bring the other ranks' updated parameters
+ * are still running: the next step's forward pass waits for them layer by layer, and every entry point of this header
+ * that reads or writes parameters waits for all of them first (onn_trainer_synchronize included).  A caller that
+ * launches its OWN work on onn_trainer_stream() against the parameter arena, or that times steps with events on that
+ * stream, calls this first: it makes the stream wait for the gathers in flight (no host synchronisation).
+ * ONN_B200_DP_DEFER_GATHER=0 makes every step wait for its own gathers instead. */
+int onn_trainer_parameters_ready(onn_trainer* trainer);
 /* The cudaStream_t every kernel of this trainer is launched on (for event timing by the caller). */
 void* onn_trainer_stream(onn_trainer* trainer);
 

@@ -15,6 +15,7 @@ struct onn_dp_comm
     cudaStream_t stream = nullptr;
     cudaEvent_t ready = nullptr;      // compute -> comm
     cudaEvent_t done = nullptr;       // comm -> compute
+    cudaEvent_t marks[ONN_DP_MARKS] = {};   // comm -> compute, one per position a caller wants to wait for separately (made on first use)
     int world = 1, rank = 0;
     bool failed = false;              // a collective failed: the ranks no longer agree on what comes next, so nothing more is enqueued
 };
@@ -122,6 +123,21 @@ extern "C" int onn_dp_wait(onn_dp_comm* c, void* stream)
     return ONN_OK;
 }
 
+extern "C" int onn_dp_mark(onn_dp_comm* c, int slot)
+{
+    ONN_CHECK_ARG(c && slot >= 0 && slot < ONN_DP_MARKS);
+    if(c->failed) return ONN_ERR_NCCL;
+    if(!c->marks[slot] && cudaEventCreateWithFlags(&c->marks[slot], cudaEventDisableTiming) != cudaSuccess) return ONN_ERR_CUDA;
+    return cudaEventRecord(c->marks[slot], c->stream) == cudaSuccess ? ONN_OK : ONN_ERR_CUDA;
+}
+
+extern "C" int onn_dp_wait_mark(onn_dp_comm* c, int slot, void* stream)
+{
+    ONN_CHECK_ARG(c && slot >= 0 && slot < ONN_DP_MARKS && c->marks[slot]);
+    if(c->failed) return ONN_ERR_NCCL;
+    return cudaStreamWaitEvent((cudaStream_t)stream, c->marks[slot], 0) == cudaSuccess ? ONN_OK : ONN_ERR_CUDA;
+}
+
 extern "C" int onn_dp_mark_failed(onn_dp_comm* c)
 {
     ONN_CHECK_ARG(c);
@@ -136,6 +152,7 @@ extern "C" int onn_dp_finalize(onn_dp_comm* c)
     if(c->comm) ncclCommDestroy(c->comm);
     if(c->ready) cudaEventDestroy(c->ready);
     if(c->done) cudaEventDestroy(c->done);
+    for(cudaEvent_t mark : c->marks) if(mark) cudaEventDestroy(mark);
     if(c->stream) cudaStreamDestroy(c->stream);
     delete c;
     return ONN_OK;

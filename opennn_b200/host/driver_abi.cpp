@@ -58,6 +58,14 @@ struct onn_trainer
     bool sharded_step = false;            // this step reduce-scatters (set per step: update and world > 1)
     TensorCuda own_gradient, own_m, own_v;
 
+    // The all-gathers of a sharded update are not waited for at the end of the step: each bucket's gather is marked on
+    // the communication stream, and whoever reads parameters next waits for the marks it needs -- the next step's first
+    // forward pass layer by layer (so the gathers run under it), every other entry point for all of them.
+    bool defer_gather = true;             // ONN_B200_DP_DEFER_GATHER=0: wait at the end of the step
+    bool gather_in_flight = false;
+    Index gather_buckets = 0;             // buckets of the update whose gathers are in flight
+    Index awaited_bucket = -1;            // highest bucket the compute stream already waits for
+
     // SMs left to NCCL while a bucket is in flight: the persistent kernels of the next carve_launches launches (rounded
     // up to a layer) occupy 148 - carve_sms SMs, so NCCL's CTAs start at once instead of at a kernel boundary
     int carve_sms = 0, carve_launches = 4;
@@ -142,6 +150,9 @@ static void check_device_status(onn_trainer* t)
 
 extern "C" const char* onn_trainer_last_error(void) { return g_last_error.c_str(); }
 
+static void await_parameters(onn_trainer* t);
+static void settle_parameters(onn_trainer* t);
+
 extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
                                   int64_t input_sequence_length, int64_t decoder_sequence_length,
                                   int64_t input_vocabulary_size, int64_t output_vocabulary_size,
@@ -185,6 +196,7 @@ extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
         t->status_word.resize(8);
         t->adam->set_skip_word(reinterpret_cast<const uint32_t*>(t->status_word.data));
         t->sharded_update = environment_int("ONN_B200_DP_SHARDED", 1) != 0;
+        t->defer_gather = environment_int("ONN_B200_DP_DEFER_GATHER", 1) != 0;
         t->carve_sms = environment_int("ONN_B200_DP_CARVE_SMS", 0);
         t->carve_launches = environment_int("ONN_B200_DP_CARVE_LAUNCHES", 4);
         t->bucket_floats = std::max(1024, environment_int("ONN_B200_DP_BUCKET_FLOATS", 16 << 20));
@@ -199,7 +211,13 @@ extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
     });
 }
 
-extern "C" void onn_trainer_destroy(onn_trainer* trainer) { delete trainer; }
+extern "C" void onn_trainer_destroy(onn_trainer* trainer)
+{
+    // no collective may still be writing the parameter arena when it is freed (the communicator is the caller's and may
+    // be gone already, so this does not go through it)
+    if(trainer && trainer->gather_in_flight) cudaDeviceSynchronize();
+    delete trainer;
+}
 
 extern "C" int64_t onn_trainer_parameters_number(const onn_trainer* t) { return t ? t->network->get_parameters_number() : 0; }
 extern "C" int onn_trainer_layers_number(const onn_trainer* t) { return t ? int(t->network->get_layers_number()) : 0; }
@@ -221,6 +239,7 @@ extern "C" int onn_trainer_set_parameters(onn_trainer* t, const float* host_para
     if(!t || !host_parameters) return ONN_ERR_INVALID_ARGUMENT;
     return guarded([&]
     {
+        settle_parameters(t);
         vector<type>& parameters = t->network->get_parameters();
         std::memcpy(parameters.data(), host_parameters, parameters.size() * sizeof(type));
         t->network->copy_parameters_device();
@@ -232,7 +251,7 @@ extern "C" int onn_trainer_get_parameters(onn_trainer* t, float* host_parameters
     if(!t || !host_parameters) return ONN_ERR_INVALID_ARGUMENT;
     return guarded([&]
     {
-        check_cuda(cudaStreamSynchronize(t->stream), "synchronize");
+        settle_parameters(t);
         t->network->copy_parameters_host();
         const vector<type>& parameters = t->network->get_parameters();
         std::memcpy(host_parameters, parameters.data(), parameters.size() * sizeof(type));
@@ -269,6 +288,9 @@ extern "C" int onn_trainer_set_dp(onn_trainer* t, onn_dp_comm* comm, int world)
     if(!t || world < 1 || (world > 1 && !comm)) return ONN_ERR_INVALID_ARGUMENT;
     return guarded([&]
     {
+        // gathers of the old communicator and layout: the old communicator is the caller's and may be gone already
+        if(t->gather_in_flight) check_cuda(cudaDeviceSynchronize(), "set_dp");
+        t->gather_in_flight = false;
         t->comm = world > 1 ? comm : nullptr;
         t->world = world;
         t->rank = t->comm ? onn_dp_rank(comm) : 0;
@@ -313,6 +335,41 @@ extern "C" int onn_trainer_set_dp_options(onn_trainer* t, int sharded_update, in
     t->carve_launches = carve_launches;
     if(bucket_floats > 0) t->bucket_floats = bucket_floats;
     return ONN_OK;
+}
+
+static int mark_of_bucket(Index bucket) { return int(std::min<Index>(bucket, ONN_DP_MARKS - 1)); }
+
+// The compute stream waits for every parameter all-gather still in flight.
+static void await_parameters(onn_trainer* t)
+{
+    if(!t->gather_in_flight) return;
+    t->gather_in_flight = false;
+    if(t->awaited_bucket < t->gather_buckets - 1)
+        check_onn(onn_dp_wait_mark(t->comm, mark_of_bucket(t->gather_buckets - 1), t->stream), "parameter wait");
+    t->awaited_bucket = t->gather_buckets - 1;
+}
+
+// ... and for a host-side reader or writer of the parameters: nothing of the update is in flight any more
+static void settle_parameters(onn_trainer* t)
+{
+    await_parameters(t);
+    check_cuda(cudaStreamSynchronize(t->stream), "synchronize");
+}
+
+// before_layer_hook of the first forward pass after a sharded update: wait for the bucket that holds the END of this
+// layer's parameters (the communication stream runs in order, so the earlier buckets are then complete too)
+static void await_layer_parameters(void* context, Index layer)
+{
+    onn_trainer* t = static_cast<onn_trainer*>(context);
+    if(!t->gather_in_flight) return;
+    const Index low = t->layer_offsets[size_t(layer)];
+    const Index high = size_t(layer) + 1 < t->layer_offsets.size() ? t->layer_offsets[size_t(layer) + 1] : t->network->get_parameters_number();
+    if(high <= low) return;
+    const Index needed = std::min((high - 1) / t->shard_bucket, t->gather_buckets - 1);
+    if(needed <= t->awaited_bucket) return;
+    check_onn(onn_dp_wait_mark(t->comm, mark_of_bucket(needed), t->stream), "parameter wait");
+    t->awaited_bucket = needed;
+    if(needed == t->gather_buckets - 1) t->gather_in_flight = false;
 }
 
 static void narrow_for_exchange(onn_trainer* t)
@@ -396,8 +453,12 @@ static void sharded_update(onn_trainer* t)
                                    t->stream), "sharded Adam");
         // the all-gather of this bucket waits for this bucket's update only and overlaps the next bucket's
         check_onn(onn_dp_all_gather(t->comm, own_parameters, parameters + low, part, t->stream), "parameter all-gather");
+        check_onn(onn_dp_mark(t->comm, mark_of_bucket(k)), "parameter mark");
     }
-    check_onn(onn_dp_wait(t->comm, t->stream), "parameter wait");
+    t->gather_in_flight = true;
+    t->gather_buckets = buckets;
+    t->awaited_bucket = -1;
+    if(!t->defer_gather) await_parameters(t);
 }
 
 // Replays (capturing it first if need be) the forward pass, loss and back-propagation of micro-batch number `chunk`.
@@ -475,6 +536,7 @@ struct ExchangeScope
     ~ExchangeScope()
     {
         t->loss->gradient_ready_hook = nullptr;
+        t->network->before_layer_hook = nullptr;
         widen_after_exchange(t, true);
     }
     onn_trainer* t;
@@ -517,11 +579,20 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
     whole.samples_number = batch;
     whole.target = TensorViewCuda(const_cast<float*>(targets), {batch, S_dec});
     t->loss->calculate_active_tokens(whole, *t->back);
+    // The count is first read by the loss kernel, so the compute stream waits for it only there: the communication
+    // stream may still be busy with the parameter gathers of the previous step, which the forward pass overlaps.
+    bool count_pending = false;
     if(t->comm)
     {
         check_onn(onn_dp_allreduce(t->comm, t->back->active_count.data, 1, t->stream), "active-token all-reduce");
-        check_onn(onn_dp_wait(t->comm, t->stream), "active-token wait");
+        count_pending = true;
     }
+    const auto await_count = [&]
+    {
+        if(!count_pending) return;
+        count_pending = false;
+        check_onn(onn_dp_wait(t->comm, t->stream), "active-token wait");
+    };
 
     const Index chunks = batch / t->micro_batch;
     for(Index chunk = 0; chunk < chunks; chunk++)
@@ -535,9 +606,23 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
 
         const bool last = chunk == chunks - 1;
         const bool hands_out_gradients = t->comm && last;     // bucketed all-reduces are issued from inside back-propagation
-        if(t->graphs_enabled && t->eager_steps > 0 && !hands_out_gradients && replay_micro_batch(t, micro, chunk)) continue;
+        if(t->graphs_enabled && t->eager_steps > 0 && !hands_out_gradients)
+        {
+            // a replayed micro-batch cannot wait layer by layer: everything it reads must be there before it starts
+            await_parameters(t);
+            await_count();
+            if(replay_micro_batch(t, micro, chunk)) continue;
+        }
 
+        if(t->gather_in_flight)
+        {
+            t->network->before_layer_hook = await_layer_parameters;
+            t->network->before_layer_context = t;
+        }
         t->network->forward_propagate(micro.get_inputs_device(), *t->forward, true);
+        t->network->before_layer_hook = nullptr;
+        await_parameters(t);                                     // whatever no layer asked for (padding at the end of the arena)
+        await_count();
 
         if(hands_out_gradients)
         {
@@ -686,6 +771,7 @@ extern "C" int onn_trainer_forward(onn_trainer* t, const float* decoder_ids, con
     return guarded([&]
     {
         Device::instance().set_compute_stream(t->stream);
+        await_parameters(t);
         BatchCuda micro;
         micro.samples_number = t->micro_batch;
         micro.decoder = TensorViewCuda(const_cast<float*>(decoder_ids), {t->micro_batch, t->decoder_sequence_length});
@@ -700,6 +786,7 @@ extern "C" int onn_trainer_greedy_decode(onn_trainer* t, const float* encoder_id
     return guarded([&]
     {
         Device::instance().set_compute_stream(t->stream);
+        await_parameters(t);
         const Index B = t->micro_batch, S_in = t->input_sequence_length, S_dec = t->decoder_sequence_length;
         if(t->staged_encoder.size() < B * S_in) t->staged_encoder.resize(B * S_in);
         if(t->staged_decoder.size() < B * S_dec) { t->staged_decoder.resize(B * S_dec); t->staged_targets.resize(B * S_dec); }
@@ -798,6 +885,7 @@ extern "C" int onn_trainer_greedy_decode_cached(onn_trainer* t, const float* enc
     return guarded([&]
     {
         Device::instance().set_compute_stream(t->stream);
+        await_parameters(t);
         const Index B = t->micro_batch, S_in = t->input_sequence_length, S_dec = t->decoder_sequence_length;
         if(t->staged_encoder.size() < B * S_in) t->staged_encoder.resize(B * S_in);
         if(t->decode_ids.size() == 0) { t->decode_ids.resize(B * S_dec); t->decode_finished.resize(B); }
@@ -864,7 +952,13 @@ extern "C" int onn_trainer_get_layer_output(onn_trainer* t, int layer, float* ho
 extern "C" int onn_trainer_synchronize(onn_trainer* t)
 {
     if(!t) return ONN_ERR_INVALID_ARGUMENT;
-    return guarded([&] { check_cuda(cudaStreamSynchronize(t->stream), "synchronize"); check_device_status(t); });
+    return guarded([&] { settle_parameters(t); check_device_status(t); });
+}
+
+extern "C" int onn_trainer_parameters_ready(onn_trainer* t)
+{
+    if(!t) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&] { await_parameters(t); });
 }
 
 extern "C" void* onn_trainer_stream(onn_trainer* t) { return t ? t->stream : nullptr; }

@@ -100,6 +100,7 @@ void NeuralNetwork::forward_propagate(const vector<TensorViewCuda>& input_views,
                 state->inputs[port] = input_views[external];
             }
         }
+        if(before_layer_hook) before_layer_hook(before_layer_context, Index(i));
         layers[i]->forward_propagate(state, is_training);
     }
 }

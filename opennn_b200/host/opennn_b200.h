@@ -482,6 +482,12 @@ public:
     // 1 for every layer whose output depends on external input number `external` (1 = decoder ids, 2 = encoder ids)
     vector<char> layers_depending_on_input(Index external) const;
 
+    // Called before each layer's forward pass (no counterpart in OpenNN): the data-parallel trainer makes the compute
+    // stream wait here for the all-gather that brings this layer's updated parameters, so that the gathers of the later
+    // layers run under the forward pass of the earlier ones.
+    void (*before_layer_hook)(void* context, Index layer) = nullptr;
+    void* before_layer_context = nullptr;
+
 protected:
     vector<unique_ptr<Layer>> layers;
     vector<vector<Index>> layer_input_indices;
