@@ -120,6 +120,13 @@ int onn_trainer_synchronize(onn_trainer* trainer);
  * stream, calls this first: it makes the stream wait for the gathers in flight (no host synchronisation).
  * ONN_B200_DP_DEFER_GATHER=0 makes every step wait for its own gathers instead. */
 int onn_trainer_parameters_ready(onn_trainer* trainer);
+/* Phase tracing: with it on (or ONN_B200_TRACE_PHASES=1) a step records events on the trainer's stream at its start,
+ * after the forward pass of its last micro-batch, after that micro-batch's back-propagation and after the update;
+ * onn_trainer_last_step_phases synchronises the stream and returns the three intervals in milliseconds
+ * {start -> forward done (earlier micro-batches included), back-propagation, update}.  The last micro-batch must
+ * have run eagerly (a data-parallel rank's always does; otherwise onn_trainer_set_graph_capture(t, 0)). */
+int onn_trainer_trace_phases(onn_trainer* trainer, int enabled);
+int onn_trainer_last_step_phases(onn_trainer* trainer, float* milliseconds3);
 /* The cudaStream_t every kernel of this trainer is launched on (for event timing by the caller). */
 void* onn_trainer_stream(onn_trainer* trainer);
 

@@ -66,6 +66,12 @@ struct onn_trainer
     Index gather_buckets = 0;             // buckets of the update whose gathers are in flight
     Index awaited_bucket = -1;            // highest bucket the compute stream already waits for
 
+    // Phase tracing (ONN_B200_TRACE_PHASES=1 or onn_trainer_trace_phases): events on the compute stream at the start
+    // of a step, after the last micro-batch's forward pass, after its back-propagation and after the update
+    bool trace_phases = false;
+    cudaEvent_t phase_events[4] = {};
+    bool phases_recorded = false;
+
     // SMs left to NCCL while a bucket is in flight: the persistent kernels of the next carve_launches launches (rounded
     // up to a layer) occupy 148 - carve_sms SMs, so NCCL's CTAs start at once instead of at a kernel boundary
     int carve_sms = 0, carve_launches = 4;
@@ -116,6 +122,7 @@ struct onn_trainer
             if(b.copied) cudaEventDestroy(b.copied);
             if(b.consumed) cudaEventDestroy(b.consumed);
         }
+        for(cudaEvent_t e : phase_events) if(e) cudaEventDestroy(e);
         if(copy_stream) cudaStreamDestroy(copy_stream);
         if(pinned_scalars) cudaFreeHost(pinned_scalars);
         if(pinned_status) cudaFreeHost(const_cast<uint32_t*>(pinned_status));
@@ -197,6 +204,7 @@ extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
         t->adam->set_skip_word(reinterpret_cast<const uint32_t*>(t->status_word.data));
         t->sharded_update = environment_int("ONN_B200_DP_SHARDED", 1) != 0;
         t->defer_gather = environment_int("ONN_B200_DP_DEFER_GATHER", 1) != 0;
+        t->trace_phases = environment_int("ONN_B200_TRACE_PHASES", 0) != 0;
         t->carve_sms = environment_int("ONN_B200_DP_CARVE_SMS", 0);
         t->carve_launches = environment_int("ONN_B200_DP_CARVE_LAUNCHES", 4);
         t->bucket_floats = std::max(1024, environment_int("ONN_B200_DP_BUCKET_FLOATS", 16 << 20));
@@ -335,6 +343,15 @@ extern "C" int onn_trainer_set_dp_options(onn_trainer* t, int sharded_update, in
     t->carve_launches = carve_launches;
     if(bucket_floats > 0) t->bucket_floats = bucket_floats;
     return ONN_OK;
+}
+
+static void record_phase(onn_trainer* t, int phase)
+{
+    if(!t->trace_phases) return;
+    if(!t->phase_events[phase]) check_cuda(cudaEventCreate(&t->phase_events[phase]), "phase event");
+    check_cuda(cudaEventRecord(t->phase_events[phase], t->stream), "phase event");
+    if(phase == 0) t->phases_recorded = false;
+    if(phase == 3) t->phases_recorded = true;
 }
 
 static int mark_of_bucket(Index bucket) { return int(std::min<Index>(bucket, ONN_DP_MARKS - 1)); }
@@ -571,6 +588,7 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
     const Index S_dec = t->decoder_sequence_length, S_in = t->input_sequence_length;
     TensorCuda& gradients = t->back->neural_network.gradients;
 
+    record_phase(t, 0);
     if(t->gradients_dirty) gradients.fill(0);                // adaptive_moment_estimation.cpp:699 (Adam leaves them zero otherwise)
     t->gradients_dirty = true;
 
@@ -623,6 +641,7 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
         t->network->before_layer_hook = nullptr;
         await_parameters(t);                                     // whatever no layer asked for (padding at the end of the arena)
         await_count();
+        if(last) record_phase(t, 1);
 
         if(hands_out_gradients)
         {
@@ -635,6 +654,7 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
         if(hands_out_gradients) gradient_ready(t, -1);           // whatever the layer walk left (it ends at the first trainable layer)
         t->loss->gradient_ready_hook = nullptr;
         widen_after_exchange(t, true);
+        if(last) record_phase(t, 2);
     }
     t->eager_steps++;
 
@@ -662,6 +682,7 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
             check_onn(onn_grad_sqnorm(gradients.data, gradients.size(), t->optimization->square_norm.data, t->optimization->norm_workspace.data,
                                       t->stream), "gradient norm");
     }
+    record_phase(t, 3);
     check_cuda(cudaMemcpyAsync(const_cast<uint32_t*>(t->pinned_status), status_word, sizeof(uint32_t), cudaMemcpyDeviceToHost, t->stream), "status readback");
 
     if(statistics)
@@ -953,6 +974,26 @@ extern "C" int onn_trainer_synchronize(onn_trainer* t)
 {
     if(!t) return ONN_ERR_INVALID_ARGUMENT;
     return guarded([&] { settle_parameters(t); check_device_status(t); });
+}
+
+extern "C" int onn_trainer_trace_phases(onn_trainer* t, int enabled)
+{
+    if(!t) return ONN_ERR_INVALID_ARGUMENT;
+    t->trace_phases = enabled != 0;
+    t->phases_recorded = false;
+    return ONN_OK;
+}
+
+extern "C" int onn_trainer_last_step_phases(onn_trainer* t, float* milliseconds3)
+{
+    if(!t || !milliseconds3) return ONN_ERR_INVALID_ARGUMENT;
+    return guarded([&]
+    {
+        if(!t->trace_phases || !t->phases_recorded) throw std::runtime_error("last_step_phases: no traced step (the last micro-batch must have run eagerly)");
+        check_cuda(cudaStreamSynchronize(t->stream), "synchronize");
+        for(int k = 0; k < 3; k++)
+            check_cuda(cudaEventElapsedTime(milliseconds3 + k, t->phase_events[k], t->phase_events[k + 1]), "phase times");
+    });
 }
 
 extern "C" int onn_trainer_parameters_ready(onn_trainer* t)
