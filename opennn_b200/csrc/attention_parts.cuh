@@ -39,6 +39,7 @@ struct AttnParams
     float* row_inv_out;                                   // forward: 1 / sum of the row's tf32-rounded exponentials
     float* delta_out;                                     // backward: rowsum(dO * O)
     int skip_score_gradient_store;                        // backward: dS stays on the SM (nobody reads it from HBM)
+    unsigned int* work_counter;                           // items in the order the CTAs ask for them (work_ring.cuh); null: a fixed share per CTA
 };
 
 #define ONN_LIST8(M, v, o) M(v[(o)]), M(v[(o) + 1]), M(v[(o) + 2]), M(v[(o) + 3]), M(v[(o) + 4]), M(v[(o) + 5]), M(v[(o) + 6]), M(v[(o) + 7])

@@ -31,6 +31,7 @@
 #include "common.cuh"
 #include "launch_counter.h"
 #include "tcgen05.cuh"
+#include "work_ring.cuh"
 
 namespace onn
 {
@@ -78,6 +79,8 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint64_t* p_in = bars + 8;                              // [8 warps][4 blocks]: attention-weight blocks landed (backward)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 4 * kSoftmaxWarps);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    WorkRing* ring = reinterpret_cast<WorkRing*>(bars + 8 + 4 * kSoftmaxWarps + 1);   // producer -> MMA issuer and softmax warps
+    static_assert((8 + 4 * kSoftmaxWarps + 1) * 8 + sizeof(WorkRing) <= 512, "barriers beyond their 512 bytes");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -88,6 +91,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         mbar_init(smem_u32(s_full), 1); mbar_init(smem_u32(o_full), 1);
         mbar_init(smem_u32(p_ready), kSoftmaxWarps); mbar_init(smem_u32(o_free), kSoftmaxWarps);
         for(int i = 0; i < 4 * kSoftmaxWarps; i++) mbar_init(smem_u32(p_in + i), 1);
+        work_ring_init(ring, 1 + kSoftmaxWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -101,6 +105,10 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    // the first item is asked for before the wait for the preceding kernel: the counter is this launch's alone
+    const WorkSource source = { p.work_counter, (uint32_t)p.items, gridDim.x };
+    uint32_t first_work = kNoWork;
+    if(threadIdx.x == 0) first_work = source.fetch(0, blockIdx.x, gridDim.x);
     pdl_wait();                                               // set-up done; global memory only from here on
 
     if(warp == 0)
@@ -108,9 +116,15 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // ---------------- TMA producer ----------------
         if(lane == 0)
         {
+            // The producer is also the scheduler.  It asks for item t + 1 before it copies item t (the counter's round
+            // trip runs under the copies) and tells the other roles once those copies are on their way, so nobody holds
+            // more than one item beyond the one it is working on.
             uint32_t ph = 0;
-            for(long long w = blockIdx.x; w < p.items; w += gridDim.x, ph ^= 1)
+            uint32_t w = first_work;
+            bool told = work_ring_publish(ring, 0, w, abort_flag, 20);
+            for(uint32_t turn = 0; told && w != kNoWork; turn++, ph ^= 1)
             {
+                const uint32_t ahead = source.fetch(turn + 1, blockIdx.x, gridDim.x);
                 const AttnItem it = decode_item(p, w);
                 // forward: Q and K may be replaced once the previous item's score MMAs have read them; backward: V shares
                 // its buffer with the previous item's K, which the previous item's second group of MMAs reads
@@ -127,6 +141,8 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if(!mbar_wait(smem_u32(BACKWARD ? qk_empty : v_empty), BACKWARD ? ph : ph ^ 1, abort_flag, 22)) break;
                 mbar_arrive_expect_tx(smem_u32(v_full), V_BYTES);
                 tma_load_5d(smem_u32(v_smem), &map_v, smem_u32(v_full), 0, 0, it.h * KB, 0, it.b);
+                w = ahead;
+                told = work_ring_publish(ring, turn + 1, w, abort_flag, 20);
             }
             if(*abort_flag)
             {
@@ -142,7 +158,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         {
             const uint32_t idesc_s = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)((p.key_blocks * 32) >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
             uint32_t ph = 0;
-            for(long long w = blockIdx.x; w < p.items; w += gridDim.x, ph ^= 1)
+            for(uint32_t turn = 0; work_ring_take(ring, turn, abort_flag, 24) != kNoWork; turn++, ph ^= 1)
             {
                 // scores: the previous item's context MMAs were issued before these and the tensor pipe runs in order,
                 // and every softmax thread had its scores in registers before those MMAs were released (p_ready)
@@ -187,9 +203,10 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if constexpr(BACKWARD)
         {
             // the first item's four blocks of attention weights
-            if(lane == 0 && (long long)blockIdx.x < p.items)
+            const uint32_t first_item = lane == 0 ? work_ring_peek(ring, 0, abort_flag, 31) : kNoWork;
+            if(lane == 0 && first_item != kNoWork)
             {
-                const AttnItem first = decode_item(p, blockIdx.x);
+                const AttnItem first = decode_item(p, first_item);
                 const int first_row0 = first.q_tile * kQRows + quadrant * 32;
                 for(int jb = 0; jb < 4; jb++)
                     if(first_row0 < p.Sq && half * 4 + jb < p.key_blocks)
@@ -201,8 +218,14 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             __syncwarp();
         }
         uint32_t ph = 0;
-        for(long long w = blockIdx.x; w < p.items; w += gridDim.x, ph ^= 1)
+        // The item of a turn is looked up in the middle of the turn before (where the warp has a moment: its part of the
+        // critical path is over) and only handed back at the top of its own turn.
+        uint32_t w = 0, w_next = kNoWork;
+        if(lane == 0) w = work_ring_peek(ring, 0, abort_flag, 32);
+        w = __shfl_sync(0xffffffffu, w, 0);
+        for(uint32_t turn = 0; w != kNoWork; turn++, ph ^= 1, w = w_next)
         {
+            if(lane == 0) work_ring_release(ring, turn, w);
             const AttnItem it = decode_item(p, w);
             const int row0 = it.q_tile * kQRows + quadrant * 32;      // first query row of this warp
             const int q_row = row0 + lane;
@@ -303,11 +326,12 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if(lane == 0) mbar_arrive(smem_u32(p_ready));    // the dQ MMAs may start
 
                 // the next item's weights take ring blocks 0..2 as soon as this item's copies have left them (block 3 stages dQ first)
-                const long long w_next = w + gridDim.x;
+                if(lane == 0) w_next = work_ring_peek(ring, turn + 1, abort_flag, 33);
+                w_next = __shfl_sync(0xffffffffu, w_next, 0);
                 AttnItem next = it;
                 int next_row0 = 0;
                 bool next_live = false;
-                if(w_next < p.items)
+                if(w_next != kNoWork)
                 {
                     next = decode_item(p, w_next);
                     next_row0 = next.q_tile * kQRows + quadrant * 32;
@@ -458,6 +482,8 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tcgen05_fence_before();
                 __syncwarp();
                 if(lane == 0) mbar_arrive(smem_u32(p_ready));    // the context MMAs may start
+                if(lane == 0) w_next = work_ring_peek(ring, turn + 1, abort_flag, 33);
+                w_next = __shfl_sync(0xffffffffu, w_next, 0);
 
                 exchange[half * kQRows + r_local] = total;
                 pair_barrier(quadrant);
@@ -561,8 +587,12 @@ static int launch_attention_core(const CUtensorMap& a, const CUtensorMap& b1, co
 {
     static PerDeviceBytes configured;                        // per instantiation and per device
     if(!ensure_dynamic_smem(attention_core_kernel<kAttnHeadSize, BACKWARD>, configured, kAttnSmem)) return ONN_ERR_CUDA;
+    if(p.items >= (1LL << 31)) return ONN_ERR_UNSUPPORTED;
     const int grid = (int)(p.items < sm_limit() ? p.items : sm_limit());
-    const cudaError_t launched = launch_overlapped(attention_core_kernel<kAttnHeadSize, BACKWARD>, dim3(grid), dim3(kAttnThreads), kAttnSmem, stream, a, b1, b2, w, o, in, p);
+    AttnParams launch_params = p;
+    launch_params.work_counter = next_work_counter();       // items in the order the CTAs ask for them (null: fixed shares)
+    const cudaError_t launched = launch_overlapped(attention_core_kernel<kAttnHeadSize, BACKWARD>, dim3(grid), dim3(kAttnThreads), kAttnSmem, stream, a, b1, b2, w, o, in,
+                                                   launch_params);
     count_launch();
     return launched == cudaSuccess ? launch_status() : ONN_ERR_CUDA;
 }

@@ -21,6 +21,16 @@ constexpr int kSmCount = 148;   // B200: 2 dies x 74 SMs; grids are sized in mul
 // gradient bucket is being reduced.  Read on the host at launch time, so it takes effect in stream order.
 int sm_limit();
 
+// Work-item counters of the persistent kernels that can hand out their work items in the order the CTAs ask for them: a
+// CTA that gets its SM late -- another kernel, e.g. one of NCCL's, holds it -- then takes fewer items instead of making
+// the whole launch wait for a fixed share.  next_work_counter() returns the device address, on the current device, of a
+// counter at zero, taken round robin from a pool; the kernel that uses it leaves it at zero (work_ring.cuh), so it is
+// ready again long before the sequence comes back to it.  Null -- fixed shares -- unless the mode is on
+// (onn_set_dynamic_work; the data-parallel trainer turns it on).  reset_work_counters(): after a kernel gave up on a
+// wait and left its counter behind.
+unsigned int* next_work_counter();
+void reset_work_counters();
+
 #define ONN_CHECK_ARG(cond) do { if(!(cond)) return ONN_ERR_INVALID_ARGUMENT; } while(0)
 
 inline int launch_status()

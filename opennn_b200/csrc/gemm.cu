@@ -23,6 +23,43 @@ static std::atomic<int> g_sm_limit{kSmCount};
 
 int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
 
+constexpr int kWorkCounters = 8192;
+static __device__ unsigned int g_work_counters[kWorkCounters];
+// -1: as the environment says (ONN_B200_DYNAMIC_WORK=1), else off; 0 / 1: set by onn_set_dynamic_work
+static std::atomic<int> g_dynamic_work{-1};
+
+static unsigned int* work_counters_of_current_device()
+{
+    static std::mutex mutex;
+    static unsigned int* resolved[kMaxDevices] = {};
+    int device = -1;
+    if(cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(mutex);
+    if(!resolved[device])
+    {
+        unsigned int* found = nullptr;
+        if(cudaGetSymbolAddress(reinterpret_cast<void**>(&found), g_work_counters) != cudaSuccess) return nullptr;
+        resolved[device] = found;
+    }
+    return resolved[device];
+}
+
+unsigned int* next_work_counter()
+{
+    static const int from_environment = []{ const char* e = std::getenv("ONN_B200_DYNAMIC_WORK"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
+    const int mode = g_dynamic_work.load(std::memory_order_relaxed);
+    const bool enabled = from_environment >= 0 ? from_environment == 1 : mode == 1;
+    if(!enabled) return nullptr;
+    static std::atomic<unsigned long long> sequence{0};
+    unsigned int* base = work_counters_of_current_device();
+    return base ? base + (sequence++ % kWorkCounters) : nullptr;
+}
+
+void reset_work_counters()
+{
+    if(unsigned int* base = work_counters_of_current_device()) cudaMemset(base, 0, sizeof(unsigned int) * kWorkCounters);
+}
+
 int gemm_mode() { return g_mode.load(std::memory_order_relaxed); }
 
 // ORs the status words of the kernels with bounded waits into one word, in stream order.
@@ -100,6 +137,12 @@ extern "C" int onn_set_sm_limit(int sms)
     return ONN_OK;
 }
 
+extern "C" int onn_set_dynamic_work(int enabled)
+{
+    const int previous = g_dynamic_work.exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed);
+    return previous == 1 ? 1 : 0;
+}
+
 extern "C" int onn_gemm_device_status(void)
 {
     const int gemm_status = gemm_tc_read_status();
@@ -107,8 +150,10 @@ extern "C" int onn_gemm_device_status(void)
     const int loss_status = ce3d_staged_read_status();
     const int long_status = attention_long_read_status();
     const int kv_status = attention_kv_grad_read_status();
-    return gemm_status != ONN_OK ? gemm_status : attention_status != ONN_OK ? attention_status : loss_status != ONN_OK ? loss_status :
-           long_status != ONN_OK ? long_status : kv_status;
+    const int status = gemm_status != ONN_OK ? gemm_status : attention_status != ONN_OK ? attention_status : loss_status != ONN_OK ? loss_status :
+                       long_status != ONN_OK ? long_status : kv_status;
+    if(status != ONN_OK) reset_work_counters();              // a launch that gave up did not leave its counters at zero
+    return status;
 }
 
 extern "C" int onn_device_status_gather(uint32_t* device_word, void* stream)

@@ -44,6 +44,7 @@
 #include "gemm_internal.h"
 #include "launch_counter.h"
 #include "tcgen05.cuh"
+#include "work_ring.cuh"
 
 namespace onn
 {
@@ -90,6 +91,11 @@ struct Params
     unsigned long long* tail_flags;                        // [tail tile][8 epilogue warps of a pair]
     unsigned int* tail_visits;                             // same shape: adders that have seen the token (0, 1, back to 0)
     int sm_cap;                                            // host side: SMs this launch may occupy (read once per launch: the plan and the grid must agree)
+    // two-CTA kernel only: work items are handed out through this counter in the order the CTA pairs ask for them (it
+    // wraps to zero with the last pair's question past the end: work_ring.cuh).  A pair that gets its SMs late -- another
+    // kernel holds them -- then simply takes fewer items instead of making the whole launch wait for a fixed share.
+    // Null: item number t of pair q is q + t * pairs.
+    unsigned int* work_counter;
 };
 
 // Instruction descriptor: D = fp32, A = B = tf32, M = 128, N = BN, majors as given.
@@ -538,6 +544,44 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
 }
 
+// arrival that publishes nothing (a reader handing a ring slot back): no release, so the issuing thread's own work in
+// flight -- for the MMA issuer a whole tile of tcgen05.mma -- is not waited for
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+
+// bounded wait whose acquire covers what the other CTA of the pair wrote before it arrived on the barrier
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int site)
+{
+    const unsigned long long start = clock64();
+    unsigned int spins = 0;
+    while(true)
+    {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if(done) return true;
+        if((++spins & 255u) == 0)
+        {
+            if(*abort_flag) return false;
+            if(clock64() - start > kWaitCycles)
+            {
+                atomicCAS(&g_status, 0u, site);
+                *abort_flag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+
+constexpr int kTileRing = 4;                                // work items the scheduler may be ahead of the slowest role
+
 // copies of a CTA pair: data lands in the executing CTA, completion bytes go to the barrier at
 // `bar` (a shared::cluster address, here always the leader's)
 __device__ __forceinline__ void tma2_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3)
@@ -595,10 +639,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint64_t* empty_bar = bars + STAGES2;                     // [STAGES2]  both CTAs
     uint64_t* acc_full_bar = bars + 2 * STAGES2;              // [2]        both CTAs
     uint64_t* acc_empty_bar = bars + 2 * STAGES2 + 2;         // [2]        used in the leader only
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
+    uint64_t* tile_full_bar = bars + 2 * STAGES2 + 4;         // [kTileRing] both CTAs: the scheduler has written the slot
+    uint64_t* tile_empty_bar = tile_full_bar + kTileRing;     // [kTileRing] used in the leader only: every role of both CTAs has read it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_empty_bar + kTileRing);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     // [r] = 1 + the number of stage fills the producer of CTA r has started, published to both CTAs when it stops (0 = not yet)
     volatile uint32_t* fills_started = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
+    volatile uint32_t* tile_ring = reinterpret_cast<volatile uint32_t*>(tmem_slot + 4);   // [kTileRing] work item numbers, kNoWork = the end
+    static_assert((2 * STAGES2 + 4 + 2 * kTileRing) * 8 + (4 + kTileRing) * 4 <= 256, "barriers and flags beyond their 256 bytes");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -609,6 +657,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     {
         for(int s = 0; s < STAGES2; s++) { mbar_init(smem_u32(full_bar + s), 1); mbar_init(smem_u32(empty_bar + s), 1); }
         for(int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full_bar + a), 1); mbar_init(smem_u32(acc_empty_bar + a), 2 * kEpilogueWarps); }
+        // readers of a slot: the MMA issuer and the peer's producer, and the epilogue warps of both CTAs
+        for(int r = 0; r < kTileRing; r++) { mbar_init(smem_u32(tile_full_bar + r), 1); mbar_init(smem_u32(tile_empty_bar + r), 2 + 2 * kEpilogueWarps); }
         *abort_flag = 0;
         fills_started[0] = 0; fills_started[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -625,7 +675,30 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    // the scheduler's first item is asked for before the wait for the preceding kernel: the counter is this launch's alone
+    const WorkSource source = { p.work_counter, (uint32_t)p.total_work, (uint32_t)pairs };
+    uint32_t first_work = kNoWork;
+    if(threadIdx.x == 0 && leader && p.work_counter) first_work = source.fetch(0, 0, 0);
     pdl_wait();                                               // set-up done; global memory only from here on
+
+    // Work items.  With a counter the leader's producer thread is the scheduler: it takes item numbers from the counter,
+    // one ahead of the item it loads, and publishes each in a ring slot of both CTAs; every other role reads the slots in
+    // order (take_item) and frees them on the leader's barrier.  Without one, item number `turn` of this pair is fixed.
+    const bool dynamic = p.work_counter != nullptr;
+    const auto take_item = [&](uint32_t turn, unsigned int site) -> uint32_t      // one thread per role
+    {
+        if(!dynamic)
+        {
+            const long long w = pair + (long long)turn * pairs;
+            return w < p.total_work ? (uint32_t)w : kNoWork;
+        }
+        const uint32_t slot = turn % kTileRing, parity = (turn / kTileRing) & 1u;
+        if(!mbar_wait_cluster(smem_u32(tile_full_bar + slot), parity, abort_flag, site)) return kNoWork;
+        const uint32_t w = tile_ring[slot];
+        // the slot goes back only once its value has arrived in a register (the branch needs it)
+        if(w != kNoWork - 1u) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(tile_empty_bar + slot), 0));
+        return w;
+    };
 
     if(warp == 0)
     {
@@ -634,8 +707,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         {
             uint32_t stage = 0, phase = 0, fills = 0;
             bool ok = true;
-            for(long long w = pair; ok && w < p.total_work; w += pairs)
+            const bool scheduler = dynamic && leader;
+            // the scheduler's next item: asked for one item ahead, so the counter's round trip runs under the copies
+            uint32_t ahead = first_work;
+            for(uint32_t turn = 0; ok; turn++)
             {
+                uint32_t w;
+                if(scheduler)
+                {
+                    const uint32_t slot = turn % kTileRing, parity = (turn / kTileRing) & 1u;
+                    if(!mbar_wait(smem_u32(tile_empty_bar + slot), parity ^ 1u, abort_flag, 16)) break;
+                    w = ahead;
+                    tile_ring[slot] = w;
+                    asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(map_to_cta(smem_u32(const_cast<uint32_t*>(tile_ring) + slot), 1)), "r"(w) : "memory");
+                    mbar_arrive_cluster(map_to_cta(smem_u32(tile_full_bar + slot), 0));
+                    mbar_arrive_cluster(map_to_cta(smem_u32(tile_full_bar + slot), 1));
+                    if(w == kNoWork) break;
+                    ahead = source.fetch(turn + 1, 0, 0);
+                }
+                else
+                {
+                    w = take_item(turn, 17);
+                    if(w == kNoWork) break;
+                }
                 const WorkItem it = decode_work(p, w);
                 const int m0 = it.m_blk * 256 + (int)rank * 128, n0 = it.n_blk * BN + (int)rank * 128;
                 for(int kb = 0; kb < it.k_blocks; kb++)
@@ -709,7 +803,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t stage = 0, phase = 0;
             long long local = 0;
             bool ok = true;
-            for(long long w = pair; ok && w < p.total_work; w += pairs, local++)
+            // The next item is looked up before the last k-block of this one, while MMAs are queued: at the top of the
+            // loop the look-up would sit between two tiles' MMAs.  (The scheduler publishes item t + 1 once the copies of
+            // item t are on their way, which needs no more stages than the MMAs before the last k-block have freed.)
+            uint32_t w = take_item(0, 18), w_next = kNoWork;
+            for(uint32_t turn = 0; ok && w != kNoWork; turn++, local++, w = w_next)
             {
                 const WorkItem it = decode_work(p, w);
                 const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
@@ -718,6 +816,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for(int kb = 0; kb < it.k_blocks; kb++)
                 {
+                    if(kb == it.k_blocks - 1) w_next = take_item(turn + 1, 18);
                     if(!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, 13)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE2_BYTES);
@@ -750,44 +849,49 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int flag_slot = (int)rank * 4 + quadrant;      // this warp's place among the 8 epilogue warps of a pair
 
         // Split tail tiles are ADDED into by two pairs, so C must hold zeros there first (unless the caller's values
-        // are to be kept).  Pair j zeroes tail tile j while its first tile's MMAs run -- each warp its own 32 rows,
-        // from one zero-filled staging block -- and publishes that under this launch's token; the adding warps look
-        // the token up before their first reduce (three waves later: the look-up never waits in practice, it is
-        // there so that the order is guaranteed rather than likely).
-        if(p.tail_tiles > 0 && !p.accumulate)
+        // are to be kept).  Whoever takes work item j < tail_tiles -- among the first items handed out -- zeroes tail
+        // tile j before it turns to the item itself: each warp its own 32 rows, from one zero-filled staging block, and
+        // publishes that under this launch's token; the adding warps look the token up before their first reduce
+        // (the tail items are the last of the order: the look-up never waits in practice, it is there so that the order
+        // is guaranteed rather than likely).
+        const auto zero_tail_tile = [&](long long j)
         {
             const long long whole = (long long)p.m_blocks * p.n_blocks - p.tail_tiles;
-            for(long long j = pair; j < p.tail_tiles; j += pairs)
-            {
-                Params q = p;                                   // decode the tile itself, not one of its halves
-                q.tail_tiles = 0; q.splits = 1; q.batch_inner = 1; q.k_per_split = p.K;
-                const WorkItem tile = decode_work(q, whole + j);
-                const long long rows0 = (long long)tile.m_blk * 256 + (long long)rank * 128 + quadrant * 32;
+            Params q = p;                                   // decode the tile itself, not one of its halves
+            q.tail_tiles = 0; q.splits = 1; q.batch_inner = 1; q.k_per_split = p.K;
+            const WorkItem tile = decode_work(q, whole + j);
+            const long long rows0 = (long long)tile.m_blk * 256 + (long long)rank * 128 + quadrant * 32;
+            if(lane == 0) bulk_wait_read_0();               // the staging block may still be the source of an earlier store
+            __syncwarp();
 #pragma unroll
-                for(int q4 = 0; q4 < 8; q4++)
-                {
-                    const uint32_t dst = warp_blocks + (uint32_t)lane * 128u + (uint32_t)(q4 << 4);
-                    asm volatile("st.shared.v4.f32 [%0], {%1, %1, %1, %1};" :: "r"(dst), "f"(0.f));
-                }
-                fence_async_shared();
-                __syncwarp();
-                if(lane == 0)
-                {
-                    if(rows0 < p.M)
-                        for(int c = 0; c < BN / 32; c++)
-                            if((long long)tile.n_blk * BN + c * 32 < p.N) tma_store_4d(&map_c, warp_blocks, tile.n_blk * BN + c * 32, (int)rows0, 0, 0);
-                    bulk_commit();
-                    bulk_wait_all();                            // the zeros are in memory, not just on their way
-                    asm volatile("fence.proxy.async;" ::: "memory");
-                    __threadfence();
-                    asm volatile("st.release.gpu.global.u64 [%0], %1;" :: "l"(p.tail_flags + j * 8 + flag_slot), "l"(p.tail_token) : "memory");
-                }
-                __syncwarp();
+            for(int q4 = 0; q4 < 8; q4++)
+            {
+                const uint32_t dst = warp_blocks + (uint32_t)lane * 128u + (uint32_t)(q4 << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %1, %1, %1};" :: "r"(dst), "f"(0.f));
             }
-        }
+            fence_async_shared();
+            __syncwarp();
+            if(lane == 0)
+            {
+                if(rows0 < p.M)
+                    for(int c = 0; c < BN / 32; c++)
+                        if((long long)tile.n_blk * BN + c * 32 < p.N) tma_store_4d(&map_c, warp_blocks, tile.n_blk * BN + c * 32, (int)rows0, 0, 0);
+                bulk_commit();
+                bulk_wait_all();                            // the zeros are in memory, not just on their way
+                asm volatile("fence.proxy.async;" ::: "memory");
+                __threadfence();
+                asm volatile("st.release.gpu.global.u64 [%0], %1;" :: "l"(p.tail_flags + j * 8 + flag_slot), "l"(p.tail_token) : "memory");
+            }
+            __syncwarp();
+        };
 
-        for(long long w = pair; w < p.total_work; w += pairs, local++)
+        for(uint32_t turn = 0; ; turn++, local++)
         {
+            uint32_t w = 0;
+            if(lane == 0) w = take_item(turn, 19);
+            w = __shfl_sync(0xffffffffu, w, 0);
+            if(w == kNoWork) break;
+            if(p.tail_tiles > 0 && !p.accumulate && w < (uint32_t)p.tail_tiles) zero_tail_tile(w);
             const WorkItem it = decode_work(p, w);
             const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
             const long long n0 = (long long)it.n_blk * BN;
@@ -982,6 +1086,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     p.relu_bits_out = g.relu_bits_out; p.relu_bits = g.relu_bits; p.relu_bits_ld = g.relu_bits_ld;
     p.colsum = g.colsum_out; p.colsum_stride_inner = g.colsum_stride_inner;
     p.tail_tiles = 0; p.tail_token = 0; p.tail_flags = nullptr; p.tail_visits = nullptr;
+    p.work_counter = nullptr;
     p.sm_cap = sm_limit();
     p.relu = g.relu; p.accumulate = (g.flags & ONN_ACCUMULATE) != 0;
     p.batch_inner = g.batch_inner; p.batch_outer = g.batch_outer;
@@ -1033,6 +1138,8 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
                 p.total_work = tiles + tail;
             }
         }
+        // work items through a counter (null: a fixed share per CTA pair)
+        if(p.total_work + pairs_cap < (1LL << 31)) p.work_counter = next_work_counter();
         if(g.a_major == 0) ok = make_map(&map_a, g.A, g.K, g.M, g.lda, parts, g.a_stride_part, 1, 0, BK, BM, false);
         else ok = make_wide_map(&map_a, g.A, g.M, g.K, g.lda, parts, g.a_stride_part, 1, 0, BM / 32, BK);
         if(g.b_major == 0) ok = ok && make_map(&map_b, g.B, g.K, g.N, g.ldb, parts, g.b_stride_part, 1, 0, BK, 128, false);

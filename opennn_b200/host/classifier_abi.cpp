@@ -174,6 +174,7 @@ extern "C" int onn_classifier_set_dp(onn_classifier* c, onn_dp_comm* comm, int w
     if(!c || world < 1 || (world > 1 && !comm)) return ONN_ERR_INVALID_ARGUMENT;
     c->comm = world > 1 ? comm : nullptr;
     c->world = world;
+    onn_set_dynamic_work(world > 1 ? 1 : 0);                 // NCCL's kernels will share the SMs with this step's
     return ONN_OK;
 }
 

@@ -301,6 +301,9 @@ extern "C" int onn_trainer_set_dp(onn_trainer* t, onn_dp_comm* comm, int world)
         t->gather_in_flight = false;
         t->comm = world > 1 ? comm : nullptr;
         t->world = world;
+        // NCCL's kernels hold SMs while back-propagation and the next forward pass run: CTAs that start late must not own
+        // a fixed share of a launch
+        onn_set_dynamic_work(world > 1 ? 1 : 0);
         t->rank = t->comm ? onn_dp_rank(comm) : 0;
         if(t->comm && onn_dp_world(comm) != world) throw std::runtime_error("set_dp: the communicator has another number of ranks");
         t->shard_total = 0;
