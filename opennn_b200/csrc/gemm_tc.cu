@@ -91,10 +91,10 @@ struct Params
     unsigned long long* tail_flags;                        // [tail tile][8 epilogue warps of a pair]
     unsigned int* tail_visits;                             // same shape: adders that have seen the token (0, 1, back to 0)
     int sm_cap;                                            // host side: SMs this launch may occupy (read once per launch: the plan and the grid must agree)
-    // two-CTA kernel only: work items are handed out through this counter in the order the CTA pairs ask for them (it
-    // wraps to zero with the last pair's question past the end: work_ring.cuh).  A pair that gets its SMs late -- another
-    // kernel holds them -- then simply takes fewer items instead of making the whole launch wait for a fixed share.
-    // Null: item number t of pair q is q + t * pairs.
+    // work items are handed out through this counter in the order the CTAs (CTA pairs) ask for them (it wraps to zero
+    // with the last one's question past the end: work_ring.cuh).  A CTA that gets its SM late -- another kernel holds
+    // it -- then simply takes fewer items instead of making the whole launch wait for a fixed share.
+    // Null: item number t of CTA (pair) q is q + t * grid.
     unsigned int* work_counter;
 };
 
@@ -329,6 +329,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* acc_empty_bar = bars + 2 * STAGES + 2;        // [2]       epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    WorkRing* ring = reinterpret_cast<WorkRing*>(bars + 2 * STAGES + 5);      // producer -> MMA issuer and epilogue warps
+    static_assert((2 * STAGES + 5) * 8 + sizeof(WorkRing) <= 256, "barriers beyond their 256 bytes");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -336,6 +338,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     {
         for(int s = 0; s < STAGES; s++) { mbar_init(smem_u32(full_bar + s), 1); mbar_init(smem_u32(empty_bar + s), 1); }
         for(int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full_bar + a), 1); mbar_init(smem_u32(acc_empty_bar + a), kEpilogueWarps); }
+        work_ring_init(ring, 1 + kEpilogueWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -349,6 +352,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    // the producer is also the scheduler (work_ring.cuh); its first item is asked for before the wait for the preceding
+    // kernel: the counter is this launch's alone
+    const WorkSource source = { p.work_counter, (uint32_t)p.total_work, gridDim.x };
+    uint32_t first_work = kNoWork;
+    if(threadIdx.x == 0) first_work = source.fetch(0, blockIdx.x, gridDim.x);
     pdl_wait();                                               // set-up done; global memory only from here on
 
     if(warp == 0)
@@ -361,8 +369,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for(int s = 0; s < STAGES; s++) armed[s] = 0;
             bool ok = true;
-            for(long long w = blockIdx.x; ok && w < p.total_work; w += gridDim.x)
+            uint32_t w = first_work;
+            ok = work_ring_publish(ring, 0, w, abort_flag, 5);
+            for(uint32_t turn = 0; ok && w != kNoWork; turn++)
             {
+                // item t + 1 is asked for before item t is copied and announced once those copies are on their way
+                const uint32_t ahead = source.fetch(turn + 1, blockIdx.x, gridDim.x);
                 const WorkItem it = decode_work(p, w);
                 const int m0 = it.m_blk * BM, n0 = it.n_blk * BN;
                 const int a_zi = p.a_batch_inner_on ? it.zi : 0, a_zo = p.a_batch_outer_on ? it.zo : 0;
@@ -400,6 +412,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tma_load_4d(b_dst, &map_b, bar, k0, n0, b_zi, b_zo);
                     if(++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
+                w = ahead;
+                if(ok) ok = work_ring_publish(ring, turn + 1, w, abort_flag, 5);
             }
             if(*abort_flag)
             {
@@ -424,7 +438,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t stage = 0, phase = 0;
             long long local = 0;
             bool ok = true;
-            for(long long w = blockIdx.x; ok && w < p.total_work; w += gridDim.x, local++)
+            // the next item is looked up before the last k-block of this one, while MMAs are queued
+            uint32_t w = work_ring_take(ring, 0, abort_flag, 6), w_next = kNoWork;
+            for(uint32_t turn = 0; ok && w != kNoWork; turn++, local++, w = w_next)
             {
                 const WorkItem it = decode_work(p, w);
                 const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
@@ -433,6 +449,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for(int kb = 0; kb < it.k_blocks; kb++)
                 {
+                    if(kb == it.k_blocks - 1) w_next = work_ring_take(ring, turn + 1, abort_flag, 6);
                     if(!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, 3)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
@@ -461,8 +478,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quadrant = warp & 3;                       // TMEM lanes this warp may read: 32*quadrant ..
         long long local = 0;
         unsigned int staged_chunks = 0;                      // blocks this warp has handed to the copy engine
-        for(long long w = blockIdx.x; w < p.total_work; w += gridDim.x, local++)
+        for(uint32_t turn = 0; ; turn++, local++)
         {
+            uint32_t w = 0;
+            if(lane == 0) w = work_ring_take(ring, turn, abort_flag, 7);
+            w = __shfl_sync(0xffffffffu, w, 0);
+            if(w == kNoWork) break;
             const WorkItem it = decode_work(p, w);
             const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
             const long long n0 = (long long)it.n_blk * BN;
@@ -1161,6 +1182,7 @@ int gemm_tc_launch(const onn_gemm_args& g, cudaStream_t stream)
     ok = ok && make_map(&map_c, g.C, g.N, g.M, g.ldc, g.batch_inner, g.c_stride_inner, g.batch_outer, g.c_stride_outer, 32, 32, false, false);
     if(!ok) return ONN_ERR_UNSUPPORTED;
 
+    if(p.total_work + 2 * kSmCount < (1LL << 31)) p.work_counter = next_work_counter();
     if(g.a_major == 0 && g.b_major == 0) return launch_majors<0, 0>(bn, map_a, map_b, map_c, p, stream);
     if(g.a_major == 0 && g.b_major == 1) return launch_majors<0, 1>(bn, map_a, map_b, map_c, p, stream);
     if(g.a_major == 1 && g.b_major == 1) return launch_majors<1, 1>(bn, map_a, map_b, map_c, p, stream);

@@ -130,22 +130,54 @@ embedding_bwd_kernel(const float* __restrict__ ids, const float* __restrict__ dY
 // registers: mean first, then the mean of centred squares (the reference's formulation).
 // gamma and beta are read per row (8 KiB, they stay in L1): keeping them in registers as well would cost 64 registers
 // per thread and halve the rows in flight per SM, which is what the memory system is fed by.
+// Rows of a row kernel, one warp per row.  Without a counter warp q of the grid takes rows q, q + warps, ...; with one
+// (common.cuh: next_work_counter) every warp asks for its next row while it works on the current one, so that CTAs which
+// find their SM taken by another kernel do not leave a fixed share of the rows waiting.  The counter wraps to zero when
+// the last warp has asked once past the end.
+struct RowWalk
+{
+    unsigned int* counter;
+    long long rows, warps, next_fixed;
+    uint32_t ahead;
+
+    __device__ __forceinline__ RowWalk(unsigned int* counter_in, long long rows_in, int lane) : counter(counter_in), rows(rows_in)
+    {
+        warps = (long long)gridDim.x * (blockDim.x >> 5);
+        next_fixed = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        ahead = 0;
+        if(counter && lane == 0) ahead = atomicInc(counter, (unsigned int)(rows + warps - 1));
+    }
+    // the warp's next row, or -1; all lanes call it
+    __device__ __forceinline__ long long next(int lane)
+    {
+        if(!counter)
+        {
+            const long long row = next_fixed;
+            next_fixed += warps;
+            return row < rows ? row : -1;
+        }
+        const uint32_t mine = __shfl_sync(0xffffffffu, ahead, 0);
+        if((long long)mine >= rows) return -1;
+        if(lane == 0) ahead = atomicInc(counter, (unsigned int)(rows + warps - 1));
+        return (long long)mine;
+    }
+};
+
 template <int VEC>
 __global__ void __launch_bounds__(kRowThreads, 4)
 layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
                      const float* __restrict__ gamma, const float* __restrict__ beta,
                      float* __restrict__ Y, float* __restrict__ sum_out,
                      float* __restrict__ mean_out, float* __restrict__ inv_std_out, uint8_t* __restrict__ row_is_zero,
-                     long long rows, int E, float eps)
+                     long long rows, int E, float eps, unsigned int* work_counter)
 {
     pdl_launch_dependents();
-    pdl_wait();
     const int lane = threadIdx.x & 31;
-    const long long warp = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
-    const long long stride = (long long)gridDim.x * kRowWarps;
+    RowWalk walk(work_counter, rows, lane);                   // the first row is asked for before the wait: the counter is this launch's alone
+    pdl_wait();
     const float inv_E = 1.0f / (float)E;
 
-    for(long long row = warp; row < rows; row += stride)
+    for(long long row = walk.next(lane); row >= 0; row = walk.next(lane))
     {
         const float* a_row = A + row * (long long)E;
         const float* r_row = R ? R + row * (long long)E : nullptr;
@@ -259,16 +291,15 @@ __global__ void __launch_bounds__(kRowThreads, 2)
 layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2, const float* __restrict__ dY3,
                      const float* __restrict__ X, const float* __restrict__ mean_in, const float* __restrict__ inv_std_in,
                      const float* __restrict__ gamma, float* __restrict__ dX, float* __restrict__ partials,
-                     long long rows, int E)
+                     long long rows, int E, unsigned int* work_counter)
 {
     pdl_launch_dependents();
+    RowWalk walk(work_counter, rows, threadIdx.x & 31);
     pdl_wait();
     // [kRowWarps][2][E]: every warp keeps its running column sums here, and every lane only ever touches
     // its own columns, so plain loads and stores suffice; registers stay free for two CTAs per SM
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
-    const long long warp = (long long)blockIdx.x * kRowWarps + warp_in_block;
-    const long long stride = (long long)gridDim.x * kRowWarps;
     const float inv_E = 1.0f / (float)E;
     constexpr int SETS = DX_SUM ? 3 : 2;
     float* acc_gamma = smem + (size_t)warp_in_block * SETS * E;
@@ -286,7 +317,7 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
         }
     }
 
-    for(long long row = warp; row < rows; row += stride)
+    for(long long row = walk.next(lane); row >= 0; row = walk.next(lane))
     {
         const long long base = row * (long long)E;
         const float mean = mean_in[row], inv_std = inv_std_in[row];
@@ -487,7 +518,8 @@ extern "C" int onn_layernorm_fwd(const float* A, const float* R, const float* ga
     cudaStream_t s = (cudaStream_t)stream;
     const bool fast = (E & 3) == 0 && E <= 128 * kMaxVec && host_aligned16(A) && host_aligned16(Y) &&
                       host_aligned16(gamma) && host_aligned16(beta) && (!R || host_aligned16(R)) && (!sum || host_aligned16(sum));
-#define ONN_LN_FWD(V) launch_overlapped(layernorm_fwd_kernel<V>, dim3(grid), dim3(kRowThreads), 0, s, A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, (long long)rows, (int)E, eps)
+    unsigned int* work_counter = rows + (long long)grid * kRowWarps < (1LL << 31) ? next_work_counter() : nullptr;
+#define ONN_LN_FWD(V) launch_overlapped(layernorm_fwd_kernel<V>, dim3(grid), dim3(kRowThreads), 0, s, A, R, gamma, beta, Y, sum, mean, inv_std, row_is_zero, (long long)rows, (int)E, eps, work_counter)
     if(fast)
     {
         switch(vec_count(E))
@@ -535,8 +567,9 @@ int layernorm_bwd_launch(const float* dY, const float* dY2, const float* dY3, co
                       host_aligned16(gamma) && (!dY2 || host_aligned16(dY2)) && (!dY3 || host_aligned16(dY3));
     const bool dx_sum = fast_path_sums_dx(dX_colsum, E);
     const int sets = dx_sum ? 3 : 2;
-#define ONN_LN_BWD(V) do { if(dx_sum) launch_overlapped(layernorm_bwd_kernel<V, true>, dim3(grid), dim3(kRowThreads), smem, s, dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, (long long)rows, (int)E); \
-                           else launch_overlapped(layernorm_bwd_kernel<V, false>, dim3(grid), dim3(kRowThreads), smem, s, dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, (long long)rows, (int)E); } while(0)
+    unsigned int* work_counter = rows + (long long)grid * kRowWarps < (1LL << 31) ? next_work_counter() : nullptr;
+#define ONN_LN_BWD(V) do { if(dx_sum) launch_overlapped(layernorm_bwd_kernel<V, true>, dim3(grid), dim3(kRowThreads), smem, s, dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, (long long)rows, (int)E, work_counter); \
+                           else launch_overlapped(layernorm_bwd_kernel<V, false>, dim3(grid), dim3(kRowThreads), smem, s, dY, dY2, dY3, X, mean, inv_std, gamma, dX, partials, (long long)rows, (int)E, work_counter); } while(0)
     if(fast)
     {
         const size_t smem = (size_t)kRowWarps * sets * E * sizeof(float);   // 64 KiB (96 KiB with the dx sums) at E = 1024

@@ -313,6 +313,46 @@ def test_sm_limit_keeps_results(capi, sms):
     assert capi.lib().onn_gemm_device_status() == 0
 
 
+@pytest.mark.parametrize("sms", [0, 132, 6])
+def test_dynamic_work_keeps_results(capi, sms):
+    """onn_set_dynamic_work: the persistent kernels take their tiles from a per-launch counter in the order the CTAs ask
+    instead of a fixed share per CTA (what the data-parallel trainer runs with, so that SMs held by NCCL do not make a
+    launch wait for the shares of CTAs that start late).  Same tiles, other owners: results equal up to the order of the
+    split sums, launch after launch (the counters must come back to zero), with a split tail wave, split-K, the batched
+    one-CTA kernel, attention forward and backward, and LayerNorm, on all SMs and on a few."""
+    rng = np.random.default_rng(11 + sms)
+    M, N, K = 4864, 1024, 512                           # 76 tile pairs: a split tail wave on 74 pairs
+    a, b = dev(rng.standard_normal((M, K))), dev(0.05 * rng.standard_normal((K, N)))
+    B, H, S, E = 3, 4, 256, 256
+    x, dy = dev(rng.standard_normal((B, S, E))), dev(rng.standard_normal((B, S, E)))
+    p = {n: dev(rng.uniform(-0.1, 0.1, (E, E))) for n in ("Wq", "Wk", "Wv", "Wo")}
+    p.update({n: dev(0.05 * rng.standard_normal(E)) for n in ("bq", "bk", "bv", "bo")})
+    gamma, beta = dev(rng.standard_normal(E)), dev(rng.standard_normal(E))
+
+    def run():
+        c, dw = torch.zeros(M, N, device="cuda"), torch.zeros(K, N, device="cuda")
+        capi.gemm(a, b, c, M, N, K, K, N, N, 0, 1)
+        capi.gemm(a, c, dw, K, N, M, K, N, N, 1, 1, split_k=4)
+        y, ws = capi.mha_fwd(x, x, p, H, True)
+        grads, dxq, _ = capi.mha_bwd(x, x, p, H, True, ws, dy)
+        normed, mean, inv_std, _ = capi.layernorm_fwd(x, gamma, beta)
+        dx, dgamma, dbeta = capi.layernorm_bwd(dy, x, mean, inv_std, gamma)
+        return [host(t) for t in (c, dw, y, dxq, grads["dWq"], grads["dWv"], normed, dx, dgamma)]
+
+    names = ("product", "split-K product", "attention output", "attention input gradient", "dWq", "dWv", "LayerNorm", "LayerNorm dx", "dgamma")
+    reference = run()
+    capi.check(capi.lib().onn_set_sm_limit(sms))
+    previous = capi.lib().onn_set_dynamic_work(1)
+    try:
+        for repeat in range(3):
+            for got, expected, what in zip(run(), reference, names):
+                assert_close(got, expected, 1e-4, f"{what}, run {repeat}")
+    finally:
+        capi.lib().onn_set_dynamic_work(previous)
+        capi.check(capi.lib().onn_set_sm_limit(0))
+    assert capi.lib().onn_gemm_device_status() == 0
+
+
 def test_adam_and_norm(capi):
     from oracle import opennn_oracle as O
     rng = np.random.default_rng(7)
