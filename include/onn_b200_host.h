@@ -125,6 +125,11 @@ int onn_trainer_parameters_ready(onn_trainer* trainer);
  * onn_trainer_last_step_phases synchronises the stream and returns the three intervals in milliseconds
  * {start -> forward done (earlier micro-batches included), back-propagation, update}.  The last micro-batch must
  * have run eagerly (a data-parallel rank's always does; otherwise onn_trainer_set_graph_capture(t, 0)). */
+/* Graph segments the data-parallel rank's exchanging micro-batch is replayed from (it cannot be one graph: between its
+ * kernels the host enqueues collectives and waits for marks of the communication stream, so it is cut there and the
+ * host acts between the segments); 0 = that micro-batch runs kernel by kernel (not recorded yet, graphs off, phase
+ * tracing or SM carving on, or the recording failed). */
+int onn_trainer_exchange_segments(const onn_trainer* trainer);
 int onn_trainer_trace_phases(onn_trainer* trainer, int enabled);
 int onn_trainer_last_step_phases(onn_trainer* trainer, float* milliseconds3);
 /* The cudaStream_t every kernel of this trainer is launched on (for event timing by the caller). */

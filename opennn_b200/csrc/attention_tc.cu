@@ -105,11 +105,13 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
-    // the first item is asked for before the wait for the preceding kernel: the counter is this launch's alone
+    pdl_wait();                                               // set-up done; global memory only from here on
+    // Only now may the counter be touched: a counter of the pool can come round to two launches that follow each other
+    // on the stream (one of them replayed from a graph captured long ago), and before the wait the earlier one may
+    // still be running.
     const WorkSource source = { p.work_counter, (uint32_t)p.items, gridDim.x };
     uint32_t first_work = kNoWork;
     if(threadIdx.x == 0) first_work = source.fetch(0, blockIdx.x, gridDim.x);
-    pdl_wait();                                               // set-up done; global memory only from here on
 
     if(warp == 0)
     {

@@ -24,8 +24,12 @@ int sm_limit();
 // Work-item counters of the persistent kernels that can hand out their work items in the order the CTAs ask for them: a
 // CTA that gets its SM late -- another kernel, e.g. one of NCCL's, holds it -- then takes fewer items instead of making
 // the whole launch wait for a fixed share.  next_work_counter() returns the device address, on the current device, of a
-// counter at zero, taken round robin from a pool; the kernel that uses it leaves it at zero (work_ring.cuh), so it is
-// ready again long before the sequence comes back to it.  Null -- fixed shares -- unless the mode is on
+// counter at zero, taken round robin from a pool; the kernel that uses it leaves it at zero (work_ring.cuh) and touches
+// it only after it has waited for the launch before it on its stream, so two launches of one stream can share a counter
+// (a graph replays the counters it was captured with, and the pool comes round to them).  Launches of DIFFERENT streams
+// that run at the same time must not: with 8192 counters that takes a graph replay on one stream meeting, on another,
+// the one eager launch in 8192 that drew the same counter -- callers that run this library on several streams at once
+// keep the mode off.  Null -- fixed shares -- unless the mode is on
 // (onn_set_dynamic_work; the data-parallel trainer turns it on).  reset_work_counters(): after a kernel gave up on a
 // wait and left its counter behind.
 unsigned int* next_work_counter();

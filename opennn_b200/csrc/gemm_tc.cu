@@ -352,12 +352,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
-    // the producer is also the scheduler (work_ring.cuh); its first item is asked for before the wait for the preceding
-    // kernel: the counter is this launch's alone
+    pdl_wait();                                               // set-up done; global memory only from here on
+    // the producer is also the scheduler (work_ring.cuh).  The counter is touched only after the wait: a counter of the
+    // pool can come round to two launches that follow each other on the stream
     const WorkSource source = { p.work_counter, (uint32_t)p.total_work, gridDim.x };
     uint32_t first_work = kNoWork;
     if(threadIdx.x == 0) first_work = source.fetch(0, blockIdx.x, gridDim.x);
-    pdl_wait();                                               // set-up done; global memory only from here on
 
     if(warp == 0)
     {
@@ -696,11 +696,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
-    // the scheduler's first item is asked for before the wait for the preceding kernel: the counter is this launch's alone
+    pdl_wait();                                               // set-up done; global memory only from here on
+    // the counter is touched only after the wait: a counter of the pool can come round to two launches that follow each
+    // other on the stream
     const WorkSource source = { p.work_counter, (uint32_t)p.total_work, (uint32_t)pairs };
     uint32_t first_work = kNoWork;
     if(threadIdx.x == 0 && leader && p.work_counter) first_work = source.fetch(0, 0, 0);
-    pdl_wait();                                               // set-up done; global memory only from here on
 
     // Work items.  With a counter the leader's producer thread is the scheduler: it takes item numbers from the counter,
     // one ahead of the item it loads, and publishes each in a ring slot of both CTAs; every other role reads the slots in

@@ -172,9 +172,9 @@ layernorm_fwd_kernel(const float* __restrict__ A, const float* __restrict__ R,
                      long long rows, int E, float eps, unsigned int* work_counter)
 {
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31;
-    RowWalk walk(work_counter, rows, lane);                   // the first row is asked for before the wait: the counter is this launch's alone
     pdl_wait();
+    const int lane = threadIdx.x & 31;
+    RowWalk walk(work_counter, rows, lane);                   // after the wait: the launch before this one may have used the same counter
     const float inv_E = 1.0f / (float)E;
 
     for(long long row = walk.next(lane); row >= 0; row = walk.next(lane))
@@ -294,8 +294,8 @@ layernorm_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ dY2
                      long long rows, int E, unsigned int* work_counter)
 {
     pdl_launch_dependents();
-    RowWalk walk(work_counter, rows, threadIdx.x & 31);
     pdl_wait();
+    RowWalk walk(work_counter, rows, threadIdx.x & 31);      // after the wait: the launch before this one may have used the same counter
     // [kRowWarps][2][E]: every warp keeps its running column sums here, and every lane only ever touches
     // its own columns, so plain loads and stores suffice; registers stay free for two CTAs per SM
     extern __shared__ float smem[];

@@ -102,6 +102,23 @@ struct onn_trainer
     bool graphs_enabled = true;
     Index eager_steps = 0;                // graphs are captured only after one eager step has configured every kernel
 
+    // The micro-batch that hands gradient buckets to the exchange cannot be ONE graph: between its kernels the host
+    // enqueues collectives on the communication stream and makes the compute stream wait for marks recorded there.  It
+    // is replayed as a chain of graph segments instead, cut wherever such an action happens; the actions themselves run
+    // between the segments as they do in an eager step.
+    struct ExchangeAction { int kind; Index argument; };   // 0: wait for parameter bucket, 1: end of forward pass (all parameters, active-token count), 2: reduce-scatter bucket, -1: none
+    struct SegmentedGraph
+    {
+        vector<cudaGraphExec_t> segments;
+        vector<ExchangeAction> actions;                     // actions[i] follows segments[i]
+        uint64_t launches = 0;
+        Index chunk = -1;                                   // micro-batch number it was recorded for (its statistics slot is a captured argument)
+        bool failed = false;
+    };
+    SegmentedGraph exchange_graph;
+    bool recording = false;                                 // hooks cut segments instead of acting
+    Index recorded_bucket = -1;                             // highest parameter bucket a recorded wait covers
+
     // cached greedy decoding: one executable graph per target position (the position is part of the captured pointers
     // and arguments), captured from the second call on; ids and END flags live in buffers that never move
     vector<cudaGraphExec_t> decode_graphs;
@@ -113,6 +130,7 @@ struct onn_trainer
     ~onn_trainer()
     {
         for(MicroGraph& g : micro_graphs) if(g.executable) cudaGraphExecDestroy(g.executable);
+        for(cudaGraphExec_t g : exchange_graph.segments) if(g) cudaGraphExecDestroy(g);
         for(cudaGraphExec_t g : decode_graphs) if(g) cudaGraphExecDestroy(g);
         for(IdBuffers& b : id_buffers)
         {
@@ -159,6 +177,7 @@ extern "C" const char* onn_trainer_last_error(void) { return g_last_error.c_str(
 
 static void await_parameters(onn_trainer* t);
 static void settle_parameters(onn_trainer* t);
+static void cut_segment(onn_trainer* t, int kind, Index argument);
 
 extern "C" int onn_trainer_create(onn_trainer** out, int network_kind,
                                   int64_t input_sequence_length, int64_t decoder_sequence_length,
@@ -299,6 +318,9 @@ extern "C" int onn_trainer_set_dp(onn_trainer* t, onn_dp_comm* comm, int world)
         // gathers of the old communicator and layout: the old communicator is the caller's and may be gone already
         if(t->gather_in_flight) check_cuda(cudaDeviceSynchronize(), "set_dp");
         t->gather_in_flight = false;
+        // the recorded exchange belongs to the old communicator and bucket grid
+        for(cudaGraphExec_t g : t->exchange_graph.segments) if(g) cudaGraphExecDestroy(g);
+        t->exchange_graph = onn_trainer::SegmentedGraph();
         t->comm = world > 1 ? comm : nullptr;
         t->world = world;
         // NCCL's kernels hold SMs while back-propagation and the next forward pass run: CTAs that start late must not own
@@ -381,10 +403,17 @@ static void settle_parameters(onn_trainer* t)
 static void await_layer_parameters(void* context, Index layer)
 {
     onn_trainer* t = static_cast<onn_trainer*>(context);
-    if(!t->gather_in_flight) return;
+    if(!t->gather_in_flight && !t->recording) return;
     const Index low = t->layer_offsets[size_t(layer)];
     const Index high = size_t(layer) + 1 < t->layer_offsets.size() ? t->layer_offsets[size_t(layer) + 1] : t->network->get_parameters_number();
     if(high <= low) return;
+    if(t->recording)
+    {
+        // every replay may find gathers in flight: cut wherever a layer's parameters end in a bucket no earlier wait covers
+        const Index bucket = (high - 1) / t->shard_bucket;
+        if(bucket > t->recorded_bucket) { cut_segment(t, 0, bucket); t->recorded_bucket = bucket; }
+        return;
+    }
     const Index needed = std::min((high - 1) / t->shard_bucket, t->gather_buckets - 1);
     if(needed <= t->awaited_bucket) return;
     check_onn(onn_dp_wait_mark(t->comm, mark_of_bucket(needed), t->stream), "parameter wait");
@@ -431,6 +460,7 @@ static void gradient_ready(void* context, Index layer)
     {
         for(; t->pending_bucket >= 0 && t->pending_bucket * t->shard_bucket >= low; t->pending_bucket--)
         {
+            if(t->recording) { cut_segment(t, 2, t->pending_bucket); continue; }
             if(!issued) narrow_for_exchange(t);
             issued = true;
             reduce_scatter_bucket(t, t->pending_bucket);
@@ -549,6 +579,141 @@ static bool replay_micro_batch(onn_trainer* t, const BatchCuda& source, Index ch
     return true;
 }
 
+// What the host does between two segments of the exchanging micro-batch (and what an eager step does at the same place).
+static void perform(onn_trainer* t, const onn_trainer::ExchangeAction& action)
+{
+    switch(action.kind)
+    {
+        case 0:                                              // the forward pass is about to read parameters up to this bucket
+            if(t->gather_in_flight)
+            {
+                const Index needed = std::min(action.argument, t->gather_buckets - 1);
+                if(needed > t->awaited_bucket)
+                {
+                    check_onn(onn_dp_wait_mark(t->comm, mark_of_bucket(needed), t->stream), "parameter wait");
+                    t->awaited_bucket = needed;
+                    if(needed == t->gather_buckets - 1) t->gather_in_flight = false;
+                }
+            }
+            break;
+        case 1:                                              // forward pass done: the loss reads the global active-token count
+            await_parameters(t);
+            check_onn(onn_dp_wait(t->comm, t->stream), "active-token wait");
+            break;
+        case 2:
+            reduce_scatter_bucket(t, action.argument);
+            break;
+        default: break;
+    }
+}
+
+// Ends the segment being captured, remembers the action that follows it, and starts the next one.
+static void cut_segment(onn_trainer* t, int kind, Index argument)
+{
+    onn_trainer::SegmentedGraph& graph = t->exchange_graph;
+    cudaGraph_t captured = nullptr;
+    if(cudaStreamEndCapture(t->stream, &captured) != cudaSuccess || !captured) throw std::runtime_error("segment capture failed");
+    cudaGraphExec_t executable = nullptr;
+    const bool ok = cudaGraphInstantiate(&executable, captured, 0) == cudaSuccess;
+    cudaGraphDestroy(captured);
+    if(!ok) throw std::runtime_error("segment instantiation failed");
+    graph.segments.push_back(executable);
+    graph.actions.push_back({kind, argument});
+    if(kind >= 0 && cudaStreamBeginCapture(t->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+        throw std::runtime_error("segment capture failed");
+}
+
+// Replays (recording it first if need be) the micro-batch that hands its gradient buckets to the reduce-scatter.
+// Returns false if it cannot be done this way; the caller then runs the micro-batch eagerly.
+static bool replay_exchange_micro_batch(onn_trainer* t, const BatchCuda& source, Index chunk)
+{
+    onn_trainer::SegmentedGraph& graph = t->exchange_graph;
+    if(graph.failed || (graph.chunk >= 0 && graph.chunk != chunk)) return false;
+    const Index S_dec = t->decoder_sequence_length, S_in = t->input_sequence_length;
+    if(t->micro_decoder.size() == 0)
+    {
+        t->micro_decoder.resize(t->micro_batch * S_dec);
+        t->micro_targets.resize(t->micro_batch * S_dec);
+        if(!t->decoder_only) t->micro_encoder.resize(t->micro_batch * S_in);
+    }
+    // the captured kernels read their ids from these fixed buffers
+    const size_t decoder_bytes = size_t(t->micro_batch * S_dec) * sizeof(type);
+    check_cuda(cudaMemcpyAsync(t->micro_decoder.data, source.decoder.data, decoder_bytes, cudaMemcpyDeviceToDevice, t->stream), "micro ids");
+    check_cuda(cudaMemcpyAsync(t->micro_targets.data, source.target.data, decoder_bytes, cudaMemcpyDeviceToDevice, t->stream), "micro targets");
+    if(!t->decoder_only)
+        check_cuda(cudaMemcpyAsync(t->micro_encoder.data, source.input.data, size_t(t->micro_batch * S_in) * sizeof(type),
+                                   cudaMemcpyDeviceToDevice, t->stream), "micro ids");
+
+    if(graph.segments.empty())
+    {
+        BatchCuda micro;
+        micro.samples_number = t->micro_batch;
+        micro.decoder = TensorViewCuda(t->micro_decoder.data, {t->micro_batch, S_dec});
+        if(!t->decoder_only) micro.input = TensorViewCuda(t->micro_encoder.data, {t->micro_batch, S_in});
+        micro.target = TensorViewCuda(t->micro_targets.data, {t->micro_batch, S_dec});
+
+        const Index slot_before = t->back->statistics_slot;
+        const uint64_t launches_before = onn_launch_count();
+        bool ok = cudaStreamBeginCapture(t->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if(ok)
+        {
+            t->recording = true;
+            t->recorded_bucket = -1;
+            try
+            {
+                t->network->before_layer_hook = await_layer_parameters;
+                t->network->before_layer_context = t;
+                t->network->forward_propagate(micro.get_inputs_device(), *t->forward, true);
+                t->network->before_layer_hook = nullptr;
+                cut_segment(t, 1, 0);
+                t->pending_bucket = (t->shard_total - 1) / t->shard_bucket;
+                t->loss->gradient_ready_hook = gradient_ready;
+                t->loss->gradient_ready_context = t;
+                t->loss->back_propagate(micro, *t->forward, *t->back, chunk > 0);
+                gradient_ready(t, -1);
+                t->loss->gradient_ready_hook = nullptr;
+                cut_segment(t, -1, 0);
+            }
+            catch(...)
+            {
+                ok = false;
+                cudaGraph_t abandoned = nullptr;
+                cudaStreamEndCapture(t->stream, &abandoned);     // leaves capture mode whatever state it is in
+                if(abandoned) cudaGraphDestroy(abandoned);
+            }
+            t->recording = false;
+            t->network->before_layer_hook = nullptr;
+            t->loss->gradient_ready_hook = nullptr;
+        }
+        t->back->statistics_slot = slot_before;
+        if(!ok)
+        {
+            // nothing of the micro-batch has run; give up on this way of running it and let the caller run it eagerly
+            cudaGetLastError();
+            for(cudaGraphExec_t g : graph.segments) if(g) cudaGraphExecDestroy(g);
+            graph.segments.clear();
+            graph.actions.clear();
+            graph.failed = true;
+            onn_launch_count_add(0 - (onn_launch_count() - launches_before));
+            return false;
+        }
+        graph.launches = onn_launch_count() - launches_before;    // counted at capture; the replay below is that launch
+        graph.chunk = chunk;
+        onn_launch_count_add(0 - graph.launches);
+    }
+
+    // host-side bookkeeping the captured code did when it ran eagerly
+    if(chunk == 0) t->back->statistics_slot = 0;
+    t->back->statistics_slot++;
+    for(size_t i = 0; i < graph.segments.size(); i++)
+    {
+        check_cuda(cudaGraphLaunch(graph.segments[i], t->stream), "segment launch");
+        perform(t, graph.actions[i]);
+    }
+    onn_launch_count_add(graph.launches);
+    return true;
+}
+
 // Whatever ends the step, the hook that hands gradients to the exchange does not outlive it and the SM limit is lifted.
 struct ExchangeScope
 {
@@ -633,6 +798,13 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
             await_parameters(t);
             await_count();
             if(replay_micro_batch(t, micro, chunk)) continue;
+        }
+
+        if(hands_out_gradients && t->sharded_step && t->graphs_enabled && t->eager_steps > 0 && !t->trace_phases && t->carve_sms == 0 &&
+           replay_exchange_micro_batch(t, micro, chunk))
+        {
+            count_pending = false;                               // waited for between the segments
+            continue;
         }
 
         if(t->gather_in_flight)
@@ -977,6 +1149,11 @@ extern "C" int onn_trainer_synchronize(onn_trainer* t)
 {
     if(!t) return ONN_ERR_INVALID_ARGUMENT;
     return guarded([&] { settle_parameters(t); check_device_status(t); });
+}
+
+extern "C" int onn_trainer_exchange_segments(const onn_trainer* t)
+{
+    return t ? int(t->exchange_graph.segments.size()) : 0;
 }
 
 extern "C" int onn_trainer_trace_phases(onn_trainer* t, int enabled)

@@ -23,7 +23,7 @@ HOST_EXPORTS = [
     "onn_trainer_layers_number", "onn_trainer_layer_info", "onn_trainer_set_parameters", "onn_trainer_get_parameters",
     "onn_trainer_get_gradients", "onn_trainer_set_learning_rate", "onn_trainer_set_iteration", "onn_trainer_set_dp",
     "onn_trainer_step_device", "onn_trainer_step_host", "onn_trainer_step_host_i32", "onn_trainer_forward", "onn_trainer_get_layer_output",
-    "onn_trainer_synchronize", "onn_trainer_parameters_ready", "onn_trainer_trace_phases", "onn_trainer_last_step_phases", "onn_trainer_stream", "onn_trainer_set_graph_capture", "onn_trainer_set_dp_options",
+    "onn_trainer_synchronize", "onn_trainer_parameters_ready", "onn_trainer_exchange_segments", "onn_trainer_trace_phases", "onn_trainer_last_step_phases", "onn_trainer_stream", "onn_trainer_set_graph_capture", "onn_trainer_set_dp_options",
     "onn_trainer_greedy_decode", "onn_trainer_greedy_decode_cached",
     "onn_classifier_last_error", "onn_classifier_create", "onn_classifier_destroy", "onn_classifier_parameters_number",
     "onn_classifier_layers_number", "onn_classifier_layer_info", "onn_classifier_set_parameters", "onn_classifier_get_parameters",
@@ -188,6 +188,9 @@ class Trainer:
 
     def synchronize(self):
         _check(host_lib().onn_trainer_synchronize(self._handle), "synchronize")
+
+    def exchange_segments(self):
+        return int(host_lib().onn_trainer_exchange_segments(self._handle))
 
     def trace_phases(self, enabled=True):
         _check(host_lib().onn_trainer_trace_phases(self._handle, int(bool(enabled))), "trace_phases")

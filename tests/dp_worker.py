@@ -47,7 +47,8 @@ def main(out_path):
         # a step without statistics in between: nothing of the exchange may depend on the read-back
         t.step_device(dec, enc, tgt, update=True, want_statistics=False)
         last = t.step_device(dec, enc, tgt, update=True)
-        results[label] = dict(stats=np.array(stats), gradient=gradient, history=np.array(history), params=t.get_parameters(), last=np.array(last))
+        results[label] = dict(stats=np.array(stats), gradient=gradient, history=np.array(history), params=t.get_parameters(), last=np.array(last),
+                              segments=np.array(t.exchange_segments()))
         t.close()
 
     case = "classifier_tiny"

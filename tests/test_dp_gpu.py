@@ -64,7 +64,12 @@ def test_two_gpus_match_one(built):
         assert np.abs(dp[f"{label}_params"] - after).max() <= 2.2e-3 * (steps + 2)
     # the two data-parallel modes reduce the same per-rank gradients (up to the order of floating-point atomics): their
     # parameters agree as closely as two runs of one mode do
-    assert_close(dp["sharded_params"], dp["replicated_params"], 1e-4, "parameters, sharded update vs update on every rank")
+    # (with work items by counter the order of the floating-point atomics also changes from run to run, and Adam turns the
+    # sign of a gradient that is rounding noise into a step: L2 as two runs of one mode, single elements within Adam's steps)
+    _, l2_err = errors(dp["sharded_params"], dp["replicated_params"])
+    assert l2_err <= 1e-4, f"parameters, sharded update vs update on every rank: l2-rel {l2_err:.2e}"
+    assert np.abs(dp["sharded_params"] - dp["replicated_params"]).max() <= 2.2e-3 * (steps + 2)
+    assert dp["sharded_segments"] > 2, "the exchanging micro-batch of the sharded update is replayed from graph segments"
 
     # text classifier: the two ranks' averaged gradient and their steps against one GPU on the whole batch
     from tests.golden.make_golden import CLASSIFIER_CASES, classifier_inputs
