@@ -439,6 +439,70 @@ def time_row_kernels(capi, torch, w, peaks=None, repeats=3):
             "peak_source": ("copy bandwidth, " + peaks["source"]) if peaks else None, "kernels": out}
 
 
+def time_under_contention(capi, torch, w):
+    """What a resident kernel of another library (NCCL's CTAs during a collective) costs the persistent kernels: the FFN
+    GEMM, an attention layer and a LayerNorm pair of one micro-batch, timed alone and while `held` SMs are occupied by
+    the library's bounded stand-in kernel on a second stream -- with a fixed share of the tiles per CTA and with tiles
+    handed out by counter (onn_set_dynamic_work)."""
+    import ctypes
+    import numpy as np
+    L = capi.lib()
+    M, K, N = w["micro_batch"] * w["S_dec"], w["E"], w["F"]
+    A, B, C = torch.randn(M, K, device="cuda"), torch.randn(N, K, device="cuda") / 32, torch.empty(M, N, device="cuda")
+    Bt, H, S, E = 32, w["H"], w["S_dec"], w["E"]
+    rng = np.random.default_rng(0)
+    p = {n: torch.from_numpy((rng.standard_normal((E, E)) / 32).astype(np.float32)).cuda() for n in ("Wq", "Wk", "Wv", "Wo")}
+    p.update({n: torch.zeros(E, device="cuda") for n in ("bq", "bk", "bv", "bo")})
+    x, dy = torch.randn(Bt, S, E, device="cuda"), torch.randn(Bt, S, E, device="cuda")
+    rows = torch.randn(M, E, device="cuda")
+    gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
+    side = torch.cuda.Stream()
+
+    def gemm():
+        capi.gemm(A, B, C, M, N, K, K, K, N, 0, 0)
+
+    def attention():
+        y, ws = capi.mha_fwd(x, x, p, H, True)
+        capi.mha_bwd(x, x, p, H, True, ws, dy)
+
+    def norms():
+        y, mean, inv_std, _ = capi.layernorm_fwd(rows, gamma, beta)
+        capi.layernorm_bwd(rows, rows, mean, inv_std, gamma)
+
+    def timed(fn, repeats, held):
+        # the median of five: a stand-in that got its SMs late in one repeat must not decide the figure
+        seen = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if held:
+                capi.check(L.onn_selftest_hold_sms(held, ctypes.c_int64(12_000_000), ctypes.c_void_p(side.cuda_stream)), "onn_selftest_hold_sms")
+                torch.cuda._sleep(1_000_000)               # ~0.5 ms: the stand-in has its SMs before the timed launches start
+            start.record()
+            for _ in range(repeats):
+                fn()
+            stop.record()
+            torch.cuda.synchronize()
+            seen.append(start.elapsed_time(stop) / repeats)
+        return statistics.median(seen)
+
+    out = {}
+    for fn in (gemm, attention, norms):
+        fn()
+    for mode, label in ((0, "fixed_share"), (1, "by_counter")):
+        previous = L.onn_set_dynamic_work(mode)
+        try:
+            for fn, name, repeats in ((gemm, "ffn_gemm", 20), (attention, "attention_layer_fwd_bwd", 4), (norms, "layernorm_fwd_bwd", 8)):
+                fn()
+                out[f"{name}_{label}_ms"] = {f"held_{held}": round(timed(fn, repeats, held), 4) for held in (0, 8, 16, 32)}
+        finally:
+            L.onn_set_dynamic_work(previous)
+    if L.onn_gemm_device_status() != 0:
+        raise SystemExit("a kernel gave up on a bounded wait: the numbers are void")
+    return {"kernel": "two-CTA GEMM 16384 x 4096 x 1024, attention layer 32 x 16 heads x 256 x 256, LayerNorm 16384 x 1024: alone and with SMs held",
+            "contention": out}
+
+
 def time_greedy_decode(trainer, torch, w, rows, tokens):
     """Greedy decoding of `rows` source sequences with cached keys and values, `tokens` target positions each (the
     caller of the same layers on the inference side): one eager call, one that captures a graph per position, then timed
@@ -528,6 +592,9 @@ def run_ours(args):
         return
     if args.profile_kernel == "attention":
         emit(dict(time_attention_core(capi, torch, w), profiling_only=True))
+        return
+    if args.profile_kernel == "contention":
+        emit(dict(time_under_contention(capi, torch, w), profiling_only=True))
         return
     if args.profile_kernel == "classifier":
         emit(dict(time_classifier_step(trainer, torch, w, args.profile_batch or 64, max(args.steps, 5)), profiling_only=True))
@@ -730,7 +797,7 @@ def main():
     parser.add_argument("--workload", default="config5", choices=["config5", "config2", "config3", "config4"],
                         help="config5 is the benchmark; config2 prints a profiling line for the launch-bound small network, config3 / config4 "
                              "one for the mid encoder-decoder and the long-sequence decoder-only stack (with the reference CPU library beside it)")
-    parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention", "rowwise", "decode", "classifier"],
+    parser.add_argument("--profile-kernel", nargs="?", const="gemm", default=None, choices=["gemm", "attention", "rowwise", "decode", "classifier", "contention"],
                         help="profiling aid: launch only the dominant GEMM (FFN-up shape) four times on buffers larger than L2, "
                              "or only one attention layer (forward and backward, 32 samples) twice, or only the HBM-bound kernels "
                              "(LayerNorm forward / backward, fused softmax-cross-entropy, Adam) at the benchmark's sizes; decode: greedy decoding "

@@ -142,6 +142,11 @@ int onn_set_sm_limit(int sms);
  * for as long as it has a communicator.  Takes effect at the next launch; ONN_B200_DYNAMIC_WORK=0 / 1 in the
  * environment overrides the call.  Returns the previous setting. */
 int onn_set_dynamic_work(int enabled);
+/* Measurement aid for the above (no counterpart in the reference): a kernel of `sms` CTAs that each occupy one SM's
+ * shared memory and spin for `cycles` clock cycles (at most 2^26, about 35 ms), then end by themselves -- what a
+ * resident CTA of another library is to the persistent kernels.  Launch it on a second stream, then time kernels on
+ * the first (tests/test_layers_gpu.py, bench.py --profile-kernel contention). */
+int onn_selftest_hold_sms(int sms, int64_t cycles, void* stream);
 /* Failure-detection self-test (no counterpart in the reference): runs a one-thread kernel that waits, with a
  * 1 ms limit, on a barrier nothing ever signals.  *gave_up receives 1 when the wait ran out as it must; the
  * kernel returns normally, the context stays usable, and the next onn_gemm_device_status() reports

@@ -58,7 +58,7 @@ EXPORTS = [
     "onn_relu_bits_words_per_row", "onn_dense_fwd", "onn_dense_bwd", "onn_pooling3d_fwd", "onn_pooling3d_bwd", "onn_softmax_rows",
     "onn_mha_fwd_workspace_floats", "onn_mha_bwd_workspace_floats", "onn_mha_fwd", "onn_mha_bwd",
     "onn_mha_attention_weights", "onn_ce2d_fwd_bwd", "onn_ce2d_binary_fwd_bwd", "onn_dense_fwd_shared_input", "onn_greedy_next_token", "onn_greedy_next_token_rows", "onn_greedy_next_token_logits", "onn_decode_attention", "onn_rows_are_zero", "onn_ce3d_count_active", "onn_ce3d_fwd_bwd",
-    "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam", "onn_adam_guarded", "onn_device_status_gather", "onn_set_sm_limit", "onn_set_dynamic_work",
+    "onn_grad_sqnorm_workspace_floats", "onn_grad_sqnorm", "onn_adam", "onn_adam_guarded", "onn_device_status_gather", "onn_set_sm_limit", "onn_set_dynamic_work", "onn_selftest_hold_sms",
     "onn_dp_unique_id", "onn_dp_init", "onn_dp_init_config", "onn_dp_world", "onn_dp_rank", "onn_dp_allreduce", "onn_dp_reduce_scatter",
     "onn_dp_all_gather", "onn_dp_zero", "onn_dp_wait", "onn_dp_mark", "onn_dp_wait_mark", "onn_dp_mark_failed", "onn_dp_finalize",
 ]

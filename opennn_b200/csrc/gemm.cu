@@ -137,6 +137,28 @@ extern "C" int onn_set_sm_limit(int sms)
     return ONN_OK;
 }
 
+// Stand-in for another library's resident kernel (what NCCL's CTAs are to the persistent kernels here): `sms` CTAs that
+// each take an SM's shared memory and spin for a fixed number of cycles.  No waiting on anything: it ends by itself.
+__global__ void hold_sms_kernel(long long cycles)
+{
+    extern __shared__ int held[];
+    const long long start = clock64();
+    long long now = start;
+    while(now - start < cycles) now = clock64();
+    if(now == 0) held[0] = 0;
+}
+
+extern "C" int onn_selftest_hold_sms(int sms, int64_t cycles, void* stream)
+{
+    ONN_CHECK_ARG(sms > 0 && sms <= kSmCount && cycles > 0 && cycles <= (1LL << 26));    // at most ~35 ms
+    constexpr int kHeldBytes = 200 * 1024;                   // no CTA of the persistent kernels fits beside it
+    static PerDeviceBytes configured;
+    if(!ensure_dynamic_smem(hold_sms_kernel, configured, kHeldBytes)) return ONN_ERR_CUDA;
+    hold_sms_kernel<<<sms, 128, kHeldBytes, (cudaStream_t)stream>>>((long long)cycles);
+    count_launch();
+    return launch_status();
+}
+
 extern "C" int onn_set_dynamic_work(int enabled)
 {
     const int previous = g_dynamic_work.exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed);
