@@ -110,6 +110,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // on the stream (one of them replayed from a graph captured long ago), and before the wait the earlier one may
     // still be running.
     const WorkSource source = { p.work_counter, (uint32_t)p.items, gridDim.x };
+    const WorkView work = { ring, p.work_counter != nullptr, (uint32_t)p.items };
     uint32_t first_work = kNoWork;
     if(threadIdx.x == 0) first_work = source.fetch(0, blockIdx.x, gridDim.x);
 
@@ -123,7 +124,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             // more than one item beyond the one it is working on.
             uint32_t ph = 0;
             uint32_t w = first_work;
-            bool told = work_ring_publish(ring, 0, w, abort_flag, 20);
+            bool told = work.publish(0, w, abort_flag, 20);
             for(uint32_t turn = 0; told && w != kNoWork; turn++, ph ^= 1)
             {
                 const uint32_t ahead = source.fetch(turn + 1, blockIdx.x, gridDim.x);
@@ -144,7 +145,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 mbar_arrive_expect_tx(smem_u32(v_full), V_BYTES);
                 tma_load_5d(smem_u32(v_smem), &map_v, smem_u32(v_full), 0, 0, it.h * KB, 0, it.b);
                 w = ahead;
-                told = work_ring_publish(ring, turn + 1, w, abort_flag, 20);
+                told = work.publish(turn + 1, w, abort_flag, 20);
             }
             if(*abort_flag)
             {
@@ -160,7 +161,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         {
             const uint32_t idesc_s = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)((p.key_blocks * 32) >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
             uint32_t ph = 0;
-            for(uint32_t turn = 0; work_ring_take(ring, turn, abort_flag, 24) != kNoWork; turn++, ph ^= 1)
+            for(uint32_t turn = 0; work.take(turn, abort_flag, 24) != kNoWork; turn++, ph ^= 1)
             {
                 // scores: the previous item's context MMAs were issued before these and the tensor pipe runs in order,
                 // and every softmax thread had its scores in registers before those MMAs were released (p_ready)
@@ -205,7 +206,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if constexpr(BACKWARD)
         {
             // the first item's four blocks of attention weights
-            const uint32_t first_item = lane == 0 ? work_ring_peek(ring, 0, abort_flag, 31) : kNoWork;
+            const uint32_t first_item = lane == 0 ? work.peek(0, abort_flag, 31) : kNoWork;
             if(lane == 0 && first_item != kNoWork)
             {
                 const AttnItem first = decode_item(p, first_item);
@@ -220,14 +221,16 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             __syncwarp();
         }
         uint32_t ph = 0;
-        // The item of a turn is looked up in the middle of the turn before (where the warp has a moment: its part of the
-        // critical path is over) and only handed back at the top of its own turn.
-        uint32_t w = 0, w_next = kNoWork;
-        if(lane == 0) w = work_ring_peek(ring, 0, abort_flag, 32);
-        w = __shfl_sync(0xffffffffu, w, 0);
-        for(uint32_t turn = 0; w != kNoWork; turn++, ph ^= 1, w = w_next)
+        // Backward: the item of a turn is looked up in the middle of the turn before (the warp asks for that item's
+        // attention weights there) and only handed back at the top of its own turn.  Forward: looked up at the top; the
+        // kernel has no register to spare for carrying it.
+        [[maybe_unused]] uint32_t w_next = BACKWARD ? work.warp_peek(0, lane, abort_flag, 32) : kNoWork;
+        for(uint32_t turn = 0; ; turn++, ph ^= 1)
         {
-            if(lane == 0) work_ring_release(ring, turn, w);
+            uint32_t w;
+            if constexpr(BACKWARD) { w = w_next; work.warp_release(turn, w, lane); }
+            else w = work.warp_take(turn, lane, abort_flag, 32);
+            if(w == kNoWork) break;
             const AttnItem it = decode_item(p, w);
             const int row0 = it.q_tile * kQRows + quadrant * 32;      // first query row of this warp
             const int q_row = row0 + lane;
@@ -328,8 +331,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if(lane == 0) mbar_arrive(smem_u32(p_ready));    // the dQ MMAs may start
 
                 // the next item's weights take ring blocks 0..2 as soon as this item's copies have left them (block 3 stages dQ first)
-                if(lane == 0) w_next = work_ring_peek(ring, turn + 1, abort_flag, 33);
-                w_next = __shfl_sync(0xffffffffu, w_next, 0);
+                w_next = work.warp_peek(turn + 1, lane, abort_flag, 33);
                 AttnItem next = it;
                 int next_row0 = 0;
                 bool next_live = false;
@@ -484,8 +486,6 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tcgen05_fence_before();
                 __syncwarp();
                 if(lane == 0) mbar_arrive(smem_u32(p_ready));    // the context MMAs may start
-                if(lane == 0) w_next = work_ring_peek(ring, turn + 1, abort_flag, 33);
-                w_next = __shfl_sync(0xffffffffu, w_next, 0);
 
                 exchange[half * kQRows + r_local] = total;
                 pair_barrier(quadrant);

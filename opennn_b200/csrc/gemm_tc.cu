@@ -356,6 +356,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // the producer is also the scheduler (work_ring.cuh).  The counter is touched only after the wait: a counter of the
     // pool can come round to two launches that follow each other on the stream
     const WorkSource source = { p.work_counter, (uint32_t)p.total_work, gridDim.x };
+    const WorkView work = { ring, p.work_counter != nullptr, (uint32_t)p.total_work };
     uint32_t first_work = kNoWork;
     if(threadIdx.x == 0) first_work = source.fetch(0, blockIdx.x, gridDim.x);
 
@@ -370,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for(int s = 0; s < STAGES; s++) armed[s] = 0;
             bool ok = true;
             uint32_t w = first_work;
-            ok = work_ring_publish(ring, 0, w, abort_flag, 5);
+            ok = work.publish(0, w, abort_flag, 5);
             for(uint32_t turn = 0; ok && w != kNoWork; turn++)
             {
                 // item t + 1 is asked for before item t is copied and announced once those copies are on their way
@@ -413,7 +414,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if(++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 w = ahead;
-                if(ok) ok = work_ring_publish(ring, turn + 1, w, abort_flag, 5);
+                if(ok) ok = work.publish(turn + 1, w, abort_flag, 5);
             }
             if(*abort_flag)
             {
@@ -439,7 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             long long local = 0;
             bool ok = true;
             // the next item is looked up before the last k-block of this one, while MMAs are queued
-            uint32_t w = work_ring_take(ring, 0, abort_flag, 6), w_next = kNoWork;
+            uint32_t w = work.take(0, abort_flag, 6), w_next = kNoWork;
             for(uint32_t turn = 0; ok && w != kNoWork; turn++, local++, w = w_next)
             {
                 const WorkItem it = decode_work(p, w);
@@ -449,7 +450,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for(int kb = 0; kb < it.k_blocks; kb++)
                 {
-                    if(kb == it.k_blocks - 1) w_next = work_ring_take(ring, turn + 1, abort_flag, 6);
+                    if(kb == it.k_blocks - 1) w_next = work.take(turn + 1, abort_flag, 6);
                     if(!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, 3)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
@@ -480,9 +481,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         unsigned int staged_chunks = 0;                      // blocks this warp has handed to the copy engine
         for(uint32_t turn = 0; ; turn++, local++)
         {
-            uint32_t w = 0;
-            if(lane == 0) w = work_ring_take(ring, turn, abort_flag, 7);
-            w = __shfl_sync(0xffffffffu, w, 0);
+            const uint32_t w = work.warp_take(turn, lane, abort_flag, 7);
             if(w == kNoWork) break;
             const WorkItem it = decode_work(p, w);
             const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);

@@ -52,7 +52,8 @@ struct WorkSource
     }
 };
 
-// scheduler: item number `item` becomes turn `turn` of every reading role
+// scheduler: item number `item` becomes turn `turn` of every reading role.  The callers below skip the ring altogether
+// when the launch has no counter: every role can then compute its items itself, as a kernel without a ring would.
 __device__ __forceinline__ bool work_ring_publish(WorkRing* ring, uint32_t turn, uint32_t item, volatile int* abort_flag, unsigned int site)
 {
     const uint32_t slot = turn % kWorkRing, parity = (turn / kWorkRing) & 1u;
@@ -86,6 +87,56 @@ __device__ __forceinline__ uint32_t work_ring_take(WorkRing* ring, uint32_t turn
     work_ring_release(ring, turn, item);
     return item;
 }
+
+// What a role of a one-CTA kernel uses: the ring when the launch hands its items out by counter, plain arithmetic on the
+// CTA's fixed share when it does not.
+struct WorkView
+{
+    WorkRing* ring;
+    bool by_counter;
+    uint32_t total;
+
+    __device__ __forceinline__ uint32_t fixed(uint32_t turn) const
+    {
+        const uint32_t w = blockIdx.x + turn * gridDim.x;
+        return w < total ? w : kNoWork;
+    }
+    __device__ __forceinline__ bool publish(uint32_t turn, uint32_t item, volatile int* abort_flag, unsigned int site) const
+    {
+        return by_counter ? work_ring_publish(ring, turn, item, abort_flag, site) : true;
+    }
+    __device__ __forceinline__ uint32_t peek(uint32_t turn, volatile int* abort_flag, unsigned int site) const
+    {
+        return by_counter ? work_ring_peek(ring, turn, abort_flag, site) : fixed(turn);
+    }
+    __device__ __forceinline__ void release(uint32_t turn, uint32_t item) const
+    {
+        if(by_counter) work_ring_release(ring, turn, item);
+    }
+    __device__ __forceinline__ uint32_t take(uint32_t turn, volatile int* abort_flag, unsigned int site) const
+    {
+        return by_counter ? work_ring_take(ring, turn, abort_flag, site) : fixed(turn);
+    }
+    // the same for a whole warp (all lanes call, all lanes get the number): lane 0 asks the ring and hands the answer
+    // round; with fixed shares every lane computes it and nothing is exchanged
+    __device__ __forceinline__ uint32_t warp_peek(uint32_t turn, int lane, volatile int* abort_flag, unsigned int site) const
+    {
+        if(!by_counter) return fixed(turn);
+        uint32_t w = 0;
+        if(lane == 0) w = work_ring_peek(ring, turn, abort_flag, site);
+        return __shfl_sync(0xffffffffu, w, 0);
+    }
+    __device__ __forceinline__ void warp_release(uint32_t turn, uint32_t item, int lane) const
+    {
+        if(by_counter && lane == 0) work_ring_release(ring, turn, item);
+    }
+    __device__ __forceinline__ uint32_t warp_take(uint32_t turn, int lane, volatile int* abort_flag, unsigned int site) const
+    {
+        const uint32_t w = warp_peek(turn, lane, abort_flag, site);
+        warp_release(turn, w, lane);
+        return w;
+    }
+};
 
 }  // namespace tc
 }  // namespace onn

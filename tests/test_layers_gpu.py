@@ -358,6 +358,9 @@ def test_dynamic_work_under_contention(capi):
     two-CTA GEMM whose CTAs own fixed shares waits for the shares of the CTAs that could not start; by counter it loses
     about the held SMs' share.  The margin asked for is far inside what is measured (0.32 ms against 0.21 ms)."""
     import ctypes
+    import os
+    if os.environ.get("ONN_B200_DYNAMIC_WORK") is not None:
+        pytest.skip("the environment pins the mode this test switches")
     L = capi.lib()
     M, N, K = 16384, 4096, 1024
     a, b, c = torch.randn(M, K, device="cuda"), torch.randn(N, K, device="cuda") / 32, torch.empty(M, N, device="cuda")
