@@ -115,7 +115,9 @@ struct onn_trainer
         Index chunk = -1;                                   // micro-batch number it was recorded for (its statistics slot is a captured argument)
         bool failed = false;
     };
-    SegmentedGraph exchange_graph;
+    SegmentedGraph exchange_graph;                          // the micro-batch that hands out the gradient buckets (the last one)
+    SegmentedGraph first_graph;                             // the first micro-batch of a step when it is not also the last: waits for parameter buckets only
+    SegmentedGraph* recording_graph = nullptr;              // where cut_segment puts what it ends
     bool recording = false;                                 // hooks cut segments instead of acting
     Index recorded_bucket = -1;                             // highest parameter bucket a recorded wait covers
 
@@ -131,6 +133,7 @@ struct onn_trainer
     {
         for(MicroGraph& g : micro_graphs) if(g.executable) cudaGraphExecDestroy(g.executable);
         for(cudaGraphExec_t g : exchange_graph.segments) if(g) cudaGraphExecDestroy(g);
+        for(cudaGraphExec_t g : first_graph.segments) if(g) cudaGraphExecDestroy(g);
         for(cudaGraphExec_t g : decode_graphs) if(g) cudaGraphExecDestroy(g);
         for(IdBuffers& b : id_buffers)
         {
@@ -320,7 +323,9 @@ extern "C" int onn_trainer_set_dp(onn_trainer* t, onn_dp_comm* comm, int world)
         t->gather_in_flight = false;
         // the recorded exchange belongs to the old communicator and bucket grid
         for(cudaGraphExec_t g : t->exchange_graph.segments) if(g) cudaGraphExecDestroy(g);
+        for(cudaGraphExec_t g : t->first_graph.segments) if(g) cudaGraphExecDestroy(g);
         t->exchange_graph = onn_trainer::SegmentedGraph();
+        t->first_graph = onn_trainer::SegmentedGraph();
         t->comm = world > 1 ? comm : nullptr;
         t->world = world;
         // NCCL's kernels hold SMs while back-propagation and the next forward pass run: CTAs that start late must not own
@@ -610,7 +615,7 @@ static void perform(onn_trainer* t, const onn_trainer::ExchangeAction& action)
 // Ends the segment being captured, remembers the action that follows it, and starts the next one.
 static void cut_segment(onn_trainer* t, int kind, Index argument)
 {
-    onn_trainer::SegmentedGraph& graph = t->exchange_graph;
+    onn_trainer::SegmentedGraph& graph = *t->recording_graph;
     cudaGraph_t captured = nullptr;
     if(cudaStreamEndCapture(t->stream, &captured) != cudaSuccess || !captured) throw std::runtime_error("segment capture failed");
     cudaGraphExec_t executable = nullptr;
@@ -623,11 +628,12 @@ static void cut_segment(onn_trainer* t, int kind, Index argument)
         throw std::runtime_error("segment capture failed");
 }
 
-// Replays (recording it first if need be) the micro-batch that hands its gradient buckets to the reduce-scatter.
-// Returns false if it cannot be done this way; the caller then runs the micro-batch eagerly.
-static bool replay_exchange_micro_batch(onn_trainer* t, const BatchCuda& source, Index chunk)
+// Replays (recording it first if need be) a micro-batch in whose middle the host has to act: the one that hands its
+// gradient buckets to the reduce-scatter (hands_out), and the first one of a step, whose forward pass waits for the
+// parameter gathers of the step before.  Returns false if it cannot be done this way; the caller then runs the
+// micro-batch another way.
+static bool replay_segmented_micro_batch(onn_trainer* t, onn_trainer::SegmentedGraph& graph, const BatchCuda& source, Index chunk, bool hands_out)
 {
-    onn_trainer::SegmentedGraph& graph = t->exchange_graph;
     if(graph.failed || (graph.chunk >= 0 && graph.chunk != chunk)) return false;
     const Index S_dec = t->decoder_sequence_length, S_in = t->input_sequence_length;
     if(t->micro_decoder.size() == 0)
@@ -658,6 +664,7 @@ static bool replay_exchange_micro_batch(onn_trainer* t, const BatchCuda& source,
         if(ok)
         {
             t->recording = true;
+            t->recording_graph = &graph;
             t->recorded_bucket = -1;
             try
             {
@@ -666,11 +673,14 @@ static bool replay_exchange_micro_batch(onn_trainer* t, const BatchCuda& source,
                 t->network->forward_propagate(micro.get_inputs_device(), *t->forward, true);
                 t->network->before_layer_hook = nullptr;
                 cut_segment(t, 1, 0);
-                t->pending_bucket = (t->shard_total - 1) / t->shard_bucket;
-                t->loss->gradient_ready_hook = gradient_ready;
-                t->loss->gradient_ready_context = t;
+                if(hands_out)
+                {
+                    t->pending_bucket = (t->shard_total - 1) / t->shard_bucket;
+                    t->loss->gradient_ready_hook = gradient_ready;
+                    t->loss->gradient_ready_context = t;
+                }
                 t->loss->back_propagate(micro, *t->forward, *t->back, chunk > 0);
-                gradient_ready(t, -1);
+                if(hands_out) gradient_ready(t, -1);
                 t->loss->gradient_ready_hook = nullptr;
                 cut_segment(t, -1, 0);
             }
@@ -794,14 +804,22 @@ static void run_step_body(onn_trainer* t, const float* decoder_ids, const float*
         const bool hands_out_gradients = t->comm && last;     // bucketed all-reduces are issued from inside back-propagation
         if(t->graphs_enabled && t->eager_steps > 0 && !hands_out_gradients)
         {
-            // a replayed micro-batch cannot wait layer by layer: everything it reads must be there before it starts
+            // the first micro-batch after a sharded update: cut where its forward pass meets a parameter bucket the
+            // gathers may still be bringing, so that they run under it
+            if(chunk == 0 && t->comm && t->sharded_update && t->shard_total > 0 && !t->trace_phases &&
+               replay_segmented_micro_batch(t, t->first_graph, micro, chunk, false))
+            {
+                count_pending = false;
+                continue;
+            }
+            // a micro-batch replayed as one graph cannot wait layer by layer: everything it reads must be there before it starts
             await_parameters(t);
             await_count();
             if(replay_micro_batch(t, micro, chunk)) continue;
         }
 
         if(hands_out_gradients && t->sharded_step && t->graphs_enabled && t->eager_steps > 0 && !t->trace_phases && t->carve_sms == 0 &&
-           replay_exchange_micro_batch(t, micro, chunk))
+           replay_segmented_micro_batch(t, t->exchange_graph, micro, chunk, true))
         {
             count_pending = false;                               // waited for between the segments
             continue;
