@@ -280,10 +280,13 @@ extern "C" int onn_mha_fwd(const float* Xq, const float* Xs, const onn_mha_param
     const bool aligned = host_aligned16(q) && host_aligned16(k) && host_aligned16(v) && host_aligned16(p) && host_aligned16(ctx);
     if(fused_enabled && gemm_mode() != 1 && attention_fwd_fused_supported(q, k, v, p, ctx, B, Sq, Sk, E, H))
     {
-        // back-propagation forms the weights again from Q, K and these per-row statistics, and needs the key flags for it
-        if(pad_flags != reinterpret_cast<const uint8_t*>(ws + L.pad) &&
+        // when back-propagation is to form the weights again from Q, K (onn_mha_set_kv_grad_by_recomputation) it needs
+        // these per-row statistics and the key flags; otherwise nothing extra is written or copied
+        const bool keep_for_recomputation = g_kv_grad_by_recomputation.load(std::memory_order_relaxed) != 0;
+        if(keep_for_recomputation && pad_flags != reinterpret_cast<const uint8_t*>(ws + L.pad) &&
            cudaMemcpyAsync(ws + L.pad, pad_flags, (size_t)(B * Sk), cudaMemcpyDeviceToDevice, s) != cudaSuccess) return ONN_ERR_CUDA;
-        ONN_TRY(attention_fwd_fused_launch(q, k, v, pad_flags, p, ctx, ws + L.row_max, ws + L.row_inv, B, Sq, Sk, E, H, causal, scale, s));
+        ONN_TRY(attention_fwd_fused_launch(q, k, v, pad_flags, p, ctx, keep_for_recomputation ? ws + L.row_max : nullptr,
+                                           keep_for_recomputation ? ws + L.row_inv : nullptr, B, Sq, Sk, E, H, causal, scale, s));
     }
     else if(fused_enabled && gemm_mode() != 1 && aligned && attention_long_supported(B, Sq, Sk, E, H))
     {
