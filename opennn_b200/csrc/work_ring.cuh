@@ -2,7 +2,7 @@
 //
 // The kernels built on tcgen05.cuh split a CTA into roles (copy producer, MMA issuer, arithmetic warps) that all walk the
 // same sequence of work items.  With a fixed share per CTA (item = blockIdx.x + turn * gridDim.x) every role can compute
-// the sequence itself; when the items come from a global counter (common.cuh: next_work_counters) one thread asks the
+// the sequence itself; when the items come from a global counter (common.cuh: next_work_counter) one thread asks the
 // counter and the others must be told.  The ring below does that: kWorkRing slots in shared memory, a "full" barrier per
 // slot that the scheduler completes after writing the item number, an "empty" barrier that every reading role arrives on
 // once it has the number in a register.  Item kNoWork ends the sequence.  All waits are bounded like every other wait of
