@@ -439,10 +439,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t stage = 0, phase = 0;
             long long local = 0;
             bool ok = true;
-            // the next item is looked up before the last k-block of this one, while MMAs are queued
-            uint32_t w = work.take(0, abort_flag, 6), w_next = kNoWork;
-            for(uint32_t turn = 0; ok && w != kNoWork; turn++, local++, w = w_next)
+            for(uint32_t turn = 0; ok; turn++, local++)
             {
+                const uint32_t w = work.take(turn, abort_flag, 6);
+                if(w == kNoWork) break;
                 const WorkItem it = decode_work(p, w);
                 const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
                 if(!mbar_wait(smem_u32(acc_empty_bar + acc), acc_phase ^ 1, abort_flag, 2)) break;
@@ -450,7 +450,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for(int kb = 0; kb < it.k_blocks; kb++)
                 {
-                    if(kb == it.k_blocks - 1) w_next = work.take(turn + 1, abort_flag, 6);
                     if(!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, 3)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
@@ -824,12 +823,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t stage = 0, phase = 0;
             long long local = 0;
             bool ok = true;
-            // The next item is looked up before the last k-block of this one, while MMAs are queued: at the top of the
-            // loop the look-up would sit between two tiles' MMAs.  (The scheduler publishes item t + 1 once the copies of
-            // item t are on their way, which needs no more stages than the MMAs before the last k-block have freed.)
-            uint32_t w = take_item(0, 18), w_next = kNoWork;
-            for(uint32_t turn = 0; ok && w != kNoWork; turn++, local++, w = w_next)
+            // (Looking the next item up inside the k-block loop, while MMAs are queued, was tried: the extra branch in that
+            // loop cost 4-6 % of the kernel, far more than the look-up at the top costs between two tiles.)
+            for(uint32_t turn = 0; ok; turn++, local++)
             {
+                const uint32_t w = take_item(turn, 18);
+                if(w == kNoWork) break;
                 const WorkItem it = decode_work(p, w);
                 const uint32_t acc = (uint32_t)(local & 1), acc_phase = (uint32_t)((local >> 1) & 1);
                 if(!mbar_wait(smem_u32(acc_empty_bar + acc), acc_phase ^ 1, abort_flag, 12)) break;
@@ -837,7 +836,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for(int kb = 0; kb < it.k_blocks; kb++)
                 {
-                    if(kb == it.k_blocks - 1) w_next = take_item(turn + 1, 18);
                     if(!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, 13)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE2_BYTES);
