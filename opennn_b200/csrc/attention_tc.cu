@@ -221,15 +221,12 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             __syncwarp();
         }
         uint32_t ph = 0;
-        // Backward: the item of a turn is looked up in the middle of the turn before (the warp asks for that item's
-        // attention weights there) and only handed back at the top of its own turn.  Forward: looked up at the top; the
-        // kernel has no register to spare for carrying it.
-        [[maybe_unused]] uint32_t w_next = BACKWARD ? work.warp_peek(0, lane, abort_flag, 32) : kNoWork;
+        // The item of a turn is taken at the top of the turn.  The backward kernel also looks at the NEXT turn's item in
+        // the middle of this one (it asks for that item's attention weights there) without taking it; nothing is
+        // carried round the loop: the forward kernel in particular has no register to spare.
         for(uint32_t turn = 0; ; turn++, ph ^= 1)
         {
-            uint32_t w;
-            if constexpr(BACKWARD) { w = w_next; work.warp_release(turn, w, lane); }
-            else w = work.warp_take(turn, lane, abort_flag, 32);
+            const uint32_t w = work.warp_take(turn, lane, abort_flag, 32);
             if(w == kNoWork) break;
             const AttnItem it = decode_item(p, w);
             const int row0 = it.q_tile * kQRows + quadrant * 32;      // first query row of this warp
@@ -331,7 +328,7 @@ attention_core_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if(lane == 0) mbar_arrive(smem_u32(p_ready));    // the dQ MMAs may start
 
                 // the next item's weights take ring blocks 0..2 as soon as this item's copies have left them (block 3 stages dQ first)
-                w_next = work.warp_peek(turn + 1, lane, abort_flag, 33);
+                const uint32_t w_next = work.warp_peek(turn + 1, lane, abort_flag, 33);
                 AttnItem next = it;
                 int next_row0 = 0;
                 bool next_live = false;
