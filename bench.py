@@ -711,6 +711,26 @@ def run_ours(args):
     # through the library's communicator, as bus bandwidth 2(n-1)/n * bytes / time; (b) the same local batches stepped
     # without any exchange: the difference to the data-parallel step is the time the exchange is NOT hidden behind
     # back-propagation (replicas diverge from here on, which no longer matters: nothing is measured after it).
+    # --trace-phases: where a step's time goes on each rank (events on the trainer's stream at the start of a step, after
+    # the last micro-batch's forward pass, after its back-propagation, after the update), on untimed steps after the
+    # timed ones; with it on the exchanging micro-batch runs kernel by kernel (a segment replay has no such events)
+    phases = None
+    if args.trace_phases:
+        t.trace_phases(True)
+        rows = []
+        for i in range(6):
+            device_step(i)
+            rows.append(t.last_step_phases())
+        t.trace_phases(False)
+        mine = torch.tensor([statistics.median(r[k] for r in rows[1:]) for k in range(3)], device="cuda")
+        if world > 1:
+            gathered = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(gathered, mine)
+        else:
+            gathered = [mine]
+        phases = {"unit": "ms, median of 5 steps, per rank", "forward_incl_earlier_micro_batches": [round(float(g[0]), 2) for g in gathered],
+                  "back_propagation_last_micro_batch": [round(float(g[1]), 2) for g in gathered], "update": [round(float(g[2]), 2) for g in gathered]}
+
     allreduce = None
     if world > 1:
         import ctypes
@@ -783,6 +803,8 @@ def run_ours(args):
         }
         if allreduce:
             line["allreduce"] = allreduce
+        if phases:
+            line["phases"] = phases
         emit(line)
 
     t.close()
@@ -797,6 +819,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--trace-phases", action="store_true",
+                        help="add per-rank forward / back-propagation / update times of a step (untimed extra steps) to the line")
     parser.add_argument("--profile-batch", type=int, default=0,
                         help="profiling aid: run the device-resident loop only, on a global batch of this many samples "
                              "(the line it prints is not a benchmark result)")
